@@ -1,0 +1,376 @@
+// relu / add / mul / where / strided copy: HBM-bound streaming kernels.
+//
+// Fast path: every operand contiguous (or a single broadcast scalar), same dtype,
+// 16-byte aligned -> each thread moves kUnroll independent 16-byte vectors per operand
+// so ~128 KB per SM is in flight, accesses are fully coalesced and marked streaming.
+// Slow path: TensorIterator-style strided indexing with runtime dtypes (broadcasts,
+// transposes, mixed-precision promotion); correctness first, one element per thread.
+#include "b200_common.cuh"
+
+namespace b200 {
+
+constexpr int kEwThreads = 256;
+constexpr int kUnroll = 4;
+
+struct ReluOp { __device__ __forceinline__ float operator()(float x) const { return x <= 0.f ? 0.f : x; } };
+struct AddOp {
+  float alpha;
+  __device__ __forceinline__ float operator()(float a, float b) const { return fmaf(alpha, b, a); }
+};
+struct AddConstOp { float c; __device__ __forceinline__ float operator()(float x) const { return x + c; } };
+struct MulConstOp { float c; __device__ __forceinline__ float operator()(float x) const { return x * c; } };
+struct MulOp { __device__ __forceinline__ float operator()(float a, float b) const { return a * b; } };
+
+template <typename T, typename Op>
+__global__ void __launch_bounds__(kEwThreads) ew_unary_vec(const T* __restrict__ x, T* __restrict__ out, int64_t n, Op op) {
+  constexpr int VE = Vec<T>::N;
+  const int64_t nvec = n / VE;
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * (kEwThreads * kUnroll) + threadIdx.x;
+  Vec<T> v[kUnroll];
+#pragma unroll
+  for (int u = 0; u < kUnroll; ++u) {
+    const int64_t i = base + u * kEwThreads;
+    if (i < nvec) v[u].raw = ld_stream(x + i * VE);
+  }
+#pragma unroll
+  for (int u = 0; u < kUnroll; ++u) {
+    const int64_t i = base + u * kEwThreads;
+    if (i < nvec) {
+#pragma unroll
+      for (int e = 0; e < VE; ++e) v[u].set(e, from_f32<T>(op(to_f32(v[u].get(e)))));
+      st_stream(out + i * VE, v[u].raw);
+    }
+  }
+  // ragged tail (< VE elements): the last block's first threads
+  if (blockIdx.x == gridDim.x - 1) {
+    const int64_t i = nvec * VE + threadIdx.x;
+    if (i < n) out[i] = from_f32<T>(op(to_f32(x[i])));
+  }
+}
+
+// MODE 0: a[i] op b[i]; MODE 1: a[i] op b[0]; MODE 2: a[0] op b[i]
+template <typename T, typename Op, int MODE>
+__global__ void __launch_bounds__(kEwThreads) ew_binary_vec(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out, int64_t n, Op op) {
+  constexpr int VE = Vec<T>::N;
+  const int64_t nvec = n / VE;
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * (kEwThreads * kUnroll) + threadIdx.x;
+  Vec<T> va[kUnroll], vb[kUnroll];
+  float sa = 0.f, sb = 0.f;
+  if (MODE == 1) sb = to_f32(b[0]);
+  if (MODE == 2) sa = to_f32(a[0]);
+#pragma unroll
+  for (int u = 0; u < kUnroll; ++u) {
+    const int64_t i = base + u * kEwThreads;
+    if (i < nvec) {
+      if (MODE != 2) va[u].raw = ld_stream(a + i * VE);
+      if (MODE != 1) vb[u].raw = ld_stream(b + i * VE);
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < kUnroll; ++u) {
+    const int64_t i = base + u * kEwThreads;
+    if (i < nvec) {
+      Vec<T> r;
+#pragma unroll
+      for (int e = 0; e < VE; ++e) {
+        const float fa = MODE == 2 ? sa : to_f32(va[u].get(e));
+        const float fb = MODE == 1 ? sb : to_f32(vb[u].get(e));
+        r.set(e, from_f32<T>(op(fa, fb)));
+      }
+      st_stream(out + i * VE, r.raw);
+    }
+  }
+  if (blockIdx.x == gridDim.x - 1) {
+    const int64_t i = nvec * VE + threadIdx.x;
+    if (i < n) {
+      const float fa = MODE == 2 ? sa : to_f32(a[i]);
+      const float fb = MODE == 1 ? sb : to_f32(b[i]);
+      out[i] = from_f32<T>(op(fa, fb));
+    }
+  }
+}
+
+// where on contiguous same-size operands: U is an unsigned type of the element size
+// (pure bit select, so NaN payloads and -0 survive untouched).
+template <typename U>
+__global__ void __launch_bounds__(kEwThreads) ew_where_vec(const uint8_t* __restrict__ c, const U* __restrict__ x, const U* __restrict__ y, U* __restrict__ out, int64_t n) {
+  constexpr int VE = 16 / sizeof(U);
+  const int64_t nvec = n / VE;
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * (kEwThreads * kUnroll) + threadIdx.x;
+  Vec<U> vx[kUnroll], vy[kUnroll];
+  uint8_t cc[kUnroll][VE];
+#pragma unroll
+  for (int u = 0; u < kUnroll; ++u) {
+    const int64_t i = base + u * kEwThreads;
+    if (i < nvec) {
+      vx[u].raw = ld_stream(x + i * VE);
+      vy[u].raw = ld_stream(y + i * VE);
+      if (VE == 4) {
+        *reinterpret_cast<uint32_t*>(cc[u]) = __ldcs(reinterpret_cast<const uint32_t*>(c + i * VE));
+      } else if (VE == 8) {
+        *reinterpret_cast<uint2*>(cc[u]) = __ldcs(reinterpret_cast<const uint2*>(c + i * VE));
+      } else {
+#pragma unroll
+        for (int e = 0; e < VE; ++e) cc[u][e] = c[i * VE + e];
+      }
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < kUnroll; ++u) {
+    const int64_t i = base + u * kEwThreads;
+    if (i < nvec) {
+      Vec<U> r;
+#pragma unroll
+      for (int e = 0; e < VE; ++e) r.set(e, cc[u][e] ? vx[u].get(e) : vy[u].get(e));
+      st_stream(out + i * VE, r.raw);
+    }
+  }
+  if (blockIdx.x == gridDim.x - 1) {
+    const int64_t i = nvec * VE + threadIdx.x;
+    if (i < n) out[i] = c[i] ? x[i] : y[i];
+  }
+}
+
+// ------------------------------------------------------------------ strided slow path
+struct StridedArgs {
+  int ndim;
+  int64_t n;
+  int64_t shape[B200_MAX_DIMS];
+  int64_t s0[B200_MAX_DIMS], s1[B200_MAX_DIMS], s2[B200_MAX_DIMS];
+};
+
+__device__ __forceinline__ void unravel3(const StridedArgs& A, int64_t lin, int64_t& o0, int64_t& o1, int64_t& o2) {
+  o0 = o1 = o2 = 0;
+  for (int d = A.ndim - 1; d >= 0; --d) {
+    const int64_t q = lin / A.shape[d];
+    const int64_t r = lin - q * A.shape[d];
+    o0 += r * A.s0[d];
+    o1 += r * A.s1[d];
+    o2 += r * A.s2[d];
+    lin = q;
+  }
+}
+
+enum { OP_RELU = 0, OP_ADD = 1, OP_MUL = 2, OP_COPY = 3, OP_ADDC = 4, OP_MULC = 5 };
+
+template <int OP>
+__global__ void __launch_bounds__(kEwThreads) ew_strided(const void* a, const void* b, void* out, StridedArgs A, int dta, int dtb, int dto, float alpha) {
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * kEwThreads + threadIdx.x; i < A.n; i += static_cast<int64_t>(gridDim.x) * kEwThreads) {
+    int64_t oa, ob, oc;
+    unravel3(A, i, oa, ob, oc);
+    float r;
+    if (OP == OP_RELU) {
+      const float x = load_as_f32(a, oa, dta);
+      r = x <= 0.f ? 0.f : x;
+    } else if (OP == OP_COPY) {
+      r = load_as_f32(a, oa, dta);
+    } else if (OP == OP_ADDC) {
+      r = load_as_f32(a, oa, dta) + alpha;
+    } else if (OP == OP_MULC) {
+      r = load_as_f32(a, oa, dta) * alpha;
+    } else {
+      const float x = load_as_f32(a, oa, dta), y = load_as_f32(b, ob, dtb);
+      r = OP == OP_ADD ? fmaf(alpha, y, x) : x * y;
+    }
+    store_from_f32(out, i, dto, r);
+  }
+}
+
+// Bit-exact strided copy for any element size (same dtype in and out).
+template <typename U>
+__global__ void __launch_bounds__(kEwThreads) copy_strided_bits(const U* x, U* out, StridedArgs A) {
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * kEwThreads + threadIdx.x; i < A.n; i += static_cast<int64_t>(gridDim.x) * kEwThreads) {
+    int64_t oa, ob, oc;
+    unravel3(A, i, oa, ob, oc);
+    out[i] = x[oa];
+  }
+}
+
+// where, strided: cond/x/y offsets in s0/s1/s2. Same-dtype operands are bit-selected;
+// mixed float dtypes go through fp32 (exact: every bf16/f16 value is an fp32 value).
+template <typename U, bool BITS>
+__global__ void __launch_bounds__(kEwThreads) where_strided(const uint8_t* c, const void* x, const void* y, void* out, StridedArgs A, int dtx, int dty, int dto) {
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * kEwThreads + threadIdx.x; i < A.n; i += static_cast<int64_t>(gridDim.x) * kEwThreads) {
+    int64_t oc, ox, oy;
+    unravel3(A, i, oc, ox, oy);
+    const bool take = c[oc] != 0;
+    if (BITS) {
+      static_cast<U*>(out)[i] = take ? static_cast<const U*>(x)[ox] : static_cast<const U*>(y)[oy];
+    } else {
+      store_from_f32(out, i, dto, take ? load_as_f32(x, ox, dtx) : load_as_f32(y, oy, dty));
+    }
+  }
+}
+
+static int fill_args(StridedArgs& A, int ndim, const int64_t* shape, const int64_t* s0, const int64_t* s1, const int64_t* s2) {
+  if (ndim < 0 || ndim > B200_MAX_DIMS || (ndim > 0 && !shape)) return B200_EINVAL;
+  A.ndim = ndim;
+  A.n = 1;
+  for (int d = 0; d < ndim; ++d) {
+    if (shape[d] < 0) return B200_EINVAL;
+    A.shape[d] = shape[d];
+    A.n *= shape[d];
+    A.s0[d] = s0 ? s0[d] : 0;
+    A.s1[d] = s1 ? s1[d] : 0;
+    A.s2[d] = s2 ? s2[d] : 0;
+  }
+  return B200_OK;
+}
+
+static int strided_grid(int64_t n) {
+  int64_t g = (n + kEwThreads - 1) / kEwThreads;
+  const int64_t cap = static_cast<int64_t>(kNumSMs) * 32;
+  return static_cast<int>(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+template <typename Op>
+static int launch_unary_fast(const void* x, void* out, int64_t n, int dtype, Op op, cudaStream_t st) {
+  const int per_block = kEwThreads * kUnroll;
+  switch (dtype) {
+    case B200_F32: ew_unary_vec<float, Op><<<grid_for(n / 4 + 1, per_block), kEwThreads, 0, st>>>(static_cast<const float*>(x), static_cast<float*>(out), n, op); break;
+    case B200_BF16: ew_unary_vec<__nv_bfloat16, Op><<<grid_for(n / 8 + 1, per_block), kEwThreads, 0, st>>>(static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(out), n, op); break;
+    case B200_F16: ew_unary_vec<__half, Op><<<grid_for(n / 8 + 1, per_block), kEwThreads, 0, st>>>(static_cast<const __half*>(x), static_cast<__half*>(out), n, op); break;
+    default: return B200_EDTYPE;
+  }
+  return check_launch();
+}
+
+template <typename T, typename Op>
+static void launch_binary_T(const void* a, const void* b, void* out, int64_t n, int mode, Op op, cudaStream_t st) {
+  const int g = grid_for(n / Vec<T>::N + 1, kEwThreads * kUnroll);
+  const T* pa = static_cast<const T*>(a);
+  const T* pb = static_cast<const T*>(b);
+  T* po = static_cast<T*>(out);
+  if (mode == 0) ew_binary_vec<T, Op, 0><<<g, kEwThreads, 0, st>>>(pa, pb, po, n, op);
+  else if (mode == 1) ew_binary_vec<T, Op, 1><<<g, kEwThreads, 0, st>>>(pa, pb, po, n, op);
+  else ew_binary_vec<T, Op, 2><<<g, kEwThreads, 0, st>>>(pa, pb, po, n, op);
+}
+
+template <typename Op, int OPCODE>
+static int binary_entry(const void* a, const void* b, void* out, int ndim, const int64_t* shape, const int64_t* sa, const int64_t* sb, int dta, int dtb, int dto, Op op, float alpha, cudaStream_t st) {
+  StridedArgs A;
+  if (int rc = fill_args(A, ndim, shape, sa, sb, nullptr)) return rc;
+  if (!is_float_dtype(dta) || !is_float_dtype(dtb) || !is_float_dtype(dto)) return B200_EDTYPE;
+  if (A.n == 0) return B200_OK;
+  if (!a || !b || !out) return B200_EINVAL;
+  const bool same = dta == dtb && dtb == dto;
+  const bool a_full = is_contiguous(ndim, shape, sa), b_full = is_contiguous(ndim, shape, sb);
+  const bool a_scalar = all_zero_strides(ndim, shape, sa), b_scalar = all_zero_strides(ndim, shape, sb);
+  int mode = -1;
+  if (same && aligned16(out)) {
+    if (a_full && b_full && aligned16(a) && aligned16(b)) mode = 0;
+    else if (a_full && b_scalar && aligned16(a) && A.n > 1) mode = 1;
+    else if (a_scalar && b_full && aligned16(b) && A.n > 1) mode = 2;
+  }
+  if (mode >= 0) {
+    switch (dto) {
+      case B200_F32: launch_binary_T<float, Op>(a, b, out, A.n, mode, op, st); break;
+      case B200_BF16: launch_binary_T<__nv_bfloat16, Op>(a, b, out, A.n, mode, op, st); break;
+      default: launch_binary_T<__half, Op>(a, b, out, A.n, mode, op, st); break;
+    }
+  } else {
+    ew_strided<OPCODE><<<strided_grid(A.n), kEwThreads, 0, st>>>(a, b, out, A, dta, dtb, dto, alpha);
+  }
+  return check_launch();
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_relu(const void* x, void* out, int ndim, const int64_t* shape, const int64_t* sx, int dtype, void* stream) {
+  StridedArgs A;
+  if (int rc = fill_args(A, ndim, shape, sx, nullptr, nullptr)) return rc;
+  if (!is_float_dtype(dtype)) return B200_EDTYPE;
+  if (A.n == 0) return B200_OK;
+  if (!x || !out) return B200_EINVAL;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (is_contiguous(ndim, shape, sx) && aligned16(x) && aligned16(out)) return launch_unary_fast(x, out, A.n, dtype, ReluOp{}, st);
+  ew_strided<OP_RELU><<<strided_grid(A.n), kEwThreads, 0, st>>>(x, nullptr, out, A, dtype, dtype, dtype, 0.f);
+  return check_launch();
+}
+
+template <typename Op, int OPCODE>
+static int scalar_entry(const void* x, void* out, int ndim, const int64_t* shape, const int64_t* sx, int dtx, int dto, Op op, float c, cudaStream_t st) {
+  StridedArgs A;
+  if (int rc = fill_args(A, ndim, shape, sx, nullptr, nullptr)) return rc;
+  if (!is_float_dtype(dtx) || !is_float_dtype(dto)) return B200_EDTYPE;
+  if (A.n == 0) return B200_OK;
+  if (!x || !out) return B200_EINVAL;
+  if (dtx == dto && is_contiguous(ndim, shape, sx) && aligned16(x) && aligned16(out)) return launch_unary_fast(x, out, A.n, dtx, op, st);
+  ew_strided<OPCODE><<<strided_grid(A.n), kEwThreads, 0, st>>>(x, nullptr, out, A, dtx, dtx, dto, c);
+  return check_launch();
+}
+
+extern "C" int b200_add_scalar(const void* x, void* out, int ndim, const int64_t* shape, const int64_t* sx, int dtx, int dto, double value, void* stream) {
+  const float c = static_cast<float>(value);
+  return scalar_entry<AddConstOp, OP_ADDC>(x, out, ndim, shape, sx, dtx, dto, AddConstOp{c}, c, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int b200_mul_scalar(const void* x, void* out, int ndim, const int64_t* shape, const int64_t* sx, int dtx, int dto, double value, void* stream) {
+  const float c = static_cast<float>(value);
+  return scalar_entry<MulConstOp, OP_MULC>(x, out, ndim, shape, sx, dtx, dto, MulConstOp{c}, c, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int b200_add(const void* a, const void* b, void* out, int ndim, const int64_t* shape, const int64_t* sa, const int64_t* sb, int dta, int dtb, int dto, double alpha, void* stream) {
+  const float al = static_cast<float>(alpha);
+  return binary_entry<AddOp, OP_ADD>(a, b, out, ndim, shape, sa, sb, dta, dtb, dto, AddOp{al}, al, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int b200_mul(const void* a, const void* b, void* out, int ndim, const int64_t* shape, const int64_t* sa, const int64_t* sb, int dta, int dtb, int dto, void* stream) {
+  return binary_entry<MulOp, OP_MUL>(a, b, out, ndim, shape, sa, sb, dta, dtb, dto, MulOp{}, 1.f, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int b200_where(const void* cond, const void* x, const void* y, void* out, int ndim, const int64_t* shape, const int64_t* sc, const int64_t* sx, const int64_t* sy, int dtx, int dty, int dto, void* stream) {
+  StridedArgs A;
+  if (int rc = fill_args(A, ndim, shape, sc, sx, sy)) return rc;
+  const int es = dtype_size(dto);
+  if (es == 0 || dtype_size(dtx) == 0 || dtype_size(dty) == 0) return B200_EDTYPE;
+  if (A.n == 0) return B200_OK;
+  if (!cond || !x || !y || !out) return B200_EINVAL;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const uint8_t* c = static_cast<const uint8_t*>(cond);
+  const bool same = dtx == dty && dty == dto;
+  if (!same && !(is_float_dtype(dtx) && is_float_dtype(dty) && is_float_dtype(dto))) return B200_EDTYPE;
+  const bool contig = is_contiguous(ndim, shape, sc) && is_contiguous(ndim, shape, sx) && is_contiguous(ndim, shape, sy);
+  if (same && contig && (es == 2 || es == 4) && aligned16(x) && aligned16(y) && aligned16(out) && (reinterpret_cast<uintptr_t>(cond) & 7u) == 0) {
+    if (es == 4) ew_where_vec<uint32_t><<<grid_for(A.n / 4 + 1, kEwThreads * kUnroll), kEwThreads, 0, st>>>(c, static_cast<const uint32_t*>(x), static_cast<const uint32_t*>(y), static_cast<uint32_t*>(out), A.n);
+    else ew_where_vec<uint16_t><<<grid_for(A.n / 8 + 1, kEwThreads * kUnroll), kEwThreads, 0, st>>>(c, static_cast<const uint16_t*>(x), static_cast<const uint16_t*>(y), static_cast<uint16_t*>(out), A.n);
+    return check_launch();
+  }
+  const int g = strided_grid(A.n);
+  if (same) {
+    switch (es) {
+      case 1: where_strided<uint8_t, true><<<g, kEwThreads, 0, st>>>(c, x, y, out, A, dtx, dty, dto); break;
+      case 2: where_strided<uint16_t, true><<<g, kEwThreads, 0, st>>>(c, x, y, out, A, dtx, dty, dto); break;
+      case 4: where_strided<uint32_t, true><<<g, kEwThreads, 0, st>>>(c, x, y, out, A, dtx, dty, dto); break;
+      default: where_strided<uint64_t, true><<<g, kEwThreads, 0, st>>>(c, x, y, out, A, dtx, dty, dto); break;
+    }
+  } else {
+    where_strided<uint32_t, false><<<g, kEwThreads, 0, st>>>(c, x, y, out, A, dtx, dty, dto);
+  }
+  return check_launch();
+}
+
+extern "C" int b200_copy_strided(const void* x, void* out, int ndim, const int64_t* shape, const int64_t* sx, int dti, int dto, void* stream) {
+  StridedArgs A;
+  if (int rc = fill_args(A, ndim, shape, sx, nullptr, nullptr)) return rc;
+  const int es = dtype_size(dti);
+  if (es == 0 || dtype_size(dto) == 0) return B200_EDTYPE;
+  if (A.n == 0) return B200_OK;
+  if (!x || !out) return B200_EINVAL;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int g = strided_grid(A.n);
+  if (dti == dto) {
+    switch (es) {
+      case 1: copy_strided_bits<uint8_t><<<g, kEwThreads, 0, st>>>(static_cast<const uint8_t*>(x), static_cast<uint8_t*>(out), A); break;
+      case 2: copy_strided_bits<uint16_t><<<g, kEwThreads, 0, st>>>(static_cast<const uint16_t*>(x), static_cast<uint16_t*>(out), A); break;
+      case 4: copy_strided_bits<uint32_t><<<g, kEwThreads, 0, st>>>(static_cast<const uint32_t*>(x), static_cast<uint32_t*>(out), A); break;
+      default: copy_strided_bits<uint64_t><<<g, kEwThreads, 0, st>>>(static_cast<const uint64_t*>(x), static_cast<uint64_t*>(out), A); break;
+    }
+  } else {
+    if (!is_float_dtype(dto)) return B200_EDTYPE;
+    ew_strided<OP_COPY><<<g, kEwThreads, 0, st>>>(x, nullptr, out, A, dti, dti, dto, 0.f);
+  }
+  return check_launch();
+}

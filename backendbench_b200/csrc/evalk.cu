@@ -1,0 +1,134 @@
+// Device side of the evaluation path: one fused pass that answers both questions the
+// harness asks about a (reference, result) pair -- "are they close?" (assert_close with
+// equal_nan) and "how far apart?" (max abs / max rel error) -- plus the L2 flush used
+// between timed repetitions. One read of each tensor, one 32-byte record back.
+#include "b200_common.cuh"
+
+namespace b200 {
+
+struct CloseAcc {
+  unsigned long long bad;
+  float max_abs, max_rel;
+  unsigned nan_seen;
+};
+
+__device__ __forceinline__ void close_step(CloseAcc& a, float r, float s, float rtol, float atol) {
+  const bool rn = r != r, sn = s != s;
+  const float diff = fabsf(r - s);
+  // closeness: equal (covers equal infinities), both NaN, or inside the tolerance band
+  // around the second operand, as torch.isclose(actual, expected) does with
+  // actual = reference output and expected = backend output.
+  const bool close = (r == s) || (rn && sn) || (!rn && !sn && isfinite(diff) && diff <= atol + rtol * fabsf(s));
+  if (!close) ++a.bad;
+  // error magnitudes follow `(ref - res).abs().max()`: any NaN difference makes the max NaN
+  if (diff != diff) a.nan_seen = 1;
+  else {
+    a.max_abs = fmaxf(a.max_abs, diff);
+    a.max_rel = fmaxf(a.max_rel, diff / (fabsf(r) + 1e-10f));
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) allclose_kernel(const T* __restrict__ ref, const T* __restrict__ res, int64_t n, float rtol, float atol, b200_close_record* rec, int vec_ok) {
+  constexpr int VE = Vec<T>::N;
+  CloseAcc a{0ull, 0.f, 0.f, 0u};
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int64_t t0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  int64_t done = 0;
+  if (vec_ok) {
+    const int64_t nvec = n / VE;
+    for (int64_t j = t0; j < nvec; j += stride) {
+      Vec<T> vr, vs;
+      vr.raw = ld_stream(ref + j * VE);
+      vs.raw = ld_stream(res + j * VE);
+#pragma unroll
+      for (int e = 0; e < VE; ++e) close_step(a, to_f32(vr.get(e)), to_f32(vs.get(e)), rtol, atol);
+    }
+    done = nvec * VE;
+  }
+  for (int64_t i = done + t0; i < n; i += stride) close_step(a, to_f32(ref[i]), to_f32(res[i]), rtol, atol);
+  // warp, then one set of atomics per warp (non-negative floats order like their bit patterns)
+  for (int o = 16; o > 0; o >>= 1) {
+    a.bad += __shfl_xor_sync(0xffffffffu, a.bad, o);
+    a.max_abs = fmaxf(a.max_abs, __shfl_xor_sync(0xffffffffu, a.max_abs, o));
+    a.max_rel = fmaxf(a.max_rel, __shfl_xor_sync(0xffffffffu, a.max_rel, o));
+    a.nan_seen |= __shfl_xor_sync(0xffffffffu, a.nan_seen, o);
+  }
+  if ((threadIdx.x & 31) == 0) {
+    if (a.bad) atomicAdd(reinterpret_cast<unsigned long long*>(&rec->mismatches), a.bad);
+    if (a.max_abs > 0.f) atomicMax(reinterpret_cast<unsigned*>(&rec->max_abs), __float_as_uint(a.max_abs));
+    if (a.max_rel > 0.f) atomicMax(reinterpret_cast<unsigned*>(&rec->max_rel), __float_as_uint(a.max_rel));
+    if (a.nan_seen) atomicOr(&rec->nan_seen, 1u);
+  }
+}
+
+// Integer / bool tensors: exact comparison in int64 (|a-b| <= 1e-2 means a == b), error
+// magnitudes after conversion to fp32 as the host formula does.
+template <typename T>
+__global__ void __launch_bounds__(256) allclose_int_kernel(const T* __restrict__ ref, const T* __restrict__ res, int64_t n, b200_close_record* rec) {
+  CloseAcc a{0ull, 0.f, 0.f, 0u};
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const T r = ref[i], s = res[i];
+    if (r != s) ++a.bad;
+    const float fr = static_cast<float>(r), fs = static_cast<float>(s);
+    const float diff = fabsf(fr - fs);
+    a.max_abs = fmaxf(a.max_abs, diff);
+    a.max_rel = fmaxf(a.max_rel, diff / (fabsf(fr) + 1e-10f));
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    a.bad += __shfl_xor_sync(0xffffffffu, a.bad, o);
+    a.max_abs = fmaxf(a.max_abs, __shfl_xor_sync(0xffffffffu, a.max_abs, o));
+    a.max_rel = fmaxf(a.max_rel, __shfl_xor_sync(0xffffffffu, a.max_rel, o));
+  }
+  if ((threadIdx.x & 31) == 0) {
+    if (a.bad) atomicAdd(reinterpret_cast<unsigned long long*>(&rec->mismatches), a.bad);
+    if (a.max_abs > 0.f) atomicMax(reinterpret_cast<unsigned*>(&rec->max_abs), __float_as_uint(a.max_abs));
+    if (a.max_rel > 0.f) atomicMax(reinterpret_cast<unsigned*>(&rec->max_rel), __float_as_uint(a.max_rel));
+  }
+}
+
+__global__ void __launch_bounds__(256) l2_flush_kernel(uint4* __restrict__ p, int64_t nvec) {
+  const uint4 z = make_uint4(0, 0, 0, 0);
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += static_cast<int64_t>(gridDim.x) * blockDim.x) p[i] = z;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_allclose(const void* ref, const void* res, int64_t n, int dtype, double rtol, double atol, b200_close_record* rec, int reset, void* stream) {
+  if (n < 0 || !rec) return B200_EINVAL;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (reset) {
+    const cudaError_t e = cudaMemsetAsync(rec, 0, sizeof(b200_close_record), st);
+    if (e != cudaSuccess) { set_last_cuda_error(e); return B200_ELAUNCH; }
+  }
+  if (n == 0) return B200_OK;
+  if (!ref || !res) return B200_EINVAL;
+  const int es = dtype_size(dtype);
+  if (es == 0) return B200_EDTYPE;
+  int64_t blocks = (n + 256 * 8 - 1) / (256 * 8);
+  const int64_t cap = static_cast<int64_t>(kNumSMs) * 16;
+  const int g = static_cast<int>(blocks < 1 ? 1 : (blocks > cap ? cap : blocks));
+  const int vec_ok = aligned16(ref) && aligned16(res);
+  const float rt = static_cast<float>(rtol), at = static_cast<float>(atol);
+  switch (dtype) {
+    case B200_F32: allclose_kernel<float><<<g, 256, 0, st>>>(static_cast<const float*>(ref), static_cast<const float*>(res), n, rt, at, rec, vec_ok); break;
+    case B200_BF16: allclose_kernel<__nv_bfloat16><<<g, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(ref), static_cast<const __nv_bfloat16*>(res), n, rt, at, rec, vec_ok); break;
+    case B200_F16: allclose_kernel<__half><<<g, 256, 0, st>>>(static_cast<const __half*>(ref), static_cast<const __half*>(res), n, rt, at, rec, vec_ok); break;
+    case B200_I64: allclose_int_kernel<int64_t><<<g, 256, 0, st>>>(static_cast<const int64_t*>(ref), static_cast<const int64_t*>(res), n, rec); break;
+    case B200_I32: allclose_int_kernel<int32_t><<<g, 256, 0, st>>>(static_cast<const int32_t*>(ref), static_cast<const int32_t*>(res), n, rec); break;
+    case B200_I16: allclose_int_kernel<int16_t><<<g, 256, 0, st>>>(static_cast<const int16_t*>(ref), static_cast<const int16_t*>(res), n, rec); break;
+    case B200_I8: allclose_int_kernel<int8_t><<<g, 256, 0, st>>>(static_cast<const int8_t*>(ref), static_cast<const int8_t*>(res), n, rec); break;
+    case B200_BOOL: case B200_U8: allclose_int_kernel<uint8_t><<<g, 256, 0, st>>>(static_cast<const uint8_t*>(ref), static_cast<const uint8_t*>(res), n, rec); break;
+    default: return B200_EDTYPE;
+  }
+  return check_launch();
+}
+
+extern "C" int b200_l2_flush(void* scratch, int64_t bytes, void* stream) {
+  if (bytes < 0 || (bytes > 0 && !scratch) || !aligned16(scratch)) return B200_EINVAL;
+  if (bytes < 16) return B200_OK;
+  l2_flush_kernel<<<kNumSMs * 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<uint4*>(scratch), bytes / 16);
+  return check_launch();
+}

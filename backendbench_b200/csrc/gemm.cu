@@ -1,0 +1,47 @@
+// mm / addmm / bmm entry point: picks the tcgen05 tensor-core kernel when the operands
+// qualify (bf16/f16, TMA-compatible layout) and the CUDA-core kernel otherwise.
+#include "b200_common.cuh"
+
+namespace b200 {
+int gemm_simt_dispatch(const void* A, const void* B, const void* bias, void* C, int64_t batch, int64_t M, int64_t N, int64_t K, int64_t sAb, int64_t sAm, int64_t sAk,
+                       int64_t sBb, int64_t sBk, int64_t sBn, int64_t sbm, int64_t sbn, double alpha, double beta, int dtype, cudaStream_t st);
+bool gemm_tc_eligible(int64_t batch, int64_t M, int64_t N, int64_t K, int64_t sAb, int64_t sAm, int64_t sAk, int64_t sBb, int64_t sBk, int64_t sBn, int dtype,
+                      const void* A, const void* B, const void* C);
+int gemm_tc_dispatch(const void* A, const void* B, const void* bias, void* C, int64_t batch, int64_t M, int64_t N, int64_t K, int64_t sAb, int64_t sAm, int64_t sAk,
+                     int64_t sBb, int64_t sBk, int64_t sBn, int64_t sbm, int64_t sbn, double alpha, double beta, int dtype, uint32_t* status, cudaStream_t st);
+
+__global__ void fill_bias_only(void* C, const void* bias, int64_t batch, int64_t M, int64_t N, int64_t sbm, int64_t sbn, float beta, int dt) {
+  const int64_t total = batch * M * N;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t n = i % N, m = (i / N) % M;
+    const float r = (bias && beta != 0.f) ? beta * load_as_f32(bias, m * sbm + n * sbn, dt) : 0.f;
+    store_from_f32(C, i, dt, r);
+  }
+}
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_gemm_uses_tensor_cores(int64_t batch, int64_t M, int64_t N, int64_t K, int64_t sAb, int64_t sAm, int64_t sAk, int64_t sBb, int64_t sBk, int64_t sBn,
+                                           int dtype, const void* A, const void* B, const void* C) {
+  return gemm_tc_eligible(batch, M, N, K, sAb, sAm, sAk, sBb, sBk, sBn, dtype, A, B, C) ? 1 : 0;
+}
+
+extern "C" int b200_gemm(const void* A, const void* B, const void* bias, void* C, int64_t batch, int64_t M, int64_t N, int64_t K, int64_t sAb, int64_t sAm, int64_t sAk,
+                         int64_t sBb, int64_t sBk, int64_t sBn, int64_t sbm, int64_t sbn, double alpha, double beta, int dtype, uint32_t* status, void* stream) {
+  if (batch < 0 || M < 0 || N < 0 || K < 0) return B200_EINVAL;
+  if (!is_float_dtype(dtype)) return B200_EDTYPE;
+  if (batch == 0 || M == 0 || N == 0) return B200_OK;
+  if (!C) return B200_EINVAL;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (K == 0) {  // empty contraction: the product is zero, only beta * bias remains
+    int64_t blocks = (batch * M * N + 255) / 256;
+    if (blocks > kNumSMs * 16) blocks = kNumSMs * 16;
+    fill_bias_only<<<static_cast<int>(blocks), 256, 0, st>>>(C, bias, batch, M, N, sbm, sbn, static_cast<float>(beta), dtype);
+    return check_launch();
+  }
+  if (!A || !B) return B200_EINVAL;
+  if (gemm_tc_eligible(batch, M, N, K, sAb, sAm, sAk, sBb, sBk, sBn, dtype, A, B, C))
+    return gemm_tc_dispatch(A, B, bias, C, batch, M, N, K, sAb, sAm, sAk, sBb, sBk, sBn, sbm, sbn, alpha, beta, dtype, status, st);
+  return gemm_simt_dispatch(A, B, bias, C, batch, M, N, K, sAb, sAm, sAk, sBb, sBk, sBn, sbm, sbn, alpha, beta, dtype, st);
+}

@@ -1,0 +1,205 @@
+// embedding / index_select / gather: bit-exact data movement driven by integer indices.
+//
+// Rows (embedding, index_select dim 0) are copied with 16-byte accesses, one CTA per
+// output row when rows are wide (>= 1 KB) and a flattened (row, vector) space when they
+// are narrow, so loads within a row and all stores are coalesced. gather moves single
+// elements: index reads and output writes are coalesced, source reads hit one 32-byte
+// sector each and are served by L2 when the source fits there.
+// An index outside [0, size) never faults: the element/row is written as zero and
+// B200_DEV_INDEX_OOB is OR-ed into the caller's status word. Negative indices are out of
+// range here, as they are for the aten CPU kernels.
+#include "b200_common.cuh"
+
+namespace b200 {
+
+__device__ __forceinline__ int64_t load_index(const void* idx, int64_t i, int idx_i32) {
+  return idx_i32 ? static_cast<int64_t>(static_cast<const int32_t*>(idx)[i]) : static_cast<const int64_t*>(idx)[i];
+}
+__device__ __forceinline__ void flag_oob(uint32_t* status) {
+  if (status) atomicOr(status, B200_DEV_INDEX_OOB);
+}
+template <typename U> __device__ __forceinline__ U zero_of() { U z; memset(&z, 0, sizeof(U)); return z; }
+
+// One CTA (128 threads) per output row; rows are `nvec` 16-byte vectors.
+__global__ void __launch_bounds__(128) gather_rows_wide(const uint4* __restrict__ table, const void* __restrict__ idx, uint4* __restrict__ out,
+                                                        int64_t table_rows, int64_t nvec, int64_t n_idx, int idx_i32, uint32_t* status) {
+  for (int64_t r = blockIdx.x; r < n_idx; r += gridDim.x) {
+    const int64_t src = load_index(idx, r, idx_i32);
+    const bool ok = src >= 0 && src < table_rows;
+    if (!ok && threadIdx.x == 0) flag_oob(status);
+    const uint4* s = table + (ok ? src : 0) * nvec;
+    uint4* d = out + r * nvec;
+    int64_t j = threadIdx.x;
+    for (; j + 3 * 128 < nvec; j += 4 * 128) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = ok ? __ldcs(s + j + u * 128) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) __stcs(d + j + u * 128, v[u]);
+    }
+    for (; j < nvec; j += 128) __stcs(d + j, ok ? __ldcs(s + j) : make_uint4(0, 0, 0, 0));
+  }
+}
+
+// Flattened index_select: x is [outer, dim_size, inner] in units of U, out is
+// [outer, n_idx, inner]; one unit per thread iteration.
+template <typename U>
+__global__ void __launch_bounds__(256) index_select_flat(const U* __restrict__ x, const void* __restrict__ idx, U* __restrict__ out, int64_t outer, int64_t dim_size,
+                                                         int64_t inner, int64_t n_idx, int idx_i32, uint32_t* status) {
+  const int64_t total = outer * n_idx * inner;
+  for (int64_t p = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; p < total; p += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t q = p / inner, i = p - q * inner;
+    const int64_t o = q / n_idx, k = q - o * n_idx;
+    const int64_t src = load_index(idx, k, idx_i32);
+    if (src < 0 || src >= dim_size) {
+      flag_oob(status);
+      out[p] = zero_of<U>();
+    } else {
+      out[p] = x[(o * dim_size + src) * inner + i];
+    }
+  }
+}
+
+struct GatherArgs {
+  int ndim, dim;
+  int64_t n;
+  int64_t shape[B200_MAX_DIMS], self_stride[B200_MAX_DIMS], idx_stride[B200_MAX_DIMS];
+  int64_t self_dim_size;
+};
+
+template <typename U>
+__global__ void __launch_bounds__(256) gather_generic(const U* __restrict__ self, const int64_t* __restrict__ index, U* __restrict__ out, GatherArgs A, uint32_t* status) {
+  for (int64_t p = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; p < A.n; p += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    int64_t lin = p, io = 0, so = 0;
+    for (int d = A.ndim - 1; d >= 0; --d) {
+      const int64_t q = lin / A.shape[d], r = lin - q * A.shape[d];
+      io += r * A.idx_stride[d];
+      if (d != A.dim) so += r * A.self_stride[d];
+      lin = q;
+    }
+    const int64_t k = index[io];
+    if (k < 0 || k >= A.self_dim_size) {
+      flag_oob(status);
+      out[p] = zero_of<U>();
+    } else {
+      out[p] = self[so + k * A.self_stride[A.dim]];
+    }
+  }
+}
+
+// 2-D, dim 0, contiguous index [R, C] and unit column stride in self (row pitch
+// `self_pitch`): each thread produces 4 adjacent outputs -- two 16-byte index loads,
+// four sector reads, one 16-byte store (4-byte elements).
+__global__ void __launch_bounds__(256) gather_dim0_vec4(const uint32_t* __restrict__ self, const int64_t* __restrict__ index, uint32_t* __restrict__ out,
+                                                        int64_t rows, int64_t cols, int64_t self_pitch, int64_t self_rows, uint32_t* status) {
+  const int64_t nquad = rows * cols / 4;
+  for (int64_t q = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; q < nquad; q += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t p = q * 4;
+    const int64_t col = p % cols;  // cols % 4 == 0, so the quad stays inside one row
+    const longlong2 i01 = __ldcs(reinterpret_cast<const longlong2*>(index + p));
+    const longlong2 i23 = __ldcs(reinterpret_cast<const longlong2*>(index + p + 2));
+    const int64_t k[4] = {i01.x, i01.y, i23.x, i23.y};
+    uint32_t v[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      if (k[e] < 0 || k[e] >= self_rows) {
+        flag_oob(status);
+        v[e] = 0;
+      } else {
+        v[e] = __ldg(self + k[e] * self_pitch + col + e);
+      }
+    }
+    __stcs(reinterpret_cast<uint4*>(out + p), make_uint4(v[0], v[1], v[2], v[3]));
+  }
+}
+
+static int capped_grid(int64_t items, int per_block, int waves) {
+  int64_t g = (items + per_block - 1) / per_block;
+  const int64_t cap = static_cast<int64_t>(kNumSMs) * waves;
+  return static_cast<int>(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+// Largest power-of-two unit (<= 16 bytes) dividing `bytes` and every pointer's address.
+static int common_unit(int64_t bytes, const void* a, const void* b) {
+  uintptr_t m = static_cast<uintptr_t>(bytes) | reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b);
+  int u = 16;
+  while (u > 1 && (m & (u - 1))) u >>= 1;
+  return u;
+}
+
+template <typename U>
+static void launch_flat(const void* x, const void* idx, void* out, int64_t outer, int64_t dim_size, int64_t inner_units, int64_t n_idx, int idx_i32, uint32_t* status, cudaStream_t st) {
+  const int64_t total = outer * n_idx * inner_units;
+  index_select_flat<U><<<capped_grid(total, 256, 16), 256, 0, st>>>(static_cast<const U*>(x), idx, static_cast<U*>(out), outer, dim_size, inner_units, n_idx, idx_i32, status);
+}
+
+static int index_select_bytes(const void* x, const void* idx, void* out, int64_t outer, int64_t dim_size, int64_t inner_bytes, int64_t n_idx, int idx_dtype, uint32_t* status, cudaStream_t st) {
+  if (idx_dtype != B200_I32 && idx_dtype != B200_I64) return B200_EDTYPE;
+  const int i32 = idx_dtype == B200_I32;
+  const int unit = common_unit(inner_bytes, x, out);
+  const int64_t units = inner_bytes / unit;
+  if (outer == 1 && unit == 16 && units >= 64) {
+    gather_rows_wide<<<capped_grid(n_idx, 1, 64), 128, 0, st>>>(static_cast<const uint4*>(x), idx, static_cast<uint4*>(out), dim_size, units, n_idx, i32, status);
+    return check_launch();
+  }
+  switch (unit) {
+    case 16: launch_flat<uint4>(x, idx, out, outer, dim_size, units, n_idx, i32, status, st); break;
+    case 8: launch_flat<uint64_t>(x, idx, out, outer, dim_size, units, n_idx, i32, status, st); break;
+    case 4: launch_flat<uint32_t>(x, idx, out, outer, dim_size, units, n_idx, i32, status, st); break;
+    case 2: launch_flat<uint16_t>(x, idx, out, outer, dim_size, units, n_idx, i32, status, st); break;
+    default: launch_flat<uint8_t>(x, idx, out, outer, dim_size, units, n_idx, i32, status, st); break;
+  }
+  return check_launch();
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_gather_rows(const void* table, const void* idx, void* out, int64_t table_rows, int64_t row_bytes, int64_t n_idx, int idx_dtype, uint32_t* status, void* stream) {
+  if (table_rows < 0 || row_bytes < 0 || n_idx < 0) return B200_EINVAL;
+  if (n_idx == 0 || row_bytes == 0) return B200_OK;
+  if (!idx || !out || (!table && table_rows > 0)) return B200_EINVAL;
+  return index_select_bytes(table, idx, out, 1, table_rows, row_bytes, n_idx, idx_dtype, status, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int b200_index_select(const void* x, const void* idx, void* out, int64_t outer, int64_t dim_size, int64_t inner, int64_t n_idx, int elem_size, int idx_dtype, uint32_t* status, void* stream) {
+  if (outer < 0 || dim_size < 0 || inner < 0 || n_idx < 0 || elem_size <= 0) return B200_EINVAL;
+  if (outer == 0 || inner == 0 || n_idx == 0) return B200_OK;
+  if (!idx || !out || (!x && dim_size > 0)) return B200_EINVAL;
+  return index_select_bytes(x, idx, out, outer, dim_size, inner * elem_size, n_idx, idx_dtype, status, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int b200_gather(const void* self, const void* index, void* out, int ndim, const int64_t* index_shape, const int64_t* self_strides, const int64_t* index_strides, int64_t self_dim_size, int dim, int elem_size, uint32_t* status, void* stream) {
+  if (ndim < 1 || ndim > B200_MAX_DIMS || dim < 0 || dim >= ndim || !index_shape || !self_strides || !index_strides) return B200_EINVAL;
+  GatherArgs A;
+  A.ndim = ndim;
+  A.dim = dim;
+  A.n = 1;
+  A.self_dim_size = self_dim_size;
+  for (int d = 0; d < ndim; ++d) {
+    if (index_shape[d] < 0) return B200_EINVAL;
+    A.shape[d] = index_shape[d];
+    A.self_stride[d] = self_strides[d];
+    A.idx_stride[d] = index_strides[d];
+    A.n *= index_shape[d];
+  }
+  if (A.n == 0) return B200_OK;
+  if (!self || !index || !out) return B200_EINVAL;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool idx_contig = is_contiguous(ndim, index_shape, index_strides);
+  if (ndim == 2 && dim == 0 && elem_size == 4 && idx_contig && self_strides[1] == 1 && index_shape[1] % 4 == 0 && aligned16(index) && aligned16(out)) {
+    gather_dim0_vec4<<<capped_grid(A.n / 4, 256, 32), 256, 0, st>>>(static_cast<const uint32_t*>(self), static_cast<const int64_t*>(index), static_cast<uint32_t*>(out), index_shape[0], index_shape[1], self_strides[0], self_dim_size, status);
+    return check_launch();
+  }
+  const int g = capped_grid(A.n, 256, 32);
+  const int64_t* pi = static_cast<const int64_t*>(index);
+  switch (elem_size) {
+    case 1: gather_generic<uint8_t><<<g, 256, 0, st>>>(static_cast<const uint8_t*>(self), pi, static_cast<uint8_t*>(out), A, status); break;
+    case 2: gather_generic<uint16_t><<<g, 256, 0, st>>>(static_cast<const uint16_t*>(self), pi, static_cast<uint16_t*>(out), A, status); break;
+    case 4: gather_generic<uint32_t><<<g, 256, 0, st>>>(static_cast<const uint32_t*>(self), pi, static_cast<uint32_t*>(out), A, status); break;
+    case 8: gather_generic<uint64_t><<<g, 256, 0, st>>>(static_cast<const uint64_t*>(self), pi, static_cast<uint64_t*>(out), A, status); break;
+    default: return B200_EDTYPE;
+  }
+  return check_launch();
+}

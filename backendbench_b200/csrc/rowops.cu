@@ -1,0 +1,646 @@
+// _softmax / _log_softmax / native_layer_norm / sum.dim_IntList / argmax.
+//
+// The input is contiguous, viewed as [outer, dim, inner], the op runs along `dim`.
+//   inner == 1, row fits in registers : "resident" kernels -- the row is read from HBM
+//       exactly once with 16-byte streaming loads, held as fp32 in registers by one
+//       warp (short rows) or one CTA (long rows), reduced with warp shuffles (+ one
+//       shared-memory hop for CTA rows) and written once: 1 read + 1 write per element.
+//   inner == 1, anything else        : "streaming" kernels, one CTA per row, scalar
+//       accesses, re-reads served by L2.
+//   inner  > 1                        : one thread per (outer, inner) column, coalesced
+//       across `inner`, sequential along `dim`.
+// sum and argmax are single-pass; when few outputs face a long reduction the reduction
+// is split over gridDim.y CTAs and finished by a second tiny kernel from scratch memory.
+#include <math_constants.h>
+
+#include "b200_common.cuh"
+
+namespace b200 {
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+// ---- group = one warp (WARP) or the whole CTA: reductions over the threads of a row
+template <bool WARP, typename F>
+__device__ __forceinline__ float group_reduce(float v, F f, float identity, float* smem) {
+  if (WARP) return warp_reduce(v, f);
+  return block_reduce(v, f, identity, smem);
+}
+
+// Store VE fp32 values at element offset `e0` of `out`, as T (16-byte store) or as fp32.
+template <typename T>
+__device__ __forceinline__ void store_row_vec(void* out, int64_t e0, const float* f, bool out_f32) {
+  constexpr int VE = Vec<T>::N;
+  if (sizeof(T) == 4 || out_f32) {
+    float* o = static_cast<float*>(out) + e0;
+#pragma unroll
+    for (int q = 0; q < VE / 4; ++q) st_stream(o + 4 * q, make_uint4(__float_as_uint(f[4 * q]), __float_as_uint(f[4 * q + 1]), __float_as_uint(f[4 * q + 2]), __float_as_uint(f[4 * q + 3])));
+  } else {
+    Vec<T> r;
+#pragma unroll
+    for (int e = 0; e < VE; ++e) r.set(e, from_f32<T>(f[e]));
+    st_stream(static_cast<T*>(out) + e0, r.raw);
+  }
+}
+
+// Load VE weights (dtype TW) starting at element e0 as fp32; weights are re-read by
+// every row, so they take the cached read-only path.
+template <int VE, typename TW>
+__device__ __forceinline__ void load_weights(const TW* w, int e0, float* f) {
+  constexpr int PER = 16 / sizeof(TW);
+#pragma unroll
+  for (int q = 0; q < VE / PER; ++q) {
+    Vec<TW> v;
+    v.raw = ld_keep(w + e0 + q * PER);
+#pragma unroll
+    for (int e = 0; e < PER; ++e) f[q * PER + e] = to_f32(v.get(e));
+  }
+}
+
+// ------------------------------------------------------------------ softmax, resident
+template <typename T, int VPT, bool WARP>
+__global__ void __launch_bounds__(WARP ? 128 : 1024)
+softmax_resident(const T* __restrict__ x, void* __restrict__ out, int64_t rows, int cols, int out_f32, int is_log) {
+  constexpr int VE = Vec<T>::N;
+  __shared__ float red[33];
+  const int tpr = WARP ? 32 : blockDim.x;
+  const int t = WARP ? (threadIdx.x & 31) : threadIdx.x;
+  const int64_t row = WARP ? static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5) : blockIdx.x;
+  if (WARP && row >= rows) return;
+  const int nvec = cols / VE;
+  const T* xr = x + row * cols;
+  float f[VPT][VE];
+  float m = -CUDART_INF_F;
+#pragma unroll
+  for (int u = 0; u < VPT; ++u) {
+    const int j = t + u * tpr;
+    if (j < nvec) {
+      Vec<T> v;
+      v.raw = ld_stream(xr + static_cast<int64_t>(j) * VE);
+#pragma unroll
+      for (int e = 0; e < VE; ++e) {
+        f[u][e] = to_f32(v.get(e));
+        m = fmaxf(m, f[u][e]);
+      }
+    }
+  }
+  m = group_reduce<WARP>(m, MaxF{}, -CUDART_INF_F, red);
+  float s = 0.f;
+#pragma unroll
+  for (int u = 0; u < VPT; ++u) {
+    const int j = t + u * tpr;
+    if (j < nvec) {
+#pragma unroll
+      for (int e = 0; e < VE; ++e) {
+        const float d = f[u][e] - m;
+        const float ex = exp2f(d * kLog2e);
+        s += ex;
+        f[u][e] = is_log ? d : ex;
+      }
+    }
+  }
+  s = group_reduce<WARP>(s, SumF{}, 0.f, red);
+  const float k = is_log ? logf(s) : 1.f / s;
+#pragma unroll
+  for (int u = 0; u < VPT; ++u) {
+    const int j = t + u * tpr;
+    if (j < nvec) {
+#pragma unroll
+      for (int e = 0; e < VE; ++e) f[u][e] = is_log ? f[u][e] - k : f[u][e] * k;
+      store_row_vec<T>(out, row * cols + static_cast<int64_t>(j) * VE, f[u], out_f32 != 0);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ softmax, streaming
+// One CTA per row, three scalar passes (max, sum of exponentials, write); the second
+// and third read come from L2. Any `cols`, any alignment. NaN / inf rows behave as in
+// the resident kernel: the arithmetic is the same, only the data path differs.
+template <typename T>
+__global__ void __launch_bounds__(256) softmax_stream(const T* __restrict__ x, void* __restrict__ out, int64_t cols, int dto, int is_log) {
+  __shared__ float red[33];
+  const int64_t row = blockIdx.x;
+  const T* xr = x + row * cols;
+  float m = -CUDART_INF_F;
+  for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) m = fmaxf(m, to_f32(xr[c]));
+  m = block_reduce(m, MaxF{}, -CUDART_INF_F, red);
+  float s = 0.f;
+  for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) s += exp2f((to_f32(xr[c]) - m) * kLog2e);
+  s = block_reduce(s, SumF{}, 0.f, red);
+  const float k = is_log ? logf(s) : 1.f / s;
+  for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) {
+    const float d = to_f32(xr[c]) - m;
+    store_from_f32(out, row * cols + c, dto, is_log ? d - k : exp2f(d * kLog2e) * k);
+  }
+}
+
+// ------------------------------------------------------------------ softmax, inner > 1
+template <typename T>
+__global__ void __launch_bounds__(128) softmax_cols(const T* __restrict__ x, void* __restrict__ out, int64_t dim, int64_t inner, int dto, int is_log) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= inner) return;
+  const int64_t base = static_cast<int64_t>(blockIdx.y) * dim * inner + i;
+  float m = -CUDART_INF_F;
+  for (int64_t k = 0; k < dim; ++k) m = fmaxf(m, to_f32(x[base + k * inner]));
+  float s = 0.f;
+  for (int64_t k = 0; k < dim; ++k) s += exp2f((to_f32(x[base + k * inner]) - m) * kLog2e);
+  const float kk = is_log ? logf(s) : 1.f / s;
+  for (int64_t k = 0; k < dim; ++k) {
+    const float d = to_f32(x[base + k * inner]) - m;
+    store_from_f32(out, base + k * inner, dto, is_log ? d - kk : exp2f(d * kLog2e) * kk);
+  }
+}
+
+// ------------------------------------------------------------------ layer norm, resident
+template <typename T, typename TW, int VPT, bool WARP>
+__global__ void __launch_bounds__(WARP ? 128 : 1024)
+layernorm_resident(const T* __restrict__ x, const TW* __restrict__ w, const TW* __restrict__ b, T* __restrict__ y,
+                   void* __restrict__ mean, void* __restrict__ rstd, int64_t rows, int cols, float eps, int dt_stat) {
+  constexpr int VE = Vec<T>::N;
+  __shared__ float red[33];
+  const int tpr = WARP ? 32 : blockDim.x;
+  const int t = WARP ? (threadIdx.x & 31) : threadIdx.x;
+  const int64_t row = WARP ? static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5) : blockIdx.x;
+  if (WARP && row >= rows) return;
+  const int nvec = cols / VE;
+  const T* xr = x + row * cols;
+  float f[VPT][VE];
+  float s = 0.f;
+#pragma unroll
+  for (int u = 0; u < VPT; ++u) {
+    const int j = t + u * tpr;
+    if (j < nvec) {
+      Vec<T> v;
+      v.raw = ld_stream(xr + static_cast<int64_t>(j) * VE);
+#pragma unroll
+      for (int e = 0; e < VE; ++e) {
+        f[u][e] = to_f32(v.get(e));
+        s += f[u][e];
+      }
+    }
+  }
+  s = group_reduce<WARP>(s, SumF{}, 0.f, red);
+  const float mu = s / static_cast<float>(cols);
+  float q = 0.f;
+#pragma unroll
+  for (int u = 0; u < VPT; ++u) {
+    const int j = t + u * tpr;
+    if (j < nvec) {
+#pragma unroll
+      for (int e = 0; e < VE; ++e) {
+        const float d = f[u][e] - mu;
+        q = fmaf(d, d, q);
+      }
+    }
+  }
+  q = group_reduce<WARP>(q, SumF{}, 0.f, red);
+  const float rs = rsqrtf(q / static_cast<float>(cols) + eps);
+  if (t == 0) {
+    store_from_f32(mean, row, dt_stat, mu);
+    store_from_f32(rstd, row, dt_stat, rs);
+  }
+#pragma unroll
+  for (int u = 0; u < VPT; ++u) {
+    const int j = t + u * tpr;
+    if (j < nvec) {
+      float wv[VE], bv[VE];
+      if (w) load_weights<VE, TW>(w, j * VE, wv);
+      if (b) load_weights<VE, TW>(b, j * VE, bv);
+#pragma unroll
+      for (int e = 0; e < VE; ++e) {
+        float r = (f[u][e] - mu) * rs;
+        if (w) r *= wv[e];
+        if (b) r += bv[e];
+        f[u][e] = r;
+      }
+      store_row_vec<T>(y, row * cols + static_cast<int64_t>(j) * VE, f[u], false);
+    }
+  }
+}
+
+// layer norm, streaming: one CTA per row, three scalar passes (second and third from L2).
+__global__ void __launch_bounds__(256) layernorm_stream(const void* __restrict__ x, const void* __restrict__ w, const void* __restrict__ b, void* __restrict__ y,
+                                                        void* __restrict__ mean, void* __restrict__ rstd, int64_t cols, float eps, int dt, int dt_wb, int dt_stat) {
+  __shared__ float red[33];
+  const int64_t row = blockIdx.x, base = row * cols;
+  float s = 0.f;
+  for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) s += load_as_f32(x, base + c, dt);
+  s = block_reduce(s, SumF{}, 0.f, red);
+  const float mu = s / static_cast<float>(cols);
+  float q = 0.f;
+  for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) {
+    const float d = load_as_f32(x, base + c, dt) - mu;
+    q = fmaf(d, d, q);
+  }
+  q = block_reduce(q, SumF{}, 0.f, red);
+  const float rs = rsqrtf(q / static_cast<float>(cols) + eps);
+  if (threadIdx.x == 0) {
+    store_from_f32(mean, row, dt_stat, mu);
+    store_from_f32(rstd, row, dt_stat, rs);
+  }
+  for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) {
+    float r = (load_as_f32(x, base + c, dt) - mu) * rs;
+    if (w) r *= load_as_f32(w, c, dt_wb);
+    if (b) r += load_as_f32(b, c, dt_wb);
+    store_from_f32(y, base + c, dt, r);
+  }
+}
+
+// ------------------------------------------------------------------ sum / argmax
+// argmax order: NaN beats everything, then larger value, then smaller index.
+struct ArgPair {
+  float v;
+  int64_t i;
+};
+__device__ __forceinline__ bool arg_better(float v, int64_t i, float bv, int64_t bi) {
+  const bool vn = v != v, bn = bv != bv;
+  if (vn || bn) return vn && (!bn || i < bi);
+  return v > bv || (v == bv && i < bi);
+}
+__device__ __forceinline__ void arg_take(ArgPair& a, float v, int64_t i) {
+  if (a.i < 0 || arg_better(v, i, a.v, a.i)) { a.v = v; a.i = i; }
+}
+__device__ __forceinline__ ArgPair arg_warp_reduce(ArgPair a) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float v = __shfl_xor_sync(0xffffffffu, a.v, o);
+    const int64_t i = __shfl_xor_sync(0xffffffffu, a.i, o);
+    if (i >= 0) arg_take(a, v, i);
+  }
+  return a;
+}
+
+// Row reduction (inner == 1). grid = (row groups, splits). A row's [c0, c1) slice of
+// split blockIdx.y is consumed by one warp (WARP) or one CTA with 16-byte loads when
+// VECOK (row pitch and base 16-byte aligned), else scalar loads.
+template <typename T, bool WARP, bool ARG, bool VECOK>
+__global__ void __launch_bounds__(256) reduce_rows(const T* __restrict__ x, void* __restrict__ out, float* __restrict__ part_v, int64_t* __restrict__ part_i,
+                                                   int64_t rows, int64_t cols, int64_t chunk, int dto) {
+  constexpr int VE = Vec<T>::N;
+  __shared__ float red[33];
+  __shared__ float av[32];
+  __shared__ int64_t ai[32];
+  const int tpr = WARP ? 32 : blockDim.x;
+  const int t = WARP ? (threadIdx.x & 31) : threadIdx.x;
+  const int64_t row = WARP ? static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5) : blockIdx.x;
+  if (WARP && row >= rows) return;
+  const int64_t c0 = static_cast<int64_t>(blockIdx.y) * chunk;
+  const int64_t c1 = c0 + chunk < cols ? c0 + chunk : cols;
+  const T* xr = x + row * cols;
+  float s = 0.f;
+  ArgPair a{0.f, -1};
+  if (VECOK) {
+    // chunk is a multiple of VE, so every slice starts on a vector boundary
+    const int64_t v0 = c0 / VE, v1 = c1 / VE;
+    int64_t j = v0 + t;
+    for (; j + 3 * tpr < v1; j += 4 * tpr) {
+      Vec<T> v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u].raw = ld_stream(xr + (j + u * tpr) * VE);
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int e = 0; e < VE; ++e) {
+          const float fv = to_f32(v[u].get(e));
+          if (ARG) arg_take(a, fv, (j + u * tpr) * VE + e);
+          else s += fv;
+        }
+    }
+    for (; j < v1; j += tpr) {
+      Vec<T> v;
+      v.raw = ld_stream(xr + j * VE);
+#pragma unroll
+      for (int e = 0; e < VE; ++e) {
+        const float fv = to_f32(v.get(e));
+        if (ARG) arg_take(a, fv, j * VE + e);
+        else s += fv;
+      }
+    }
+    for (int64_t c = v1 * VE + t; c < c1; c += tpr) {  // ragged end of the last slice
+      const float fv = to_f32(xr[c]);
+      if (ARG) arg_take(a, fv, c);
+      else s += fv;
+    }
+  } else {
+    for (int64_t c = c0 + t; c < c1; c += tpr) {
+      const float fv = to_f32(xr[c]);
+      if (ARG) arg_take(a, fv, c);
+      else s += fv;
+    }
+  }
+  const bool split = gridDim.y > 1;
+  const int64_t slot = static_cast<int64_t>(blockIdx.y) * rows + row;
+  if (!ARG) {
+    s = group_reduce<WARP>(s, SumF{}, 0.f, red);
+    if (t == 0) {
+      if (split) part_v[slot] = s;
+      else store_from_f32(out, row, dto, s);
+    }
+  } else {
+    a = arg_warp_reduce(a);
+    if (!WARP) {
+      const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+      if (lane == 0) { av[warp] = a.v; ai[warp] = a.i; }
+      __syncthreads();
+      if (warp == 0) {
+        a.v = lane < (blockDim.x >> 5) ? av[lane] : 0.f;
+        a.i = lane < (blockDim.x >> 5) ? ai[lane] : -1;
+        a = arg_warp_reduce(a);
+      }
+    }
+    if (threadIdx.x == 0 || (WARP && t == 0)) {
+      if (split) { part_v[slot] = a.v; part_i[slot] = a.i; }
+      else static_cast<int64_t*>(out)[row] = a.i;
+    }
+  }
+}
+
+// Column reduction (inner > 1): thread per inner element, grid = (inner tiles, outer, splits).
+template <typename T, bool ARG>
+__global__ void __launch_bounds__(256) reduce_cols(const T* __restrict__ x, void* __restrict__ out, float* __restrict__ part_v, int64_t* __restrict__ part_i,
+                                                   int64_t outer, int64_t dim, int64_t inner, int64_t chunk, int dto) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= inner) return;
+  const int64_t o = blockIdx.y;
+  const int64_t k0 = static_cast<int64_t>(blockIdx.z) * chunk;
+  const int64_t k1 = k0 + chunk < dim ? k0 + chunk : dim;
+  const T* p = x + o * dim * inner + i;
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  ArgPair a{0.f, -1};
+  int64_t k = k0;
+  if (!ARG) {
+    for (; k + 3 < k1; k += 4) {
+      s0 += to_f32(p[k * inner]);
+      s1 += to_f32(p[(k + 1) * inner]);
+      s2 += to_f32(p[(k + 2) * inner]);
+      s3 += to_f32(p[(k + 3) * inner]);
+    }
+  }
+  for (; k < k1; ++k) {
+    const float fv = to_f32(p[k * inner]);
+    if (ARG) arg_take(a, fv, k);
+    else s0 += fv;
+  }
+  const float s = (s0 + s1) + (s2 + s3);
+  const int64_t oi = o * inner + i;
+  if (gridDim.z > 1) {
+    const int64_t slot = static_cast<int64_t>(blockIdx.z) * outer * inner + oi;
+    if (ARG) { part_v[slot] = a.v; part_i[slot] = a.i; }
+    else part_v[slot] = s;
+  } else {
+    if (ARG) static_cast<int64_t*>(out)[oi] = a.i;
+    else store_from_f32(out, oi, dto, s);
+  }
+}
+
+// Second stage of a split reduction: n outputs, `splits` partials each, ascending split
+// order (so the earliest index wins argmax ties and sums are run-to-run identical).
+template <bool ARG>
+__global__ void __launch_bounds__(256) reduce_finalize(const float* __restrict__ part_v, const int64_t* __restrict__ part_i, void* __restrict__ out, int64_t n, int splits, int dto) {
+  const int64_t o = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (o >= n) return;
+  if (ARG) {
+    ArgPair a{0.f, -1};
+    for (int s = 0; s < splits; ++s) {
+      const int64_t i = part_i[s * n + o];
+      if (i >= 0) arg_take(a, part_v[s * n + o], i);
+    }
+    static_cast<int64_t*>(out)[o] = a.i;
+  } else {
+    float s = 0.f;
+    for (int k = 0; k < splits; ++k) s += part_v[k * n + o];
+    store_from_f32(out, o, dto, s);
+  }
+}
+
+__global__ void fill_zero_typed(void* out, int64_t n, int dto) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < n) store_from_f32(out, i, dto, 0.f);
+}
+
+// ------------------------------------------------------------------ host-side planning
+struct ReducePlan {
+  int splits;
+  int64_t chunk;  // elements of `dim` per split (multiple of 64)
+};
+
+static ReducePlan plan_reduce(int64_t outer, int64_t dim, int64_t inner) {
+  // CTAs available without splitting
+  int64_t ctas = inner == 1 ? outer : outer * ((inner + 255) / 256);
+  ReducePlan p{1, dim};
+  const int64_t want = 2LL * kNumSMs;
+  if (ctas >= want || dim < 16384) return p;
+  int64_t s = (want + ctas - 1) / ctas;
+  const int64_t max_s = dim / 4096;  // keep >= 4096 elements per split
+  if (s > max_s) s = max_s;
+  if (s > 1024) s = 1024;
+  if (s <= 1) return p;
+  int64_t chunk = (dim + s - 1) / s;
+  chunk = (chunk + 63) / 64 * 64;
+  p.splits = static_cast<int>((dim + chunk - 1) / chunk);
+  p.chunk = chunk;
+  return p;
+}
+
+template <typename T, bool ARG>
+static int launch_reduce_T(const void* x, void* out, int64_t outer, int64_t dim, int64_t inner, int dto, void* scratch, int64_t scratch_bytes, cudaStream_t st) {
+  const ReducePlan p = plan_reduce(outer, dim, inner);
+  const int64_t nout = outer * inner;
+  float* pv = nullptr;
+  int64_t* pi = nullptr;
+  if (p.splits > 1) {
+    const int64_t need = static_cast<int64_t>(p.splits) * nout * 16;
+    if (!scratch || scratch_bytes < need) return B200_ESCRATCH;
+    pi = static_cast<int64_t*>(scratch);  // int64 block first keeps it 8-byte aligned
+    pv = reinterpret_cast<float*>(pi + static_cast<int64_t>(p.splits) * nout);
+  }
+  const T* px = static_cast<const T*>(x);
+  if (inner == 1) {
+    constexpr int VE = Vec<T>::N;
+    const bool vecok = aligned16(x) && (dim % VE == 0);
+    const bool warp = p.splits == 1 && dim * static_cast<int64_t>(sizeof(T)) <= 8192;
+    if (!warp && outer > 0x7fffffffLL) return B200_EINVAL;
+    if (warp) {
+      dim3 g(grid_for(outer, 8), 1);
+      if (vecok) reduce_rows<T, true, ARG, true><<<g, 256, 0, st>>>(px, out, pv, pi, outer, dim, p.chunk, dto);
+      else reduce_rows<T, true, ARG, false><<<g, 256, 0, st>>>(px, out, pv, pi, outer, dim, p.chunk, dto);
+    } else {
+      dim3 g(static_cast<unsigned>(outer), p.splits);
+      if (vecok) reduce_rows<T, false, ARG, true><<<g, 256, 0, st>>>(px, out, pv, pi, outer, dim, p.chunk, dto);
+      else reduce_rows<T, false, ARG, false><<<g, 256, 0, st>>>(px, out, pv, pi, outer, dim, p.chunk, dto);
+    }
+  } else {
+    if (outer > 65535) {
+      // grid.y limit: fold by launching per slab of 65535 outer rows
+      for (int64_t o0 = 0; o0 < outer; o0 += 65535) {
+        const int64_t on = outer - o0 < 65535 ? outer - o0 : 65535;
+        dim3 g(grid_for(inner, 256), static_cast<unsigned>(on), 1);
+        void* o_ptr = ARG ? static_cast<void*>(static_cast<int64_t*>(out) + o0 * inner) : static_cast<void*>(static_cast<char*>(out) + o0 * inner * dtype_size(dto));
+        reduce_cols<T, ARG><<<g, 256, 0, st>>>(px + o0 * dim * inner, o_ptr, nullptr, nullptr, on, dim, inner, dim, dto);
+      }
+      return check_launch();
+    }
+    dim3 g(grid_for(inner, 256), static_cast<unsigned>(outer), p.splits);
+    reduce_cols<T, ARG><<<g, 256, 0, st>>>(px, out, pv, pi, outer, dim, inner, p.chunk, dto);
+  }
+  if (p.splits > 1) reduce_finalize<ARG><<<grid_for(nout, 256), 256, 0, st>>>(pv, pi, out, nout, p.splits, dto);
+  return check_launch();
+}
+
+// Resident-kernel geometry for `nvec` 16-byte vectors per row.
+struct ResidentCfg {
+  bool ok, warp;
+  int vpt, threads;
+};
+static ResidentCfg resident_cfg(int64_t nvec, int max_vpt) {
+  ResidentCfg c{false, false, 1, 128};
+  if (nvec <= 0) return c;
+  auto pow2_at_least = [](int64_t v) { int64_t p = 1; while (p < v) p <<= 1; return p; };
+  if (nvec <= 32LL * max_vpt && nvec <= 256) {
+    c.ok = true; c.warp = true; c.threads = 128;
+    c.vpt = static_cast<int>(pow2_at_least((nvec + 31) / 32));
+    return c;
+  }
+  int64_t th = pow2_at_least((nvec + 3) / 4);
+  if (th < 128) th = 128;
+  if (th > 1024) th = 1024;
+  const int64_t vpt = pow2_at_least((nvec + th - 1) / th);
+  if (vpt > max_vpt) return c;
+  c.ok = true; c.warp = false; c.threads = static_cast<int>(th); c.vpt = static_cast<int>(vpt);
+  return c;
+}
+
+#define B200_DISPATCH_VPT(VPT_VALUE, MAXV, BODY)                     \
+  switch (VPT_VALUE) {                                               \
+    case 1: { constexpr int VPT = 1; BODY; } break;                  \
+    case 2: { constexpr int VPT = 2; BODY; } break;                  \
+    case 4: { constexpr int VPT = 4; BODY; } break;                  \
+    default: { constexpr int VPT = (MAXV) >= 8 ? 8 : 4; BODY; } break; \
+  }
+
+template <typename T>
+static int softmax_T(const void* x, void* out, int64_t outer, int64_t dim, int64_t inner, int dto, int is_log, cudaStream_t st) {
+  constexpr int VE = Vec<T>::N;
+  constexpr int MAXV = 32 / VE;  // at most 32 fp32 registers of row data per thread
+  const T* px = static_cast<const T*>(x);
+  const int out_f32 = dto == B200_F32;
+  if (inner == 1) {
+    const ResidentCfg c = (dim % VE == 0 && aligned16(x) && aligned16(out) && dim < (1LL << 30)) ? resident_cfg(dim / VE, MAXV) : ResidentCfg{false, false, 1, 128};
+    if (c.ok && outer <= 0x7fffffffLL) {
+      if (c.warp) {
+        B200_DISPATCH_VPT(c.vpt, MAXV, (softmax_resident<T, VPT, true><<<grid_for(outer, 4), 128, 0, st>>>(px, out, outer, static_cast<int>(dim), out_f32, is_log)))
+      } else {
+        B200_DISPATCH_VPT(c.vpt, MAXV, (softmax_resident<T, VPT, false><<<static_cast<unsigned>(outer), c.threads, 0, st>>>(px, out, outer, static_cast<int>(dim), out_f32, is_log)))
+      }
+    } else {
+      if (outer > 0x7fffffffLL) return B200_EINVAL;
+      softmax_stream<T><<<static_cast<unsigned>(outer), 256, 0, st>>>(px, out, dim, dto, is_log);
+    }
+  } else {
+    for (int64_t o0 = 0; o0 < outer; o0 += 65535) {
+      const int64_t on = outer - o0 < 65535 ? outer - o0 : 65535;
+      dim3 g(grid_for(inner, 128), static_cast<unsigned>(on));
+      softmax_cols<T><<<g, 128, 0, st>>>(px + o0 * dim * inner, static_cast<char*>(out) + o0 * dim * inner * dtype_size(dto), dim, inner, dto, is_log);
+    }
+  }
+  return check_launch();
+}
+
+template <typename T, typename TW>
+static int layernorm_T(const void* x, const void* w, const void* b, void* y, void* mean, void* rstd, int64_t rows, int64_t cols, float eps, int dt_stat, const ResidentCfg& c, cudaStream_t st) {
+  constexpr int VE = Vec<T>::N;
+  constexpr int MAXV = 32 / VE;
+  const T* px = static_cast<const T*>(x);
+  const TW* pw = static_cast<const TW*>(w);
+  const TW* pb = static_cast<const TW*>(b);
+  T* py = static_cast<T*>(y);
+  if (c.warp) {
+    B200_DISPATCH_VPT(c.vpt, MAXV, (layernorm_resident<T, TW, VPT, true><<<grid_for(rows, 4), 128, 0, st>>>(px, pw, pb, py, mean, rstd, rows, static_cast<int>(cols), eps, dt_stat)))
+  } else {
+    B200_DISPATCH_VPT(c.vpt, MAXV, (layernorm_resident<T, TW, VPT, false><<<static_cast<unsigned>(rows), c.threads, 0, st>>>(px, pw, pb, py, mean, rstd, rows, static_cast<int>(cols), eps, dt_stat)))
+  }
+  return check_launch();
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_softmax(const void* x, void* out, int64_t outer, int64_t dim, int64_t inner, int dti, int dto, int is_log, void* stream) {
+  if (outer < 0 || dim < 0 || inner < 0) return B200_EINVAL;
+  if (!is_float_dtype(dti) || !(dto == dti || dto == B200_F32)) return B200_EDTYPE;
+  if (outer == 0 || dim == 0 || inner == 0) return B200_OK;
+  if (!x || !out) return B200_EINVAL;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (dti) {
+    case B200_F32: return softmax_T<float>(x, out, outer, dim, inner, dto, is_log, st);
+    case B200_BF16: return softmax_T<__nv_bfloat16>(x, out, outer, dim, inner, dto, is_log, st);
+    default: return softmax_T<__half>(x, out, outer, dim, inner, dto, is_log, st);
+  }
+}
+
+extern "C" int64_t b200_reduce_scratch_bytes(int64_t outer, int64_t dim, int64_t inner) {
+  if (outer <= 0 || dim <= 0 || inner <= 0) return 0;
+  const ReducePlan p = plan_reduce(outer, dim, inner);
+  return p.splits > 1 ? static_cast<int64_t>(p.splits) * outer * inner * 16 : 0;
+}
+
+extern "C" int b200_sum(const void* x, void* out, int64_t outer, int64_t dim, int64_t inner, int dti, int dto, void* scratch, int64_t scratch_bytes, void* stream) {
+  if (outer < 0 || dim < 0 || inner < 0) return B200_EINVAL;
+  if (!is_float_dtype(dti) || !is_float_dtype(dto)) return B200_EDTYPE;
+  if (outer == 0 || inner == 0) return B200_OK;
+  if (!out) return B200_EINVAL;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dim == 0) {  // empty reduction: the sum is 0
+    fill_zero_typed<<<grid_for(outer * inner, 256), 256, 0, st>>>(out, outer * inner, dto);
+    return check_launch();
+  }
+  if (!x) return B200_EINVAL;
+  switch (dti) {
+    case B200_F32: return launch_reduce_T<float, false>(x, out, outer, dim, inner, dto, scratch, scratch_bytes, st);
+    case B200_BF16: return launch_reduce_T<__nv_bfloat16, false>(x, out, outer, dim, inner, dto, scratch, scratch_bytes, st);
+    default: return launch_reduce_T<__half, false>(x, out, outer, dim, inner, dto, scratch, scratch_bytes, st);
+  }
+}
+
+extern "C" int b200_argmax(const void* x, int64_t* out, int64_t outer, int64_t dim, int64_t inner, int dt, void* scratch, int64_t scratch_bytes, void* stream) {
+  if (outer < 0 || dim <= 0 || inner < 0) return B200_EINVAL;
+  if (!is_float_dtype(dt)) return B200_EDTYPE;
+  if (outer == 0 || inner == 0) return B200_OK;
+  if (!x || !out) return B200_EINVAL;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (dt) {
+    case B200_F32: return launch_reduce_T<float, true>(x, out, outer, dim, inner, B200_I64, scratch, scratch_bytes, st);
+    case B200_BF16: return launch_reduce_T<__nv_bfloat16, true>(x, out, outer, dim, inner, B200_I64, scratch, scratch_bytes, st);
+    default: return launch_reduce_T<__half, true>(x, out, outer, dim, inner, B200_I64, scratch, scratch_bytes, st);
+  }
+}
+
+extern "C" int b200_layer_norm(const void* x, const void* w, const void* b, void* y, void* mean, void* rstd, int64_t rows, int64_t cols, double eps, int dt, int dt_wb, int dt_stat, void* stream) {
+  if (rows < 0 || cols < 0) return B200_EINVAL;
+  if (!is_float_dtype(dt) || !is_float_dtype(dt_stat) || ((w || b) && !is_float_dtype(dt_wb))) return B200_EDTYPE;
+  if (rows == 0) return B200_OK;
+  if (!mean || !rstd) return B200_EINVAL;
+  if (cols > 0 && (!x || !y)) return B200_EINVAL;
+  if (rows > 0x7fffffffLL) return B200_EINVAL;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const float e = static_cast<float>(eps);
+  const int ve = 16 / dtype_size(dt);
+  const bool wb_ok = (!w && !b) || dt_wb == dt || dt_wb == B200_F32;
+  const bool al = aligned16(x) && aligned16(y) && (!w || aligned16(w)) && (!b || aligned16(b));
+  ResidentCfg c{false, false, 1, 128};
+  if (cols > 0 && cols % ve == 0 && (dt_wb != B200_F32 || cols % 4 == 0) && al && wb_ok && cols < (1LL << 30)) c = resident_cfg(cols / ve, 32 / ve);
+  if (!c.ok) {
+    layernorm_stream<<<static_cast<unsigned>(rows), 256, 0, st>>>(x, w, b, y, mean, rstd, cols, e, dt, dt_wb, dt_stat);
+    return check_launch();
+  }
+  const bool wf32 = (w || b) && dt_wb == B200_F32;
+  switch (dt) {
+    case B200_F32: return layernorm_T<float, float>(x, w, b, y, mean, rstd, rows, cols, e, dt_stat, c, st);
+    case B200_BF16:
+      return wf32 ? layernorm_T<__nv_bfloat16, float>(x, w, b, y, mean, rstd, rows, cols, e, dt_stat, c, st)
+                  : layernorm_T<__nv_bfloat16, __nv_bfloat16>(x, w, b, y, mean, rstd, rows, cols, e, dt_stat, c, st);
+    default:
+      return wf32 ? layernorm_T<__half, float>(x, w, b, y, mean, rstd, rows, cols, e, dt_stat, c, st)
+                  : layernorm_T<__half, __half>(x, w, b, y, mean, rstd, rows, cols, e, dt_stat, c, st);
+  }
+}

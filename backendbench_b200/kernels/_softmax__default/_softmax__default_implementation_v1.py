@@ -1,0 +1,20 @@
+"""aten._softmax.default on B200: softmax along dim, fp32 internal math.
+
+Loaded by a BackendBench DirectoryBackend (BackendBench/backends/directory.py:47-100):
+the folder name is the overload with "." spelt "__", the exported callable is
+`<folder>_kernel_impl`. The arithmetic runs in libb200ops.so through the C-ABI; this
+file only forwards the aten arguments to the host wrapper.
+"""
+
+import os
+import sys
+
+try:
+    from backendbench_b200 import ops as _ops
+except ImportError:  # loaded by path from outside the repository root
+    sys.path.insert(0, os.path.abspath(os.path.join(os.path.dirname(__file__), "..", "..", "..")))
+    from backendbench_b200 import ops as _ops
+
+
+def _softmax__default_kernel_impl(*args, **kwargs):
+    return _ops._softmax_default(*args, **kwargs)
