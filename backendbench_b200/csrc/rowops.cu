@@ -179,7 +179,10 @@ layernorm_resident(const T* __restrict__ x, const TW* __restrict__ w, const TW* 
     }
   }
   s = group_reduce<WARP>(s, SumF{}, 0.f, red);
-  const float mu = s / static_cast<float>(cols);
+  float mu = s / static_cast<float>(cols);
+  // a row holding NaN or inf has NaN statistics in aten (its running moments turn inf
+  // into NaN once another element follows), not mean = inf
+  if (!isfinite(mu)) mu = CUDART_NAN_F;
   float q = 0.f;
 #pragma unroll
   for (int u = 0; u < VPT; ++u) {
@@ -225,7 +228,8 @@ __global__ void __launch_bounds__(256) layernorm_stream(const void* __restrict__
   float s = 0.f;
   for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) s += load_as_f32(x, base + c, dt);
   s = block_reduce(s, SumF{}, 0.f, red);
-  const float mu = s / static_cast<float>(cols);
+  float mu = s / static_cast<float>(cols);
+  if (!isfinite(mu)) mu = CUDART_NAN_F;  // same non-finite rule as the resident kernel
   float q = 0.f;
   for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) {
     const float d = load_as_f32(x, base + c, dt) - mu;

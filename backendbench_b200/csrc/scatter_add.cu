@@ -15,8 +15,9 @@
 //     the algorithmic minimum: self, index, src read once, out written once.
 //
 //   line kernel (everything else): one thread per "line" (all coordinates but `dim`
-//     fixed) applies its contributions sequentially to `out` in global memory, after
-//     a device-to-device copy of self into out.
+//     fixed) applies its contributions sequentially in global memory, after a copy of
+//     self. bf16/f16 tensors accumulate in an fp32 copy of self held in caller scratch
+//     and are rounded once at the end, as the aten CPU kernel does with its fp32 buffer.
 #include <cuda_pipeline.h>
 
 #include "b200_common.cuh"
@@ -137,7 +138,7 @@ struct ScatterArgs {
 };
 
 template <typename T>
-__global__ void __launch_bounds__(128) scatter_add_lines(T* __restrict__ out, const int64_t* __restrict__ index, const T* __restrict__ src, ScatterArgs A, uint32_t* status) {
+__global__ void __launch_bounds__(128) scatter_add_lines(float* __restrict__ out, const int64_t* __restrict__ index, const T* __restrict__ src, ScatterArgs A, uint32_t* status) {
   const int64_t line = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (line >= A.nlines) return;
   int64_t lin = line, oo = 0, io = 0, so = 0;
@@ -155,9 +156,7 @@ __global__ void __launch_bounds__(128) scatter_add_lines(T* __restrict__ out, co
       if (status) atomicOr(status, B200_DEV_INDEX_OOB);
       continue;
     }
-    T* d = out + oo + key * os;
-    // one rounding per addition, like `*self_data += *src_data` on the element type
-    *d = from_f32<T>(to_f32(*d) + to_f32(src[so + k * ss]));
+    out[oo + key * os] += to_f32(src[so + k * ss]);
   }
 }
 
@@ -166,7 +165,7 @@ __global__ void __launch_bounds__(128) scatter_add_lines(T* __restrict__ out, co
 using namespace b200;
 
 extern "C" int b200_scatter_add(const void* self, const void* index, const void* src, void* out, int ndim, const int64_t* self_shape, const int64_t* index_shape,
-                                const int64_t* index_strides, const int64_t* src_strides, int dim, int dtype, uint32_t* status, void* stream) {
+                                const int64_t* index_strides, const int64_t* src_strides, int dim, int dtype, void* scratch, int64_t scratch_bytes, uint32_t* status, void* stream) {
   if (ndim < 1 || ndim > B200_MAX_DIMS || dim < 0 || dim >= ndim || !self_shape || !index_shape || !index_strides || !src_strides) return B200_EINVAL;
   if (!is_float_dtype(dtype)) return B200_EDTYPE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -197,33 +196,48 @@ extern "C" int b200_scatter_add(const void* self, const void* index, const void*
     }
   }
 
-  // ---- generic: out = self, then ordered lines
-  if (out != self) {
-    const cudaError_t ce = cudaMemcpyAsync(out, self, static_cast<size_t>(n_self) * es, cudaMemcpyDeviceToDevice, st);
-    if (ce != cudaSuccess) { set_last_cuda_error(ce); return B200_ELAUNCH; }
+  // ---- generic: acc = fp32(self), ordered lines on acc, out = round(acc)
+  const bool wide = dtype == B200_F32;
+  float* acc = wide ? static_cast<float*>(out) : static_cast<float*>(scratch);
+  if (!wide && (!scratch || scratch_bytes < n_self * 4)) return B200_ESCRATCH;
+  if (wide) {
+    if (out != self) {
+      const cudaError_t ce = cudaMemcpyAsync(out, self, static_cast<size_t>(n_self) * es, cudaMemcpyDeviceToDevice, st);
+      if (ce != cudaSuccess) { set_last_cuda_error(ce); return B200_ELAUNCH; }
+    }
+  } else {
+    const int64_t one = 1;
+    if (int rc = b200_copy_strided(self, acc, 1, &n_self, &one, dtype, B200_F32, stream)) return rc;
   }
-  if (n_idx == 0) return B200_OK;
-  if (!index || !src) return B200_EINVAL;
-  ScatterArgs A;
-  A.ndim = ndim;
-  A.dim = dim;
-  A.dim_len = index_shape[dim];
-  A.self_dim_size = self_shape[dim];
-  A.nlines = 1;
-  int64_t st_out = 1;
-  for (int d = ndim - 1; d >= 0; --d) {
-    A.shape[d] = d == dim ? 1 : index_shape[d];
-    A.nlines *= A.shape[d];
-    A.out_stride[d] = st_out;
-    st_out *= self_shape[d];
-    A.idx_stride[d] = index_strides[d];
-    A.src_stride[d] = src_strides[d];
+  if (n_idx > 0) {
+    if (!index || !src) return B200_EINVAL;
+    ScatterArgs A;
+    A.ndim = ndim;
+    A.dim = dim;
+    A.dim_len = index_shape[dim];
+    A.self_dim_size = self_shape[dim];
+    A.nlines = 1;
+    int64_t st_out = 1;
+    for (int d = ndim - 1; d >= 0; --d) {
+      A.shape[d] = d == dim ? 1 : index_shape[d];
+      A.nlines *= A.shape[d];
+      A.out_stride[d] = st_out;
+      st_out *= self_shape[d];
+      A.idx_stride[d] = index_strides[d];
+      A.src_stride[d] = src_strides[d];
+    }
+    const int g = grid_for(A.nlines, 128);
+    const int64_t* pi = static_cast<const int64_t*>(index);
+    switch (dtype) {
+      case B200_F32: scatter_add_lines<float><<<g, 128, 0, st>>>(acc, pi, static_cast<const float*>(src), A, status); break;
+      case B200_BF16: scatter_add_lines<__nv_bfloat16><<<g, 128, 0, st>>>(acc, pi, static_cast<const __nv_bfloat16*>(src), A, status); break;
+      default: scatter_add_lines<__half><<<g, 128, 0, st>>>(acc, pi, static_cast<const __half*>(src), A, status); break;
+    }
+    if (int rc = check_launch()) return rc;
   }
-  const int g = grid_for(A.nlines, 128);
-  switch (dtype) {
-    case B200_F32: scatter_add_lines<float><<<g, 128, 0, st>>>(static_cast<float*>(out), static_cast<const int64_t*>(index), static_cast<const float*>(src), A, status); break;
-    case B200_BF16: scatter_add_lines<__nv_bfloat16><<<g, 128, 0, st>>>(static_cast<__nv_bfloat16*>(out), static_cast<const int64_t*>(index), static_cast<const __nv_bfloat16*>(src), A, status); break;
-    default: scatter_add_lines<__half><<<g, 128, 0, st>>>(static_cast<__half*>(out), static_cast<const int64_t*>(index), static_cast<const __half*>(src), A, status); break;
+  if (!wide) {
+    const int64_t one = 1;
+    return b200_copy_strided(acc, out, 1, &n_self, &one, B200_F32, dtype, stream);
   }
-  return check_launch();
+  return B200_OK;
 }

@@ -160,11 +160,14 @@ int b200_gather(const void* self, const void* index, void* out, int ndim,
 /* aten.scatter_add.default(self, dim, index, src): out = self, then for every p in
  * index's shape out[p with p[dim] := index[p]] += src[p], applied in ASCENDING p[dim]
  * for each destination element -- the order of the sequential aten CPU kernel, so fp
- * results are bit-identical to it. self/out contiguous; index/src strided. */
+ * results are bit-identical to it. self/out contiguous; index/src strided. bf16/f16
+ * tensors accumulate in fp32 and round once (as aten CPU does): `scratch` must then
+ * hold numel(self) * 4 bytes; fp32 tensors need none (NULL, 0). */
 int b200_scatter_add(const void* self, const void* index, const void* src, void* out, int ndim,
                      const int64_t* self_shape, const int64_t* index_shape,
                      const int64_t* index_strides, const int64_t* src_strides, int dim,
-                     int dtype, uint32_t* status, void* stream);
+                     int dtype, void* scratch, int64_t scratch_bytes, uint32_t* status,
+                     void* stream);
 
 /* ------------------------------------------------------------------ contraction
  * aten.mm.default, aten.addmm.default, aten.bmm.default (eval.py:100-102):

@@ -1,0 +1,76 @@
+import json
+import os
+import sys
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+GOLDEN = os.path.join(ROOT, "tests", "golden")
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (B200); run with -m gpu")
+
+
+@pytest.fixture(scope="session")
+def golden_cases():
+    return torch.load(os.path.join(GOLDEN, "aten_ops_golden.pt"), weights_only=False)["cases"]
+
+
+@pytest.fixture(scope="session")
+def harness_golden():
+    with open(os.path.join(GOLDEN, "harness_golden.json")) as fh:
+        return json.load(fh)
+
+
+@pytest.fixture(scope="session", autouse=True)
+def _built():
+    """The shared library and the oracle are built once per session (seconds, CPU only)."""
+    from backendbench_b200.build import build
+
+    build()
+    import oracle
+
+    oracle.build()
+
+
+EXACT_OPS = ("embedding.default", "index_select.default", "gather.default", "scatter_add.default", "argmax.default", "where.self")
+
+
+def tolerance_for_case(op: str, dtype) -> tuple:
+    """(atol, rtol) the parity tests use: 0 for the bit-exact operators, the harness's
+    1e-2 for bf16/f16 results, 1e-5 for fp32 elementwise, 1e-4 for fp32 reductions,
+    normalisations and contractions (accumulation order differs)."""
+    if op in EXACT_OPS:
+        return 0.0, 0.0
+    if dtype in (torch.bfloat16, torch.float16):
+        return 1e-2, 1e-2
+    if op.split(".")[0] in ("relu", "add", "mul"):
+        return 1e-5, 1e-5
+    return 1e-4, 1e-4
+
+
+def first_dtype(x):
+    if isinstance(x, torch.Tensor):
+        return x.dtype
+    for y in x:
+        d = first_dtype(y)
+        if d is not None:
+            return d
+    return None
+
+
+def bits_equal(a: torch.Tensor, b: torch.Tensor) -> bool:
+    """Same shape, dtype and bit pattern (NaN payloads and signed zeros included)."""
+    if a.shape != b.shape or a.dtype != b.dtype:
+        return False
+    if a.numel() == 0:
+        return True
+    a = a.detach().cpu().contiguous().reshape(-1)
+    b = b.detach().cpu().contiguous().reshape(-1)
+    if a.dtype == torch.bool:
+        return torch.equal(a, b)
+    return torch.equal(a.view(torch.uint8), b.view(torch.uint8))
