@@ -42,6 +42,7 @@ SIGNATURES = {
     "b200_abi_version": (c_int, []),
     "b200_strerror": (c_char_p, [c_int]),
     "b200_last_cuda_error": (c_char_p, []),
+    "b200_launch_count": (ctypes.c_longlong, []),
     "b200_relu": (c_int, [c_void_p, c_void_p, c_int, I64P, I64P, c_int, c_void_p]),
     "b200_add": (c_int, [c_void_p, c_void_p, c_void_p, c_int, I64P, I64P, I64P, c_int, c_int, c_int, c_double, c_void_p]),
     "b200_mul": (c_int, [c_void_p, c_void_p, c_void_p, c_int, I64P, I64P, I64P, c_int, c_int, c_int, c_void_p]),

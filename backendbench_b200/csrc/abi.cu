@@ -1,7 +1,11 @@
 // Library-level entry points: version, error strings, last CUDA error.
 #include "b200_common.cuh"
 
+#include <atomic>
+
 namespace b200 {
+static std::atomic<long long> g_launches{0};
+void note_launches(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 static thread_local cudaError_t g_last_cuda_error = cudaSuccess;
 const char* set_last_cuda_error(cudaError_t e) {
   g_last_cuda_error = e;
@@ -25,3 +29,5 @@ extern "C" const char* b200_strerror(int code) {
 }
 
 extern "C" const char* b200_last_cuda_error(void) { return cudaGetErrorString(b200::g_last_cuda_error); }
+
+extern "C" long long b200_launch_count(void) { return b200::g_launches.load(std::memory_order_relaxed); }

@@ -14,7 +14,9 @@ constexpr int kNumSMs = 148;  // B200: 2 dies x 74 SMs
 
 // ---------------------------------------------------------------- error plumbing
 const char* set_last_cuda_error(cudaError_t e);
-inline int check_launch() {
+void note_launches(int n);  // feeds b200_launch_count()
+inline int check_launch(int launches = 1) {
+  note_launches(launches);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_last_cuda_error(e);

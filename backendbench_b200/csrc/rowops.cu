@@ -487,7 +487,7 @@ static int launch_reduce_T(const void* x, void* out, int64_t outer, int64_t dim,
     reduce_cols<T, ARG><<<g, 256, 0, st>>>(px, out, pv, pi, outer, dim, inner, p.chunk, dto);
   }
   if (p.splits > 1) reduce_finalize<ARG><<<grid_for(nout, 256), 256, 0, st>>>(pv, pi, out, nout, p.splits, dto);
-  return check_launch();
+  return check_launch(p.splits > 1 ? 2 : 1);
 }
 
 // Resident-kernel geometry for `nvec` 16-byte vectors per row.

@@ -107,13 +107,13 @@ def _record(device) -> torch.Tensor:
 class _Compare:
     """Accumulates the verdict over every tensor pair of one (reference, result) structure."""
 
-    def __init__(self, atol, rtol):
+    def __init__(self, atol, rtol, rec=None):
         self.atol, self.rtol = atol, rtol
         self.ok = True
         self.max_abs = None
         self.max_rel = None
         self.nan = False
-        self.rec = None
+        self.rec = rec  # caller-owned 8 x int32 device record, or None for the shared one
         self.rec_used = False
         self.saw_tensor_ref = self.saw_tensor_res = False
 
@@ -206,6 +206,23 @@ def compare(ref, res, atol=HARNESS_ATOL, rtol=HARNESS_RTOL):
     c = _Compare(atol, rtol)
     c.walk(ref, res)
     return c.finish()
+
+
+def compare_enqueue(ref, res, atol, rtol, rec: torch.Tensor) -> bool:
+    """Queue the comparison of CUDA structures into the caller's 8 x int32 device record
+    without reading anything back (many cases, one read at the end: `decode_record`).
+    Returns False when the structures already differ in shape / dtype / length."""
+    c = _Compare(atol, rtol, rec)
+    c.walk(ref, res)
+    if not c.rec_used:  # nothing was queued (empty tensors): leave a clean record behind
+        rec.zero_()
+    return c.ok
+
+
+def decode_record(words) -> Tuple[int, float, float, bool]:
+    """(mismatches, max_abs, max_rel, nan_seen) from the 8 int32 words of one record."""
+    mism, mabs, mrel, nan_seen = struct.unpack("<QffI", struct.pack("8i", *words)[:20])
+    return mism, mabs, mrel, bool(nan_seen)
 
 
 def allclose(a, b, atol=HARNESS_ATOL, rtol=HARNESS_RTOL) -> bool:

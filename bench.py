@@ -1,0 +1,404 @@
+"""Benchmark of the B200 operator backend on the 512-case sharded sweep.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+One STEP is one correctness pass of the sweep on each rank: for each of the 512 seeded
+(op, shape, dtype) cases the backend kernel is launched on inputs resident in HBM and its
+result is checked on the device against the resident aten reference result by the fused
+allclose kernel; the 512 verdict records are read back once at the end of the step.
+Ranks share nothing (weak scaling: every rank owns a full sweep with its own seeds), so
+the only communication is the barrier around the timed region and the max over ranks of
+the device time. `value` = cases all ranks processed / that time.
+
+The JSON line also carries: `e2e` (the same pass through the public plugin call with the
+inputs in pinned HOST memory, H2D copies and the verdict read-back inside the timed
+region), `roofline` (the kernel with the largest share of device time in the sweep),
+`per_op` (every named operator configuration: GB/s or TFLOP/s against the measured and
+nominal peaks, and the speed-up over aten CUDA), `cpu_baseline` (the reference's aten-CPU
+path on a bounded sample, host cores), `clocks` and `gpu_launches`.
+
+`--impl reference` times the reference's own CPU path (AtenBackend + the reference's
+correctness evaluation, restated in oracle/aten_cpu_path.py) on a bounded sample.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+N_CASES = 512
+SWEEP_SEED = 0
+NOMINAL_HBM_GBS = 8000.0
+NOMINAL_BF16_TFLOPS = 2250.0
+FALLBACK_HBM_GBS = 6650.0
+FALLBACK_BF16_TFLOPS = 1590.0
+EXACT_VS_CPU = ("scatter_add.default",)  # aten CUDA scatter_add is order-nondeterministic: its reference comes from aten CPU
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as fh:
+            p = json.load(fh)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]), "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), "source": "measured"}
+    except Exception:
+        return {"hbm_gbs": FALLBACK_HBM_GBS, "bf16_tflops": FALLBACK_BF16_TFLOPS, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200", "-i", str(self.gpu_index)],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def _dist_env():
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, local, world
+
+
+def _bytes_of(args):
+    return sum(a.numel() * a.element_size() for a in args if isinstance(a, torch.Tensor))
+
+
+# ------------------------------------------------------------------------- b200 arm
+def prepare_cases(cases, backend, device):
+    """Inputs generated on the device from each case's seed, aten reference results resident."""
+    from backendbench_b200.eval import tolerances_for
+    from backendbench_b200.opregistry import get_operator
+
+    prepared = []
+    for c in cases:
+        op = get_operator(c.op)
+        args, kwargs = c.build(device)
+        if c.op in EXACT_VS_CPU:
+            cpu_args = [a.cpu() if isinstance(a, torch.Tensor) else a for a in args]
+            ref = op(*cpu_args, **kwargs).to(device)
+            atol = rtol = 0.0
+        else:
+            ref = op(*args, **kwargs)
+            first = ref[0] if isinstance(ref, (tuple, list)) else ref
+            atol, rtol = tolerances_for(op, first.dtype)
+            if c.op in ("embedding.default", "index_select.default", "gather.default", "where.self", "argmax.default"):
+                atol = rtol = 0.0
+        prepared.append({"case": c, "op": op, "impl": backend[op], "args": args, "kwargs": kwargs, "ref": ref, "atol": atol, "rtol": rtol})
+    torch.cuda.synchronize()
+    return prepared
+
+
+def sweep_pass(prepared, records, host_inputs=None, device=None):
+    """One correctness pass; returns the (n, 8) int32 verdict records on the host."""
+    from backendbench_b200.eval import compare_enqueue
+
+    structural = []
+    for i, p in enumerate(prepared):
+        if host_inputs is not None:
+            args = [a.to(device, non_blocking=True) if isinstance(a, torch.Tensor) else a for a in host_inputs[i]]
+        else:
+            args = p["args"]
+        res = p["impl"](*args, **p["kwargs"])
+        structural.append(compare_enqueue(p["ref"], res, p["atol"], p["rtol"], records[i]))
+    host = records.cpu()  # the step's single device->host read
+    return host, structural
+
+
+def count_correct(host_records, structural):
+    from backendbench_b200.eval import decode_record
+
+    ok, bad = 0, []
+    rows = host_records.tolist()
+    for i, (row, s) in enumerate(zip(rows, structural)):
+        mism = decode_record(row)[0]
+        if s and mism == 0:
+            ok += 1
+        else:
+            bad.append(i)
+    return ok, bad
+
+
+def time_steps(fn, steps, warmup):
+    """`warmup` untimed calls, then `steps` calls between a barrier + synchronize on both
+    sides, timed on the device with CUDA events on the current stream; max over ranks."""
+    from backendbench_b200.sharding import barrier, max_over_ranks
+
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    barrier()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    last = None
+    for _ in range(steps):
+        last = fn()
+    end.record()
+    torch.cuda.synchronize()
+    barrier()
+    torch.cuda.synchronize()
+    return max_over_ranks(start.elapsed_time(end)), last
+
+
+def per_kernel_profile(prepared):
+    """Device time of every case's backend launch (CUDA events, L2 flushed before each)
+    aggregated per operator: the share table and the dominant kernel's roofline input."""
+    from backendbench_b200.eval import l2_flush
+
+    by_op = {}
+    n = len(prepared)
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(n)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(n)]
+    for i, p in enumerate(prepared):
+        l2_flush()
+        starts[i].record()
+        p["impl"](*p["args"], **p["kwargs"])
+        ends[i].record()
+    torch.cuda.synchronize()
+    for i, p in enumerate(prepared):
+        c = p["case"]
+        d = by_op.setdefault(c.op, {"ms": 0.0, "bytes": 0, "flops": 0, "launches": 0})
+        d["ms"] += starts[i].elapsed_time(ends[i])
+        d["bytes"] += c.algorithmic_bytes()
+        d["flops"] += c.flops()
+        d["launches"] += 1
+    return by_op
+
+
+def named_config_table(backend, device, peaks, reps):
+    """Throughput of every named operator configuration, next to aten CUDA on the same tensors."""
+    from backendbench_b200.cases import named_cases
+    from backendbench_b200.eval import cuda_bench
+    from backendbench_b200.opregistry import get_operator
+
+    rows = []
+    for c in named_cases():
+        op = get_operator(c.op)
+        impl = backend[op]
+        args, kwargs = c.build(device)
+        try:
+            ms = cuda_bench(lambda: impl(*args, **kwargs), warmup=3, reps=reps)
+            aten_ms = cuda_bench(lambda: op(*args, **kwargs), warmup=3, reps=reps)
+        except Exception as e:  # a failing configuration must not hide the others
+            rows.append({"name": c.name, "error": repr(e)[:200]})
+            continue
+        tensor_bound = c.op in ("mm.default", "addmm.default")
+        row = {"name": c.name, "ms": round(ms, 5), "aten_cuda_ms": round(aten_ms, 5), "speedup_vs_aten_cuda": round(aten_ms / ms, 4), "bound": "tensor" if tensor_bound else "hbm"}
+        gbs = c.algorithmic_bytes() / (ms * 1e-3) / 1e9
+        row["gbs"] = round(gbs, 1)
+        if c.flops():
+            row["tflops"] = round(c.flops() / (ms * 1e-3) / 1e12, 2)
+        if tensor_bound:
+            row["frac_measured"] = round(row["tflops"] / peaks["bf16_tflops"], 4)
+            row["frac_nominal"] = round(row["tflops"] / NOMINAL_BF16_TFLOPS, 4)
+        else:
+            row["frac_measured"] = round(gbs / peaks["hbm_gbs"], 4)
+            row["frac_nominal"] = round(gbs / NOMINAL_HBM_GBS, 4)
+        rows.append(row)
+        del args
+    torch.cuda.empty_cache()
+    return rows
+
+
+def cpu_reference_sample(cases, budget_s):
+    """The reference's aten-CPU path over a bounded sample of the sweep (every 8th case, in
+    order, until `budget_s` of CPU time is spent). Returns (cases done, seconds, description)."""
+    from backendbench_b200.opregistry import get_operator
+    from oracle.aten_cpu_path import eval_case_cpu, host_threads
+
+    sample = cases[::8]
+    built = []
+    for c in sample:
+        if c.flops() > 4e10 or c.algorithmic_bytes() > (1 << 28):
+            continue  # bounded: skip the few cases that alone would take the CPU many seconds
+        built.append((get_operator(c.op), *c.build("cpu")))
+    done, t0 = 0, time.perf_counter()
+    for op, args, kwargs in built:
+        eval_case_cpu(op, args, kwargs)
+        done += 1
+        if time.perf_counter() - t0 > budget_s:
+            break
+    secs = time.perf_counter() - t0
+    desc = f"every 8th sweep case in order, skipping cases above 4e10 FLOP or 256 MiB ({done} of {len(built)} eligible run within {budget_s:.0f} s), aten CPU, {host_threads()} threads"
+    return done, secs, desc, host_threads()
+
+
+def run_b200(args):
+    from backendbench_b200 import _abi
+    from backendbench_b200.backends import B200Backend
+    from backendbench_b200.cases import sweep_cases
+    from backendbench_b200.ops import check_device_status
+    from backendbench_b200.sharding import shard_for_rank, sum_over_ranks
+
+    rank, local, world = _dist_env()
+    if world > 1:
+        torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local))
+    torch.cuda.set_device(local)
+    device = f"cuda:{local}"
+    peaks = measured_peaks()
+    backend = B200Backend()
+    _abi.lib()  # fail loudly here if the CUDA library is missing
+
+    cases = sweep_cases(N_CASES, SWEEP_SEED)
+    mine = shard_for_rank(cases, rank, world, "weak")
+    prepared = prepare_cases(mine, backend, device)
+    records = torch.zeros(len(prepared), 8, dtype=torch.int32, device=device)
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    total_ms, last = time_steps(lambda: sweep_pass(prepared, records), args.steps, args.warmup)
+    clocks = sampler.stop() if sampler else None
+    launches0 = _abi.lib().b200_launch_count()  # one more (untimed) pass, only to count its launches
+    sweep_pass(prepared, records)
+    launches = (_abi.lib().b200_launch_count() - launches0) * args.steps
+    check_device_status(torch.device(device))
+    n_ok, bad = count_correct(*last)
+    units = sum_over_ranks(float(len(prepared) * args.steps))
+    value = units / (total_ms * 1e-3)
+
+    # ---- end to end: pinned host inputs, H2D inside the timed region
+    host_inputs = [[a.cpu().pin_memory() if isinstance(a, torch.Tensor) else a for a in p["args"]] for p in prepared]
+    h2d = sum(_bytes_of(h) for h in host_inputs)
+    e2e_steps = max(1, min(args.steps, 3))
+    e2e_ms, _ = time_steps(lambda: sweep_pass(prepared, records, host_inputs, device), e2e_steps, 1)
+    e2e_units = sum_over_ranks(float(len(prepared) * e2e_steps))
+    e2e = {"value": round(e2e_units / (e2e_ms * 1e-3), 2), "unit": "cases/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(records.numel() * 4), "steps": e2e_steps}
+    del host_inputs
+
+    line = {
+        "metric": "sweep_cases_per_sec", "value": round(value, 2), "unit": "cases/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(total_ms / args.steps, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32/bf16/f16 (fp32 accumulate)",
+        "data": "synthetic", "impl": "b200",
+        "config": {"workload": "sharded sweep: 512 seeded (op, shape, dtype) cases over 16 aten overloads, 2^8..2^26 elements, 15% edge cases; one correctness pass per step",
+                   "cases_per_rank": len(prepared), "inputs": "resident in HBM, larger than L2 in total (about 10 GB per rank)", "reference_results": "aten CUDA (aten CPU for scatter_add), precomputed, resident",
+                   "parallelism": f"{world} independent rank(s), no collective"},
+        "sweep_correct": f"{n_ok}/{len(prepared)}", "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+    }
+    if bad:
+        line["sweep_failed_cases"] = [prepared[i]["case"].label() for i in bad[:12]]
+
+    if rank == 0:
+        by_op = per_kernel_profile(prepared)
+        total = sum(d["ms"] for d in by_op.values()) or 1.0
+        shares = {op: round(d["ms"] / total, 4) for op, d in sorted(by_op.items(), key=lambda kv: -kv[1]["ms"])}
+        top_op, top = max(by_op.items(), key=lambda kv: kv[1]["ms"])
+        if top["flops"] and top_op in ("mm.default", "addmm.default", "bmm.default"):
+            ach = top["flops"] / (top["ms"] * 1e-3) / 1e12
+            roof = {"bound": "tensor", "achieved": round(ach, 2), "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": round(ach / peaks["bf16_tflops"], 4)}
+        else:
+            ach = top["bytes"] / (top["ms"] * 1e-3) / 1e9
+            roof = {"bound": "hbm", "achieved": round(ach, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(ach / peaks["hbm_gbs"], 4)}
+        roof.update({"kernel": top_op, "launches": top["launches"], "avg_launch_ms": round(top["ms"] / top["launches"], 4), "peak_source": peaks["source"], "traffic": None})
+        line["roofline"] = roof
+        line["sweep_time_share_by_op"] = shares
+        line["per_op"] = named_config_table(backend, device, peaks, reps=15)
+        if world == 1:
+            done, secs, desc, cores = cpu_reference_sample(cases, budget_s=20.0)
+            line["cpu_baseline"] = {"value": round(done / secs, 2), "unit": "cases/s", "cores": cores, "kind": "port", "sample": desc}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        torch.distributed.barrier()
+        torch.distributed.destroy_process_group()
+
+
+# ------------------------------------------------------------------------- reference arm
+def run_reference(args):
+    rank, _, world = _dist_env()
+    if rank != 0:
+        return  # the CPU arm runs once per job
+    from backendbench_b200.cases import sweep_cases
+
+    cases = sweep_cases(N_CASES, SWEEP_SEED)
+    per_step_budget = max(5.0, min(30.0, 150.0 / max(args.steps + args.warmup, 1)))
+    for _ in range(args.warmup):
+        cpu_reference_sample(cases, per_step_budget)
+    done_total, t_total, desc, cores = 0, 0.0, "", 0
+    for _ in range(args.steps):
+        done, secs, desc, cores = cpu_reference_sample(cases, per_step_budget)
+        done_total += done
+        t_total += secs
+    value = done_total / t_total
+    line = {
+        "metric": "sweep_cases_per_sec", "value": round(value, 2), "unit": "cases/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(t_total / args.steps * 1e3, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32/bf16/f16", "data": "synthetic", "impl": "reference",
+        "config": {"workload": "sharded sweep: 512 seeded (op, shape, dtype) cases; bounded CPU sample per step", "parallelism": "host cores, one process"},
+        "cpu_baseline": {"value": round(value, 2), "unit": "cases/s", "cores": cores, "kind": "port", "sample": desc},
+        "e2e": {"value": round(value, 2), "unit": "cases/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py --impl b200 needs a CUDA device; there is no CPU fallback")
+    run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -65,6 +65,9 @@ int b200_abi_version(void);
 const char* b200_strerror(int code);
 /* cudaGetErrorString of the last failing launch seen by this library on this thread. */
 const char* b200_last_cuda_error(void);
+/* Kernels (and device-to-device copies) this library has enqueued since it was loaded;
+ * the benchmark reports the difference across its timed region. */
+long long b200_launch_count(void);
 
 /* ----------------------------------------------------------------- elementwise
  * Operands are described TensorIterator-style: one broadcast `shape[ndim]` and one

@@ -1,0 +1,280 @@
+"""Parity of the CUDA kernels (through the C-ABI-backed operators) with the golden vectors
+made by the reference harness over aten CPU, with the CPU oracle on seeded sweep cases,
+and -- at the full named sizes -- through aten on the same device tensors plus
+size-independent properties. Bit-exact for integer / indexing results and scatter_add;
+floating point within the tolerance written in `conftest.tolerance_for_case`."""
+
+import math
+
+import pytest
+import torch
+
+import oracle
+from backendbench_b200 import _abi, ops
+from backendbench_b200.backends import B200Backend
+from backendbench_b200.cases import named_case, named_cases, scaled_down, sweep_cases
+from backendbench_b200.eval import compare
+from backendbench_b200.opregistry import get_operator
+from conftest import EXACT_OPS, bits_equal, first_dtype, tolerance_for_case
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.fixture(scope="module")
+def backend():
+    assert torch.cuda.is_available()
+    assert _abi.lib().b200_abi_version() == 1  # the native library is the thing under test
+    return B200Backend()
+
+
+def _to_dev(x):
+    if isinstance(x, torch.Tensor):
+        return x.to(DEV)
+    if isinstance(x, (list, tuple)):
+        return type(x)(_to_dev(y) for y in x)
+    return x
+
+
+def _tup(x):
+    return tuple(x) if isinstance(x, (tuple, list)) else (x,)
+
+
+def _check(op_name, ref, got, tag):
+    """`ref` on CPU (golden / oracle), `got` from the GPU."""
+    ref, got = _tup(ref), tuple(g.cpu() for g in _tup(got))
+    assert len(ref) == len(got), tag
+    atol, rtol = tolerance_for_case(op_name, first_dtype(ref))
+    for i, (r, g) in enumerate(zip(ref, got)):
+        if op_name == "native_layer_norm.default" and i > 0:
+            r, g = r.float(), g.float()  # statistics: CPU keeps the input dtype, CUDA fp32
+            if r.dtype != torch.float32 or atol < 1e-2:
+                pass
+            a, rt = (1e-2, 1e-2) if first_dtype(ref) != torch.float32 else (atol, rtol)
+            ok, ea, er = compare(r, g, a, rt)
+            assert ok, (tag, "stat", i, ea, er)
+            continue
+        assert r.shape == g.shape and r.dtype == g.dtype, (tag, r.shape, g.shape, r.dtype, g.dtype)
+        if op_name in EXACT_OPS:
+            assert bits_equal(r, g), (tag, "bits differ")
+        else:
+            ok, ea, er = compare(r, g, atol, rtol)
+            assert ok, (tag, ea, er)
+
+
+def test_gpu_matches_golden_vectors(backend, golden_cases):
+    for c in golden_cases:
+        impl = backend[get_operator(c["op"])]
+        got = impl(*_to_dev(c["args"]), **_to_dev(c["kwargs"]))
+        ops.check_device_status()
+        _check(c["op"], c["ref"], got, c["tag"])
+
+
+def test_gpu_matches_oracle_on_seeded_sweep_cases(backend):
+    """Every sweep case small enough for the single-threaded oracle (edge cases included:
+    zero-size dims, broadcast dims, transposed strides, NaN/Inf injection)."""
+    cases = [c for c in sweep_cases(512, seed=0) if c.algorithmic_bytes() < 6e6 and c.flops() < 6e8]
+    assert len(cases) > 250 and {c.edge for c in cases} >= {"", "zero", "bcast", "transposed", "naninf"}
+    for c in cases:
+        args, kwargs = c.build(DEV, gen_device="cpu")
+        got = backend[get_operator(c.op)](*args, **kwargs)
+        want = oracle.run(c.op, args, kwargs)
+        _check(c.op, want, got, c.label())
+    ops.check_device_status()
+
+
+def test_gpu_matches_oracle_second_seed_and_other_paths(backend):
+    cases = [c for c in sweep_cases(384, seed=1) if c.algorithmic_bytes() < 3e6 and c.flops() < 3e8]
+    for c in cases:
+        args, kwargs = c.build(DEV, gen_device="cpu")
+        got = backend[get_operator(c.op)](*args, **kwargs)
+        _check(c.op, oracle.run(c.op, args, kwargs), got, c.label())
+    ops.check_device_status()
+
+
+@pytest.mark.parametrize("name", [c.name for c in named_cases()])
+def test_named_configs_scaled_to_oracle_size(backend, name):
+    c = scaled_down(named_case(name), 16)
+    args, kwargs = c.build(DEV, gen_device="cpu")
+    got = backend[get_operator(c.op)](*args, **kwargs)
+    ops.check_device_status()
+    _check(c.op, oracle.run(c.op, args, kwargs), got, c.label())
+
+
+# ------------------------------------------------------------------ full named sizes
+def _full(name, backend):
+    c = named_case(name)
+    args, kwargs = c.build(DEV)
+    op = get_operator(c.op)
+    return c, op, backend[op], args, kwargs
+
+
+@pytest.mark.parametrize("name", ["relu_f32_4096x4096", "add_f32_4096x4096", "mul_f32_4096x4096", "where_f32_4096x4096"])
+def test_full_size_elementwise_bit_exact_vs_aten(backend, name):
+    c, op, impl, args, kwargs = _full(name, backend)
+    got, ref = impl(*args, **kwargs), op(*args, **kwargs)
+    assert bits_equal(ref, got)  # one fp32 operation per element: no rounding freedom
+    if name.startswith("relu"):
+        assert bits_equal(impl(got), got) and float(got.min()) >= 0  # idempotent, non-negative
+    if name.startswith("where"):
+        cond, x, y = args
+        other = impl(~cond, x, y)
+        assert bits_equal(torch.where(cond, got, other), x) and bits_equal(torch.where(cond, other, got), y)
+
+
+@pytest.mark.parametrize("tag", ["bf16_8192x4096", "f32_65536x1024"])
+def test_full_size_softmax_family(backend, tag):
+    c, op, impl, args, kwargs = _full(f"softmax_{tag}", backend)
+    got, ref = impl(*args, **kwargs), op(*args, **kwargs)
+    atol, rtol = tolerance_for_case(c.op, got.dtype)
+    assert compare(ref, got, atol, rtol)[0]
+    rows = got.float().sum(-1)
+    assert torch.allclose(rows, torch.ones_like(rows), atol=2e-2 if got.dtype != torch.float32 else 1e-5)
+    assert float(got.min()) >= 0
+    c, op, impl, args, kwargs = _full(f"log_softmax_{tag}", backend)
+    lg, lref = impl(*args, **kwargs), op(*args, **kwargs)
+    assert compare(lref, lg, atol, rtol)[0]
+    assert compare(got.float(), lg.float().exp(), 2e-2 if got.dtype != torch.float32 else 1e-5, 1e-2)[0]  # exp(log_softmax) == softmax
+    # shift invariance: softmax(x + c) == softmax(x) for exactly representable shifts
+    x = args[0]
+    shifted = impl((x.float() + 8.0).to(x.dtype), -1, False)
+    assert compare(got, shifted, 2e-2 if got.dtype != torch.float32 else 1e-5, 1e-2)[0]
+
+
+@pytest.mark.parametrize("tag", ["bf16_8192x4096", "f32_65536x1024"])
+def test_full_size_sum_and_layer_norm(backend, tag):
+    c, op, impl, args, kwargs = _full(f"sum_{tag}", backend)
+    got, ref = impl(*args, **kwargs), op(*args, **kwargs)
+    atol, rtol = tolerance_for_case(c.op, got.dtype)
+    assert compare(ref, got, max(atol, 1e-3), rtol)[0]
+    # against fp64 on the device, and linearity sum(2x) == 2 sum(x) (exact: scaling by 2 commutes with rounding)
+    exact = args[0].double().sum(-1)
+    assert compare(exact.to(got.dtype), got, 2.5e-1 if got.dtype != torch.float32 else 1e-3, rtol)[0]
+    assert bits_equal(impl((args[0] * 2), [-1]), got * 2)
+    c, op, impl, args, kwargs = _full(f"layer_norm_{tag}", backend)
+    (y, mean, rstd), (ry, rmean, rrstd) = impl(*args, **kwargs), op(*args, **kwargs)
+    assert mean.dtype == rmean.dtype and mean.shape == rmean.shape  # aten CUDA's statistics dtype and shape
+    assert compare(ry, y, *tolerance_for_case(c.op, y.dtype))[0]
+    assert compare(rmean, mean, 1e-4, 1e-4)[0] and compare(rrstd, rstd, 1e-4, 1e-4)[0]
+    x = args[0].float()
+    assert compare(x.mean(-1, keepdim=True), mean, 1e-4, 1e-4)[0]
+    # with unit weight and zero bias every row has mean 0 and variance 1
+    y1, _, _ = impl(args[0], args[1], None, None, 1e-5)
+    yf = y1.float()
+    tol = 2e-2 if y1.dtype != torch.float32 else 1e-4
+    assert float(yf.mean(-1).abs().max()) < tol and float((yf.var(-1, unbiased=False) - 1).abs().max()) < 5 * tol
+
+
+def test_full_size_embedding_and_index_select_bit_exact(backend):
+    c, op, impl, args, kwargs = _full("embedding_bf16_128256x4096_16384", backend)
+    got = impl(*args, **kwargs)
+    assert bits_equal(op(*args, **kwargs), got)
+    table, idx = args
+    # the oracle on the same bits (CPU copy), on a slice of the lookups
+    assert bits_equal(oracle.embedding(table.cpu(), idx[:512].cpu()), got[:512])
+    # round trip: looking up a permutation and then its inverse restores the rows
+    perm = torch.randperm(4096, device=DEV)
+    inv = torch.empty_like(perm)
+    inv[perm] = torch.arange(4096, device=DEV)
+    sub = table[:4096]
+    assert bits_equal(impl(impl(sub, perm), inv), sub)
+    c, op, impl, args, kwargs = _full("index_select_bf16_128256x4096_16384", backend)
+    assert bits_equal(op(*args, **kwargs), impl(*args, **kwargs))
+    ops.check_device_status()
+
+
+def test_full_size_gather_bit_exact(backend):
+    c, op, impl, args, kwargs = _full("gather_f32_4096x4096", backend)
+    got = impl(*args, **kwargs)
+    assert bits_equal(op(*args, **kwargs), got)
+    x, dim, idx = args
+    assert bits_equal(oracle.gather(x.cpu(), 0, idx[:64].cpu()), got[:64])
+    ident = torch.arange(4096, device=DEV).unsqueeze(1).expand(4096, 4096).contiguous()
+    assert bits_equal(impl(x, 0, ident), x)  # identity index: gather is the identity
+    assert bits_equal(op(x, 1, idx), impl(x, 1, idx))  # the other dimension
+    ops.check_device_status()
+
+
+def test_full_size_scatter_add_bit_exact_vs_aten_cpu_order(backend):
+    c, op, impl, args, kwargs = _full("scatter_add_f32_4096x4096", backend)
+    x, dim, idx, src = args
+    got = impl(x, dim, idx, src)
+    want = oracle.scatter_add(x.cpu(), 0, idx.cpu(), src.cpu())  # sequential CPU order, a second or so in C
+    assert bits_equal(want, got)
+    # identity rows: every destination gets exactly one contribution -> self + src, exactly
+    ident = torch.arange(4096, device=DEV).unsqueeze(1).expand(4096, 4096).contiguous()
+    assert bits_equal(impl(x, 0, ident, src), x + src)
+    # all rows onto row 0: a 4096-term ordered sum per column
+    zeros = torch.zeros(4096, 4096, dtype=torch.int64, device=DEV)
+    got0 = impl(x, 0, zeros, src)
+    want0 = oracle.scatter_add(x.cpu(), 0, zeros.cpu(), src.cpu())
+    assert bits_equal(want0, got0)
+    # dim 1 goes through the generic ordered path
+    got1 = impl(x[:512], 1, idx[:512], src[:512])
+    assert bits_equal(oracle.scatter_add(x[:512].cpu(), 1, idx[:512].cpu(), src[:512].cpu()), got1)
+    ops.check_device_status()
+
+
+def test_full_size_argmax_bit_exact(backend):
+    c, op, impl, args, kwargs = _full("argmax_f32_8192x32000", backend)
+    got = impl(*args, **kwargs)
+    assert got.dtype == torch.int64 and bits_equal(op(*args, **kwargs), got)
+    x = args[0]
+    assert bits_equal(x.gather(1, got.unsqueeze(1)).squeeze(1), x.max(-1).values)  # the value there is the row maximum
+    x2 = x[:64].clone()
+    x2[:, 1000] = float("nan")
+    x2[:, 2000] = float("nan")
+    assert bool((impl(x2, -1) == 1000).all())  # NaN counts as the maximum, the first one wins
+    x3 = x[:64].clone()
+    x3[:, 777] = 100.0
+    x3[:, 31999] = 100.0
+    assert bool((impl(x3, -1) == 777).all())  # ties -> first index
+    assert int(impl(x)) == int(op(x))  # flattened (split across CTAs, finished from scratch memory)
+
+
+def _gemm_rows_fp64(a, b, rows):
+    return a[rows].double().cpu() @ b.double().cpu()
+
+
+def test_full_size_mm_addmm_bmm(backend):
+    c, op, impl, args, kwargs = _full("mm_bf16_8192x4096x11008", backend)
+    a, b = args
+    got, ref = impl(a, b), op(a, b)
+    assert compare(ref, got, 1e-2, 1e-2)[0]
+    rows = torch.tensor([0, 1, 127, 128, 4095, 8191], device=DEV)
+    exact = _gemm_rows_fp64(a, b, rows)
+    assert compare(exact.to(torch.bfloat16), got[rows].cpu(), 4e-3, 1e-2)[0]  # |C| ~ 1/64: bf16 rounding + fp32 accumulation
+    # linearity in the first operand, scaling by a power of two is exact
+    assert bits_equal(impl(a * 2, b), got * 2)
+    c, op, impl, args, kwargs = _full("addmm_bf16_8192x4096x11008", backend)
+    bias, a, b = args
+    g2, r2 = impl(bias, a, b), op(bias, a, b)
+    assert compare(r2, g2, 1e-2, 1e-2)[0]
+    assert compare((exact + bias.double().cpu()).to(torch.bfloat16), g2[rows].cpu(), 2e-2, 1e-2)[0]
+    c, op, impl, args, kwargs = _full("bmm_bf16_32x2048x128x2048", backend)
+    g3, r3 = impl(*args), op(*args)
+    assert compare(r3, g3, 1e-2, 1e-2)[0]
+    e3 = (args[0][5].double() @ args[1][5].double()).to(torch.bfloat16)
+    assert compare(e3, g3[5], 1e-2, 1e-2)[0]
+
+
+def test_index_out_of_range_is_reported_not_faulted(backend):
+    """A bad index never touches memory out of bounds: the row is zero-filled, a status bit
+    is set, and the next status check raises IndexError; the context stays usable."""
+    table = torch.randn(16, 8, device=DEV)
+    idx = torch.tensor([1, 99, 3, -1], device=DEV)
+    out = backend[torch.ops.aten.embedding.default](table, idx)
+    with pytest.raises(IndexError):
+        ops.check_device_status()
+    assert bits_equal(out[0], table[1]) and bits_equal(out[2], table[3]) and float(out[1].abs().sum()) == 0.0 and float(out[3].abs().sum()) == 0.0
+    ops.check_device_status()  # cleared; and the device still works:
+    assert bits_equal(backend[torch.ops.aten.relu.default](table), torch.relu(table))
+
+
+def test_unsupported_requests_fail_loudly(backend):
+    with pytest.raises(NotImplementedError):
+        backend[torch.ops.aten.relu.default](torch.arange(4, device=DEV))  # integer relu: not implemented, no fallback
+    with pytest.raises(NotImplementedError):
+        backend[torch.ops.aten.mm.default](torch.randn(4, 4, device=DEV, dtype=torch.float64), torch.randn(4, 4, device=DEV, dtype=torch.float64))
+    with pytest.raises(RuntimeError):
+        backend[torch.ops.aten.mm.default](torch.randn(4, 5, device=DEV), torch.randn(4, 5, device=DEV))
