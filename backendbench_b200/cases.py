@@ -66,15 +66,16 @@ class CaseSpec:
         def randint(high, shape, dtype=torch.int64):
             return torch.randint(0, max(int(high), 1), shape, generator=g, device=gen_device, dtype=dtype)
 
-        def poison(t):
-            """1% of the elements become NaN / +Inf / -Inf."""
+        def poison(t, inf_ok=True):
+            """1% of the elements become NaN / +Inf / -Inf (NaN only when `inf_ok` is False)."""
             if self.edge != "naninf" or t.numel() == 0:
                 return t
             r = torch.rand(t.shape, generator=g, device=gen_device)
             t = t.clone()
-            t[r < 0.004] = float("nan")
-            t[(r >= 0.004) & (r < 0.007)] = float("inf")
-            t[(r >= 0.007) & (r < 0.010)] = float("-inf")
+            t[r < (0.004 if inf_ok else 0.010)] = float("nan")
+            if inf_ok:
+                t[(r >= 0.004) & (r < 0.007)] = float("inf")
+                t[(r >= 0.007) & (r < 0.010)] = float("-inf")
             return t
 
         def transposed(shape2d, **kw):
@@ -108,7 +109,10 @@ class CaseSpec:
                 args.append(True)
         elif op == "native_layer_norm.default":
             cols = shp[-1]
-            x = poison(normal(shp))
+            # NaN only: for a row holding +-inf aten's own kernels disagree with each other
+            # (mean comes out NaN or inf depending on where the infinity falls in the
+            # kernel's internal chunking), so there is no single reference result to match
+            x = poison(normal(shp), inf_ok=False)
             w = normal((cols,), std=0.02, mean=1.0)
             b = normal((cols,), std=0.02)
             args = [x, [cols], w, b, 1e-5]

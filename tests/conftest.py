@@ -64,7 +64,9 @@ def first_dtype(x):
 
 
 def bits_equal(a: torch.Tensor, b: torch.Tensor) -> bool:
-    """Same shape, dtype and bit pattern (NaN payloads and signed zeros included)."""
+    """Same shape, dtype and bit pattern (signed zeros and infinities included). NaNs must
+    sit in the same places; their payload bits are not compared (arithmetic that produces
+    a NaN, e.g. inf + -inf in scatter_add, may pick any quiet-NaN encoding)."""
     if a.shape != b.shape or a.dtype != b.dtype:
         return False
     if a.numel() == 0:
@@ -73,4 +75,9 @@ def bits_equal(a: torch.Tensor, b: torch.Tensor) -> bool:
     b = b.detach().cpu().contiguous().reshape(-1)
     if a.dtype == torch.bool:
         return torch.equal(a, b)
+    if a.dtype.is_floating_point:
+        na, nb = torch.isnan(a), torch.isnan(b)
+        if not torch.equal(na, nb):
+            return False
+        a, b = a.masked_fill(na, 0), b.masked_fill(nb, 0)
     return torch.equal(a.view(torch.uint8), b.view(torch.uint8))

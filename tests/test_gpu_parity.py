@@ -135,10 +135,11 @@ def test_full_size_softmax_family(backend, tag):
     lg, lref = impl(*args, **kwargs), op(*args, **kwargs)
     assert compare(lref, lg, atol, rtol)[0]
     assert compare(got.float(), lg.float().exp(), 2e-2 if got.dtype != torch.float32 else 1e-5, 1e-2)[0]  # exp(log_softmax) == softmax
-    # shift invariance: softmax(x + c) == softmax(x) for exactly representable shifts
-    x = args[0]
-    shifted = impl((x.float() + 8.0).to(x.dtype), -1, False)
-    assert compare(got, shifted, 2e-2 if got.dtype != torch.float32 else 1e-5, 1e-2)[0]
+    # shift invariance softmax(x + c) == softmax(x); in fp32 the shift perturbs x by < 1e-6
+    if got.dtype == torch.float32:
+        xs = args[0] + 8.0
+        ok, ea, er = compare(got, impl(xs, -1, False), 1e-5, 1e-3)
+        assert ok, (ea, er)
 
 
 @pytest.mark.parametrize("tag", ["bf16_8192x4096", "f32_65536x1024"])
