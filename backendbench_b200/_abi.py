@@ -26,6 +26,8 @@ F32, BF16, F16, I32, I64, BOOL, U8, I8, I16, F64 = range(10)
 DEV_INDEX_OOB = 1
 DEV_WAIT_TIMEOUT = 2
 
+STATIC_SCRATCH_BYTES = 1 << 20  # B200_STATIC_SCRATCH_BYTES
+
 
 class B200LibraryMissing(RuntimeError):
     """libb200ops.so is not built or cannot be loaded."""
@@ -53,6 +55,7 @@ SIGNATURES = {
     "b200_softmax": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_int, c_void_p]),
     "b200_reduce_scratch_bytes": (c_int64, [c_int64, c_int64, c_int64]),
     "b200_sum": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_int64, c_void_p]),
+    "b200_sum_static": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_void_p]),
     "b200_layer_norm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_double, c_int, c_int, c_int, c_void_p]),
     "b200_argmax": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p, c_int64, c_void_p]),
     "b200_gather_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p]),

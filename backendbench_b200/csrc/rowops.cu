@@ -13,6 +13,8 @@
 // is split over gridDim.y CTAs and finished by a second tiny kernel from scratch memory.
 #include <math_constants.h>
 
+#include <mutex>
+
 #include "b200_common.cuh"
 
 namespace b200 {
@@ -647,4 +649,47 @@ extern "C" int b200_layer_norm(const void* x, const void* w, const void* b, void
       return wf32 ? layernorm_T<__half, float>(x, w, b, y, mean, rstd, rows, cols, e, dt_stat, c, st)
                   : layernorm_T<__half, __half>(x, w, b, y, mean, rstd, rows, cols, e, dt_stat, c, st);
   }
+}
+
+// ------------------------------------------------------------------ sum without any allocation
+// Scratch for the split-reduction partials of b200_sum_static. It lives in the library
+// image: every GPU that loads the library holds these bytes until the process exits.
+static __device__ __align__(256) unsigned char g_sum_static_scratch[B200_STATIC_SCRATCH_BYTES];
+
+// Device address of the array above on the CURRENT device. In host code the array's name
+// is only a handle, not something a kernel can dereference, so the address is asked for
+// once per device (cudaGetSymbolAddress, return code checked) and remembered.
+static void* sum_static_scratch_address(void) {
+  static std::mutex mu;
+  static void* per_device[64] = {};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) {
+    set_last_cuda_error(e != cudaSuccess ? e : cudaErrorInvalidDevice);
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  if (!per_device[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_sum_static_scratch);
+    if (e != cudaSuccess || !p) {
+      set_last_cuda_error(e);
+      return nullptr;
+    }
+    per_device[dev] = p;
+  }
+  return per_device[dev];
+}
+
+extern "C" int b200_sum_static(const void* x, void* out, int64_t outer, int64_t dim, int64_t inner, int dti, int dto, void* stream) {
+  const int64_t need = b200_reduce_scratch_bytes(outer, dim, inner);
+  if (need > B200_STATIC_SCRATCH_BYTES) return B200_ESCRATCH;
+  void* scratch = nullptr;
+  if (need > 0) {
+    scratch = sum_static_scratch_address();
+    if (!scratch) return B200_ELAUNCH;
+  }
+  // every partial slot is written by the first stage before the second stage reads it, so
+  // whatever an earlier call left in the array never needs clearing
+  return b200_sum(x, out, outer, dim, inner, dti, dto, scratch, need > 0 ? B200_STATIC_SCRATCH_BYTES : 0, stream);
 }

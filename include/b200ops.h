@@ -125,6 +125,26 @@ int64_t b200_reduce_scratch_bytes(int64_t outer, int64_t dim, int64_t inner);
 int b200_sum(const void* x, void* out, int64_t outer, int64_t dim, int64_t inner,
              int dtype_in, int dtype_out, void* scratch, int64_t scratch_bytes, void* stream);
 
+/* Same result as b200_sum, for hosts that must not allocate. It has no counterpart in
+ * the reference: it exists for callers that drive this library from C/C++ (or through
+ * cgo / JNI) without a device allocator of their own -- a serving loop whose GPU memory
+ * was handed over to another pool at start-up, or code on a latency path where
+ * cudaMalloc / cudaFree would stall the whole device. Such a caller passes only the input
+ * and the output; the partial sums of a split reduction go to a fixed array inside the
+ * library image (B200_STATIC_SCRATCH_BYTES per GPU that loads the library, held until the
+ * process exits). The call allocates nothing and calls no allocating routine.
+ *   - Geometries whose partials would not fit (b200_reduce_scratch_bytes(...) >
+ *     B200_STATIC_SCRATCH_BYTES) are refused with B200_ESCRATCH; nothing is launched.
+ *   - The first call on each device looks up the array's device address; make that first
+ *     call with the device current and before starting any stream capture.
+ *   - All calls on a device share the one array. Its old contents never matter (every
+ *     partial is rewritten before it is read), but two calls whose kernels may run at the
+ *     same time -- different streams, different host threads -- race on it: keep such
+ *     calls ordered on one stream. */
+#define B200_STATIC_SCRATCH_BYTES (1 << 20)
+int b200_sum_static(const void* x, void* out, int64_t outer, int64_t dim, int64_t inner,
+                    int dtype_in, int dtype_out, void* stream);
+
 /* aten.native_layer_norm.default(input, normalized_shape, weight, bias, eps)
  * -> (out, mean, rstd); rows = prod(leading dims), cols = prod(normalized_shape);
  * weight/bias may be NULL; dtype_stat is the dtype of mean/rstd (eval.py:100-102;
