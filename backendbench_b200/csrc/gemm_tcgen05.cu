@@ -1,6 +1,412 @@
-// placeholder until the tensor-core kernel lands: nothing is eligible yet
+// mm / addmm / bmm on the 5th-generation tensor cores (tcgen05) for bf16 / f16 operands.
+//
+//   C[b] (M x N, row-major) = alpha * A[b] (M x K) @ B[b] (K x N) + beta * bias
+//
+// One persistent CTA per SM walks 128 x 256 output tiles. Roles by warp:
+//   warp 0   : TMA producer -- one lane issues cp.async.bulk.tensor loads (no multicast)
+//              of a 128 x 64 A slab and a 64 x 256 B slab per pipeline stage into
+//              128-byte-swizzled shared memory, completion on an mbarrier.
+//   warp 1   : owns tensor memory (allocates all 512 TMEM columns = two fp32 accumulators
+//              of 128 lanes x 256 columns) and issues tcgen05.mma (kind::f16, M128 N256
+//              K16, four per stage); tcgen05.commit releases the stage / publishes the
+//              accumulator through mbarriers.
+//   warps 2-5: epilogue -- tcgen05.ld the accumulator (each warp its own 32 TMEM lanes),
+//              scale / add bias in fp32, round once, 16-byte stores. While they drain
+//              accumulator `a`, the MMA warp already fills accumulator `a ^ 1`.
+// Operands may be K-major or MN-major in global memory (A row- or column-major, B given
+// as [K,N] or as a transposed [N,K] view): the layout goes into the shared-memory and
+// instruction descriptors, nothing is copied or transposed. Ragged M / N / K edges rely on
+// TMA zero fill for loads and predicated stores.
+//
+// Every mbarrier wait is bounded: when a wait gives up the CTA sets an abort flag, ORs
+// B200_DEV_WAIT_TIMEOUT into the caller's status word, lets outstanding copies land, frees
+// its tensor memory and returns -- a protocol bug can produce a wrong result plus an error
+// status, never a hung GPU.
+#include <cuda.h>
+
 #include "b200_common.cuh"
+
 namespace b200 {
-bool gemm_tc_eligible(int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int, const void*, const void*, const void*) { return false; }
-int gemm_tc_dispatch(const void*, const void*, const void*, void*, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, double, double, int, uint32_t*, cudaStream_t) { return B200_EINVAL; }
+
+constexpr int kBM = 128, kBN = 256, kBK = 64;          // tile: 128 x 256 outputs, 64-deep K slabs
+constexpr int kStages = 4;
+constexpr int kABytes = kBM * kBK * 2;                  // 16 KB
+constexpr int kBBytes = kBN * kBK * 2;                  // 32 KB
+constexpr int kStageBytes = kABytes + kBBytes;          // 48 KB
+constexpr int kTmemCols = 512;                          // two 256-column accumulators
+constexpr int kGemmThreads = 192;
+constexpr uint64_t kWaitLimitNs = 2000000000ull;        // every mbarrier wait gives up after 2 s
+constexpr size_t kGemmSmem = static_cast<size_t>(kStages) * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count)); }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) { asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory"); }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
+// One probe of the barrier phase; the hardware may park the thread for at most ~1 us.
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(1000u)
+      : "memory");
+  return ok != 0;
 }
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait: false when kWaitLimitNs ran out or another role already aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_ns();
+  for (uint32_t i = 0;; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 7u) == 7u) {
+      if (*abort_flag) return false;
+      if (global_ns() - t0 > kWaitLimitNs) return false;
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) { asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory"); }
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld_32x32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]),
+        "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor (128-byte swizzle, sm_100 format): start address,
+// leading-dimension byte offset and stride byte offset in 16-byte units, version 1.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((addr >> 4) & 0x3fffu);
+  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3fffu) << 16;
+  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3fffu) << 32;
+  d |= 1ull << 46;  // descriptor version for sm_100
+  d |= 2ull << 61;  // SWIZZLE_128B
+  return d;
+}
+
+struct GemmTcParams {
+  int64_t M, N, K, batch;
+  int64_t sbm, sbn;  // bias strides in elements (0 = broadcast)
+  float alpha, beta;
+  int a_mn_major, b_mn_major;  // 0: K contiguous in global memory, 1: M (resp. N) contiguous
+  int is_bf16;
+  int has_bias;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const T* __restrict__ bias, T* __restrict__ C, GemmTcParams p,
+                    uint32_t* __restrict__ status) {
+  extern __shared__ unsigned char smem_raw[];
+  // 1024-byte alignment: the 128B swizzle pattern repeats every 8 rows x 128 bytes
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+  // barrier slots: [0,S) full, [S,2S) empty, [2S,2S+2) tmem_full, [2S+2,2S+4) tmem_empty
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  volatile uint32_t* abort_flag = tmem_base_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 4);  // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_base_slot)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  const int64_t mt = (p.M + kBM - 1) / kBM, nt = (p.N + kBN - 1) / kBN;
+  const int64_t tiles = p.batch * mt * nt;
+  const int num_kb = static_cast<int>((p.K + kBK - 1) / kBK);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int64_t t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+        const int64_t b = t / (mt * nt), rem = t - b * (mt * nt);
+        const int m0 = static_cast<int>(rem % mt) * kBM, n0 = static_cast<int>(rem / mt) * kBN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
+          const uint32_t a_dst = smem_base + stage * kStageBytes, b_dst = a_dst + kABytes;
+          mbar_expect_tx(full_bar(stage), kStageBytes);
+          const int k0 = kb * kBK;
+          if (!p.a_mn_major) {
+            tma_load_3d(a_dst, &map_a, full_bar(stage), k0, m0, static_cast<int>(b));  // box [128 rows][64 k]
+          } else {
+#pragma unroll
+            for (int c = 0; c < kBM / 64; ++c) tma_load_3d(a_dst + c * 8192, &map_a, full_bar(stage), m0 + c * 64, k0, static_cast<int>(b));  // box [64 k][64 m]
+          }
+          if (!p.b_mn_major) {
+            tma_load_3d(b_dst, &map_b, full_bar(stage), k0, n0, static_cast<int>(b));  // box [256 rows][64 k]
+          } else {
+#pragma unroll
+            for (int c = 0; c < kBN / 64; ++c) tma_load_3d(b_dst + c * 8192, &map_b, full_bar(stage), n0 + c * 64, k0, static_cast<int>(b));  // box [64 k][64 n]
+          }
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        *abort_flag = 1;
+        if (status) atomicOr(status, B200_DEV_WAIT_TIMEOUT);
+      }
+    }
+    __syncwarp();  // lanes 1..31 rejoin lane 0 before the CTA-wide barrier below
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      // instruction descriptor: fp32 accumulate, A/B format, majors, N >> 3, M >> 4
+      const uint32_t fmt = p.is_bf16 ? 1u : 0u;
+      const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(p.a_mn_major) << 15) | (static_cast<uint32_t>(p.b_mn_major) << 16) |
+                             (static_cast<uint32_t>(kBN >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);
+      // per-UMMA (K = 16) advance of the start address and the two byte offsets per layout
+      const uint32_t a_adv = p.a_mn_major ? 2048u : 32u, b_adv = p.b_mn_major ? 2048u : 32u;
+      const uint32_t a_lbo = p.a_mn_major ? 8192u : 16u, b_lbo = p.b_mn_major ? 8192u : 16u;
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int64_t t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kBN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_base + stage * kStageBytes, b_addr = a_addr + kABytes;
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) {
+            const uint64_t da = smem_desc(a_addr + k * a_adv, a_lbo, 1024u);
+            const uint64_t db = smem_desc(b_addr + k * b_adv, b_lbo, 1024u);
+            tc_mma_f16(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          tc_commit(empty_bar(stage));  // the stage is free once these MMAs have read it
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        tc_commit(tfull_bar(acc));  // accumulator complete
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+      if (!ok) {
+        *abort_flag = 1;
+        if (status) atomicOr(status, B200_DEV_WAIT_TIMEOUT);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;  // TMEM lane quarter this warp may read: lanes [32q, 32q + 32)
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    const bool vec_ok = (p.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15u) == 0);
+    for (int64_t t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+      const int64_t b = t / (mt * nt), rem = t - b * (mt * nt);
+      const int64_t m0 = (rem % mt) * kBM, n0 = (rem / mt) * kBN;
+      int got = 0;
+      if (lane == 0) got = mbar_wait(tfull_bar(acc), acc_phase, abort_flag) ? 1 : 0;
+      got = __shfl_sync(0xffffffffu, got, 0);
+      if (!got) { ok = false; break; }
+      tc_fence_after();
+      const int64_t m = m0 + q * 32 + lane;
+      T* crow = C + (b * p.M + m) * p.N;
+#pragma unroll 1
+      for (int c = 0; c < kBN / 32; ++c) {
+        uint32_t r[32];
+        tc_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * kBN + c * 32), r);
+        tc_ld_wait();
+        const int64_t nb = n0 + c * 32;
+        if (m < p.M && nb < p.N) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int64_t n = nb + g * 8;
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              v[e] = p.alpha * __uint_as_float(r[g * 8 + e]);
+              if (p.has_bias && n + e < p.N) v[e] = fmaf(p.beta, to_f32(bias[m * p.sbm + (n + e) * p.sbn]), v[e]);
+            }
+            if (vec_ok && n + 8 <= p.N) {
+              Vec<T> o;
+#pragma unroll
+              for (int e = 0; e < 8; ++e) o.set(e, from_f32<T>(v[e]));
+              *reinterpret_cast<uint4*>(crow + n) = o.raw;
+            } else {
+#pragma unroll
+              for (int e = 0; e < 8; ++e)
+                if (n + e < p.N) crow[n + e] = from_f32<T>(v[e]);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));  // this warp has drained its quarter
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+    if (!ok && lane == 0) {
+      *abort_flag = 1;
+      if (status) atomicOr(status, B200_DEV_WAIT_TIMEOUT);
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (*abort_flag) {
+    // give copies that are still in flight time to land before the shared memory goes away
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess) fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+struct OperandLayout {
+  bool ok, mn_major;
+};
+// An operand [rows(MN), K] with element strides (s_mn, s_k) is TMA-loadable when one of
+// the two strides is 1 and the other (and the batch stride) keeps 16-byte alignment.
+static OperandLayout operand_layout(int64_t mn, int64_t k, int64_t s_mn, int64_t s_k, int64_t s_b, int64_t batch, const void* base) {
+  OperandLayout r{false, false};
+  if (!aligned16(base)) return r;
+  if (batch > 1 && (s_b % 8 != 0 || s_b <= 0)) return r;
+  if (s_k == 1 && (s_mn % 8 == 0) && s_mn >= k) { r.ok = true; r.mn_major = false; return r; }
+  if (s_mn == 1 && (s_k % 8 == 0) && s_k >= mn) { r.ok = true; r.mn_major = true; return r; }
+  // a single row / column is contiguous either way
+  if (mn == 1 && s_k == 1) { r.ok = true; r.mn_major = false; return r; }
+  return r;
+}
+
+bool gemm_tc_eligible(int64_t batch, int64_t M, int64_t N, int64_t K, int64_t sAb, int64_t sAm, int64_t sAk, int64_t sBb, int64_t sBk, int64_t sBn, int dtype, const void* A,
+                      const void* B, const void* C) {
+  if (dtype != B200_BF16 && dtype != B200_F16) return false;
+  if (batch < 1 || M < 1 || N < 1 || K < 1) return false;
+  if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL || batch > 0x7fffffffLL) return false;
+  // tiny problems are launch-bound either way; the CUDA-core kernel has no TMEM / barrier set-up
+  if (M * N * K < (1LL << 15)) return false;
+  if (!operand_layout(M, K, sAm, sAk, sAb, batch, A).ok) return false;
+  if (!operand_layout(N, K, sBn, sBk, sBb, batch, B).ok) return false;
+  if (!C) return false;
+  return encode_fn() != nullptr;
+}
+
+static bool encode_operand(CUtensorMap* map, const void* base, int dtype, bool mn_major, int64_t mn, int64_t k, int64_t s_mn, int64_t s_k, int64_t s_b, int64_t batch, int tile_mn) {
+  const cuuint64_t inner = mn_major ? mn : k, outer = mn_major ? k : mn;
+  int64_t outer_stride = mn_major ? s_k : s_mn;  // elements
+  if (outer == 1 && outer_stride % 8 != 0) outer_stride = (static_cast<int64_t>(inner) + 7) / 8 * 8;  // never dereferenced beyond row 0
+  int64_t batch_stride = batch > 1 ? s_b : outer_stride * static_cast<int64_t>(outer);
+  if (batch_stride % 8 != 0 || batch_stride <= 0) batch_stride = (batch_stride / 8 + 1) * 8;
+  cuuint64_t dims[3] = {inner, outer, static_cast<cuuint64_t>(batch)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(outer_stride) * 2, static_cast<cuuint64_t>(batch_stride) * 2};
+  cuuint32_t box[3] = {64, static_cast<cuuint32_t>(mn_major ? kBK : tile_mn), 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  const CUtensorMapDataType dt = dtype == B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const CUresult r = encode_fn()(map, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+int gemm_tc_dispatch(const void* A, const void* B, const void* bias, void* C, int64_t batch, int64_t M, int64_t N, int64_t K, int64_t sAb, int64_t sAm, int64_t sAk, int64_t sBb,
+                     int64_t sBk, int64_t sBn, int64_t sbm, int64_t sbn, double alpha, double beta, int dtype, uint32_t* status, cudaStream_t st) {
+  const OperandLayout la = operand_layout(M, K, sAm, sAk, sAb, batch, A);
+  const OperandLayout lb = operand_layout(N, K, sBn, sBk, sBb, batch, B);
+  if (!la.ok || !lb.ok || !encode_fn()) return B200_EALIGN;
+  alignas(64) CUtensorMap map_a, map_b;
+  if (!encode_operand(&map_a, A, dtype, la.mn_major, M, K, sAm, sAk, sAb, batch, kBM)) return B200_EDRIVER;
+  if (!encode_operand(&map_b, B, dtype, lb.mn_major, N, K, sBn, sBk, sBb, batch, kBN)) return B200_EDRIVER;
+  GemmTcParams p;
+  p.M = M; p.N = N; p.K = K; p.batch = batch;
+  p.sbm = sbm; p.sbn = sbn;
+  p.alpha = static_cast<float>(alpha);
+  p.beta = static_cast<float>(beta);
+  p.a_mn_major = la.mn_major ? 1 : 0;
+  p.b_mn_major = lb.mn_major ? 1 : 0;
+  p.is_bf16 = dtype == B200_BF16 ? 1 : 0;
+  p.has_bias = (bias != nullptr && p.beta != 0.f) ? 1 : 0;
+  const int64_t tiles = batch * ((M + kBM - 1) / kBM) * ((N + kBN - 1) / kBN);
+  const int grid = static_cast<int>(tiles < kNumSMs ? tiles : kNumSMs);
+  cudaError_t e;
+  if (dtype == B200_BF16) {
+    e = cudaFuncSetAttribute(gemm_tcgen05_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemmSmem));
+    if (e != cudaSuccess) { set_last_cuda_error(e); return B200_ELAUNCH; }
+    gemm_tcgen05_kernel<__nv_bfloat16><<<grid, kGemmThreads, kGemmSmem, st>>>(map_a, map_b, static_cast<const __nv_bfloat16*>(bias), static_cast<__nv_bfloat16*>(C), p, status);
+  } else {
+    e = cudaFuncSetAttribute(gemm_tcgen05_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemmSmem));
+    if (e != cudaSuccess) { set_last_cuda_error(e); return B200_ELAUNCH; }
+    gemm_tcgen05_kernel<__half><<<grid, kGemmThreads, kGemmSmem, st>>>(map_a, map_b, static_cast<const __half*>(bias), static_cast<__half*>(C), p, status);
+  }
+  return check_launch();
+}
+
+}  // namespace b200
