@@ -1,0 +1,49 @@
+"""Run one named operator configuration on the current GPU a few times and print its
+device time -- the small, self-contained command used for profiler captures.
+
+    python -m backendbench_b200.run_case --case softmax_bf16_8192x4096 [--scale 4] [--reps 3] [--warmup 2]
+    python -m backendbench_b200.run_case --list
+
+`--scale F` divides the leading extent by F (same operator, same row length) so that a
+full-metrics profiler capture holds a few hundred MB instead of GBs.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+from .backends import B200Backend
+from .cases import named_case, named_cases, scaled_down
+from .eval import cuda_bench
+from .opregistry import get_operator
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--case")
+    ap.add_argument("--scale", type=int, default=1)
+    ap.add_argument("--reps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=2)
+    ap.add_argument("--list", action="store_true")
+    args = ap.parse_args()
+    if args.list or not args.case:
+        print("\n".join(c.name for c in named_cases()))
+        return
+    case = named_case(args.case)
+    if args.scale > 1:
+        case = scaled_down(case, args.scale)
+    op = get_operator(case.op)
+    impl = B200Backend()[op]
+    a, kw = case.build("cuda")
+    ms = cuda_bench(lambda: impl(*a, **kw), warmup=args.warmup, reps=args.reps)
+    out = {"case": case.label(), "ms": round(ms, 5), "algorithmic_bytes": case.algorithmic_bytes(), "gbs": round(case.algorithmic_bytes() / ms / 1e6, 1)}
+    if case.flops():
+        out["tflops"] = round(case.flops() / ms / 1e9, 2)
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()

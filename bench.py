@@ -314,13 +314,15 @@ def run_b200(args):
     value = units / (total_ms * 1e-3)
 
     # ---- end to end: pinned host inputs, H2D inside the timed region
-    host_inputs = [[a.cpu().pin_memory() if isinstance(a, torch.Tensor) else a for a in p["args"]] for p in prepared]
-    h2d = sum(_bytes_of(h) for h in host_inputs)
-    e2e_steps = max(1, min(args.steps, 3))
-    e2e_ms, _ = time_steps(lambda: sweep_pass(prepared, records, host_inputs, device), e2e_steps, 1)
-    e2e_units = sum_over_ranks(float(len(prepared) * e2e_steps))
-    e2e = {"value": round(e2e_units / (e2e_ms * 1e-3), 2), "unit": "cases/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(records.numel() * 4), "steps": e2e_steps}
-    del host_inputs
+    e2e = None
+    if not args.sweep_only:
+        host_inputs = [[a.cpu().pin_memory() if isinstance(a, torch.Tensor) else a for a in p["args"]] for p in prepared]
+        h2d = sum(_bytes_of(h) for h in host_inputs)
+        e2e_steps = max(1, min(args.steps, 3))
+        e2e_ms, _ = time_steps(lambda: sweep_pass(prepared, records, host_inputs, device), e2e_steps, 1)
+        e2e_units = sum_over_ranks(float(len(prepared) * e2e_steps))
+        e2e = {"value": round(e2e_units / (e2e_ms * 1e-3), 2), "unit": "cases/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(records.numel() * 4), "steps": e2e_steps}
+        del host_inputs
 
     line = {
         "metric": "sweep_cases_per_sec", "value": round(value, 2), "unit": "cases/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -348,8 +350,9 @@ def run_b200(args):
         roof.update({"kernel": top_op, "launches": top["launches"], "avg_launch_ms": round(top["ms"] / top["launches"], 4), "peak_source": peaks["source"], "traffic": None})
         line["roofline"] = roof
         line["sweep_time_share_by_op"] = shares
-        line["per_op"] = named_config_table(backend, device, peaks, reps=15)
-        if world == 1:
+        if not args.sweep_only:
+            line["per_op"] = named_config_table(backend, device, peaks, reps=15)
+        if world == 1 and not args.sweep_only:
             done, secs, desc, cores = cpu_reference_sample(cases, budget_s=20.0)
             line["cpu_baseline"] = {"value": round(done / secs, 2), "unit": "cases/s", "cores": cores, "kind": "port", "sample": desc}
         print(json.dumps(line), flush=True)
@@ -391,6 +394,7 @@ def main():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--sweep-only", action="store_true", help="time the sweep only (no e2e pass, per-op table or CPU sample): the short run used for profiler launch lists")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
