@@ -10,9 +10,12 @@
 //              of 128 lanes x 256 columns) and issues tcgen05.mma (kind::f16, M128 N256
 //              K16, four per stage); tcgen05.commit releases the stage / publishes the
 //              accumulator through mbarriers.
-//   warps 2-5: epilogue -- tcgen05.ld the accumulator (each warp its own 32 TMEM lanes),
-//              scale / add bias in fp32, round once, 16-byte stores. While they drain
-//              accumulator `a`, the MMA warp already fills accumulator `a ^ 1`.
+//   warps 2-9: epilogue -- tcgen05.ld the accumulator (a warp may read only the 32 TMEM
+//              lanes of its quarter, so two warps share a quarter and split the 256
+//              columns), scale / add bias in fp32, round once, 16-byte stores. While they
+//              drain accumulator `a`, the MMA warp already fills accumulator `a ^ 1`.
+// Tiles are walked in groups of 16 row-blocks x all column-blocks so that the CTAs running
+// at the same time share A and B slabs in L2.
 // Operands may be K-major or MN-major in global memory (A row- or column-major, B given
 // as [K,N] or as a transposed [N,K] view): the layout goes into the shared-memory and
 // instruction descriptors, nothing is copied or transposed. Ragged M / N / K edges rely on
@@ -34,7 +37,8 @@ constexpr int kABytes = kBM * kBK * 2;                  // 16 KB
 constexpr int kBBytes = kBN * kBK * 2;                  // 32 KB
 constexpr int kStageBytes = kABytes + kBBytes;          // 48 KB
 constexpr int kTmemCols = 512;                          // two 256-column accumulators
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 320;                       // TMA warp, MMA warp, 8 epilogue warps
+constexpr int kGroupM = 16;                             // row-blocks per rasterisation group
 constexpr uint64_t kWaitLimitNs = 2000000000ull;        // every mbarrier wait gives up after 2 s
 constexpr size_t kGemmSmem = static_cast<size_t>(kStages) * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
 
@@ -121,7 +125,23 @@ struct GemmTcParams {
   int a_mn_major, b_mn_major;  // 0: K contiguous in global memory, 1: M (resp. N) contiguous
   int is_bf16;
   int has_bias;
+  int col_fastest;  // tile order: 1 = column-block fastest (write-bound shapes), 0 = grouped row-block fastest
 };
+
+// Tile t of one batch entry -> (row-block, column-block): column-block fastest, or groups of
+// kGroupM row-blocks with the row-block fastest inside a group.
+__device__ __forceinline__ void tile_coords(int64_t rem, int64_t mt, int64_t nt, int& mb, int& nb, int col_fastest) {
+  if (col_fastest) {
+    mb = static_cast<int>(rem / nt);
+    nb = static_cast<int>(rem - static_cast<int64_t>(mb) * nt);
+    return;
+  }
+  const int64_t per_group = static_cast<int64_t>(kGroupM) * nt;
+  const int64_t g = rem / per_group, in_g = rem - g * per_group;
+  const int64_t gm = (mt - g * kGroupM) < kGroupM ? (mt - g * kGroupM) : kGroupM;  // the last group may be short
+  mb = static_cast<int>(g * kGroupM + in_g % gm);
+  nb = static_cast<int>(in_g / gm);
+}
 
 template <typename T>
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -150,7 +170,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), 4);  // one arrival per epilogue warp
+      mbar_init(tempty_bar(a), 8);  // one arrival per epilogue warp
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -176,7 +196,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       bool ok = true;
       for (int64_t t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
         const int64_t b = t / (mt * nt), rem = t - b * (mt * nt);
-        const int m0 = static_cast<int>(rem % mt) * kBM, n0 = static_cast<int>(rem / mt) * kBN;
+        int mb, nb;
+        tile_coords(rem, mt, nt, mb, nb, p.col_fastest);
+        const int m0 = mb * kBM, n0 = nb * kBN;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
           const uint32_t a_dst = smem_base + stage * kStageBytes, b_dst = a_dst + kABytes;
@@ -245,15 +267,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------------------ epilogue (warps 2..5)
-    const int q = warp & 3;  // TMEM lane quarter this warp may read: lanes [32q, 32q + 32)
+    // ------------------------------------------------------------ epilogue (warps 2..9)
+    const int q = warp & 3;             // TMEM lane quarter this warp may read: lanes [32q, 32q + 32)
+    const int chalf = (warp - 2) >> 2;  // which 128 of the 256 columns
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
     const bool vec_ok = (p.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15u) == 0);
     for (int64_t t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
       const int64_t b = t / (mt * nt), rem = t - b * (mt * nt);
-      const int64_t m0 = (rem % mt) * kBM, n0 = (rem / mt) * kBN;
+      int mb, nb_blk;
+      tile_coords(rem, mt, nt, mb, nb_blk, p.col_fastest);
+      const int64_t m0 = static_cast<int64_t>(mb) * kBM, n0 = static_cast<int64_t>(nb_blk) * kBN + chalf * (kBN / 2);
       int got = 0;
       if (lane == 0) got = mbar_wait(tfull_bar(acc), acc_phase, abort_flag) ? 1 : 0;
       got = __shfl_sync(0xffffffffu, got, 0);
@@ -261,15 +286,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       tc_fence_after();
       const int64_t m = m0 + q * 32 + lane;
       T* crow = C + (b * p.M + m) * p.N;
+      const uint32_t t_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * kBN + chalf * (kBN / 2));
 #pragma unroll 1
-      for (int c = 0; c < kBN / 32; ++c) {
-        uint32_t r[32];
-        tc_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * kBN + c * 32), r);
+      for (int c = 0; c < kBN / 2 / 64; ++c) {
+        uint32_t r[64];
+        tc_ld_32x32(t_base + c * 64, r);  // two loads in flight before the wait
+        tc_ld_32x32(t_base + c * 64 + 32, r + 32);
         tc_ld_wait();
-        const int64_t nb = n0 + c * 32;
+        const int64_t nb = n0 + c * 64;
         if (m < p.M && nb < p.N) {
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
+          for (int g = 0; g < 8; ++g) {
             const int64_t n = nb + g * 8;
             float v[8];
 #pragma unroll
@@ -292,7 +319,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(tempty_bar(acc));  // this warp has drained its quarter
+      if (lane == 0) mbar_arrive(tempty_bar(acc));  // this warp has drained its part
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
@@ -394,6 +421,10 @@ int gemm_tc_dispatch(const void* A, const void* B, const void* bias, void* C, in
   p.b_mn_major = lb.mn_major ? 1 : 0;
   p.is_bf16 = dtype == B200_BF16 ? 1 : 0;
   p.has_bias = (bias != nullptr && p.beta != 0.f) ? 1 : 0;
+  // few K slabs per tile: the kernel is bound by writing C, so CTAs that run together should
+  // write neighbouring column blocks of the same rows (whole DRAM pages); otherwise order
+  // tiles for operand reuse in L2
+  p.col_fastest = (K + kBK - 1) / kBK <= 4 ? 1 : 0;
   const int64_t tiles = batch * ((M + kBM - 1) / kBM) * ((N + kBN - 1) / kBN);
   const int grid = static_cast<int>(tiles < kNumSMs ? tiles : kNumSMs);
   cudaError_t e;

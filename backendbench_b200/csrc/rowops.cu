@@ -265,6 +265,15 @@ __device__ __forceinline__ bool arg_better(float v, int64_t i, float bv, int64_t
 __device__ __forceinline__ void arg_take(ArgPair& a, float v, int64_t i) {
   if (a.i < 0 || arg_better(v, i, a.v, a.i)) { a.v = v; a.i = i; }
 }
+// Streaming form for a thread that visits its elements in ASCENDING index order: one
+// compare per element on the common path. `v <= best` is false when v is larger, when v is
+// NaN, or when best is already NaN; only then the slow test runs (a NaN best is final:
+// the first NaN wins; otherwise v is larger or NaN and, being the earliest such, is taken).
+__device__ __forceinline__ void arg_take_ascending(ArgPair& a, float v, int64_t i) {
+  if (!(v <= a.v)) {
+    if (a.i < 0 || a.v == a.v) { a.v = v; a.i = i; }
+  }
+}
 __device__ __forceinline__ ArgPair arg_warp_reduce(ArgPair a) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
@@ -293,7 +302,7 @@ __global__ void __launch_bounds__(256) reduce_rows(const T* __restrict__ x, void
   const int64_t c1 = c0 + chunk < cols ? c0 + chunk : cols;
   const T* xr = x + row * cols;
   float s = 0.f;
-  ArgPair a{0.f, -1};
+  ArgPair a{CUDART_NAN_F, -1};  // NaN start: the first element fails `v <= NaN` and is taken through a.i < 0
   if (VECOK) {
     // chunk is a multiple of VE, so every slice starts on a vector boundary
     const int64_t v0 = c0 / VE, v1 = c1 / VE;
@@ -307,7 +316,7 @@ __global__ void __launch_bounds__(256) reduce_rows(const T* __restrict__ x, void
 #pragma unroll
         for (int e = 0; e < VE; ++e) {
           const float fv = to_f32(v[u].get(e));
-          if (ARG) arg_take(a, fv, (j + u * tpr) * VE + e);
+          if (ARG) arg_take_ascending(a, fv, (j + u * tpr) * VE + e);
           else s += fv;
         }
     }
@@ -317,19 +326,19 @@ __global__ void __launch_bounds__(256) reduce_rows(const T* __restrict__ x, void
 #pragma unroll
       for (int e = 0; e < VE; ++e) {
         const float fv = to_f32(v.get(e));
-        if (ARG) arg_take(a, fv, j * VE + e);
+        if (ARG) arg_take_ascending(a, fv, j * VE + e);
         else s += fv;
       }
     }
     for (int64_t c = v1 * VE + t; c < c1; c += tpr) {  // ragged end of the last slice
       const float fv = to_f32(xr[c]);
-      if (ARG) arg_take(a, fv, c);
+      if (ARG) arg_take_ascending(a, fv, c);
       else s += fv;
     }
   } else {
     for (int64_t c = c0 + t; c < c1; c += tpr) {
       const float fv = to_f32(xr[c]);
-      if (ARG) arg_take(a, fv, c);
+      if (ARG) arg_take_ascending(a, fv, c);
       else s += fv;
     }
   }

@@ -323,6 +323,26 @@ def cuda_bench(fn, warmup=3, reps=20, flush=True, return_all=False):
     return times[len(times) // 2]
 
 
+def cuda_bench_rotating(fns, reps=30, warmup=None):
+    """Mean device time per call in MILLISECONDS over `reps` back-to-back launches that
+    cycle through `fns` -- closures over DISTINCT input sets whose total footprint exceeds
+    L2, so every launch reads its inputs from HBM and evicts its predecessors' outputs, as
+    in steady state. One pair of CUDA events brackets the whole loop (no per-launch event or
+    flush overhead); the last len(fns) results are kept alive so outputs rotate too."""
+    n = len(fns)
+    ring = [None] * n
+    for i in range(warmup if warmup is not None else max(3, n)):
+        ring[i % n] = fns[i % n]()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(reps):
+        ring[i % n] = fns[i % n]()
+    end.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(end) / reps
+
+
 def _on_cuda(x) -> bool:
     if isinstance(x, torch.Tensor):
         return x.is_cuda

@@ -222,24 +222,31 @@ def per_kernel_profile(prepared):
 
 
 def named_config_table(backend, device, peaks, reps):
-    """Throughput of every named operator configuration, next to aten CUDA on the same tensors."""
+    """Throughput of every named operator configuration, next to aten CUDA on the same
+    tensors. Each configuration is instantiated several times (different seeds) until the
+    input sets exceed twice the L2 size; `reps` back-to-back launches rotate through the
+    sets between one pair of CUDA events."""
+    from dataclasses import replace
+
     from backendbench_b200.cases import named_cases
-    from backendbench_b200.eval import cuda_bench
+    from backendbench_b200.eval import cuda_bench_rotating
     from backendbench_b200.opregistry import get_operator
 
+    l2_bytes = 126 << 20
     rows = []
     for c in named_cases():
         op = get_operator(c.op)
         impl = backend[op]
-        args, kwargs = c.build(device)
+        nsets = max(2, min(8, -(-2 * l2_bytes // max(c.algorithmic_bytes(), 1))))
         try:
-            ms = cuda_bench(lambda: impl(*args, **kwargs), warmup=3, reps=reps)
-            aten_ms = cuda_bench(lambda: op(*args, **kwargs), warmup=3, reps=reps)
+            sets = [replace(c, seed=c.seed + i).build(device) for i in range(nsets)]
+            ms = cuda_bench_rotating([(lambda a=a, k=k: impl(*a, **k)) for a, k in sets], reps=reps)
+            aten_ms = cuda_bench_rotating([(lambda a=a, k=k: op(*a, **k)) for a, k in sets], reps=reps)
         except Exception as e:  # a failing configuration must not hide the others
             rows.append({"name": c.name, "error": repr(e)[:200]})
             continue
         tensor_bound = c.op in ("mm.default", "addmm.default")
-        row = {"name": c.name, "ms": round(ms, 5), "aten_cuda_ms": round(aten_ms, 5), "speedup_vs_aten_cuda": round(aten_ms / ms, 4), "bound": "tensor" if tensor_bound else "hbm"}
+        row = {"name": c.name, "ms": round(ms, 5), "aten_cuda_ms": round(aten_ms, 5), "speedup_vs_aten_cuda": round(aten_ms / ms, 4), "bound": "tensor" if tensor_bound else "hbm", "input_sets": nsets}
         gbs = c.algorithmic_bytes() / (ms * 1e-3) / 1e9
         row["gbs"] = round(gbs, 1)
         if c.flops():
@@ -251,8 +258,8 @@ def named_config_table(backend, device, peaks, reps):
             row["frac_measured"] = round(gbs / peaks["hbm_gbs"], 4)
             row["frac_nominal"] = round(gbs / NOMINAL_HBM_GBS, 4)
         rows.append(row)
-        del args
-    torch.cuda.empty_cache()
+        del sets
+        torch.cuda.empty_cache()
     return rows
 
 
@@ -351,7 +358,7 @@ def run_b200(args):
         line["roofline"] = roof
         line["sweep_time_share_by_op"] = shares
         if not args.sweep_only:
-            line["per_op"] = named_config_table(backend, device, peaks, reps=15)
+            line["per_op"] = named_config_table(backend, device, peaks, reps=40)
         if world == 1 and not args.sweep_only:
             done, secs, desc, cores = cpu_reference_sample(cases, budget_s=20.0)
             line["cpu_baseline"] = {"value": round(done / secs, 2), "unit": "cases/s", "cores": cores, "kind": "port", "sample": desc}
