@@ -40,7 +40,9 @@ constexpr int kTmemCols = 512;                          // two 256-column accumu
 constexpr int kGemmThreads = 320;                       // TMA warp, MMA warp, 8 epilogue warps
 constexpr int kGroupM = 16;                             // row-blocks per rasterisation group
 constexpr uint64_t kWaitLimitNs = 2000000000ull;        // every mbarrier wait gives up after 2 s
-constexpr size_t kGemmSmem = static_cast<size_t>(kStages) * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int kEpiWarps = 8;
+constexpr int kEpiStageBytes = 32 * 128;                // per epilogue warp: 32 rows x 64 16-bit outputs, TMA-store staging
+constexpr size_t kGemmSmem = static_cast<size_t>(kStages) * kStageBytes + kEpiWarps * kEpiStageBytes + 1024 /*align*/ + 256 /*barriers*/;
 
 // ------------------------------------------------------------------ PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -82,6 +84,15 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
   asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
                : "memory");
 }
+
+// Tiled store shared -> global through the copy engine; clips at the tensor's edges.
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -125,6 +136,7 @@ struct GemmTcParams {
   int a_mn_major, b_mn_major;  // 0: K contiguous in global memory, 1: M (resp. N) contiguous
   int is_bf16;
   int has_bias;
+  int tma_store;    // 1 = C goes out through TMA tile stores (N % 8 == 0, aligned), 0 = plain stores
   int col_fastest;  // tile order: 1 = column-block fastest (write-bound shapes), 0 = grouped row-block fastest
 };
 
@@ -145,12 +157,13 @@ __device__ __forceinline__ void tile_coords(int64_t rem, int64_t mt, int64_t nt,
 
 template <typename T>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const T* __restrict__ bias, T* __restrict__ C, GemmTcParams p,
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c, const T* __restrict__ bias, T* __restrict__ C, GemmTcParams p,
                     uint32_t* __restrict__ status) {
   extern __shared__ unsigned char smem_raw[];
   // 1024-byte alignment: the 128B swizzle pattern repeats every 8 rows x 128 bytes
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+  unsigned char* epi_stage = smem + kStages * kStageBytes;  // kEpiWarps x 4 KB, each 1024-byte aligned
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes + kEpiWarps * kEpiStageBytes);
   // barrier slots: [0,S) full, [S,2S) empty, [2S,2S+2) tmem_full, [2S+2,2S+4) tmem_empty
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
   volatile uint32_t* abort_flag = tmem_base_slot + 1;
@@ -285,7 +298,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       if (!got) { ok = false; break; }
       tc_fence_after();
       const int64_t m = m0 + q * 32 + lane;
-      T* crow = C + (b * p.M + m) * p.N;
       const uint32_t t_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * kBN + chalf * (kBN / 2));
 #pragma unroll 1
       for (int c = 0; c < kBN / 2 / 64; ++c) {
@@ -294,7 +306,36 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         tc_ld_32x32(t_base + c * 64 + 32, r + 32);
         tc_ld_wait();
         const int64_t nb = n0 + c * 64;
-        if (m < p.M && nb < p.N) {
+        if (p.tma_store) {
+          // scale / bias in fp32, round once, park the lane's 64 outputs of its row in this
+          // warp's 32 x 128-byte buffer in the 128-byte-swizzle layout (16-byte chunk index
+          // XOR row) -- conflict-free to write and exactly what a SWIZZLE_128B tiled store
+          // reads -- then one lane hands the 32 x 64 tile to the copy engine, which writes
+          // whole lines and clips at the edges of C.
+          unsigned char* mine = epi_stage + (warp - 2) * kEpiStageBytes;
+          if (lane == 0) tma_store_wait_read();  // the previous tile store has finished reading the buffer
+          __syncwarp();
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            const int64_t n = nb + g * 8;
+            Vec<T> o;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              float v = p.alpha * __uint_as_float(r[g * 8 + e]);
+              if (p.has_bias && m < p.M && n + e < p.N) v = fmaf(p.beta, to_f32(bias[m * p.sbm + (n + e) * p.sbn]), v);
+              o.set(e, from_f32<T>(v));
+            }
+            *reinterpret_cast<uint4*>(mine + lane * 128 + ((g ^ (lane & 7)) << 4)) = o.raw;
+          }
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0 && nb < p.N && m0 + q * 32 < p.M) {
+            tma_store_3d(&map_c, smem_u32(mine), static_cast<int>(nb), static_cast<int>(m0 + q * 32), static_cast<int>(b));
+            tma_store_commit();
+          }
+        } else if (m < p.M && nb < p.N) {
+          T* crow = C + (b * p.M + m) * p.N;
+
 #pragma unroll
           for (int g = 0; g < 8; ++g) {
             const int64_t n = nb + g * 8;
@@ -323,10 +364,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
+    if (lane == 0) tma_store_wait_all();  // tile stores must have left shared memory before the CTA exits
     if (!ok && lane == 0) {
       *abort_flag = 1;
       if (status) atomicOr(status, B200_DEV_WAIT_TIMEOUT);
     }
+    __syncwarp();
   }
 
   // ---------------------------------------------------------------- teardown
@@ -412,7 +455,21 @@ int gemm_tc_dispatch(const void* A, const void* B, const void* bias, void* C, in
   alignas(64) CUtensorMap map_a, map_b;
   if (!encode_operand(&map_a, A, dtype, la.mn_major, M, K, sAm, sAk, sAb, batch, kBM)) return B200_EDRIVER;
   if (!encode_operand(&map_b, B, dtype, lb.mn_major, N, K, sBn, sBk, sBb, batch, kBN)) return B200_EDRIVER;
+  alignas(64) CUtensorMap map_c;
+  const bool tma_store = (N % 8 == 0) && aligned16(C);
+  if (tma_store) {
+    cuuint64_t dims[3] = {static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(M), static_cast<cuuint64_t>(batch)};
+    cuuint64_t strides[2] = {static_cast<cuuint64_t>(N) * 2, static_cast<cuuint64_t>(M) * static_cast<cuuint64_t>(N) * 2};
+    cuuint32_t box[3] = {64, 32, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    const CUtensorMapDataType dt = dtype == B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    if (encode_fn()(&map_c, dt, 3, C, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return B200_EDRIVER;
+  } else {
+    map_c = map_a;  // unused by the kernel in this mode
+  }
   GemmTcParams p;
+  p.tma_store = tma_store ? 1 : 0;
   p.M = M; p.N = N; p.K = K; p.batch = batch;
   p.sbm = sbm; p.sbn = sbn;
   p.alpha = static_cast<float>(alpha);
@@ -431,11 +488,11 @@ int gemm_tc_dispatch(const void* A, const void* B, const void* bias, void* C, in
   if (dtype == B200_BF16) {
     e = cudaFuncSetAttribute(gemm_tcgen05_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemmSmem));
     if (e != cudaSuccess) { set_last_cuda_error(e); return B200_ELAUNCH; }
-    gemm_tcgen05_kernel<__nv_bfloat16><<<grid, kGemmThreads, kGemmSmem, st>>>(map_a, map_b, static_cast<const __nv_bfloat16*>(bias), static_cast<__nv_bfloat16*>(C), p, status);
+    gemm_tcgen05_kernel<__nv_bfloat16><<<grid, kGemmThreads, kGemmSmem, st>>>(map_a, map_b, map_c, static_cast<const __nv_bfloat16*>(bias), static_cast<__nv_bfloat16*>(C), p, status);
   } else {
     e = cudaFuncSetAttribute(gemm_tcgen05_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemmSmem));
     if (e != cudaSuccess) { set_last_cuda_error(e); return B200_ELAUNCH; }
-    gemm_tcgen05_kernel<__half><<<grid, kGemmThreads, kGemmSmem, st>>>(map_a, map_b, static_cast<const __half*>(bias), static_cast<__half*>(C), p, status);
+    gemm_tcgen05_kernel<__half><<<grid, kGemmThreads, kGemmSmem, st>>>(map_a, map_b, map_c, static_cast<const __half*>(bias), static_cast<__half*>(C), p, status);
   }
   return check_launch();
 }

@@ -318,6 +318,278 @@ __global__ void __launch_bounds__(128) scatter_add_lines(float* __restrict__ out
   }
 }
 
+// ------------------------------------------------------------------ bucket path
+// For shapes with little column / row parallelism (tall and narrow, ragged, strided) the
+// sources are first grouped by DESTINATION: count per destination (integer atomics -- their
+// order does not matter), exclusive scan, then every source drops (position along the
+// scatter dimension, value) into its destination's segment at an arbitrary slot. One thread
+// per destination finally replays its segment in ascending position, i.e. in the aten CPU
+// order. Fully parallel over sources and destinations; ~3x the algorithmic traffic.
+// Destinations with more than kLightMax contributions go to a CTA-cooperative replay.
+constexpr int kLightMax = 32;
+constexpr int kScanBlock = 256, kScanItems = 16, kScanTile = kScanBlock * kScanItems;
+constexpr int kHeavyWindow = 4096;
+
+struct BucketArgs {
+  int ndim, dim;
+  int64_t n_idx, n_self, dim_len, self_dim_size;
+  int64_t shape[B200_MAX_DIMS];  // index shape
+  int64_t out_stride[B200_MAX_DIMS], idx_stride[B200_MAX_DIMS], src_stride[B200_MAX_DIMS];
+};
+
+__device__ __forceinline__ bool bucket_decode(const BucketArgs& A, int64_t p, const int64_t* __restrict__ index, int64_t& dest, int64_t& so, int& pos, uint32_t* status) {
+  int64_t lin = p, oo = 0, io = 0;
+  so = 0;
+  pos = 0;
+  for (int d = A.ndim - 1; d >= 0; --d) {
+    const int64_t q = lin / A.shape[d], r = lin - q * A.shape[d];
+    io += r * A.idx_stride[d];
+    so += r * A.src_stride[d];
+    if (d == A.dim) pos = static_cast<int>(r);
+    else oo += r * A.out_stride[d];
+    lin = q;
+  }
+  const int64_t key = index[io];
+  if (key < 0 || key >= A.self_dim_size) {
+    flag_oob(status);
+    return false;
+  }
+  dest = oo + key * A.out_stride[A.dim];
+  return true;
+}
+
+__global__ void __launch_bounds__(256) bucket_count(const int64_t* __restrict__ index, int* __restrict__ cnt, BucketArgs A, uint32_t* status) {
+  for (int64_t p = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; p < A.n_idx; p += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    int64_t dest, so;
+    int pos;
+    if (bucket_decode(A, p, index, dest, so, pos, nullptr)) atomicAdd(&cnt[dest], 1);
+  }
+}
+
+// Exclusive scan of cnt[0, n) in three launches: per-tile totals, scan of the totals by one
+// CTA, per-tile rescan with the tile's prefix. Writes offs (in place) and a copy in cursor.
+__global__ void __launch_bounds__(kScanBlock) scan_tile_totals(const int* __restrict__ cnt, int* __restrict__ totals, int64_t n) {
+  __shared__ int red[kScanBlock / 32];
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * kScanTile;
+  int s = 0;
+  for (int i = threadIdx.x; i < kScanTile; i += kScanBlock)
+    if (base + i < n) s += cnt[base + i];
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int t = 0;
+    for (int w = 0; w < kScanBlock / 32; ++w) t += red[w];
+    totals[blockIdx.x] = t;
+  }
+}
+__global__ void __launch_bounds__(1024) scan_totals(int* __restrict__ totals, int64_t ntiles, int* __restrict__ grand_total) {
+  __shared__ int warp_sums[32];
+  __shared__ int carry;
+  if (threadIdx.x == 0) carry = 0;
+  __syncthreads();
+  for (int64_t base = 0; base < ntiles; base += 1024) {
+    const int64_t i = base + threadIdx.x;
+    const int v = i < ntiles ? totals[i] : 0;
+    int inc = v;
+    for (int o = 1; o < 32; o <<= 1) {
+      const int y = __shfl_up_sync(0xffffffffu, inc, o);
+      if ((threadIdx.x & 31) >= o) inc += y;
+    }
+    if ((threadIdx.x & 31) == 31) warp_sums[threadIdx.x >> 5] = inc;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      int w = warp_sums[threadIdx.x];
+      for (int o = 1; o < 32; o <<= 1) {
+        const int y = __shfl_up_sync(0xffffffffu, w, o);
+        if (threadIdx.x >= o) w += y;
+      }
+      warp_sums[threadIdx.x] = w;
+    }
+    __syncthreads();
+    const int warp_prefix = (threadIdx.x >> 5) ? warp_sums[(threadIdx.x >> 5) - 1] : 0;
+    const int excl = carry + warp_prefix + inc - v;
+    if (i < ntiles) totals[i] = excl;
+    __syncthreads();
+    if (threadIdx.x == 1023) carry = excl + v;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) *grand_total = carry;
+}
+__global__ void __launch_bounds__(kScanBlock) scan_apply(int* __restrict__ cnt_offs, int* __restrict__ cursor, const int* __restrict__ totals, int64_t n) {
+  __shared__ int warp_sums[kScanBlock / 32];
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * kScanTile + static_cast<int64_t>(threadIdx.x) * kScanItems;
+  int v[kScanItems], s = 0;
+#pragma unroll
+  for (int k = 0; k < kScanItems; ++k) {
+    v[k] = base + k < n ? cnt_offs[base + k] : 0;
+    s += v[k];
+  }
+  int inc = s;
+  for (int o = 1; o < 32; o <<= 1) {
+    const int y = __shfl_up_sync(0xffffffffu, inc, o);
+    if ((threadIdx.x & 31) >= o) inc += y;
+  }
+  if ((threadIdx.x & 31) == 31) warp_sums[threadIdx.x >> 5] = inc;
+  __syncthreads();
+  int prefix = totals[blockIdx.x] + inc - s;
+  for (int w = 0; w < (threadIdx.x >> 5); ++w) prefix += warp_sums[w];
+#pragma unroll
+  for (int k = 0; k < kScanItems; ++k) {
+    if (base + k < n) {
+      cnt_offs[base + k] = prefix;
+      cursor[base + k] = prefix;
+    }
+    prefix += v[k];
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) bucket_fill(const int64_t* __restrict__ index, const T* __restrict__ src, int* __restrict__ cursor, int* __restrict__ seg_pos, float* __restrict__ seg_val,
+                                                   BucketArgs A, uint32_t* status) {
+  for (int64_t p = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; p < A.n_idx; p += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    int64_t dest, so;
+    int pos;
+    if (bucket_decode(A, p, index, dest, so, pos, status)) {
+      const int slot = atomicAdd(&cursor[dest], 1);
+      seg_pos[slot] = pos;
+      seg_val[slot] = to_f32(src[so]);
+    }
+  }
+}
+
+// One thread per destination: replay its segment in ascending source position.
+template <typename T>
+__global__ void __launch_bounds__(256) bucket_replay(const T* __restrict__ self, T* __restrict__ out, const int* __restrict__ offs, const int* __restrict__ grand_total,
+                                                     const int* __restrict__ seg_pos, const float* __restrict__ seg_val, int64_t n_self, int* __restrict__ heavy_count,
+                                                     int* __restrict__ heavy_list) {
+  for (int64_t d = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; d < n_self; d += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int b = offs[d], e = d + 1 < n_self ? offs[d + 1] : *grand_total;
+    const int c = e - b;
+    if (c == 0) {
+      out[d] = self[d];
+    } else if (c <= kLightMax) {
+      float acc = to_f32(self[d]);
+      int last = -1;
+      for (int i = 0; i < c; ++i) {
+        int best = 0x7fffffff;
+        float bv = 0.f;
+        for (int j = b; j < e; ++j) {
+          const int pj = seg_pos[j];
+          if (pj > last && pj < best) { best = pj; bv = seg_val[j]; }
+        }
+        acc += bv;
+        last = best;
+      }
+      out[d] = from_f32<T>(acc);
+    } else {
+      heavy_list[atomicAdd(heavy_count, 1)] = static_cast<int>(d);
+    }
+  }
+}
+
+// Destinations with long segments: one CTA each. The segment is visited in windows of
+// kHeavyWindow source positions; inside a window every element is parked at its position,
+// the occupied slots are compacted in order with a block scan, and one thread adds them.
+template <typename T>
+__global__ void __launch_bounds__(256) bucket_replay_heavy(const T* __restrict__ self, T* __restrict__ out, const int* __restrict__ offs, const int* __restrict__ grand_total,
+                                                           const int* __restrict__ seg_pos, const float* __restrict__ seg_val, int64_t n_self, int64_t dim_len,
+                                                           const int* __restrict__ heavy_count, const int* __restrict__ heavy_list) {
+  __shared__ float slot_val[kHeavyWindow];
+  __shared__ unsigned char slot_set[kHeavyWindow];
+  __shared__ float ordered[kHeavyWindow];
+  __shared__ int warp_sums[8];
+  __shared__ int window_count;
+  __shared__ float acc_s;
+  const int nheavy = *heavy_count;
+  constexpr int kPer = kHeavyWindow / 256;
+  for (int h = blockIdx.x; h < nheavy; h += gridDim.x) {
+    const int64_t d = heavy_list[h];
+    const int b = offs[d], e = d + 1 < n_self ? offs[d + 1] : *grand_total;
+    if (threadIdx.x == 0) acc_s = to_f32(self[d]);
+    for (int64_t w0 = 0; w0 < dim_len; w0 += kHeavyWindow) {
+      for (int i = threadIdx.x; i < kHeavyWindow; i += 256) slot_set[i] = 0;
+      __syncthreads();
+      for (int j = b + threadIdx.x; j < e; j += 256) {
+        const int64_t pj = seg_pos[j];
+        if (pj >= w0 && pj < w0 + kHeavyWindow) {
+          slot_val[pj - w0] = seg_val[j];
+          slot_set[pj - w0] = 1;
+        }
+      }
+      __syncthreads();
+      int mine = 0;
+#pragma unroll
+      for (int k = 0; k < kPer; ++k) mine += slot_set[threadIdx.x * kPer + k];
+      int inc = mine;
+      for (int o = 1; o < 32; o <<= 1) {
+        const int y = __shfl_up_sync(0xffffffffu, inc, o);
+        if ((threadIdx.x & 31) >= o) inc += y;
+      }
+      if ((threadIdx.x & 31) == 31) warp_sums[threadIdx.x >> 5] = inc;
+      __syncthreads();
+      int prefix = inc - mine;
+      for (int w = 0; w < (threadIdx.x >> 5); ++w) prefix += warp_sums[w];
+      if (threadIdx.x == 255) window_count = prefix + mine;
+#pragma unroll
+      for (int k = 0; k < kPer; ++k)
+        if (slot_set[threadIdx.x * kPer + k]) ordered[prefix++] = slot_val[threadIdx.x * kPer + k];
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        float acc = acc_s;
+        const int n = window_count;
+        for (int i = 0; i < n; ++i) acc += ordered[i];
+        acc_s = acc;
+      }
+      __syncthreads();
+    }
+    if (threadIdx.x == 0) out[d] = from_f32<T>(acc_s);
+    __syncthreads();
+  }
+}
+
+struct BucketScratch {
+  int64_t offs_bytes, cursor_bytes, pos_bytes, val_bytes, totals_bytes, heavy_bytes, total;
+};
+static BucketScratch bucket_scratch(int64_t n_self, int64_t n_idx) {
+  auto up = [](int64_t b) { return (b + 255) / 256 * 256; };
+  BucketScratch s;
+  s.offs_bytes = up(4 * (n_self + 1));
+  s.cursor_bytes = up(4 * n_self);
+  s.pos_bytes = up(4 * n_idx);
+  s.val_bytes = up(4 * n_idx);
+  s.totals_bytes = up(4 * ((n_self + kScanTile - 1) / kScanTile + 2));
+  s.heavy_bytes = up(4 * (n_idx / (kLightMax + 1) + 4));
+  s.total = s.offs_bytes + s.cursor_bytes + s.pos_bytes + s.val_bytes + s.totals_bytes + s.heavy_bytes;
+  return s;
+}
+
+template <typename T>
+static int launch_bucket(const void* self, const void* index, const void* src, void* out, const BucketArgs& A, void* scratch, uint32_t* status, cudaStream_t st) {
+  const BucketScratch S = bucket_scratch(A.n_self, A.n_idx);
+  char* base = static_cast<char*>(scratch);
+  int* offs = reinterpret_cast<int*>(base);
+  int* cursor = reinterpret_cast<int*>(base + S.offs_bytes);
+  int* seg_pos = reinterpret_cast<int*>(base + S.offs_bytes + S.cursor_bytes);
+  float* seg_val = reinterpret_cast<float*>(base + S.offs_bytes + S.cursor_bytes + S.pos_bytes);
+  int* totals = reinterpret_cast<int*>(base + S.offs_bytes + S.cursor_bytes + S.pos_bytes + S.val_bytes);
+  int* heavy = reinterpret_cast<int*>(base + S.offs_bytes + S.cursor_bytes + S.pos_bytes + S.val_bytes + S.totals_bytes);  // [0] count, [1] grand total, [4..] list
+  cudaError_t e = cudaMemsetAsync(offs, 0, static_cast<size_t>(S.offs_bytes), st);
+  if (e == cudaSuccess) e = cudaMemsetAsync(heavy, 0, 16, st);
+  if (e != cudaSuccess) { set_last_cuda_error(e); return B200_ELAUNCH; }
+  const int64_t* pi = static_cast<const int64_t*>(index);
+  auto grid = [](int64_t n, int per) { int64_t g = (n + per - 1) / per; const int64_t cap = 32LL * kNumSMs; return static_cast<int>(g < 1 ? 1 : (g > cap ? cap : g)); };
+  const int64_t ntiles = (A.n_self + kScanTile - 1) / kScanTile;
+  bucket_count<<<grid(A.n_idx, 256), 256, 0, st>>>(pi, offs, A, status);
+  scan_tile_totals<<<static_cast<unsigned>(ntiles), kScanBlock, 0, st>>>(offs, totals, A.n_self);
+  scan_totals<<<1, 1024, 0, st>>>(totals, ntiles, heavy + 1);
+  scan_apply<<<static_cast<unsigned>(ntiles), kScanBlock, 0, st>>>(offs, cursor, totals, A.n_self);
+  bucket_fill<T><<<grid(A.n_idx, 256), 256, 0, st>>>(pi, static_cast<const T*>(src), cursor, seg_pos, seg_val, A, status);
+  bucket_replay<T><<<grid(A.n_self, 256), 256, 0, st>>>(static_cast<const T*>(self), static_cast<T*>(out), offs, heavy + 1, seg_pos, seg_val, A.n_self, heavy, heavy + 4);
+  bucket_replay_heavy<T><<<2 * kNumSMs, 256, 0, st>>>(static_cast<const T*>(self), static_cast<T*>(out), offs, heavy + 1, seg_pos, seg_val, A.n_self, A.dim_len, heavy, heavy + 4);
+  return check_launch(7);
+}
+
 template <typename T>
 static int launch_strip(const void* self, const void* index, const void* src, void* out, StripArgs A, uint32_t* status, cudaStream_t st) {
   const int tile_bytes = kTileRows * kStripCols * (8 + static_cast<int>(sizeof(T)));
@@ -362,29 +634,34 @@ static int launch_rows(const void* self, const void* index, const void* src, voi
 
 }  // namespace b200
 
-using namespace b200;
+namespace b200 {
 
-extern "C" int b200_scatter_add(const void* self, const void* index, const void* src, void* out, int ndim, const int64_t* self_shape, const int64_t* index_shape,
-                                const int64_t* index_strides, const int64_t* src_strides, int dim, int dtype, void* scratch, int64_t scratch_bytes, uint32_t* status, void* stream) {
-  if (ndim < 1 || ndim > B200_MAX_DIMS || dim < 0 || dim >= ndim || !self_shape || !index_shape || !index_strides || !src_strides) return B200_EINVAL;
-  if (!is_float_dtype(dtype)) return B200_EDTYPE;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int64_t n_self = numel_of(ndim, self_shape);
-  const int64_t n_idx = numel_of(ndim, index_shape);
-  for (int d = 0; d < ndim; ++d)
-    if (self_shape[d] < 0 || index_shape[d] < 0 || (d != dim && index_shape[d] > self_shape[d])) return B200_EINVAL;
-  if (n_self == 0) return B200_OK;
-  if (!self || !out) return B200_EINVAL;
+enum ScatterPath { kPathNone = 0, kPathStrip, kPathRows, kPathBucket, kPathLines };
+
+struct ScatterPlan {
+  ScatterPath path;
+  int64_t n_self, n_idx, scratch_bytes;
+  StripArgs strip;
+  RowArgs rows;
+};
+
+// Decides which kernel family serves a geometry (shared by the launcher and the scratch
+// query so that both always agree).
+static ScatterPlan plan_scatter(const void* self, const void* index, const void* src, const void* out, int ndim, const int64_t* self_shape, const int64_t* index_shape,
+                                const int64_t* index_strides, const int64_t* src_strides, int dim, int dtype) {
+  ScatterPlan P{};
+  P.n_self = numel_of(ndim, self_shape);
+  P.n_idx = numel_of(ndim, index_shape);
   const int es = dtype_size(dtype);
-
-  // ---- [outer, rows, cols] view; index / src must be plain row-major views of it
-  if (n_idx > 0 && index && src && aligned16(self) && aligned16(out) && aligned16(index) && aligned16(src)) {
+  P.path = kPathLines;
+  if (P.n_self == 0 || P.n_idx == 0) { P.path = kPathNone; return P; }
+  const bool small = P.n_idx <= (1 << 16);  // launch-bound either way
+  if (aligned16(self) && aligned16(out) && aligned16(index) && aligned16(src)) {
     int64_t outer = 1, cols = 1, idx_outer = 1, idx_cols = 1;
     for (int d = 0; d < dim; ++d) { outer *= self_shape[d]; idx_outer *= index_shape[d]; }
     for (int d = dim + 1; d < ndim; ++d) { cols *= self_shape[d]; idx_cols *= index_shape[d]; }
     const int64_t rows = self_shape[dim], idx_rows = index_shape[dim];
-    // collapsible only when at most one leading and one trailing dim are non-trivial
-    int lead = 0, trail = 0, dl = -1, dt = -1;
+    int lead = 0, trail = 0, dl = -1, dt = -1;  // collapsible only with at most one non-trivial dim on each side
     for (int d = 0; d < dim; ++d)
       if (self_shape[d] > 1 || index_shape[d] > 1) { ++lead; dl = d; }
     for (int d = dim + 1; d < ndim; ++d)
@@ -395,26 +672,97 @@ extern "C" int b200_scatter_add(const void* self, const void* index, const void*
         const bool inner_ok = index_strides[dt] == 1 && src_strides[dt] == 1;
         const bool shape_ok = cols % kStripCols == 0 && idx_cols % kStripCols == 0;
         const bool stride_ok = (src_strides[dim] * es) % 4 == 0 && (src_so * es) % 4 == 0;  // 4-byte value granules
-        if (inner_ok && shape_ok && stride_ok) {
-          StripArgs A{outer, rows, cols, idx_outer, idx_rows, idx_cols, idx_so, index_strides[dim], src_so, src_strides[dim], 0, 0};
-          switch (dtype) {
-            case B200_F32: return launch_strip<float>(self, index, src, out, A, status, st);
-            case B200_BF16: return launch_strip<__nv_bfloat16>(self, index, src, out, A, status, st);
-            default: return launch_strip<__half>(self, index, src, out, A, status, st);
-          }
+        const int64_t strips = outer * (cols / kStripCols);
+        const bool fits = rows * kStripCols * 4 <= 2 * (kSmemBudget - 64 * 1024);  // at most two destination windows
+        if (inner_ok && shape_ok && stride_ok && fits && (strips >= 32 || small)) {
+          P.path = kPathStrip;
+          P.strip = StripArgs{outer, rows, cols, idx_outer, idx_rows, idx_cols, idx_so, index_strides[dim], src_so, src_strides[dim], 0, 0};
+          return P;
         }
       } else if (index_strides[dim] == 1 && src_strides[dim] == 1) {
-        RowArgs A{outer, rows, idx_outer, idx_rows, idx_so, src_so, 0};
-        switch (dtype) {
-          case B200_F32: return launch_rows<float>(self, index, src, out, A, status, st);
-          case B200_BF16: return launch_rows<__nv_bfloat16>(self, index, src, out, A, status, st);
-          default: return launch_rows<__half>(self, index, src, out, A, status, st);
+        const bool fits = rows * 2 * 4 <= kSmemBudget - 16 * 1024;
+        if (fits && (outer >= 64 || small)) {
+          P.path = kPathRows;
+          P.rows = RowArgs{outer, rows, idx_outer, idx_rows, idx_so, src_so, 0};
+          return P;
         }
       }
     }
   }
+  // short lines are cheapest walked by one thread each; anything longer is grouped by destination
+  if (P.n_self < 0x7fffffffLL && P.n_idx < 0x7fffffffLL && index_shape[dim] < 0x7fffffffLL && index_shape[dim] > 64) {
+    P.path = kPathBucket;
+    P.scratch_bytes = bucket_scratch(P.n_self, P.n_idx).total;
+    return P;
+  }
+  P.scratch_bytes = dtype == B200_F32 ? 0 : P.n_self * 4;  // fp32 accumulator of the line kernel
+  return P;
+}
 
-  // ---- generic: acc = fp32(self), ordered lines on acc, out = round(acc)
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int64_t b200_scatter_add_scratch_bytes(const void* self, const void* index, const void* src, const void* out, int ndim, const int64_t* self_shape,
+                                                   const int64_t* index_shape, const int64_t* index_strides, const int64_t* src_strides, int dim, int dtype) {
+  if (ndim < 1 || ndim > B200_MAX_DIMS || dim < 0 || dim >= ndim || !self_shape || !index_shape || !index_strides || !src_strides || !is_float_dtype(dtype)) return 0;
+  return plan_scatter(self, index, src, out, ndim, self_shape, index_shape, index_strides, src_strides, dim, dtype).scratch_bytes;
+}
+
+extern "C" int b200_scatter_add(const void* self, const void* index, const void* src, void* out, int ndim, const int64_t* self_shape, const int64_t* index_shape,
+                                const int64_t* index_strides, const int64_t* src_strides, int dim, int dtype, void* scratch, int64_t scratch_bytes, uint32_t* status, void* stream) {
+  if (ndim < 1 || ndim > B200_MAX_DIMS || dim < 0 || dim >= ndim || !self_shape || !index_shape || !index_strides || !src_strides) return B200_EINVAL;
+  if (!is_float_dtype(dtype)) return B200_EDTYPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  for (int d = 0; d < ndim; ++d)
+    if (self_shape[d] < 0 || index_shape[d] < 0 || (d != dim && index_shape[d] > self_shape[d])) return B200_EINVAL;
+  const int64_t n_self = numel_of(ndim, self_shape);
+  const int64_t n_idx = numel_of(ndim, index_shape);
+  if (n_self == 0) return B200_OK;
+  if (!self || !out) return B200_EINVAL;
+  if (n_idx > 0 && (!index || !src)) return B200_EINVAL;
+  const int es = dtype_size(dtype);
+  const ScatterPlan P = plan_scatter(self, index, src, out, ndim, self_shape, index_shape, index_strides, src_strides, dim, dtype);
+
+  if (P.path == kPathStrip) {
+    switch (dtype) {
+      case B200_F32: return launch_strip<float>(self, index, src, out, P.strip, status, st);
+      case B200_BF16: return launch_strip<__nv_bfloat16>(self, index, src, out, P.strip, status, st);
+      default: return launch_strip<__half>(self, index, src, out, P.strip, status, st);
+    }
+  }
+  if (P.path == kPathRows) {
+    switch (dtype) {
+      case B200_F32: return launch_rows<float>(self, index, src, out, P.rows, status, st);
+      case B200_BF16: return launch_rows<__nv_bfloat16>(self, index, src, out, P.rows, status, st);
+      default: return launch_rows<__half>(self, index, src, out, P.rows, status, st);
+    }
+  }
+  if (P.path == kPathBucket) {
+    if (!scratch || scratch_bytes < P.scratch_bytes) return B200_ESCRATCH;
+    BucketArgs A;
+    A.ndim = ndim;
+    A.dim = dim;
+    A.n_idx = n_idx;
+    A.n_self = n_self;
+    A.dim_len = index_shape[dim];
+    A.self_dim_size = self_shape[dim];
+    int64_t st_out = 1;
+    for (int d = ndim - 1; d >= 0; --d) {
+      A.shape[d] = index_shape[d];
+      A.out_stride[d] = st_out;
+      st_out *= self_shape[d];
+      A.idx_stride[d] = index_strides[d];
+      A.src_stride[d] = src_strides[d];
+    }
+    switch (dtype) {
+      case B200_F32: return launch_bucket<float>(self, index, src, out, A, scratch, status, st);
+      case B200_BF16: return launch_bucket<__nv_bfloat16>(self, index, src, out, A, scratch, status, st);
+      default: return launch_bucket<__half>(self, index, src, out, A, scratch, status, st);
+    }
+  }
+
+  // ---- line kernel: acc = fp32(self), ordered lines on acc, out = round(acc)
   const bool wide = dtype == B200_F32;
   float* acc = wide ? static_cast<float*>(out) : static_cast<float*>(scratch);
   if (!wide && (!scratch || scratch_bytes < n_self * 4)) return B200_ESCRATCH;

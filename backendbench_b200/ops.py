@@ -578,12 +578,16 @@ def scatter_add_default(self: torch.Tensor, dim: int, index: torch.Tensor, src: 
         rstr = list(src.stride()) or [1]
     else:
         ishape, istr, rstr = [0] * nd, [0] * nd, [0] * nd
-    need = 0 if x.dtype == torch.float32 else x.numel() * 4  # fp32 accumulator for 16-bit tensors
+    L = lib()
+    a_self, a_idx, a_src = i64_array(sshape), i64_array(ishape), i64_array(istr)
+    a_rstr = i64_array(rstr)
+    idx_ptr = index.data_ptr() if index.numel() else None
+    src_ptr = src.data_ptr() if index.numel() else None
+    need = L.b200_scatter_add_scratch_bytes(x.data_ptr(), idx_ptr, src_ptr, out.data_ptr(), nd, a_self, a_idx, a_src, a_rstr, dim, _dt(x.dtype))
     scratch = _scratch(x.device, need) if need else None
     check(
-        lib().b200_scatter_add(
-            x.data_ptr(), index.data_ptr() if index.numel() else None, src.data_ptr() if index.numel() else None, out.data_ptr(),
-            nd, i64_array(sshape), i64_array(ishape), i64_array(istr), i64_array(rstr), dim, _dt(x.dtype),
+        L.b200_scatter_add(
+            x.data_ptr(), idx_ptr, src_ptr, out.data_ptr(), nd, a_self, a_idx, a_src, a_rstr, dim, _dt(x.dtype),
             scratch.data_ptr() if need else None, need, _status(x.device).data_ptr(), _stream_handle(),
         ),
         "b200_scatter_add",

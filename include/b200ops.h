@@ -184,8 +184,14 @@ int b200_gather(const void* self, const void* index, void* out, int ndim,
  * index's shape out[p with p[dim] := index[p]] += src[p], applied in ASCENDING p[dim]
  * for each destination element -- the order of the sequential aten CPU kernel, so fp
  * results are bit-identical to it. self/out contiguous; index/src strided. bf16/f16
- * tensors accumulate in fp32 and round once (as aten CPU does): `scratch` must then
- * hold numel(self) * 4 bytes; fp32 tensors need none (NULL, 0). */
+ * tensors accumulate in fp32 and round once (as aten CPU does). Wide matrices run on
+ * shared-memory strip / row kernels without scratch; tall, narrow or strided geometries
+ * are grouped by destination first and need scratch (counters, segment storage): ask
+ * b200_scatter_add_scratch_bytes with the same arguments and pass at least that much. */
+int64_t b200_scatter_add_scratch_bytes(const void* self, const void* index, const void* src,
+                                       const void* out, int ndim, const int64_t* self_shape,
+                                       const int64_t* index_shape, const int64_t* index_strides,
+                                       const int64_t* src_strides, int dim, int dtype);
 int b200_scatter_add(const void* self, const void* index, const void* src, void* out, int ndim,
                      const int64_t* self_shape, const int64_t* index_shape,
                      const int64_t* index_strides, const int64_t* src_strides, int dim,

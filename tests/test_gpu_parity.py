@@ -217,6 +217,35 @@ def test_full_size_scatter_add_bit_exact_vs_aten_cpu_order(backend):
     ops.check_device_status()
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_scatter_add_grouped_by_destination_path_bit_exact(backend, dtype):
+    """Tall / narrow / ragged / strided geometries (too little column or row parallelism for
+    the shared-memory kernels) are grouped by destination and replayed in source order; a
+    few destinations with thousands of contributions take the cooperative replay."""
+    impl = backend[torch.ops.aten.scatter_add.default]
+    g = torch.Generator().manual_seed(21)
+
+    def rn(*shape):
+        return torch.randn(*shape, generator=g).to(dtype)
+
+    def ri(high, *shape):
+        return torch.randint(0, high, shape, generator=g)
+
+    cases = [
+        (rn(20000, 8), 0, ri(20000, 20000, 8), rn(20000, 8)),
+        (rn(30000, 24), 0, ri(30000, 15000, 24), rn(15000, 24)),
+        (rn(70000, 9), 0, ri(70000, 70000, 9), rn(70000, 9)),
+        (rn(64, 16), 0, ri(3, 9000, 16), rn(9000, 16)),  # ~3000 contributions per destination
+        (rn(16, 100000), 1, ri(100000, 16, 100000), rn(16, 100000)),
+        (rn(4, 3000, 10), 1, ri(3000, 4, 9000, 10), rn(4, 9000, 10)),
+        (rn(5000, 40), 0, ri(5000, 4000, 33), rn(6000, 48)[:, :40]),  # index narrower than self, strided src
+    ]
+    for x, dim, idx, src in cases:
+        got = impl(x.to(DEV), dim, idx.to(DEV), src.to(DEV))
+        assert bits_equal(oracle.scatter_add(x, dim, idx, src), got), (tuple(x.shape), dim, tuple(idx.shape))
+    ops.check_device_status()
+
+
 def test_full_size_argmax_bit_exact(backend):
     c, op, impl, args, kwargs = _full("argmax_f32_8192x32000", backend)
     got = impl(*args, **kwargs)
