@@ -432,6 +432,86 @@ __global__ void fill_zero_typed(void* out, int64_t n, int dto) {
   if (i < n) store_from_f32(out, i, dto, 0.f);
 }
 
+// ------------------------------------------------------------------ very short rows (dim <= 32, inner == 1)
+// Millions of rows of a handful of elements: one THREAD per row, the row in registers. A
+// warp reads 32 consecutive rows, i.e. one contiguous span, so the loads coalesce through L1.
+constexpr int kSmallRow = 32;
+enum { SMALL_SOFTMAX = 0, SMALL_LOGSOFTMAX = 1, SMALL_SUM = 2, SMALL_ARGMAX = 3, SMALL_LAYERNORM = 4 };
+
+template <typename T, int OP>
+__global__ void __launch_bounds__(256) rows_small(const T* __restrict__ x, void* __restrict__ out, int64_t rows, int cols, int dto, const void* __restrict__ w, const void* __restrict__ b,
+                                                  int dt_wb, void* __restrict__ mean, void* __restrict__ rstd, int dt_stat, float eps) {
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (row >= rows) return;
+  const T* xr = x + row * cols;
+  float f[kSmallRow];
+#pragma unroll
+  for (int c = 0; c < kSmallRow; ++c) f[c] = c < cols ? to_f32(xr[c]) : 0.f;
+  if (OP == SMALL_SUM) {
+    float s = 0.f;
+#pragma unroll
+    for (int c = 0; c < kSmallRow; ++c) s += c < cols ? f[c] : 0.f;
+    store_from_f32(out, row, dto, s);
+  } else if (OP == SMALL_ARGMAX) {
+    ArgPair a{CUDART_NAN_F, -1};
+#pragma unroll
+    for (int c = 0; c < kSmallRow; ++c)
+      if (c < cols) arg_take_ascending(a, f[c], c);
+    static_cast<int64_t*>(out)[row] = a.i;
+  } else if (OP == SMALL_LAYERNORM) {
+    float s = 0.f;
+#pragma unroll
+    for (int c = 0; c < kSmallRow; ++c) s += c < cols ? f[c] : 0.f;
+    float mu = s / static_cast<float>(cols);
+    if (!isfinite(mu)) mu = CUDART_NAN_F;
+    float q = 0.f;
+#pragma unroll
+    for (int c = 0; c < kSmallRow; ++c) {
+      const float d = f[c] - mu;
+      q = c < cols ? fmaf(d, d, q) : q;
+    }
+    const float rs = rsqrtf(q / static_cast<float>(cols) + eps);
+    store_from_f32(mean, row, dt_stat, mu);
+    store_from_f32(rstd, row, dt_stat, rs);
+#pragma unroll
+    for (int c = 0; c < kSmallRow; ++c)
+      if (c < cols) {
+        float r = (f[c] - mu) * rs;
+        if (w) r *= load_as_f32(w, c, dt_wb);
+        if (b) r += load_as_f32(b, c, dt_wb);
+        store_from_f32(out, row * cols + c, dto, r);
+      }
+  } else {
+    float m = -CUDART_INF_F;
+#pragma unroll
+    for (int c = 0; c < kSmallRow; ++c) m = c < cols ? fmaxf(m, f[c]) : m;
+    float s = 0.f;
+#pragma unroll
+    for (int c = 0; c < kSmallRow; ++c) {
+      const float d = f[c] - m;
+      const float ex = exp2f(d * kLog2e);
+      s += c < cols ? ex : 0.f;
+      f[c] = OP == SMALL_LOGSOFTMAX ? d : ex;
+    }
+    const float k = OP == SMALL_LOGSOFTMAX ? logf(s) : 1.f / s;
+#pragma unroll
+    for (int c = 0; c < kSmallRow; ++c)
+      if (c < cols) store_from_f32(out, row * cols + c, dto, OP == SMALL_LOGSOFTMAX ? f[c] - k : f[c] * k);
+  }
+}
+
+template <int OP>
+static int launch_rows_small(const void* x, void* out, int64_t rows, int cols, int dti, int dto, const void* w, const void* b, int dt_wb, void* mean, void* rstd, int dt_stat, float eps,
+                             cudaStream_t st) {
+  const int g = grid_for(rows, 256);
+  switch (dti) {
+    case B200_F32: rows_small<float, OP><<<g, 256, 0, st>>>(static_cast<const float*>(x), out, rows, cols, dto, w, b, dt_wb, mean, rstd, dt_stat, eps); break;
+    case B200_BF16: rows_small<__nv_bfloat16, OP><<<g, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), out, rows, cols, dto, w, b, dt_wb, mean, rstd, dt_stat, eps); break;
+    default: rows_small<__half, OP><<<g, 256, 0, st>>>(static_cast<const __half*>(x), out, rows, cols, dto, w, b, dt_wb, mean, rstd, dt_stat, eps); break;
+  }
+  return check_launch();
+}
+
 // ------------------------------------------------------------------ host-side planning
 struct ReducePlan {
   int splits;
@@ -443,9 +523,9 @@ static ReducePlan plan_reduce(int64_t outer, int64_t dim, int64_t inner) {
   int64_t ctas = inner == 1 ? outer : outer * ((inner + 255) / 256);
   ReducePlan p{1, dim};
   const int64_t want = 2LL * kNumSMs;
-  if (ctas >= want || dim < 16384) return p;
+  if (ctas >= want || dim < 4096) return p;
   int64_t s = (want + ctas - 1) / ctas;
-  const int64_t max_s = dim / 4096;  // keep >= 4096 elements per split
+  const int64_t max_s = dim / 1024;  // keep >= 1024 elements per split
   if (s > max_s) s = max_s;
   if (s > 1024) s = 1024;
   if (s <= 1) return p;
@@ -586,6 +666,9 @@ extern "C" int b200_softmax(const void* x, void* out, int64_t outer, int64_t dim
   if (outer == 0 || dim == 0 || inner == 0) return B200_OK;
   if (!x || !out) return B200_EINVAL;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (inner == 1 && dim <= kSmallRow && outer >= 4096)
+    return is_log ? launch_rows_small<SMALL_LOGSOFTMAX>(x, out, outer, static_cast<int>(dim), dti, dto, nullptr, nullptr, 0, nullptr, nullptr, 0, 0.f, st)
+                  : launch_rows_small<SMALL_SOFTMAX>(x, out, outer, static_cast<int>(dim), dti, dto, nullptr, nullptr, 0, nullptr, nullptr, 0, 0.f, st);
   switch (dti) {
     case B200_F32: return softmax_T<float>(x, out, outer, dim, inner, dto, is_log, st);
     case B200_BF16: return softmax_T<__nv_bfloat16>(x, out, outer, dim, inner, dto, is_log, st);
@@ -610,6 +693,7 @@ extern "C" int b200_sum(const void* x, void* out, int64_t outer, int64_t dim, in
     return check_launch();
   }
   if (!x) return B200_EINVAL;
+  if (inner == 1 && dim <= kSmallRow && outer >= 4096) return launch_rows_small<SMALL_SUM>(x, out, outer, static_cast<int>(dim), dti, dto, nullptr, nullptr, 0, nullptr, nullptr, 0, 0.f, st);
   switch (dti) {
     case B200_F32: return launch_reduce_T<float, false>(x, out, outer, dim, inner, dto, scratch, scratch_bytes, st);
     case B200_BF16: return launch_reduce_T<__nv_bfloat16, false>(x, out, outer, dim, inner, dto, scratch, scratch_bytes, st);
@@ -623,6 +707,7 @@ extern "C" int b200_argmax(const void* x, int64_t* out, int64_t outer, int64_t d
   if (outer == 0 || inner == 0) return B200_OK;
   if (!x || !out) return B200_EINVAL;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (inner == 1 && dim <= kSmallRow && outer >= 4096) return launch_rows_small<SMALL_ARGMAX>(x, out, outer, static_cast<int>(dim), dt, B200_I64, nullptr, nullptr, 0, nullptr, nullptr, 0, 0.f, st);
   switch (dt) {
     case B200_F32: return launch_reduce_T<float, true>(x, out, outer, dim, inner, B200_I64, scratch, scratch_bytes, st);
     case B200_BF16: return launch_reduce_T<__nv_bfloat16, true>(x, out, outer, dim, inner, B200_I64, scratch, scratch_bytes, st);
@@ -639,6 +724,7 @@ extern "C" int b200_layer_norm(const void* x, const void* w, const void* b, void
   if (rows > 0x7fffffffLL) return B200_EINVAL;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const float e = static_cast<float>(eps);
+  if (cols > 0 && cols <= kSmallRow && rows >= 4096) return launch_rows_small<SMALL_LAYERNORM>(x, y, rows, static_cast<int>(cols), dt, dt, w, b, dt_wb, mean, rstd, dt_stat, e, st);
   const int ve = 16 / dtype_size(dt);
   const bool wb_ok = (!w && !b) || dt_wb == dt || dt_wb == B200_F32;
   const bool al = aligned16(x) && aligned16(y) && (!w || aligned16(w)) && (!b || aligned16(b));

@@ -311,8 +311,19 @@ def _softmax_impl(self: torch.Tensor, dim: int, half_to_float: bool, log: bool) 
     out_dtype = torch.float32 if half_to_float else self.dtype
     out = torch.empty(self.shape, dtype=out_dtype, device=self.device)
     if out.numel():
+        outer, d, inner = _split_at(list(self.shape) or [1], dim)
+        if inner > 1 and d >= 128 and outer * ((inner + 127) // 128) < 592:
+            # a long reduction over a non-last dim with few columns: too few threads for the
+            # column kernel. Move the dim last with the strided-copy kernel, run the row
+            # kernel, and copy the result back through the inverse permutation.
+            xt = _contig(self.movedim(dim, -1))
+            tmp = torch.empty(xt.shape, dtype=out_dtype, device=self.device)
+            check(lib().b200_softmax(xt.data_ptr(), tmp.data_ptr(), xt.numel() // d, d, 1, _dt(xt.dtype), _dt(out_dtype), 1 if log else 0, _stream_handle()), "b200_softmax")
+            back = tmp.movedim(-1, dim)  # a view with out's shape
+            nd, shp, (st,) = _iter_layout(out.shape, [back])
+            check(lib().b200_copy_strided(back.data_ptr(), out.data_ptr(), nd, shp, st, _dt(out_dtype), _dt(out_dtype), _stream_handle()), "b200_copy_strided")
+            return out
         x = _contig(self)
-        outer, d, inner = _split_at(list(x.shape) or [1], dim)
         check(lib().b200_softmax(x.data_ptr(), out.data_ptr(), outer, d, inner, _dt(x.dtype), _dt(out_dtype), 1 if log else 0, _stream_handle()), "b200_softmax")
     return out
 

@@ -222,13 +222,18 @@ def per_kernel_profile(prepared):
         p["impl"](*p["args"], **p["kwargs"])
         ends[i].record()
     torch.cuda.synchronize()
+    per_case = []
     for i, p in enumerate(prepared):
         c = p["case"]
+        per_case.append((starts[i].elapsed_time(ends[i]), c.label() + (" " + str(dict(c.extra)) if c.extra else "")))
         d = by_op.setdefault(c.op, {"ms": 0.0, "bytes": 0, "flops": 0, "launches": 0})
         d["ms"] += starts[i].elapsed_time(ends[i])
         d["bytes"] += c.algorithmic_bytes()
         d["flops"] += c.flops()
         d["launches"] += 1
+    per_case.sort(reverse=True)
+    by_op["__slowest__"] = [{"ms": round(ms, 3), "case": label} for ms, label in per_case[:12]]
+    by_op["__total_ms__"] = round(sum(ms for ms, _ in per_case), 3)
     return by_op
 
 
@@ -378,6 +383,8 @@ def run_b200(args):
 
     if rank == 0:
         by_op = per_kernel_profile(prepared)
+        line["sweep_slowest_cases"] = by_op.pop("__slowest__")
+        line["sweep_device_ms_sum"] = by_op.pop("__total_ms__")
         total = sum(d["ms"] for d in by_op.values()) or 1.0
         shares = {op: round(d["ms"] / total, 4) for op, d in sorted(by_op.items(), key=lambda kv: -kv[1]["ms"])}
         top_op, top = max(by_op.items(), key=lambda kv: kv[1]["ms"])

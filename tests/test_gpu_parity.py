@@ -246,6 +246,28 @@ def test_scatter_add_grouped_by_destination_path_bit_exact(backend, dtype):
     ops.check_device_status()
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_many_short_rows_and_long_non_last_dims(backend, dtype):
+    """Millions-of-tiny-rows geometries take the thread-per-row kernels; a long reduction over
+    a non-last dim with few columns takes the transposed route / split reductions."""
+    g = torch.Generator().manual_seed(31)
+    x = torch.randn(6000, 17, generator=g).to(dtype)
+    x[5, 3] = float("nan")
+    x[7, :] = float("-inf")
+    w, b = torch.randn(17, generator=g).to(dtype), torch.randn(17, generator=g).to(dtype)
+    tall = torch.randn(3000, 24, generator=g).to(dtype)
+    jobs = [
+        ("_softmax.default", [x, -1, False]), ("_log_softmax.default", [x, -1, False]), ("sum.dim_IntList", [x[:, :7].contiguous(), [-1]]),
+        ("argmax.default", [x, -1]), ("native_layer_norm.default", [x[8:], [17], w, b, 1e-5]), ("native_layer_norm.default", [x[8:, :5].contiguous(), [5], None, None, 1e-5]),
+        ("_softmax.default", [tall, 0, False]), ("_log_softmax.default", [tall, 0, False]), ("sum.dim_IntList", [tall, [0]]), ("argmax.default", [tall, 0]),
+        ("_softmax.default", [tall.view(3000, 4, 6), 0, False]), ("sum.dim_IntList", [torch.randn(9000, 40, generator=g).to(dtype), [0], True]),
+    ]
+    for op_name, args in jobs:
+        got = backend[get_operator(op_name)](*_to_dev(args))
+        _check(op_name, oracle.run(op_name, args, {}), got, (op_name, tuple(args[0].shape)))
+    ops.check_device_status()
+
+
 def test_full_size_argmax_bit_exact(backend):
     c, op, impl, args, kwargs = _full("argmax_f32_8192x32000", backend)
     got = impl(*args, **kwargs)
