@@ -18,6 +18,18 @@ __device__ __forceinline__ int64_t load_index(const void* idx, int64_t i, int id
 __device__ __forceinline__ void flag_oob(uint32_t* status) {
   if (status) atomicOr(status, B200_DEV_INDEX_OOB);
 }
+// The gathered-from tensor is re-read at random while index and output stream through once:
+// pin the former in L2 (evict_last) so the streams do not push it out.
+__device__ __forceinline__ uint64_t l2_keep_policy() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ uint32_t ld_keep_l2(const uint32_t* p, uint64_t pol) {
+  uint32_t v;
+  asm volatile("ld.global.nc.L2::cache_hint.u32 %0, [%1], %2;" : "=r"(v) : "l"(p), "l"(pol));
+  return v;
+}
 template <typename U> __device__ __forceinline__ U zero_of() { U z; memset(&z, 0, sizeof(U)); return z; }
 
 // One CTA (128 threads) per output row; rows are `nvec` 16-byte vectors.
@@ -93,6 +105,7 @@ __global__ void __launch_bounds__(256) gather_generic(const U* __restrict__ self
 __global__ void __launch_bounds__(256) gather_dim0_vec4(const uint32_t* __restrict__ self, const int64_t* __restrict__ index, uint32_t* __restrict__ out,
                                                         int64_t rows, int64_t cols, int64_t self_pitch, int64_t self_rows, uint32_t* status) {
   const int64_t nquad = rows * cols / 4;
+  const uint64_t keep = l2_keep_policy();
   for (int64_t q = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; q < nquad; q += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     const int64_t p = q * 4;
     const int64_t col = p % cols;  // cols % 4 == 0, so the quad stays inside one row
@@ -106,7 +119,7 @@ __global__ void __launch_bounds__(256) gather_dim0_vec4(const uint32_t* __restri
         flag_oob(status);
         v[e] = 0;
       } else {
-        v[e] = __ldg(self + k[e] * self_pitch + col + e);
+        v[e] = ld_keep_l2(self + k[e] * self_pitch + col + e, keep);
       }
     }
     __stcs(reinterpret_cast<uint4*>(out + p), make_uint4(v[0], v[1], v[2], v[3]));

@@ -586,7 +586,7 @@ struct ResidentCfg {
   bool ok, warp;
   int vpt, threads;
 };
-static ResidentCfg resident_cfg(int64_t nvec, int max_vpt) {
+static ResidentCfg resident_cfg(int64_t nvec, int max_vpt, int target_vpt = 2) {
   ResidentCfg c{false, false, 1, 128};
   if (nvec <= 0) return c;
   auto pow2_at_least = [](int64_t v) { int64_t p = 1; while (p < v) p <<= 1; return p; };
@@ -595,7 +595,9 @@ static ResidentCfg resident_cfg(int64_t nvec, int max_vpt) {
     c.vpt = static_cast<int>(pow2_at_least((nvec + 31) / 32));
     return c;
   }
-  int64_t th = pow2_at_least((nvec + 3) / 4);
+  // softmax: two 16-byte vectors per thread (fewer registers, more resident warps);
+  // layer norm: four (its two CTA-wide reductions cost more with many warps)
+  int64_t th = pow2_at_least((nvec + target_vpt - 1) / target_vpt);
   if (th < 128) th = 128;
   if (th > 1024) th = 1024;
   const int64_t vpt = pow2_at_least((nvec + th - 1) / th);
@@ -729,7 +731,7 @@ extern "C" int b200_layer_norm(const void* x, const void* w, const void* b, void
   const bool wb_ok = (!w && !b) || dt_wb == dt || dt_wb == B200_F32;
   const bool al = aligned16(x) && aligned16(y) && (!w || aligned16(w)) && (!b || aligned16(b));
   ResidentCfg c{false, false, 1, 128};
-  if (cols > 0 && cols % ve == 0 && (dt_wb != B200_F32 || cols % 4 == 0) && al && wb_ok && cols < (1LL << 30)) c = resident_cfg(cols / ve, 32 / ve);
+  if (cols > 0 && cols % ve == 0 && (dt_wb != B200_F32 || cols % 4 == 0) && al && wb_ok && cols < (1LL << 30)) c = resident_cfg(cols / ve, 32 / ve, 4);
   if (!c.ok) {
     layernorm_stream<<<static_cast<unsigned>(rows), 256, 0, st>>>(x, w, b, y, mean, rstd, cols, e, dt, dt_wb, dt_stat);
     return check_launch();

@@ -27,6 +27,7 @@ def main():
     ap.add_argument("--scale", type=int, default=1)
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=2)
+    ap.add_argument("--rotate", action="store_true", help="time back-to-back launches over rotating input sets larger than L2 instead of flushing L2 before every launch")
     ap.add_argument("--list", action="store_true")
     args = ap.parse_args()
     if args.list or not args.case:
@@ -37,8 +38,17 @@ def main():
         case = scaled_down(case, args.scale)
     op = get_operator(case.op)
     impl = B200Backend()[op]
-    a, kw = case.build("cuda")
-    ms = cuda_bench(lambda: impl(*a, **kw), warmup=args.warmup, reps=args.reps)
+    if args.rotate:
+        from dataclasses import replace
+
+        from .eval import cuda_bench_rotating
+
+        nsets = max(2, min(8, -(-2 * (126 << 20) // max(case.algorithmic_bytes(), 1))))
+        sets = [replace(case, seed=case.seed + i).build("cuda") for i in range(nsets)]
+        ms = cuda_bench_rotating([(lambda a=a, k=k: impl(*a, **k)) for a, k in sets], reps=max(args.reps, 20))
+    else:
+        a, kw = case.build("cuda")
+        ms = cuda_bench(lambda: impl(*a, **kw), warmup=args.warmup, reps=args.reps)
     out = {"case": case.label(), "ms": round(ms, 5), "algorithmic_bytes": case.algorithmic_bytes(), "gbs": round(case.algorithmic_bytes() / ms / 1e6, 1)}
     if case.flops():
         out["tflops"] = round(case.flops() / ms / 1e9, 2)
