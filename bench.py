@@ -415,6 +415,9 @@ def run_reference(args):
         return  # the CPU arm runs once per job
     from backendbench_b200.cases import sweep_cases
 
+    # torchrun exports OMP_NUM_THREADS=1 for its ranks; this arm runs on rank 0 alone and is
+    # meant to use every host core the box has
+    torch.set_num_threads(max(os.cpu_count() or 1, 1))
     cases = sweep_cases(N_CASES, SWEEP_SEED)
     per_step_budget = max(5.0, min(30.0, 150.0 / max(args.steps + args.warmup, 1)))
     for _ in range(args.warmup):
