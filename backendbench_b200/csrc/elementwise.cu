@@ -202,6 +202,19 @@ __global__ void __launch_bounds__(kEwThreads) where_strided(const uint8_t* c, co
   }
 }
 
+// [batch, rows, cols] gather from arbitrary element strides into a pitched destination
+// (unit column stride): how the host gives a tensor-core GEMM operand a 16-byte-aligned
+// row pitch when the caller's layout has none.
+template <typename U>
+__global__ void __launch_bounds__(kEwThreads) copy_pitched(const U* __restrict__ x, U* __restrict__ out, int64_t batch, int64_t rows, int64_t cols, int64_t sxb, int64_t sxr,
+                                                           int64_t sxc, int64_t opb, int64_t opr) {
+  const int64_t total = batch * rows * cols;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * kEwThreads + threadIdx.x; i < total; i += static_cast<int64_t>(gridDim.x) * kEwThreads) {
+    const int64_t c = i % cols, r = (i / cols) % rows, b = i / (cols * rows);
+    out[b * opb + r * opr + c] = x[b * sxb + r * sxr + c * sxc];
+  }
+}
+
 static int fill_args(StridedArgs& A, int ndim, const int64_t* shape, const int64_t* s0, const int64_t* s1, const int64_t* s2) {
   if (ndim < 0 || ndim > B200_MAX_DIMS || (ndim > 0 && !shape)) return B200_EINVAL;
   A.ndim = ndim;
@@ -371,6 +384,21 @@ extern "C" int b200_copy_strided(const void* x, void* out, int ndim, const int64
   } else {
     if (!is_float_dtype(dto)) return B200_EDTYPE;
     ew_strided<OP_COPY><<<g, kEwThreads, 0, st>>>(x, nullptr, out, A, dti, dti, dto, 0.f);
+  }
+  return check_launch();
+}
+
+extern "C" int b200_copy_pitched(const void* x, void* out, int64_t batch, int64_t rows, int64_t cols, int64_t sxb, int64_t sxr, int64_t sxc, int64_t out_batch_pitch,
+                                 int64_t out_row_pitch, int elem_size, void* stream) {
+  if (batch < 0 || rows < 0 || cols < 0 || out_row_pitch < cols) return B200_EINVAL;
+  if (batch == 0 || rows == 0 || cols == 0) return B200_OK;
+  if (!x || !out) return B200_EINVAL;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int g = strided_grid(batch * rows * cols);
+  switch (elem_size) {
+    case 2: copy_pitched<uint16_t><<<g, kEwThreads, 0, st>>>(static_cast<const uint16_t*>(x), static_cast<uint16_t*>(out), batch, rows, cols, sxb, sxr, sxc, out_batch_pitch, out_row_pitch); break;
+    case 4: copy_pitched<uint32_t><<<g, kEwThreads, 0, st>>>(static_cast<const uint32_t*>(x), static_cast<uint32_t*>(out), batch, rows, cols, sxb, sxr, sxc, out_batch_pitch, out_row_pitch); break;
+    default: return B200_EDTYPE;
   }
   return check_launch();
 }

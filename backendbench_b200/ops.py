@@ -607,6 +607,23 @@ def scatter_add_default(self: torch.Tensor, dim: int, index: torch.Tensor, src: 
 
 
 # --------------------------------------------------------------------- contraction
+def _tma_ready(t: torch.Tensor, s_b: int, s_mn: int, s_k: int, batch: int) -> bool:
+    """An operand [batch, mn, k] the tensor-core kernel can load as is: one unit stride, the
+    other (and the batch stride) a multiple of 8 elements, base 16-byte aligned."""
+    if t.data_ptr() % 16 or (batch > 1 and (s_b % 8 or s_b <= 0)):
+        return False
+    return (s_k == 1 and s_mn % 8 == 0 and s_mn > 0) or (s_mn == 1 and s_k % 8 == 0 and s_k > 0)
+
+
+def _repitch(t: torch.Tensor, batch: int, rows: int, cols: int, s_b: int, s_r: int, s_c: int):
+    """Copy a [batch, rows, cols] view into a fresh buffer whose row pitch is a multiple of 8
+    elements (pad columns stay uninitialised: the tensor map's extents exclude them)."""
+    pitch = (cols + 7) // 8 * 8
+    buf = torch.empty((batch, rows, pitch), dtype=t.dtype, device=t.device)
+    check(lib().b200_copy_pitched(t.data_ptr(), buf.data_ptr(), batch, rows, cols, s_b, s_r, s_c, rows * pitch, pitch, t.element_size(), _stream_handle()), "b200_copy_pitched")
+    return buf, (rows * pitch, pitch)
+
+
 def _gemm(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor], batch: int, M: int, N: int, K: int, sa, sb, alpha: float, beta: float, out_shape) -> torch.Tensor:
     if a.dtype != b.dtype:
         raise RuntimeError(f"expected m1 and m2 to have the same dtype, but got: {a.dtype} != {b.dtype}")
@@ -615,6 +632,24 @@ def _gemm(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor], batch:
     out = torch.empty(out_shape, dtype=a.dtype, device=a.device)
     if out.numel() == 0:
         return out
+    # 16-bit operands whose layout the tensor-core path cannot load (row pitch or base off the
+    # 16-byte grid, e.g. K = 2049) are re-pitched once when the product is large enough for
+    # the tensor cores to pay for the extra copy; otherwise the CUDA-core kernel takes them
+    if a.dtype != torch.float32 and M * N * K * batch >= (1 << 24) and K >= 16:
+        if not _tma_ready(a, sa[0], sa[1], sa[2], batch):
+            if sa[1] != 1 or sa[2] == 1:  # keep A K-major unless it is M-major
+                a, (pb, pr) = _repitch(a, batch, M, K, sa[0], sa[1], sa[2])
+                sa = (pb, pr, 1)
+            else:
+                a, (pb, pr) = _repitch(a, batch, K, M, sa[0], sa[2], sa[1])
+                sa = (pb, 1, pr)
+        if not _tma_ready(b, sb[0], sb[2], sb[1], batch):
+            if sb[1] != 1 or sb[2] == 1:  # keep B N-major ([K, N] rows) unless it is K-major
+                b, (pb, pr) = _repitch(b, batch, K, N, sb[0], sb[1], sb[2])
+                sb = (pb, pr, 1)
+            else:
+                b, (pb, pr) = _repitch(b, batch, N, K, sb[0], sb[2], sb[1])
+                sb = (pb, 1, pr)
     sbm = sbn = 0
     bias_ptr = None
     if bias is not None:

@@ -1,0 +1,113 @@
+"""Command line driver: build a suite and a backend, evaluate every operator the backend
+implements (serially or one process per GPU) and print the three summary scores.
+
+Mirrors the hot-path part of BackendBench/scripts/main.py:186-303 with the same flag names
+(`--suite --backend --ops --ops-directory --num-workers --p --log-level --daemon/--no-daemon`).
+Suites here are the seeded ones this package can generate offline: `smoke` (one relu case,
+as the reference's smoke suite), `named` (the per-operator configurations throughput is
+quoted on) and `sweep` (the 512-case sharded sweep). Backends: `aten`, `directory`
+(`--ops-directory`), `b200` (the kernels shipped with this package).
+
+    python -m backendbench_b200.scripts.main --suite sweep --backend b200 --num-workers 8
+"""
+
+from __future__ import annotations
+
+import logging
+import os
+import sys
+
+import click
+import torch
+
+from .. import eval as evaluation
+from ..backends import make_backend
+from ..cases import named_cases, sweep_cases
+from ..multiprocessing_eval import BackendRef, MultiprocessingEvaluator, SpecTest
+from ..opregistry import get_operator
+from ..suite import OpTest, TestSuite, make_smoke_suite
+
+logger = logging.getLogger(__name__)
+
+
+def build_suite(name: str, device: str, ops=None, n_cases: int = 512) -> TestSuite:
+    """`smoke`: thunk-based tensors on `device`; `named` / `sweep`: one OpTest per operator whose
+    tests are `SpecTest` descriptors (inputs generated on the evaluating device from the seed)."""
+    if name == "smoke":
+        return make_smoke_suite(device)
+    specs = named_cases() if name == "named" else sweep_cases(n_cases)
+    by_op = {}
+    for c in specs:
+        if ops and c.op not in ops and c.op.split(".")[0] not in ops:
+            continue
+        by_op.setdefault(c.op, []).append(c)
+    optests = []
+    for op_name, cs in by_op.items():
+        tests = [SpecTest(c, device) for c in cs]
+        perf = tests if name == "named" else tests[:: max(len(tests) // 4, 1)][:4]
+        optests.append(OpTest(get_operator(op_name), tests, perf))
+    return TestSuite(name, optests)
+
+
+def run(suite, backend, backend_ref, num_workers=None, daemon=True, p=1.0, tolerances=None):
+    """Evaluate `suite` on `backend`; returns (mean correctness, geomean perf, perf@p, results)."""
+    overall_correctness, overall_performance, all_c, all_p = [], [], [], []
+    if num_workers is None:
+        for test in suite:
+            if test.op not in backend:
+                continue
+            _, perf, cres, pres = evaluation.eval_one_op(test.op, backend[test.op], test.correctness_tests, test.performance_tests, tolerances)
+            overall_correctness.append(all(r.is_correct for r in cres))
+            overall_performance.append(float(perf))
+            all_c.extend(cres)
+            all_p.extend(pres)
+    else:
+        with MultiprocessingEvaluator(num_workers, daemon=daemon, backend=backend_ref) as evaluator:
+            for test in suite:
+                if test.op not in backend:
+                    continue
+                evaluator.submit_task(test.op, backend_ref if backend_ref is not None else backend[test.op], test.correctness_tests, test.performance_tests, tolerances)
+            evaluator.start_evaluation()
+            results = evaluator.get_results()
+        for r in results:
+            overall_correctness.append(all(c.is_correct for c in r.correctness_results))
+            overall_performance.append(float(r.performance_score))
+            all_c.extend(r.correctness_results)
+            all_p.extend(r.performance_results)
+    if not overall_correctness:
+        return 0.0, 1.0, 0.0, (all_c, all_p)
+    mean_correctness = torch.tensor(overall_correctness).float().mean().item()
+    perf_t = torch.tensor(overall_performance, dtype=torch.float64)
+    perf_t = torch.where(torch.isnan(perf_t), torch.ones_like(perf_t), perf_t)  # operators without performance cases
+    geomean_perf = perf_t.log().mean().exp().item()
+    perf_at_p = float(evaluation.perf_at_p(overall_correctness, perf_t.tolist(), p))
+    return mean_correctness, geomean_perf, perf_at_p, (all_c, all_p)
+
+
+@click.command()
+@click.option("--log-level", default=os.getenv("LOG_LEVEL", "INFO"), type=click.Choice(["DEBUG", "INFO", "WARNING", "ERROR", "CRITICAL"], case_sensitive=False), help="Set the logging level")
+@click.option("--suite", default="smoke", type=click.Choice(["smoke", "named", "sweep"]), help="Which suite to run")
+@click.option("--backend", default="aten", type=click.Choice(["aten", "directory", "b200"]), help="Which backend to run")
+@click.option("--ops", default=None, type=str, help="Comma-separated list of ops to run")
+@click.option("--ops-directory", default="generated_kernels", type=str, help="Path to directory containing kernels (directory backend)")
+@click.option("--num-workers", default=None, type=int, help="Number of worker processes (one per GPU); default: evaluate in this process")
+@click.option("--p", default=1.0, type=float, help="Performance score threshold for the perf@p score")
+@click.option("--device", default=None, type=str, help="Device for the generated inputs (default: cuda when available, else cpu)")
+@click.option("--cases", default=512, type=int, help="Number of cases of the sweep suite")
+@click.option("--dtype-tolerances/--harness-tolerances", default=False, help="Per-dtype tolerances instead of the harness's 1e-2 for everything")
+@click.option("--daemon/--no-daemon", default=True, help="Use daemon worker processes")
+def cli(log_level, suite, backend, ops, ops_directory, num_workers, p, device, cases, dtype_tolerances, daemon):
+    logging.basicConfig(level=getattr(logging, log_level.upper()), format="[%(asctime)s][%(levelname)s][%(filename)s] %(message)s", datefmt="%Y-%m-%d %H:%M:%S")
+    device = device or ("cuda" if torch.cuda.is_available() else "cpu")
+    op_filter = [o.strip() for o in ops.split(",")] if ops else None
+    test_suite = build_suite(suite, device, op_filter, cases)
+    be = make_backend(backend, ops_directory)
+    ref = BackendRef(backend, ops_directory if backend == "directory" else None)
+    mean_correctness, geomean_perf, perf_at_p, _ = run(test_suite, be, ref, num_workers, daemon, p, "dtype" if dtype_tolerances else None)
+    print(f"correctness score (mean pass rate over all operators): {mean_correctness:.2f}")
+    print(f"performance score (geomean speedup over all operators): {geomean_perf:.2f}")
+    print(f"perf@p score (rate of correct samples with a speedup greater than p, p={p}): {perf_at_p:.2f}")
+
+
+if __name__ == "__main__":
+    cli()

@@ -107,6 +107,13 @@ int b200_where(const void* cond, const void* x, const void* y, void* out, int nd
 int b200_copy_strided(const void* x, void* out, int ndim, const int64_t* shape,
                       const int64_t* sx, int dtype_in, int dtype_out, void* stream);
 
+/* [batch, rows, cols] copy from arbitrary element strides into a destination with unit
+ * column stride and the given row / batch pitches (elements); elem_size 2 or 4. The host
+ * side uses it to give a misaligned 16-bit GEMM operand a TMA-compatible row pitch. */
+int b200_copy_pitched(const void* x, void* out, int64_t batch, int64_t rows, int64_t cols,
+                      int64_t sx_batch, int64_t sx_row, int64_t sx_col, int64_t out_batch_pitch,
+                      int64_t out_row_pitch, int elem_size, void* stream);
+
 /* ----------------------------------------------------------------- row kernels
  * The input is contiguous and viewed as [outer, dim, inner]; the op runs along `dim`. */
 

@@ -86,3 +86,19 @@ def test_layouts_the_tensor_core_path_declines_still_work():
     bv = _rand((128, 64), torch.float16, g, 1.0)
     _check(ops.mm_default(av, bv), av.double() @ bv.double(), torch.float16)
     ops.check_device_status()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_large_misaligned_operands_are_repitched_onto_tensor_cores(dtype):
+    """Row pitches / bases off the 16-byte grid (K = 2049, N = 127, sliced views): large
+    products get their operands re-pitched by the library's copy kernel and still match."""
+    g = torch.Generator(device=DEV).manual_seed(9)
+    a, b = _rand((1024, 2049), dtype, g, 2049**-0.5), _rand((2049, 127), dtype, g, 1.0)
+    _check(ops.mm_default(a, b), a.double() @ b.double(), dtype)
+    at = _rand((2049, 1030), dtype, g, 2049**-0.5).t()[1:, :]  # M-major A with an odd base offset
+    _check(ops.mm_default(at, b), at.double() @ b.double(), dtype)
+    bias = _rand((127,), dtype, g, 1.0)
+    _check(ops.addmm_default(bias, a, b, beta=2, alpha=0.5), 0.5 * (a.double() @ b.double()) + 2 * bias.double(), dtype)
+    x, y = _rand((4, 300, 1001), dtype, g, 1001**-0.5), _rand((4, 260, 1001), dtype, g, 1.0).transpose(1, 2)  # K-major B, K = 1001
+    _check(ops.bmm_default(x, y), x.double() @ y.double(), dtype)
+    ops.check_device_status()
