@@ -2,7 +2,7 @@
 //
 //   C[b] (M x N, row-major) = alpha * A[b] (M x K) @ B[b] (K x N) + beta * bias
 //
-// One persistent CTA per SM walks 128 x 256 output tiles. Roles by warp:
+// One persistent CTA per SM walks 128 x 256 (or 128 x 128) output tiles. Roles by warp:
 //   warp 0   : TMA producer -- one lane issues cp.async.bulk.tensor loads (no multicast)
 //              of a 128 x 64 A slab and a 64 x 256 B slab per pipeline stage into
 //              128-byte-swizzled shared memory, completion on an mbarrier.
@@ -31,18 +31,23 @@
 
 namespace b200 {
 
-constexpr int kBM = 128, kBN = 256, kBK = 64;          // tile: 128 x 256 outputs, 64-deep K slabs
-constexpr int kStages = 4;
+constexpr int kBM = 128, kBK = 64;                      // tile: 128 x BN outputs (BN = 256 or 128), 64-deep K slabs
 constexpr int kABytes = kBM * kBK * 2;                  // 16 KB
-constexpr int kBBytes = kBN * kBK * 2;                  // 32 KB
-constexpr int kStageBytes = kABytes + kBBytes;          // 48 KB
-constexpr int kTmemCols = 512;                          // two 256-column accumulators
+constexpr int kTmemCols = 512;                          // 512 / BN fp32 accumulators of 128 lanes x BN columns
+// BN = 256: 48 KB stages x 4, two accumulators (compute-bound shapes).
+// BN = 128: 32 KB stages x 6, four accumulators, for C no wider than 128 columns.
+template <int BN> struct TileCfg {
+  static constexpr int kBBytes = BN * kBK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = BN == 256 ? 4 : 6;
+  static constexpr int kAccs = kTmemCols / BN;
+};
 constexpr int kGemmThreads = 320;                       // TMA warp, MMA warp, 8 epilogue warps
 constexpr int kGroupM = 16;                             // row-blocks per rasterisation group
 constexpr uint64_t kWaitLimitNs = 2000000000ull;        // every mbarrier wait gives up after 2 s
 constexpr int kEpiWarps = 8;
 constexpr int kEpiStageBytes = 32 * 128;                // per epilogue warp: 32 rows x 64 16-bit outputs, TMA-store staging
-constexpr size_t kGemmSmem = static_cast<size_t>(kStages) * kStageBytes + kEpiWarps * kEpiStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+constexpr size_t kGemmSmem = static_cast<size_t>(4) * (kABytes + 256 * kBK * 2) + kEpiWarps * kEpiStageBytes + 1024 /*align*/ + 256 /*barriers*/;  // same for both tile shapes (6 x 32 KB = 4 x 48 KB)
 
 // ------------------------------------------------------------------ PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -155,17 +160,18 @@ __device__ __forceinline__ void tile_coords(int64_t rem, int64_t mt, int64_t nt,
   nb = static_cast<int>(in_g / gm);
 }
 
-template <typename T>
+template <typename T, int kBN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c, const T* __restrict__ bias, T* __restrict__ C, GemmTcParams p,
                     uint32_t* __restrict__ status) {
+  constexpr int kStages = TileCfg<kBN>::kStages, kStageBytes = TileCfg<kBN>::kStageBytes, kAccs = TileCfg<kBN>::kAccs;
   extern __shared__ unsigned char smem_raw[];
   // 1024-byte alignment: the 128B swizzle pattern repeats every 8 rows x 128 bytes
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   unsigned char* epi_stage = smem + kStages * kStageBytes;  // kEpiWarps x 4 KB, each 1024-byte aligned
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes + kEpiWarps * kEpiStageBytes);
   // barrier slots: [0,S) full, [S,2S) empty, [2S,2S+2) tmem_full, [2S+2,2S+4) tmem_empty
-  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 2 * kAccs);
   volatile uint32_t* abort_flag = tmem_base_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -174,14 +180,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
   auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
-  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + kAccs + a); };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
-    for (int a = 0; a < 2; ++a) {
+    for (int a = 0; a < kAccs; ++a) {
       mbar_init(tfull_bar(a), 1);
       mbar_init(tempty_bar(a), 8);  // one arrival per epilogue warp
     }
@@ -270,8 +276,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
         if (!ok) break;
         tc_commit(tfull_bar(acc));  // accumulator complete
-        acc ^= 1;
-        if (acc == 0) acc_phase ^= 1u;
+        if (++acc == kAccs) { acc = 0; acc_phase ^= 1u; }
       }
       if (!ok) {
         *abort_flag = 1;
@@ -361,8 +366,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(acc));  // this warp has drained its part
-      acc ^= 1;
-      if (acc == 0) acc_phase ^= 1u;
+      if (++acc == kAccs) { acc = 0; acc_phase ^= 1u; }
     }
     if (lane == 0) tma_store_wait_all();  // tile stores must have left shared memory before the CTA exits
     if (!ok && lane == 0) {
@@ -454,7 +458,8 @@ int gemm_tc_dispatch(const void* A, const void* B, const void* bias, void* C, in
   if (!la.ok || !lb.ok || !encode_fn()) return B200_EALIGN;
   alignas(64) CUtensorMap map_a, map_b;
   if (!encode_operand(&map_a, A, dtype, la.mn_major, M, K, sAm, sAk, sAb, batch, kBM)) return B200_EDRIVER;
-  if (!encode_operand(&map_b, B, dtype, lb.mn_major, N, K, sBn, sBk, sBb, batch, kBN)) return B200_EDRIVER;
+  const int bn_box = N <= 128 ? 128 : 256;  // must match the tile shape chosen below
+  if (!encode_operand(&map_b, B, dtype, lb.mn_major, N, K, sBn, sBk, sBb, batch, bn_box)) return B200_EDRIVER;
   alignas(64) CUtensorMap map_c;
   const bool tma_store = (N % 8 == 0) && aligned16(C);
   if (tma_store) {
@@ -482,18 +487,30 @@ int gemm_tc_dispatch(const void* A, const void* B, const void* bias, void* C, in
   // write neighbouring column blocks of the same rows (whole DRAM pages); otherwise order
   // tiles for operand reuse in L2
   p.col_fastest = (K + kBK - 1) / kBK <= 4 ? 1 : 0;
-  const int64_t tiles = batch * ((M + kBM - 1) / kBM) * ((N + kBN - 1) / kBN);
+  // a narrow C takes the 128-wide tile. (Write-bound shapes with few K slabs were measured
+  // slower on it: 256-byte row segments instead of 512-byte ones cost more in DRAM than the
+  // deeper pipeline gains -- bmm 32x2048x128x2048: 0.162 ms vs 0.116 ms.)
+  const bool narrow = N <= 128;
+  const int bn = narrow ? 128 : 256;
+  const int64_t tiles = batch * ((M + kBM - 1) / kBM) * ((N + bn - 1) / bn);
   const int grid = static_cast<int>(tiles < kNumSMs ? tiles : kNumSMs);
-  cudaError_t e;
+  auto launch = [&](auto kernel, auto* bias_t, auto* c_t) -> int {
+    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemmSmem));
+    if (e != cudaSuccess) { set_last_cuda_error(e); return B200_ELAUNCH; }
+    kernel<<<grid, kGemmThreads, kGemmSmem, st>>>(map_a, map_b, map_c, bias_t, c_t, p, status);
+    return B200_OK;
+  };
+  int rc;
   if (dtype == B200_BF16) {
-    e = cudaFuncSetAttribute(gemm_tcgen05_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemmSmem));
-    if (e != cudaSuccess) { set_last_cuda_error(e); return B200_ELAUNCH; }
-    gemm_tcgen05_kernel<__nv_bfloat16><<<grid, kGemmThreads, kGemmSmem, st>>>(map_a, map_b, map_c, static_cast<const __nv_bfloat16*>(bias), static_cast<__nv_bfloat16*>(C), p, status);
+    const __nv_bfloat16* bt = static_cast<const __nv_bfloat16*>(bias);
+    __nv_bfloat16* ct = static_cast<__nv_bfloat16*>(C);
+    rc = narrow ? launch(gemm_tcgen05_kernel<__nv_bfloat16, 128>, bt, ct) : launch(gemm_tcgen05_kernel<__nv_bfloat16, 256>, bt, ct);
   } else {
-    e = cudaFuncSetAttribute(gemm_tcgen05_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemmSmem));
-    if (e != cudaSuccess) { set_last_cuda_error(e); return B200_ELAUNCH; }
-    gemm_tcgen05_kernel<__half><<<grid, kGemmThreads, kGemmSmem, st>>>(map_a, map_b, map_c, static_cast<const __half*>(bias), static_cast<__half*>(C), p, status);
+    const __half* bt = static_cast<const __half*>(bias);
+    __half* ct = static_cast<__half*>(C);
+    rc = narrow ? launch(gemm_tcgen05_kernel<__half, 128>, bt, ct) : launch(gemm_tcgen05_kernel<__half, 256>, bt, ct);
   }
+  if (rc) return rc;
   return check_launch();
 }
 
