@@ -101,14 +101,20 @@ __global__ void __launch_bounds__(256) gather_generic(const U* __restrict__ self
 
 // 2-D, dim 0, contiguous index [R, C] and unit column stride in self (row pitch
 // `self_pitch`): each thread produces 4 adjacent outputs -- two 16-byte index loads,
-// four sector reads, one 16-byte store (4-byte elements).
+// four sector reads, one 16-byte store (4-byte elements). The columns are walked in blocks
+// of `wcols` (blockIdx.y), chosen so that the slice of `self` a block of columns can touch
+// (self_rows x wcols) stays L2-resident while index and output stream past it: every source
+// sector then comes from DRAM once instead of once per eviction.
 __global__ void __launch_bounds__(256) gather_dim0_vec4(const uint32_t* __restrict__ self, const int64_t* __restrict__ index, uint32_t* __restrict__ out,
-                                                        int64_t rows, int64_t cols, int64_t self_pitch, int64_t self_rows, uint32_t* status) {
-  const int64_t nquad = rows * cols / 4;
+                                                        int64_t rows, int64_t cols, int64_t self_pitch, int64_t self_rows, int64_t wcols, uint32_t* status) {
+  const int64_t j0 = static_cast<int64_t>(blockIdx.y) * wcols;
+  const int64_t wb = cols - j0 < wcols ? cols - j0 : wcols;
+  const int64_t qpr = wb / 4;  // quads per row inside this column block
+  const int64_t nquad = rows * qpr;
   const uint64_t keep = l2_keep_policy();
   for (int64_t q = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; q < nquad; q += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int64_t p = q * 4;
-    const int64_t col = p % cols;  // cols % 4 == 0, so the quad stays inside one row
+    const int64_t i = q / qpr, col = j0 + (q - i * qpr) * 4;
+    const int64_t p = i * cols + col;
     const longlong2 i01 = __ldcs(reinterpret_cast<const longlong2*>(index + p));
     const longlong2 i23 = __ldcs(reinterpret_cast<const longlong2*>(index + p + 2));
     const int64_t k[4] = {i01.x, i01.y, i23.x, i23.y};
@@ -202,8 +208,17 @@ extern "C" int b200_gather(const void* self, const void* index, void* out, int n
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool idx_contig = is_contiguous(ndim, index_shape, index_strides);
   if (ndim == 2 && dim == 0 && elem_size == 4 && idx_contig && self_strides[1] == 1 && index_shape[1] % 4 == 0 && aligned16(index) && aligned16(out)) {
-    gather_dim0_vec4<<<capped_grid(A.n / 4, 256, 32), 256, 0, st>>>(static_cast<const uint32_t*>(self), static_cast<const int64_t*>(index), static_cast<uint32_t*>(out), index_shape[0], index_shape[1], self_strides[0], self_dim_size, status);
-    return check_launch();
+    // column block: about 16 MB of `self` (self_rows x wcols x 4 bytes), a multiple of 4 columns
+    int64_t wcols = (16LL << 20) / (4 * (self_dim_size > 0 ? self_dim_size : 1));
+    wcols = wcols / 4 * 4;
+    if (wcols < 64) wcols = 64;
+    if (wcols > index_shape[1]) wcols = index_shape[1];
+    const int64_t nblocks = (index_shape[1] + wcols - 1) / wcols;
+    if (nblocks <= 65535) {
+      dim3 grid(capped_grid(index_shape[0] * wcols / 4, 256, 32), static_cast<unsigned>(nblocks));
+      gather_dim0_vec4<<<grid, 256, 0, st>>>(static_cast<const uint32_t*>(self), static_cast<const int64_t*>(index), static_cast<uint32_t*>(out), index_shape[0], index_shape[1], self_strides[0], self_dim_size, wcols, status);
+      return check_launch();
+    }
   }
   const int g = capped_grid(A.n, 256, 32);
   const int64_t* pi = static_cast<const int64_t*>(index);
