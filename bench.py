@@ -156,19 +156,54 @@ def sweep_enqueue(prepared, records):
 
 
 def sweep_pass(prepared, records, host_inputs=None, device=None):
-    """One correctness pass; returns the (n, 8) int32 verdict records on the host."""
+    """One correctness pass; returns the (n, 8) int32 verdict records on the host. With
+    `host_inputs` (pinned host tensors) every case's inputs are copied host->device first, on
+    a copy stream that runs a few cases ahead of the compute stream."""
     from backendbench_b200.eval import compare_enqueue
 
     structural = []
-    for i, p in enumerate(prepared):
-        if host_inputs is not None:
+    if host_inputs is None:
+        for i, p in enumerate(prepared):
+            res = p["impl"](*p["args"], **p["kwargs"])
+            structural.append(compare_enqueue(p["ref"], res, p["atol"], p["rtol"], records[i]))
+        return records.cpu(), structural  # the step's single device->host read
+
+    main = torch.cuda.current_stream()
+    copier = _copy_stream(device)
+    copier.wait_stream(main)
+    ahead, n, staged = 4, len(prepared), {}
+
+    def stage(i):
+        with torch.cuda.stream(copier):
             args = [a.to(device, non_blocking=True) if isinstance(a, torch.Tensor) else a for a in host_inputs[i]]
-        else:
-            args = p["args"]
+            ev = torch.cuda.Event()
+            ev.record(copier)
+        staged[i] = (args, ev)
+
+    for i in range(min(ahead, n)):
+        stage(i)
+    for i, p in enumerate(prepared):
+        args, ev = staged.pop(i)
+        main.wait_event(ev)
+        for a in args:
+            if isinstance(a, torch.Tensor):
+                a.record_stream(main)  # allocated on the copy stream, consumed here
         res = p["impl"](*args, **p["kwargs"])
         structural.append(compare_enqueue(p["ref"], res, p["atol"], p["rtol"], records[i]))
-    host = records.cpu()  # the step's single device->host read
+        if i + ahead < n:
+            stage(i + ahead)
+    host = records.cpu()
     return host, structural
+
+
+_copy_streams = {}
+
+
+def _copy_stream(device):
+    st = _copy_streams.get(str(device))
+    if st is None:
+        st = _copy_streams[str(device)] = torch.cuda.Stream(device=device)
+    return st
 
 
 def count_correct(host_records, structural):
