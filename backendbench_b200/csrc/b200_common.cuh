@@ -82,6 +82,53 @@ template <typename T> struct Vec {
   __device__ __forceinline__ void set(int i, T v) { reinterpret_cast<T*>(&raw)[i] = v; }
 };
 
+// Whole-vector conversions written on the packed words, so that each element costs one
+// instruction on the way in (a shift or a mask for bf16, one convert for f16) and half an
+// instruction on the way out (packed round-to-nearest-even converts).
+template <typename T> __device__ __forceinline__ void widen(const uint4& raw, float* f);
+template <> __device__ __forceinline__ void widen<float>(const uint4& raw, float* f) {
+  f[0] = __uint_as_float(raw.x); f[1] = __uint_as_float(raw.y); f[2] = __uint_as_float(raw.z); f[3] = __uint_as_float(raw.w);
+}
+template <> __device__ __forceinline__ void widen<__nv_bfloat16>(const uint4& raw, float* f) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+template <> __device__ __forceinline__ void widen<__half>(const uint4& raw, float* f) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 p = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+    f[2 * i] = p.x;
+    f[2 * i + 1] = p.y;
+  }
+}
+template <typename T> __device__ __forceinline__ uint4 narrow(const float* f);
+template <> __device__ __forceinline__ uint4 narrow<float>(const float* f) {
+  return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
+}
+template <> __device__ __forceinline__ uint4 narrow<__nv_bfloat16>(const float* f) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __nv_bfloat162 p = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    w[i] = *reinterpret_cast<const uint32_t*>(&p);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+template <> __device__ __forceinline__ uint4 narrow<__half>(const float* f) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __half2 p = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+    w[i] = *reinterpret_cast<const uint32_t*>(&p);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
 // Streaming (evict-first) accesses: the memory-bound kernels touch every byte once.
 __device__ __forceinline__ uint4 ld_stream(const void* p) { return __ldcs(reinterpret_cast<const uint4*>(p)); }
 __device__ __forceinline__ void st_stream(void* p, uint4 v) { __stcs(reinterpret_cast<uint4*>(p), v); }
@@ -95,6 +142,12 @@ template <typename F> __device__ __forceinline__ float warp_reduce(float v, F f)
   return v;
 }
 struct MaxF { __device__ __forceinline__ float operator()(float a, float b) const { return fmaxf(a, b); } };
+// Maximum over the warp in one instruction; like fmaxf it passes over NaN inputs.
+__device__ __forceinline__ float warp_reduce(float v, MaxF) {
+  float r;
+  asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
+  return r;
+}
 struct SumF { __device__ __forceinline__ float operator()(float a, float b) const { return a + b; } };
 
 // Reduce across the whole CTA; every thread gets the result. `smem` holds >= 33 floats.
@@ -111,6 +164,26 @@ template <typename F> __device__ __forceinline__ float block_reduce(float v, F f
   }
   __syncthreads();
   return smem[32];
+}
+
+// Same result with one barrier: every warp leaves its partial in shared memory and every
+// warp then reduces the partials itself. `smem` holds >= 64 floats in two halves;
+// consecutive calls in one kernel pass alternating `phase` (0, 1, 0, ...) so that a call
+// never overwrites partials a slower warp is still reading from the call before.
+template <typename F> __device__ __forceinline__ float block_reduce_once(float v, F f, float identity, float* smem, int phase) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+  float* part = smem + 32 * phase;
+  v = warp_reduce(v, f);
+  if (lane == 0) part[warp] = v;
+  __syncthreads();
+  return warp_reduce(lane < nwarps ? part[lane] : identity, f);
+}
+
+// 2^x by the special-function unit alone (results below 2^-126 flush to zero).
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 
 // ---------------------------------------------------------------- strided index math

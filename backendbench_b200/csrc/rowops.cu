@@ -23,9 +23,9 @@ constexpr float kLog2e = 1.4426950408889634f;
 
 // ---- group = one warp (WARP) or the whole CTA: reductions over the threads of a row
 template <bool WARP, typename F>
-__device__ __forceinline__ float group_reduce(float v, F f, float identity, float* smem) {
+__device__ __forceinline__ float group_reduce(float v, F f, float identity, float* smem, int phase) {
   if (WARP) return warp_reduce(v, f);
-  return block_reduce(v, f, identity, smem);
+  return block_reduce_once(v, f, identity, smem, phase);
 }
 
 // Store VE fp32 values at element offset `e0` of `out`, as T (16-byte store) or as fp32.
@@ -37,10 +37,7 @@ __device__ __forceinline__ void store_row_vec(void* out, int64_t e0, const float
 #pragma unroll
     for (int q = 0; q < VE / 4; ++q) st_stream(o + 4 * q, make_uint4(__float_as_uint(f[4 * q]), __float_as_uint(f[4 * q + 1]), __float_as_uint(f[4 * q + 2]), __float_as_uint(f[4 * q + 3])));
   } else {
-    Vec<T> r;
-#pragma unroll
-    for (int e = 0; e < VE; ++e) r.set(e, from_f32<T>(f[e]));
-    st_stream(static_cast<T*>(out) + e0, r.raw);
+    st_stream(static_cast<T*>(out) + e0, narrow<T>(f));
   }
 }
 
@@ -51,66 +48,79 @@ __device__ __forceinline__ void load_weights(const TW* w, int e0, float* f) {
   constexpr int PER = 16 / sizeof(TW);
 #pragma unroll
   for (int q = 0; q < VE / PER; ++q) {
-    Vec<TW> v;
-    v.raw = ld_keep(w + e0 + q * PER);
-#pragma unroll
-    for (int e = 0; e < PER; ++e) f[q * PER + e] = to_f32(v.get(e));
+    widen<TW>(ld_keep(w + e0 + q * PER), f + q * PER);
   }
 }
 
 // ------------------------------------------------------------------ softmax, resident
-template <typename T, int VPT, bool WARP>
-__global__ void __launch_bounds__(WARP ? 128 : 1024)
-softmax_resident(const T* __restrict__ x, void* __restrict__ out, int64_t rows, int cols, int out_f32, int is_log) {
+// One row by one group of threads (a warp, or the whole CTA).
+template <typename T, int VPT, bool WARP, bool IS_LOG>
+__device__ __forceinline__ void softmax_row(const T* __restrict__ xr, void* __restrict__ out, int64_t out_e0, int nvec, int t, int tpr, int out_f32, float* red) {
   constexpr int VE = Vec<T>::N;
-  __shared__ float red[33];
-  const int tpr = WARP ? 32 : blockDim.x;
-  const int t = WARP ? (threadIdx.x & 31) : threadIdx.x;
-  const int64_t row = WARP ? static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5) : blockIdx.x;
-  if (WARP && row >= rows) return;
-  const int nvec = cols / VE;
-  const T* xr = x + row * cols;
   float f[VPT][VE];
   float m = -CUDART_INF_F;
 #pragma unroll
   for (int u = 0; u < VPT; ++u) {
     const int j = t + u * tpr;
     if (j < nvec) {
-      Vec<T> v;
-      v.raw = ld_stream(xr + static_cast<int64_t>(j) * VE);
+      widen<T>(ld_stream(xr + static_cast<int64_t>(j) * VE), f[u]);
 #pragma unroll
-      for (int e = 0; e < VE; ++e) {
-        f[u][e] = to_f32(v.get(e));
-        m = fmaxf(m, f[u][e]);
-      }
+      for (int e = 0; e < VE; ++e) m = fmaxf(m, f[u][e]);
     }
   }
-  m = group_reduce<WARP>(m, MaxF{}, -CUDART_INF_F, red);
+  m = group_reduce<WARP>(m, MaxF{}, -CUDART_INF_F, red, 0);
   float s = 0.f;
+  // softmax: 2^(x*log2(e) - c) with c = m*log2(e) rounded once; the rounding of c scales
+  // every term of the row alike and cancels in the quotient. Not when c would overflow,
+  // and not for log_softmax, which needs x - m itself.
+  if (!IS_LOG && fabsf(m) < 1e37f) {
+    const float c = m * kLog2e;
 #pragma unroll
-  for (int u = 0; u < VPT; ++u) {
-    const int j = t + u * tpr;
-    if (j < nvec) {
+    for (int u = 0; u < VPT; ++u) {
+      if (t + u * tpr < nvec) {
 #pragma unroll
-      for (int e = 0; e < VE; ++e) {
-        const float d = f[u][e] - m;
-        const float ex = exp2f(d * kLog2e);
-        s += ex;
-        f[u][e] = is_log ? d : ex;
+        for (int e = 0; e < VE; ++e) {
+          f[u][e] = ex2_approx(fmaf(f[u][e], kLog2e, -c));
+          s += f[u][e];
+        }
+      }
+    }
+  } else {
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+      if (t + u * tpr < nvec) {
+#pragma unroll
+        for (int e = 0; e < VE; ++e) {
+          const float d = f[u][e] - m;
+          const float ex = ex2_approx(d * kLog2e);
+          s += ex;
+          f[u][e] = IS_LOG ? d : ex;
+        }
       }
     }
   }
-  s = group_reduce<WARP>(s, SumF{}, 0.f, red);
-  const float k = is_log ? logf(s) : 1.f / s;
+  s = group_reduce<WARP>(s, SumF{}, 0.f, red, 1);
+  const float k = IS_LOG ? logf(s) : 1.f / s;
 #pragma unroll
   for (int u = 0; u < VPT; ++u) {
     const int j = t + u * tpr;
     if (j < nvec) {
 #pragma unroll
-      for (int e = 0; e < VE; ++e) f[u][e] = is_log ? f[u][e] - k : f[u][e] * k;
-      store_row_vec<T>(out, row * cols + static_cast<int64_t>(j) * VE, f[u], out_f32 != 0);
+      for (int e = 0; e < VE; ++e) f[u][e] = IS_LOG ? f[u][e] - k : f[u][e] * k;
+      store_row_vec<T>(out, out_e0 + static_cast<int64_t>(j) * VE, f[u], out_f32 != 0);
     }
   }
+}
+
+template <typename T, int VPT, bool WARP, bool IS_LOG>
+__global__ void __launch_bounds__(WARP ? 128 : 1024)
+softmax_resident(const T* __restrict__ x, void* __restrict__ out, int64_t rows, int cols, int out_f32) {
+  __shared__ float red[64];
+  const int tpr = WARP ? 32 : blockDim.x;
+  const int t = WARP ? (threadIdx.x & 31) : threadIdx.x;
+  const int64_t row = WARP ? static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5) : blockIdx.x;
+  if (WARP && row >= rows) return;
+  softmax_row<T, VPT, WARP, IS_LOG>(x + row * cols, out, row * cols, cols / Vec<T>::N, t, tpr, out_f32, red);
 }
 
 // ------------------------------------------------------------------ softmax, streaming
@@ -153,52 +163,71 @@ __global__ void __launch_bounds__(128) softmax_cols(const T* __restrict__ x, voi
 }
 
 // ------------------------------------------------------------------ layer norm, resident
-template <typename T, typename TW, int VPT, bool WARP>
+// HOLD: the row is widened to fp32 once and held in registers (VE floats per vector);
+// otherwise it stays in its storage type (16 bytes per vector) and is widened again in
+// each of the three passes, which for 16-bit rows halves the registers held across the two
+// reductions. AFFINE: weight and bias are both present (the usual call), so the last pass
+// is one fused multiply-add per element with no per-element tests.
+template <typename T, typename TW, int VPT, bool WARP, bool HOLD, bool AFFINE>
 __global__ void __launch_bounds__(WARP ? 128 : 1024)
 layernorm_resident(const T* __restrict__ x, const TW* __restrict__ w, const TW* __restrict__ b, T* __restrict__ y,
-                   void* __restrict__ mean, void* __restrict__ rstd, int64_t rows, int cols, float eps, int dt_stat) {
+                   void* __restrict__ mean, void* __restrict__ rstd, int64_t rows, int cols, float inv_cols, float eps, int dt_stat) {
   constexpr int VE = Vec<T>::N;
-  __shared__ float red[33];
+  __shared__ float red[64];
   const int tpr = WARP ? 32 : blockDim.x;
   const int t = WARP ? (threadIdx.x & 31) : threadIdx.x;
   const int64_t row = WARP ? static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5) : blockIdx.x;
   if (WARP && row >= rows) return;
   const int nvec = cols / VE;
   const T* xr = x + row * cols;
-  float f[VPT][VE];
+  T* yr = y + row * cols;
+  uint4 raw[HOLD ? 1 : VPT];
+  float f[HOLD ? VPT : 1][VE];
   float s = 0.f;
+  if (HOLD) {
 #pragma unroll
-  for (int u = 0; u < VPT; ++u) {
-    const int j = t + u * tpr;
-    if (j < nvec) {
-      Vec<T> v;
-      v.raw = ld_stream(xr + static_cast<int64_t>(j) * VE);
+    for (int u = 0; u < VPT; ++u) {
+      const int j = t + u * tpr;
+      if (j < nvec) {
+        widen<T>(ld_stream(xr + j * VE), f[HOLD ? u : 0]);
 #pragma unroll
-      for (int e = 0; e < VE; ++e) {
-        f[u][e] = to_f32(v.get(e));
-        s += f[u][e];
+        for (int e = 0; e < VE; ++e) s += f[HOLD ? u : 0][e];
+      }
+    }
+  } else {
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+      const int j = t + u * tpr;
+      if (j < nvec) raw[HOLD ? 0 : u] = ld_stream(xr + j * VE);
+    }
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+      if (t + u * tpr < nvec) {
+        widen<T>(raw[HOLD ? 0 : u], f[0]);
+#pragma unroll
+        for (int e = 0; e < VE; ++e) s += f[0][e];
       }
     }
   }
-  s = group_reduce<WARP>(s, SumF{}, 0.f, red);
-  float mu = s / static_cast<float>(cols);
+  s = group_reduce<WARP>(s, SumF{}, 0.f, red, 0);
+  float mu = s * inv_cols;
   // a row holding NaN or inf has NaN statistics in aten (its running moments turn inf
   // into NaN once another element follows), not mean = inf
   if (!isfinite(mu)) mu = CUDART_NAN_F;
   float q = 0.f;
 #pragma unroll
   for (int u = 0; u < VPT; ++u) {
-    const int j = t + u * tpr;
-    if (j < nvec) {
+    if (t + u * tpr < nvec) {
+      if (!HOLD) widen<T>(raw[HOLD ? 0 : u], f[0]);
 #pragma unroll
       for (int e = 0; e < VE; ++e) {
-        const float d = f[u][e] - mu;
+        const float d = f[HOLD ? u : 0][e] - mu;
         q = fmaf(d, d, q);
       }
     }
   }
-  q = group_reduce<WARP>(q, SumF{}, 0.f, red);
-  const float rs = rsqrtf(q / static_cast<float>(cols) + eps);
+  q = group_reduce<WARP>(q, SumF{}, 0.f, red, 1);
+  const float rs = rsqrtf(fmaf(q, inv_cols, eps));
   if (t == 0) {
     store_from_f32(mean, row, dt_stat, mu);
     store_from_f32(rstd, row, dt_stat, rs);
@@ -207,17 +236,22 @@ layernorm_resident(const T* __restrict__ x, const TW* __restrict__ w, const TW* 
   for (int u = 0; u < VPT; ++u) {
     const int j = t + u * tpr;
     if (j < nvec) {
-      float wv[VE], bv[VE];
-      if (w) load_weights<VE, TW>(w, j * VE, wv);
-      if (b) load_weights<VE, TW>(b, j * VE, bv);
+      float o[VE], wv[VE], bv[VE];
+      if (!HOLD) widen<T>(raw[HOLD ? 0 : u], f[0]);
+      if (AFFINE || w) load_weights<VE, TW>(w, j * VE, wv);
+      if (AFFINE || b) load_weights<VE, TW>(b, j * VE, bv);
 #pragma unroll
       for (int e = 0; e < VE; ++e) {
-        float r = (f[u][e] - mu) * rs;
-        if (w) r *= wv[e];
-        if (b) r += bv[e];
-        f[u][e] = r;
+        float r = (f[HOLD ? u : 0][e] - mu) * rs;
+        if (AFFINE) {
+          r = fmaf(r, wv[e], bv[e]);
+        } else {
+          if (w) r *= wv[e];
+          if (b) r += bv[e];
+        }
+        o[e] = r;
       }
-      store_row_vec<T>(y, row * cols + static_cast<int64_t>(j) * VE, f[u], false);
+      st_stream(yr + j * VE, narrow<T>(o));
     }
   }
 }
@@ -312,22 +346,23 @@ __global__ void __launch_bounds__(256) reduce_rows(const T* __restrict__ x, void
 #pragma unroll
       for (int u = 0; u < 4; ++u) v[u].raw = ld_stream(xr + (j + u * tpr) * VE);
 #pragma unroll
-      for (int u = 0; u < 4; ++u)
+      for (int u = 0; u < 4; ++u) {
+        float fw[VE];
+        widen<T>(v[u].raw, fw);
 #pragma unroll
         for (int e = 0; e < VE; ++e) {
-          const float fv = to_f32(v[u].get(e));
-          if (ARG) arg_take_ascending(a, fv, (j + u * tpr) * VE + e);
-          else s += fv;
+          if (ARG) arg_take_ascending(a, fw[e], (j + u * tpr) * VE + e);
+          else s += fw[e];
         }
+      }
     }
     for (; j < v1; j += tpr) {
-      Vec<T> v;
-      v.raw = ld_stream(xr + j * VE);
+      float fw[VE];
+      widen<T>(ld_stream(xr + j * VE), fw);
 #pragma unroll
       for (int e = 0; e < VE; ++e) {
-        const float fv = to_f32(v.get(e));
-        if (ARG) arg_take_ascending(a, fv, j * VE + e);
-        else s += fv;
+        if (ARG) arg_take_ascending(a, fw[e], j * VE + e);
+        else s += fw[e];
       }
     }
     for (int64_t c = v1 * VE + t; c < c1; c += tpr) {  // ragged end of the last slice
@@ -345,7 +380,7 @@ __global__ void __launch_bounds__(256) reduce_rows(const T* __restrict__ x, void
   const bool split = gridDim.y > 1;
   const int64_t slot = static_cast<int64_t>(blockIdx.y) * rows + row;
   if (!ARG) {
-    s = group_reduce<WARP>(s, SumF{}, 0.f, red);
+    s = WARP ? warp_reduce(s, SumF{}) : block_reduce(s, SumF{}, 0.f, red);
     if (t == 0) {
       if (split) part_v[slot] = s;
       else store_from_f32(out, row, dto, s);
@@ -595,7 +630,7 @@ static ResidentCfg resident_cfg(int64_t nvec, int max_vpt, int target_vpt = 2) {
     c.vpt = static_cast<int>(pow2_at_least((nvec + 31) / 32));
     return c;
   }
-  // softmax: two 16-byte vectors per thread (fewer registers, more resident warps);
+  // two 16-byte vectors per thread (fewer registers, more resident warps), except fp32
   // layer norm: four (its two CTA-wide reductions cost more with many warps)
   int64_t th = pow2_at_least((nvec + target_vpt - 1) / target_vpt);
   if (th < 128) th = 128;
@@ -614,6 +649,11 @@ static ResidentCfg resident_cfg(int64_t nvec, int max_vpt, int target_vpt = 2) {
     default: { constexpr int VPT = (MAXV) >= 8 ? 8 : 4; BODY; } break; \
   }
 
+template <typename T, int VPT, bool WARP>
+static void softmax_launch(unsigned grid, int threads, cudaStream_t st, int is_log, const T* x, void* out, int64_t rows, int cols, int out_f32) {
+  if (is_log) softmax_resident<T, VPT, WARP, true><<<grid, threads, 0, st>>>(x, out, rows, cols, out_f32);
+  else softmax_resident<T, VPT, WARP, false><<<grid, threads, 0, st>>>(x, out, rows, cols, out_f32);
+}
 template <typename T>
 static int softmax_T(const void* x, void* out, int64_t outer, int64_t dim, int64_t inner, int dto, int is_log, cudaStream_t st) {
   constexpr int VE = Vec<T>::N;
@@ -624,9 +664,9 @@ static int softmax_T(const void* x, void* out, int64_t outer, int64_t dim, int64
     const ResidentCfg c = (dim % VE == 0 && aligned16(x) && aligned16(out) && dim < (1LL << 30)) ? resident_cfg(dim / VE, MAXV) : ResidentCfg{false, false, 1, 128};
     if (c.ok && outer <= 0x7fffffffLL) {
       if (c.warp) {
-        B200_DISPATCH_VPT(c.vpt, MAXV, (softmax_resident<T, VPT, true><<<grid_for(outer, 4), 128, 0, st>>>(px, out, outer, static_cast<int>(dim), out_f32, is_log)))
+        B200_DISPATCH_VPT(c.vpt, MAXV, (softmax_launch<T, VPT, true>(grid_for(outer, 4), 128, st, is_log, px, out, outer, static_cast<int>(dim), out_f32)))
       } else {
-        B200_DISPATCH_VPT(c.vpt, MAXV, (softmax_resident<T, VPT, false><<<static_cast<unsigned>(outer), c.threads, 0, st>>>(px, out, outer, static_cast<int>(dim), out_f32, is_log)))
+        B200_DISPATCH_VPT(c.vpt, MAXV, (softmax_launch<T, VPT, false>(static_cast<unsigned>(outer), c.threads, st, is_log, px, out, outer, static_cast<int>(dim), out_f32)))
       }
     } else {
       if (outer > 0x7fffffffLL) return B200_EINVAL;
@@ -642,20 +682,28 @@ static int softmax_T(const void* x, void* out, int64_t outer, int64_t dim, int64
   return check_launch();
 }
 
-template <typename T, typename TW>
-static int layernorm_T(const void* x, const void* w, const void* b, void* y, void* mean, void* rstd, int64_t rows, int64_t cols, float eps, int dt_stat, const ResidentCfg& c, cudaStream_t st) {
+template <typename T, typename TW, bool HOLD, bool AFFINE>
+static int layernorm_launch(const T* px, const TW* pw, const TW* pb, T* py, void* mean, void* rstd, int64_t rows, int64_t cols, float eps, int dt_stat, const ResidentCfg& c, cudaStream_t st) {
   constexpr int VE = Vec<T>::N;
   constexpr int MAXV = 32 / VE;
+  const float inv_cols = 1.f / static_cast<float>(cols);
+  if (c.warp) {
+    B200_DISPATCH_VPT(c.vpt, MAXV, (layernorm_resident<T, TW, VPT, true, HOLD, AFFINE><<<grid_for(rows, 4), 128, 0, st>>>(px, pw, pb, py, mean, rstd, rows, static_cast<int>(cols), inv_cols, eps, dt_stat)))
+  } else {
+    B200_DISPATCH_VPT(c.vpt, MAXV, (layernorm_resident<T, TW, VPT, false, HOLD, AFFINE><<<static_cast<unsigned>(rows), c.threads, 0, st>>>(px, pw, pb, py, mean, rstd, rows, static_cast<int>(cols), inv_cols, eps, dt_stat)))
+  }
+  return check_launch();
+}
+
+template <typename T, typename TW>
+static int layernorm_T(const void* x, const void* w, const void* b, void* y, void* mean, void* rstd, int64_t rows, int64_t cols, float eps, int dt_stat, const ResidentCfg& c, cudaStream_t st) {
   const T* px = static_cast<const T*>(x);
   const TW* pw = static_cast<const TW*>(w);
   const TW* pb = static_cast<const TW*>(b);
   T* py = static_cast<T*>(y);
-  if (c.warp) {
-    B200_DISPATCH_VPT(c.vpt, MAXV, (layernorm_resident<T, TW, VPT, true><<<grid_for(rows, 4), 128, 0, st>>>(px, pw, pb, py, mean, rstd, rows, static_cast<int>(cols), eps, dt_stat)))
-  } else {
-    B200_DISPATCH_VPT(c.vpt, MAXV, (layernorm_resident<T, TW, VPT, false><<<static_cast<unsigned>(rows), c.threads, 0, st>>>(px, pw, pb, py, mean, rstd, rows, static_cast<int>(cols), eps, dt_stat)))
-  }
-  return check_launch();
+  constexpr bool hold = sizeof(T) == 4;  // 16-bit rows stay packed: fewer registers, more resident warps
+  const bool affine = w && b;
+  return affine ? layernorm_launch<T, TW, hold, true>(px, pw, pb, py, mean, rstd, rows, cols, eps, dt_stat, c, st) : layernorm_launch<T, TW, hold, false>(px, pw, pb, py, mean, rstd, rows, cols, eps, dt_stat, c, st);
 }
 
 }  // namespace b200
@@ -731,7 +779,7 @@ extern "C" int b200_layer_norm(const void* x, const void* w, const void* b, void
   const bool wb_ok = (!w && !b) || dt_wb == dt || dt_wb == B200_F32;
   const bool al = aligned16(x) && aligned16(y) && (!w || aligned16(w)) && (!b || aligned16(b));
   ResidentCfg c{false, false, 1, 128};
-  if (cols > 0 && cols % ve == 0 && (dt_wb != B200_F32 || cols % 4 == 0) && al && wb_ok && cols < (1LL << 30)) c = resident_cfg(cols / ve, 32 / ve, 4);
+  if (cols > 0 && cols % ve == 0 && (dt_wb != B200_F32 || cols % 4 == 0) && al && wb_ok && cols < (1LL << 30)) c = resident_cfg(cols / ve, 32 / ve, ve == 4 ? 4 : 2);
   if (!c.ok) {
     layernorm_stream<<<static_cast<unsigned>(rows), 256, 0, st>>>(x, w, b, y, mean, rstd, cols, e, dt, dt_wb, dt_stat);
     return check_launch();

@@ -24,7 +24,7 @@ DEV = "cuda"
 @pytest.fixture(scope="module")
 def backend():
     assert torch.cuda.is_available()
-    assert _abi.lib().b200_abi_version() == 1  # the native library is the thing under test
+    assert _abi.lib().b200_abi_version() == _abi.ABI_VERSION  # the native library is the thing under test
     return B200Backend()
 
 
