@@ -36,9 +36,11 @@ __global__ void __launch_bounds__(kEwThreads) ew_unary_vec(const T* __restrict__
   for (int u = 0; u < kUnroll; ++u) {
     const int64_t i = base + u * kEwThreads;
     if (i < nvec) {
+      float f[VE];
+      widen<T>(v[u].raw, f);
 #pragma unroll
-      for (int e = 0; e < VE; ++e) v[u].set(e, from_f32<T>(op(to_f32(v[u].get(e)))));
-      st_stream(out + i * VE, v[u].raw);
+      for (int e = 0; e < VE; ++e) f[e] = op(f[e]);
+      st_stream(out + i * VE, narrow<T>(f));
     }
   }
   // ragged tail (< VE elements): the last block's first threads
@@ -70,14 +72,12 @@ __global__ void __launch_bounds__(kEwThreads) ew_binary_vec(const T* __restrict_
   for (int u = 0; u < kUnroll; ++u) {
     const int64_t i = base + u * kEwThreads;
     if (i < nvec) {
-      Vec<T> r;
+      float fa[VE], fb[VE];
+      if (MODE != 2) widen<T>(va[u].raw, fa);
+      if (MODE != 1) widen<T>(vb[u].raw, fb);
 #pragma unroll
-      for (int e = 0; e < VE; ++e) {
-        const float fa = MODE == 2 ? sa : to_f32(va[u].get(e));
-        const float fb = MODE == 1 ? sb : to_f32(vb[u].get(e));
-        r.set(e, from_f32<T>(op(fa, fb)));
-      }
-      st_stream(out + i * VE, r.raw);
+      for (int e = 0; e < VE; ++e) fa[e] = op(MODE == 2 ? sa : fa[e], MODE == 1 ? sb : fb[e]);
+      st_stream(out + i * VE, narrow<T>(fa));
     }
   }
   if (blockIdx.x == gridDim.x - 1) {

@@ -12,6 +12,14 @@ struct CloseAcc {
   unsigned nan_seen;
 };
 
+// max_rel = max(max_rel, diff / den), dividing only when the quotient can raise the
+// maximum. The product test is loose by 1e-6, far more than the roundings of the product
+// and of the quotient, so it never hides a new maximum; after the first few elements of a
+// thread almost every element fails it and costs a multiply instead of a division.
+__device__ __forceinline__ void take_rel(CloseAcc& a, float diff, float den) {
+  if (diff > a.max_rel * den * 0.999999f) a.max_rel = fmaxf(a.max_rel, diff / den);
+}
+
 __device__ __forceinline__ void close_step(CloseAcc& a, float r, float s, float rtol, float atol) {
   const bool rn = r != r, sn = s != s;
   const float diff = fabsf(r - s);
@@ -24,7 +32,7 @@ __device__ __forceinline__ void close_step(CloseAcc& a, float r, float s, float 
   if (diff != diff) a.nan_seen = 1;
   else {
     a.max_abs = fmaxf(a.max_abs, diff);
-    a.max_rel = fmaxf(a.max_rel, diff / (fabsf(r) + 1e-10f));
+    take_rel(a, diff, fabsf(r) + 1e-10f);
   }
 }
 
@@ -38,11 +46,11 @@ __global__ void __launch_bounds__(256) allclose_kernel(const T* __restrict__ ref
   if (vec_ok) {
     const int64_t nvec = n / VE;
     for (int64_t j = t0; j < nvec; j += stride) {
-      Vec<T> vr, vs;
-      vr.raw = ld_stream(ref + j * VE);
-      vs.raw = ld_stream(res + j * VE);
+      float fr[VE], fs[VE];
+      widen<T>(ld_stream(ref + j * VE), fr);
+      widen<T>(ld_stream(res + j * VE), fs);
 #pragma unroll
-      for (int e = 0; e < VE; ++e) close_step(a, to_f32(vr.get(e)), to_f32(vs.get(e)), rtol, atol);
+      for (int e = 0; e < VE; ++e) close_step(a, fr[e], fs[e], rtol, atol);
     }
     done = nvec * VE;
   }
@@ -73,7 +81,7 @@ __global__ void __launch_bounds__(256) allclose_int_kernel(const T* __restrict__
     const float fr = static_cast<float>(r), fs = static_cast<float>(s);
     const float diff = fabsf(fr - fs);
     a.max_abs = fmaxf(a.max_abs, diff);
-    a.max_rel = fmaxf(a.max_rel, diff / (fabsf(fr) + 1e-10f));
+    take_rel(a, diff, fabsf(fr) + 1e-10f);
   }
   for (int o = 16; o > 0; o >>= 1) {
     a.bad += __shfl_xor_sync(0xffffffffu, a.bad, o);

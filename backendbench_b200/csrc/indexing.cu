@@ -132,6 +132,61 @@ __global__ void __launch_bounds__(256) gather_dim0_vec4(const uint32_t* __restri
   }
 }
 
+// The same gather when a strip of `self` -- all its rows, kStripW columns -- fits in shared
+// memory: a CTA copies the strip in once (32-byte segments, each source sector read once)
+// and then streams index rows past it, looking every element up in shared memory. Index
+// and output move as 64- and 32-byte row segments; neighbouring CTAs work on neighbouring
+// strips, so the segments of one row meet again in L2 / DRAM pages. What the L2-resident
+// walk above pays per element -- a 32-byte sector crossing the L2-to-SM fabric for 4
+// useful bytes -- is paid here once per source element.
+// One CTA per strip, one CTA per SM at a time, so the strips go by in waves of as many
+// CTAs as there are SMs. The strips of the last, partial wave are cut into `tail_split`
+// row ranges each (blockIdx.x >= whole_strips), so that the wave's work spreads over all
+// SMs instead of leaving most of them idle.
+constexpr int kStripW = 8;
+constexpr int kStripThreads = 1024;
+constexpr int64_t kStripMaxSelfBytes = 200 * 1024;
+__global__ void __launch_bounds__(kStripThreads, 1) gather_dim0_strip(const uint32_t* __restrict__ self, const int64_t* __restrict__ index, uint32_t* __restrict__ out,
+                                                                      int64_t rows, int64_t cols, int64_t self_pitch, int self_rows, int whole_strips, int tail_split, uint32_t* status) {
+  extern __shared__ __align__(16) uint32_t strip[];  // [self_rows][kStripW]
+  int64_t s = blockIdx.x, r_begin = 0, r_end = rows;
+  if (static_cast<int>(blockIdx.x) >= whole_strips) {
+    const int q = (blockIdx.x - whole_strips) / tail_split, piece = (blockIdx.x - whole_strips) % tail_split;
+    const int64_t per = (rows + tail_split - 1) / tail_split;
+    s = whole_strips + q;
+    r_begin = piece * per;
+    r_end = r_begin + per < rows ? r_begin + per : rows;
+  }
+  const int64_t c0 = s * kStripW;
+  for (int h = threadIdx.x; h < self_rows * 2; h += kStripThreads)  // half-rows: 16 bytes each
+    reinterpret_cast<uint4*>(strip)[h] = ld_keep(self + static_cast<int64_t>(h >> 1) * self_pitch + c0 + (h & 1) * 4);
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int rsub = lane >> 2, cp = (lane & 3) * 2;  // a warp covers 8 rows x 8 columns per load
+  constexpr int U = 4;
+  constexpr int kWarps = kStripThreads / 32;
+  for (int64_t r0 = r_begin + warp * (8 * U); r0 < r_end; r0 += kWarps * (8 * U)) {
+    longlong2 k[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t row = r0 + u * 8 + rsub;
+      if (row < r_end) k[u] = __ldcs(reinterpret_cast<const longlong2*>(index + row * cols + c0 + cp));
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t row = r0 + u * 8 + rsub;
+      if (row < r_end) {
+        uint2 v = make_uint2(0u, 0u);
+        if (k[u].x < 0 || k[u].x >= self_rows) flag_oob(status);
+        else v.x = strip[static_cast<int>(k[u].x) * kStripW + cp];
+        if (k[u].y < 0 || k[u].y >= self_rows) flag_oob(status);
+        else v.y = strip[static_cast<int>(k[u].y) * kStripW + cp + 1];
+        __stcs(reinterpret_cast<uint2*>(out + row * cols + c0 + cp), v);
+      }
+    }
+  }
+}
+
 static int capped_grid(int64_t items, int per_block, int waves) {
   int64_t g = (items + per_block - 1) / per_block;
   const int64_t cap = static_cast<int64_t>(kNumSMs) * waves;
@@ -207,6 +262,27 @@ extern "C" int b200_gather(const void* self, const void* index, void* out, int n
   if (!self || !index || !out) return B200_EINVAL;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool idx_contig = is_contiguous(ndim, index_shape, index_strides);
+  if (ndim == 2 && dim == 0 && elem_size == 4 && idx_contig && self_strides[1] == 1 && index_shape[1] % kStripW == 0 && self_strides[0] % 4 == 0 && aligned16(self) && aligned16(index) &&
+      aligned16(out) && self_dim_size > 0 && self_dim_size * kStripW * 4 <= kStripMaxSelfBytes && index_shape[0] >= 512 && index_shape[0] * 2 >= self_dim_size && index_shape[1] / kStripW >= kNumSMs) {
+    const size_t smem = static_cast<size_t>(self_dim_size) * kStripW * 4;
+    static bool allowed = false;
+    if (!allowed) {
+      const cudaError_t e = cudaFuncSetAttribute(gather_dim0_strip, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kStripMaxSelfBytes));
+      if (e != cudaSuccess) { set_last_cuda_error(e); return B200_ELAUNCH; }
+      allowed = true;
+    }
+    const int64_t strips = index_shape[1] / kStripW;
+    const int64_t tail = strips % kNumSMs;
+    int64_t tail_split = tail > 0 ? kNumSMs / tail : 1;
+    if (tail_split > 8) tail_split = 8;  // every piece reloads the strip
+    if (tail_split * 256 > index_shape[0]) tail_split = 1;
+    const int64_t whole = tail_split > 1 ? strips - tail : strips;
+    const int64_t grid = whole + (strips - whole) * tail_split;
+    if (grid > 0x7fffffffLL) return B200_EINVAL;
+    gather_dim0_strip<<<static_cast<unsigned>(grid), kStripThreads, smem, st>>>(static_cast<const uint32_t*>(self), static_cast<const int64_t*>(index), static_cast<uint32_t*>(out), index_shape[0],
+                                                                              index_shape[1], self_strides[0], static_cast<int>(self_dim_size), static_cast<int>(whole), static_cast<int>(tail_split), status);
+    return check_launch();
+  }
   if (ndim == 2 && dim == 0 && elem_size == 4 && idx_contig && self_strides[1] == 1 && index_shape[1] % 4 == 0 && aligned16(index) && aligned16(out)) {
     // column block: about 16 MB of `self` (self_rows x wcols x 4 bytes), a multiple of 4 columns
     int64_t wcols = (16LL << 20) / (4 * (self_dim_size > 0 ? self_dim_size : 1));

@@ -197,6 +197,31 @@ def test_full_size_gather_bit_exact(backend):
     ops.check_device_status()
 
 
+def test_gather_rows_of_self_held_in_shared_memory(backend):
+    """dim-0 gather whose source strip fits in shared memory: ragged row counts, row splits,
+    a source with a row pitch, and an out-of-range index that must be reported, not read."""
+    impl = backend[torch.ops.aten.gather.default]
+    g = torch.Generator(device="cpu").manual_seed(7)
+    for self_rows, rows, cols in [(1000, 777, 1280), (4096, 2051, 1192), (513, 4099, 2368)]:
+        wide = torch.randn(self_rows, cols + 8, generator=g).to(DEV)
+        for x in (wide[:, :cols].contiguous(), wide[:, 4 : cols + 4]):  # dense, and pitched with an offset
+            idx = torch.randint(0, self_rows, (rows, cols), generator=g).to(DEV)
+            assert bits_equal(torch.gather(x, 0, idx), impl(x, 0, idx))
+            ops.check_device_status()
+    x = torch.randn(600, 1280, device=DEV)
+    idx = torch.randint(0, 600, (700, 1280), device=DEV)
+    idx[5, 9] = 600
+    idx[699, 1279] = -1
+    got = impl(x, 0, idx)
+    with pytest.raises(IndexError):
+        ops.check_device_status()
+    ok = idx.clamp(0, 599)
+    want = torch.gather(x, 0, ok)
+    want[5, 9] = 0
+    want[699, 1279] = 0
+    assert bits_equal(want, got)
+
+
 def test_full_size_scatter_add_bit_exact_vs_aten_cpu_order(backend):
     c, op, impl, args, kwargs = _full("scatter_add_f32_4096x4096", backend)
     x, dim, idx, src = args
