@@ -304,12 +304,26 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       tc_fence_after();
       const int64_t m = m0 + q * 32 + lane;
       const uint32_t t_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * kBN + chalf * (kBN / 2));
-#pragma unroll 1
-      for (int c = 0; c < kBN / 2 / 64; ++c) {
-        uint32_t r[64];
-        tc_ld_32x32(t_base + c * 64, r);  // two loads in flight before the wait
-        tc_ld_32x32(t_base + c * 64 + 32, r + 32);
+      // the 64-column chunks of this warp's half are double-buffered in registers: the
+      // tensor-memory load of the next chunk is in flight while this one is converted and stored
+      constexpr int kChunks = kBN / 2 / 64;
+      uint32_t r[kChunks > 1 ? 2 : 1][64];
+      tc_ld_32x32(t_base, r[0]);
+      tc_ld_32x32(t_base + 32, r[0] + 32);
+      const bool plain = p.alpha == 1.f && !p.has_bias;  // C = A x B: nothing to do but round
+#pragma unroll
+      for (int c = 0; c < kChunks; ++c) {
         tc_ld_wait();
+        if (c + 1 < kChunks) {
+          tc_ld_32x32(t_base + (c + 1) * 64, r[(c + 1) & 1]);
+          tc_ld_32x32(t_base + (c + 1) * 64 + 32, r[(c + 1) & 1] + 32);
+        } else {
+          // every value of the accumulator is in registers: hand it back to the MMA warp now
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(tempty_bar(acc));
+        }
+        const uint32_t* rc = r[c & 1];
         const int64_t nb = n0 + c * 64;
         if (p.tma_store) {
           // scale / bias in fp32, round once, park the lane's 64 outputs of its row in this
@@ -323,14 +337,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
           for (int g = 0; g < 8; ++g) {
             const int64_t n = nb + g * 8;
-            Vec<T> o;
+            float v[8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              float v = p.alpha * __uint_as_float(r[g * 8 + e]);
-              if (p.has_bias && m < p.M && n + e < p.N) v = fmaf(p.beta, to_f32(bias[m * p.sbm + (n + e) * p.sbn]), v);
-              o.set(e, from_f32<T>(v));
+            for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(rc[g * 8 + e]);
+            if (!plain) {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                v[e] *= p.alpha;
+                if (p.has_bias && m < p.M && n + e < p.N) v[e] = fmaf(p.beta, to_f32(bias[m * p.sbm + (n + e) * p.sbn]), v[e]);
+              }
             }
-            *reinterpret_cast<uint4*>(mine + lane * 128 + ((g ^ (lane & 7)) << 4)) = o.raw;
+            *reinterpret_cast<uint4*>(mine + lane * 128 + ((g ^ (lane & 7)) << 4)) = narrow<T>(v);
           }
           fence_async_smem();
           __syncwarp();
@@ -340,21 +357,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           }
         } else if (m < p.M && nb < p.N) {
           T* crow = C + (b * p.M + m) * p.N;
-
 #pragma unroll
           for (int g = 0; g < 8; ++g) {
             const int64_t n = nb + g * 8;
             float v[8];
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
-              v[e] = p.alpha * __uint_as_float(r[g * 8 + e]);
+              v[e] = p.alpha * __uint_as_float(rc[g * 8 + e]);
               if (p.has_bias && n + e < p.N) v[e] = fmaf(p.beta, to_f32(bias[m * p.sbm + (n + e) * p.sbn]), v[e]);
             }
             if (vec_ok && n + 8 <= p.N) {
-              Vec<T> o;
-#pragma unroll
-              for (int e = 0; e < 8; ++e) o.set(e, from_f32<T>(v[e]));
-              *reinterpret_cast<uint4*>(crow + n) = o.raw;
+              *reinterpret_cast<uint4*>(crow + n) = narrow<T>(v);
             } else {
 #pragma unroll
               for (int e = 0; e < 8; ++e)
@@ -363,9 +376,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           }
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(tempty_bar(acc));  // this warp has drained its part
       if (++acc == kAccs) { acc = 0; acc_phase ^= 1u; }
     }
     if (lane == 0) tma_store_wait_all();  // tile stores must have left shared memory before the CTA exits
