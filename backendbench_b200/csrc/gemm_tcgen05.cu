@@ -311,6 +311,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       tc_ld_32x32(t_base, r[0]);
       tc_ld_32x32(t_base + 32, r[0] + 32);
       const bool plain = p.alpha == 1.f && !p.has_bias;  // C = A x B: nothing to do but round
+      const bool bias_vec = p.has_bias && p.sbn == 1 && p.sbm % 8 == 0 && (reinterpret_cast<uintptr_t>(bias) & 15u) == 0;
 #pragma unroll
       for (int c = 0; c < kChunks; ++c) {
         tc_ld_wait();
@@ -341,10 +342,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
             for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(rc[g * 8 + e]);
             if (!plain) {
+              if (bias_vec && m < p.M && n + 8 <= p.N) {
+                // unit-stride bias (a row vector, or a matrix like C): eight values in one load
+                float bv[8];
+                widen<T>(ld_keep(bias + m * p.sbm + n), bv);
 #pragma unroll
-              for (int e = 0; e < 8; ++e) {
-                v[e] *= p.alpha;
-                if (p.has_bias && m < p.M && n + e < p.N) v[e] = fmaf(p.beta, to_f32(bias[m * p.sbm + (n + e) * p.sbn]), v[e]);
+                for (int e = 0; e < 8; ++e) v[e] = fmaf(p.beta, bv[e], p.alpha * v[e]);
+              } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                  v[e] *= p.alpha;
+                  if (p.has_bias && m < p.M && n + e < p.N) v[e] = fmaf(p.beta, to_f32(bias[m * p.sbm + (n + e) * p.sbn]), v[e]);
+                }
               }
             }
             *reinterpret_cast<uint4*>(mine + lane * 128 + ((g ^ (lane & 7)) << 4)) = narrow<T>(v);
