@@ -95,10 +95,10 @@ __device__ __forceinline__ void apply_in_rank_order(float* col, int k, float v, 
 // no two lanes share a destination, and the additions are applied in one go. A clash (a
 // real duplicate or a slot collision) falls back to ranking.
 constexpr int kTagSlots = 2048;
-template <int GROUP>
+template <int GROUP, int SLOTS = kTagSlots>
 __device__ __forceinline__ void ordered_step(float* col, unsigned char* tags, int k, float v, int unit, int pos, int lane) {
   constexpr int kUnits = 32 / GROUP;  // groups per warp share one table: fold the unit into the slot
-  const int slot = (k * kUnits + unit) & (kTagSlots - 1);
+  const int slot = (k * kUnits + unit) & (SLOTS - 1);
   if (k >= 0) tags[slot] = static_cast<unsigned char>(lane);
   __syncwarp();
   const bool lost = k >= 0 && tags[slot] != static_cast<unsigned char>(lane);
@@ -231,6 +231,164 @@ scatter_add_strip(const T* __restrict__ self, const int64_t* __restrict__ index,
       }
       __syncthreads();  // the strip is rewritten by the next window / item
     }
+  }
+}
+
+// ------------------------------------------------------------------ wide strip kernel
+// The strip kernel again, for destinations of at most 4096 rows, sized for the memory
+// system instead of for occupancy. A CTA owns EIGHT columns (its fp32 strip is 128 KB at
+// 4096 rows: one CTA per SM), so every source row contributes a 64-byte index segment and
+// a 32-byte (fp32) value segment -- whole sectors, fetched with 16-byte asynchronous copies
+// and no transposition. Each of the eight warps owns one column and walks a tile 32 source
+// rows at a time, lane = source row; the 16-byte chunks of a staged row are XOR-swizzled
+// by the row number so that the 32 rows of one column spread over the banks.
+// With one or two warps per scheduler the kernel runs at the speed of its dependent
+// instruction chain, so the step is kept to a couple of dozen instructions: every offset
+// that depends only on the lane is computed once, row-bound tests exist only for the
+// ragged last tile, and the steps are software-pipelined by hand (the compiler must assume
+// that the tag table and the strip alias): while step st waits for its tag read-back and
+// for the strip value it read ahead, keys, values and tags of step st + 1 are under way.
+constexpr int kWideCols = 8;
+constexpr int kWideTileRows = 128;
+constexpr int kWideThreads = 256;     // eight warps: one column each; all of them stage tiles
+constexpr int kWideTagSlots = 4096;   // one table per warp, exact up to 4096 destinations
+constexpr int kWideStages = 5;        // 12 KB tiles (fp32): 48 KB of source rows in flight per SM
+constexpr int kWideMaxRows = 4096;
+
+template <typename T>
+__global__ void __launch_bounds__(kWideThreads, 1)
+scatter_add_strip_wide(const T* __restrict__ self, const int64_t* __restrict__ index, const T* __restrict__ src, T* __restrict__ out, StripArgs A, uint32_t* status) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  constexpr int kIdxTile = kWideTileRows * kWideCols * 8;                            // 8 KB: [row][4 chunks of 2 indices]
+  constexpr int kSrcRow = kWideCols * static_cast<int>(sizeof(T));                   // 32 or 16 bytes of values per row
+  constexpr int kSrcTile = kWideTileRows * kSrcRow;
+  constexpr int kSrcChunks = kSrcRow / 16;                                           // 16-byte chunks per value row: 2 or 1
+  constexpr int kTile = kIdxTile + kSrcTile;
+  unsigned char* ring = smem_raw;
+  unsigned char* tags = smem_raw + kWideStages * kTile + (threadIdx.x >> 5) * kWideTagSlots;
+  float* strip = reinterpret_cast<float*>(smem_raw + kWideStages * kTile + (kWideThreads / 32) * kWideTagSlots);  // [8][rows]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int rows = static_cast<int>(A.rows);
+  const int64_t nstrips = A.cols / kWideCols;
+  const int ntiles = static_cast<int>((A.idx_rows + kWideTileRows - 1) / kWideTileRows);
+  constexpr int kSegsPerRow = kSrcRow / 16, kPerSeg = 16 / static_cast<int>(sizeof(T));  // 16-byte segments of a destination row
+
+  // staging: this thread copies index chunk (row sr, pair sq) and the same of row sr + 64,
+  // and (threads below 128 * kSrcChunks) value chunk (row vr, chunk vq) of every tile
+  const int sr = tid >> 2, sq = tid & 3;
+  const int s_idx_off = sr * 64 + ((sq ^ ((sr >> 1) & 3)) << 4);  // + 64 * 64 for the second row: same swizzle bits
+  const int vr = tid / kSrcChunks, vq = tid % kSrcChunks;
+  const int s_src_off = kIdxTile + vr * kSrcRow + ((kSrcChunks == 2 ? (vq ^ ((vr >> 2) & 1)) : vq) << 4);
+  // compute: this lane reads row `lane` (+ 32 per step) of column `warp`
+  const int c_idx_off = lane * 64 + (((warp >> 1) ^ ((lane >> 1) & 3)) << 4) + (warp & 1) * 8;
+  const int c_src_off = kIdxTile + lane * kSrcRow + (kSrcChunks == 2 ? (((warp >> 2) ^ ((lane >> 2) & 1)) << 4) : 0) + (warp & (kPerSeg - 1)) * static_cast<int>(sizeof(T));
+  float* col = strip + warp * rows;
+  const uint64_t urows = static_cast<uint64_t>(A.rows);
+
+  for (int64_t item = blockIdx.x; item < A.outer * nstrips; item += gridDim.x) {
+    const int64_t o = item / nstrips, j0 = (item - o * nstrips) * kWideCols;
+    const T* self_o = self + o * A.rows * A.cols + j0;
+    T* out_o = out + o * A.rows * A.cols + j0;
+    const bool active = j0 < A.idx_cols && o < A.idx_outer && ntiles > 0;
+    const int64_t* idx_g = index + o * A.idx_so + j0 + sr * A.idx_sr + sq * 2;
+    const int64_t src_pitch = A.src_sr * static_cast<int64_t>(sizeof(T));
+    const unsigned char* src_g = reinterpret_cast<const unsigned char*>(src + o * A.src_so + j0) + vr * src_pitch + vq * 16;
+    auto issue_tile = [&](int tile, int slot) {
+      if (active && tile < ntiles) {
+        unsigned char* dst = ring + slot * kTile;
+        const int64_t i0 = static_cast<int64_t>(tile) * kWideTileRows;
+        const int64_t* gi = idx_g + i0 * A.idx_sr;
+        if (i0 + kWideTileRows <= A.idx_rows) {
+          __pipeline_memcpy_async(dst + s_idx_off, gi, 16);
+          __pipeline_memcpy_async(dst + s_idx_off + 64 * 64, gi + 64 * A.idx_sr, 16);
+          if (tid < kWideTileRows * kSrcChunks) __pipeline_memcpy_async(dst + s_src_off, src_g + i0 * src_pitch, 16);
+        } else {  // the ragged last tile
+          if (i0 + sr < A.idx_rows) __pipeline_memcpy_async(dst + s_idx_off, gi, 16);
+          if (i0 + sr + 64 < A.idx_rows) __pipeline_memcpy_async(dst + s_idx_off + 64 * 64, gi + 64 * A.idx_sr, 16);
+          if (tid < kWideTileRows * kSrcChunks && i0 + vr < A.idx_rows) __pipeline_memcpy_async(dst + s_src_off, src_g + i0 * src_pitch, 16);
+        }
+      }
+      __pipeline_commit();  // one group per tile slot, empty past the end, so the wait depth stays constant
+    };
+    for (int sidx = 0; sidx < kWideStages - 1; ++sidx) issue_tile(sidx, sidx);  // in flight while the strip loads
+
+    // ---- stage self[:, j0 : j0 + 8] column-major as fp32
+    for (int q0 = 0; q0 < rows * kSegsPerRow; q0 += kWideThreads * 8) {
+      uint4 seg[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int id = q0 + u * kWideThreads + tid;
+        if (id < rows * kSegsPerRow) seg[u] = ld_wide(reinterpret_cast<const uint4*>(self_o + static_cast<int64_t>(id / kSegsPerRow) * A.cols + (id % kSegsPerRow) * kPerSeg));
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int id = q0 + u * kWideThreads + tid;
+        if (id < rows * kSegsPerRow) {
+          float f[kPerSeg];
+          widen<T>(seg[u], f);
+          const int r = id / kSegsPerRow, c0 = (id % kSegsPerRow) * kPerSeg;
+#pragma unroll
+          for (int c = 0; c < kPerSeg; ++c) strip[(c0 + c) * rows + r] = f[c];
+        }
+      }
+    }
+
+    if (active) {
+      int slot = 0, fill_slot = kWideStages - 1;
+      for (int tile = 0; tile < ntiles; ++tile) {
+        __pipeline_wait_prior(kWideStages - 2);  // this thread's copies of tile `tile` have landed
+        __syncthreads();                         // ... everyone's have; all warps are also done with tile - 1 (and with staging the strip)
+        issue_tile(tile + kWideStages - 1, fill_slot);
+        const unsigned char* tile_s = ring + slot * kTile;
+        const int valid_rows = static_cast<int>(A.idx_rows - static_cast<int64_t>(tile) * kWideTileRows);  // >= 128 except in the last tile
+        constexpr int kSteps = kWideTileRows / 32;
+        auto fetch = [&](int st, int& k, float& v) {
+          k = -1 - lane;
+          v = 0.f;
+          if (st * 32 + lane < valid_rows) {
+            const int64_t key = *reinterpret_cast<const int64_t*>(tile_s + c_idx_off + st * (32 * 64));
+            if (static_cast<uint64_t>(key) < urows) {
+              k = static_cast<int>(key);
+              v = to_f32(*reinterpret_cast<const T*>(tile_s + c_src_off + st * (32 * kSrcRow)));
+            } else {
+              flag_oob(status);
+            }
+          }
+        };
+        int k[2];
+        float v[2];
+        fetch(0, k[0], v[0]);
+        if (k[0] >= 0) tags[k[0] & (kWideTagSlots - 1)] = static_cast<unsigned char>(lane);
+#pragma unroll
+        for (int st = 0; st < kSteps; ++st) {
+          const int cur = st & 1, nxt = cur ^ 1;
+          if (st + 1 < kSteps) fetch(st + 1, k[nxt], v[nxt]);
+          __syncwarp();  // the tags of step st are written
+          const bool lost = k[cur] >= 0 && tags[k[cur] & (kWideTagSlots - 1)] != static_cast<unsigned char>(lane);
+          const float old = k[cur] >= 0 ? col[k[cur]] : 0.f;  // read ahead; used only when nothing clashes
+          if (st + 1 < kSteps && k[nxt] >= 0) tags[k[nxt] & (kWideTagSlots - 1)] = static_cast<unsigned char>(lane);  // after this step's read-back, in program order
+          if (!__any_sync(0xffffffffu, lost)) {
+            if (k[cur] >= 0) col[k[cur]] = old + v[cur];
+          } else {
+            apply_in_rank_order(col, k[cur], v[cur], rank_among_earlier<32>(k[cur], lane));
+          }
+        }
+        __syncwarp();
+        if (++slot == kWideStages) slot = 0;
+        if (++fill_slot == kWideStages) fill_slot = 0;
+      }
+    }
+    __pipeline_wait_prior(0);
+    __syncthreads();
+    // ---- write the strip back, rounding once
+    for (int id = tid; id < rows * kSegsPerRow; id += kWideThreads) {
+      const int r = id / kSegsPerRow, c0 = (id % kSegsPerRow) * kPerSeg;
+      float f[kPerSeg];
+#pragma unroll
+      for (int c = 0; c < kPerSeg; ++c) f[c] = strip[(c0 + c) * rows + r];
+      __stcs(reinterpret_cast<uint4*>(out_o + static_cast<int64_t>(r) * A.cols + c0), narrow<T>(f));
+    }
+    __syncthreads();  // the strip and the ring are rewritten by the next item
   }
 }
 
@@ -614,6 +772,17 @@ static int launch_strip(const void* self, const void* index, const void* src, vo
 }
 
 template <typename T>
+static int launch_strip_wide(const void* self, const void* index, const void* src, void* out, const StripArgs& A, uint32_t* status, cudaStream_t st) {
+  const size_t smem = static_cast<size_t>(kWideStages) * kWideTileRows * kWideCols * (8 + sizeof(T)) + (kWideThreads / 32) * kWideTagSlots + static_cast<size_t>(A.rows) * kWideCols * 4;
+  const cudaError_t ae = cudaFuncSetAttribute(scatter_add_strip_wide<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+  if (ae != cudaSuccess) { set_last_cuda_error(ae); return B200_ELAUNCH; }
+  const int64_t items = A.outer * (A.cols / kWideCols);
+  const int grid = static_cast<int>(items < 2LL * kNumSMs ? items : 2LL * kNumSMs);
+  scatter_add_strip_wide<T><<<grid, kWideThreads, smem, st>>>(static_cast<const T*>(self), static_cast<const int64_t*>(index), static_cast<const T*>(src), static_cast<T*>(out), A, status);
+  return check_launch();
+}
+
+template <typename T>
 static int launch_rows(const void* self, const void* index, const void* src, void* out, RowArgs A, uint32_t* status, cudaStream_t st) {
   // two destination rows per warp; shrink the CTA before windowing the destination
   int warps = 8;
@@ -636,7 +805,7 @@ static int launch_rows(const void* self, const void* index, const void* src, voi
 
 namespace b200 {
 
-enum ScatterPath { kPathNone = 0, kPathStrip, kPathRows, kPathBucket, kPathLines };
+enum ScatterPath { kPathNone = 0, kPathStrip, kPathStripWide, kPathRows, kPathBucket, kPathLines };
 
 struct ScatterPlan {
   ScatterPath path;
@@ -677,6 +846,10 @@ static ScatterPlan plan_scatter(const void* self, const void* index, const void*
         if (inner_ok && shape_ok && stride_ok && fits && (strips >= 32 || small)) {
           P.path = kPathStrip;
           P.strip = StripArgs{outer, rows, cols, idx_outer, idx_rows, idx_cols, idx_so, index_strides[dim], src_so, src_strides[dim], 0, 0};
+          // eight columns per CTA when the whole destination strip fits and every staged chunk is 16-byte aligned
+          const bool wide_shape = cols % kWideCols == 0 && idx_cols % kWideCols == 0 && rows <= kWideMaxRows && idx_rows >= 256 && idx_rows < 0x7fffffffLL && outer * (cols / kWideCols) >= kNumSMs / 2;
+          const bool wide_align = index_strides[dim] % 2 == 0 && idx_so % 2 == 0 && (src_strides[dim] * es) % 16 == 0 && (src_so * es) % 16 == 0;
+          if (wide_shape && wide_align && !getenv("B200_NO_WIDE")) P.path = kPathStripWide;
           return P;
         }
       } else if (index_strides[dim] == 1 && src_strides[dim] == 1) {
@@ -729,6 +902,13 @@ extern "C" int b200_scatter_add(const void* self, const void* index, const void*
       case B200_F32: return launch_strip<float>(self, index, src, out, P.strip, status, st);
       case B200_BF16: return launch_strip<__nv_bfloat16>(self, index, src, out, P.strip, status, st);
       default: return launch_strip<__half>(self, index, src, out, P.strip, status, st);
+    }
+  }
+  if (P.path == kPathStripWide) {
+    switch (dtype) {
+      case B200_F32: return launch_strip_wide<float>(self, index, src, out, P.strip, status, st);
+      case B200_BF16: return launch_strip_wide<__nv_bfloat16>(self, index, src, out, P.strip, status, st);
+      default: return launch_strip_wide<__half>(self, index, src, out, P.strip, status, st);
     }
   }
   if (P.path == kPathRows) {

@@ -243,6 +243,43 @@ def test_full_size_scatter_add_bit_exact_vs_aten_cpu_order(backend):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_scatter_add_eight_column_strips_bit_exact(backend, dtype):
+    """Destinations of at most 4096 rows with many columns take the eight-column strip
+    kernel: ragged source-row counts, few destinations (every step collides and is ranked),
+    an index narrower than self, a batch dimension, a strided source, a bad index."""
+    impl = backend[torch.ops.aten.scatter_add.default]
+    g = torch.Generator().manual_seed(33)
+
+    def rn(*shape):
+        return torch.randn(*shape, generator=g).to(dtype)
+
+    def ri(high, *shape):
+        return torch.randint(0, high, shape, generator=g)
+
+    cases = [
+        (rn(300, 1024), 0, ri(300, 1000, 1024), rn(1000, 1024)),
+        (rn(4096, 640), 0, ri(4096, 2051, 640), rn(2051, 640)),
+        (rn(7, 1184), 0, ri(7, 700, 1184), rn(700, 1184)),  # 7 destinations: ~2 rows of every 16 collide
+        (rn(1, 1184), 0, ri(1, 300, 1184), rn(300, 1184)),  # one destination: a fully ordered sum
+        (rn(2, 500, 768), 1, ri(500, 2, 777, 760), rn(2, 777, 768)[:, :, :760]),  # batch, narrower index, strided src
+        (rn(1000, 1280), 0, ri(1000, 512, 1280), rn(600, 1288)[:512, 8:]),
+    ]
+    for x, dim, idx, src in cases:
+        got = impl(x.to(DEV), dim, idx.to(DEV), src.to(DEV))
+        assert bits_equal(oracle.scatter_add(x, dim, idx, src), got), (tuple(x.shape), dim, tuple(idx.shape))
+    ops.check_device_status()
+    x, idx, src = rn(300, 1024), ri(300, 1000, 1024), rn(1000, 1024)
+    idx[17, 5] = 300
+    idx[999, 1023] = -2
+    got = impl(x.to(DEV), 0, idx.to(DEV), src.to(DEV))
+    with pytest.raises(IndexError):
+        ops.check_device_status()
+    src[17, 5] = 0  # a skipped contribution is a contribution of nothing
+    src[999, 1023] = 0
+    assert bits_equal(oracle.scatter_add(x, 0, idx.clamp(0, 299), src), got)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
 def test_scatter_add_grouped_by_destination_path_bit_exact(backend, dtype):
     """Tall / narrow / ragged / strided geometries (too little column or row parallelism for
     the shared-memory kernels) are grouped by destination and replayed in source order; a
