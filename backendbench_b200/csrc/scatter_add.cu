@@ -364,13 +364,30 @@ scatter_add_strip_wide(const T* __restrict__ self, const int64_t* __restrict__ i
           const int cur = st & 1, nxt = cur ^ 1;
           if (st + 1 < kSteps) fetch(st + 1, k[nxt], v[nxt]);
           __syncwarp();  // the tags of step st are written
-          const bool lost = k[cur] >= 0 && tags[k[cur] & (kWideTagSlots - 1)] != static_cast<unsigned char>(lane);
-          const float old = k[cur] >= 0 ? col[k[cur]] : 0.f;  // read ahead; used only when nothing clashes
+          const unsigned winner = k[cur] >= 0 ? tags[k[cur] & (kWideTagSlots - 1)] : static_cast<unsigned>(lane);
+          const bool lost = winner != static_cast<unsigned>(lane);
+          const float old = k[cur] >= 0 ? col[k[cur]] : 0.f;  // read ahead; used only by lanes that nothing clashes with
           if (st + 1 < kSteps && k[nxt] >= 0) tags[k[nxt] & (kWideTagSlots - 1)] = static_cast<unsigned char>(lane);  // after this step's read-back, in program order
-          if (!__any_sync(0xffffffffu, lost)) {
+          const unsigned losers = __ballot_sync(0xffffffffu, lost);
+          if (losers == 0u) {
             if (k[cur] >= 0) col[k[cur]] = old + v[cur];
           } else {
-            apply_in_rank_order(col, k[cur], v[cur], rank_among_earlier<32>(k[cur], lane));
+            // All lanes that share a slot read the same tag: the one lane it names is not
+            // lost, every other one is. So the lanes in a clash are exactly the losers and
+            // the lanes they name; everybody else adds at once, and the few involved add one
+            // after the other in lane order, which is source-row order.
+            unsigned involved = losers | __reduce_or_sync(0xffffffffu, lost ? 1u << winner : 0u);
+            if (__popc(involved) <= 8) {
+              if (k[cur] >= 0 && !((involved >> lane) & 1u)) col[k[cur]] = old + v[cur];
+              while (involved) {
+                const int l = __ffs(involved) - 1;
+                if (lane == l) col[k[cur]] += v[cur];
+                involved &= involved - 1;
+                __syncwarp();
+              }
+            } else {
+              apply_in_rank_order(col, k[cur], v[cur], rank_among_earlier<32>(k[cur], lane));
+            }
           }
         }
         __syncwarp();
