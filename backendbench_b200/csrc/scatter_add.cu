@@ -313,15 +313,15 @@ scatter_add_strip_wide(const T* __restrict__ self, const int64_t* __restrict__ i
     for (int sidx = 0; sidx < kWideStages - 1; ++sidx) issue_tile(sidx, sidx);  // in flight while the strip loads
 
     // ---- stage self[:, j0 : j0 + 8] column-major as fp32
-    for (int q0 = 0; q0 < rows * kSegsPerRow; q0 += kWideThreads * 8) {
-      uint4 seg[8];
+    for (int q0 = 0; q0 < rows * kSegsPerRow; q0 += kWideThreads * 16) {
+      uint4 seg[16];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
+      for (int u = 0; u < 16; ++u) {
         const int id = q0 + u * kWideThreads + tid;
         if (id < rows * kSegsPerRow) seg[u] = ld_wide(reinterpret_cast<const uint4*>(self_o + static_cast<int64_t>(id / kSegsPerRow) * A.cols + (id % kSegsPerRow) * kPerSeg));
       }
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
+      for (int u = 0; u < 16; ++u) {
         const int id = q0 + u * kWideThreads + tid;
         if (id < rows * kSegsPerRow) {
           float f[kPerSeg];
@@ -866,7 +866,7 @@ static ScatterPlan plan_scatter(const void* self, const void* index, const void*
           // eight columns per CTA when the whole destination strip fits and every staged chunk is 16-byte aligned
           const bool wide_shape = cols % kWideCols == 0 && idx_cols % kWideCols == 0 && rows <= kWideMaxRows && idx_rows >= 256 && idx_rows < 0x7fffffffLL && outer * (cols / kWideCols) >= kNumSMs / 2;
           const bool wide_align = index_strides[dim] % 2 == 0 && idx_so % 2 == 0 && (src_strides[dim] * es) % 16 == 0 && (src_so * es) % 16 == 0;
-          if (wide_shape && wide_align && !getenv("B200_NO_WIDE")) P.path = kPathStripWide;
+          if (wide_shape && wide_align) P.path = kPathStripWide;
           return P;
         }
       } else if (index_strides[dim] == 1 && src_strides[dim] == 1) {
