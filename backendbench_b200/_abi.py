@@ -66,6 +66,8 @@ SIGNATURES = {
     "b200_scatter_add": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, I64P, I64P, I64P, I64P, c_int, c_int, c_void_p, c_int64, c_void_p, c_void_p]),
     "b200_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p] + [c_int64] * 12 + [c_double, c_double, c_int, c_void_p, c_void_p]),
     "b200_gemm_uses_tensor_cores": (c_int, [c_int64] * 10 + [c_int, c_void_p, c_void_p, c_void_p]),
+    "b200_gemm_f32_scratch_bytes": (c_int64, [c_int64, c_int64, c_int64, c_int64]),
+    "b200_gemm_f32": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p] + [c_int64] * 12 + [c_double, c_double, c_void_p, c_int64, c_void_p, c_void_p]),
     "b200_allclose": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_double, c_double, c_void_p, c_int, c_void_p]),
     "b200_l2_flush": (c_int, [c_void_p, c_int64, c_void_p]),
 }

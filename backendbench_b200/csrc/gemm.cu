@@ -10,6 +10,11 @@ bool gemm_tc_eligible(int64_t batch, int64_t M, int64_t N, int64_t K, int64_t sA
 int gemm_tc_dispatch(const void* A, const void* B, const void* bias, void* C, int64_t batch, int64_t M, int64_t N, int64_t K, int64_t sAb, int64_t sAm, int64_t sAk,
                      int64_t sBb, int64_t sBk, int64_t sBn, int64_t sbm, int64_t sbn, double alpha, double beta, int dtype, uint32_t* status, cudaStream_t st);
 
+int64_t gemm_f32_split_scratch_bytes(int64_t batch, int64_t M, int64_t N, int64_t K);
+bool gemm_f32_split_eligible(int64_t batch, int64_t M, int64_t N, int64_t K);
+int gemm_f32_split_dispatch(const void* A, const void* B, const void* bias, void* C, int64_t batch, int64_t M, int64_t N, int64_t K, int64_t sAb, int64_t sAm, int64_t sAk, int64_t sBb,
+                            int64_t sBk, int64_t sBn, int64_t sbm, int64_t sbn, double alpha, double beta, void* scratch, int64_t scratch_bytes, uint32_t* status, cudaStream_t st);
+
 __global__ void fill_bias_only(void* C, const void* bias, int64_t batch, int64_t M, int64_t N, int64_t sbm, int64_t sbn, float beta, int dt) {
   const int64_t total = batch * M * N;
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
@@ -44,4 +49,19 @@ extern "C" int b200_gemm(const void* A, const void* B, const void* bias, void* C
   if (gemm_tc_eligible(batch, M, N, K, sAb, sAm, sAk, sBb, sBk, sBn, dtype, A, B, C))
     return gemm_tc_dispatch(A, B, bias, C, batch, M, N, K, sAb, sAm, sAk, sBb, sBk, sBn, sbm, sbn, alpha, beta, dtype, status, st);
   return gemm_simt_dispatch(A, B, bias, C, batch, M, N, K, sAb, sAm, sAk, sBb, sBk, sBn, sbm, sbn, alpha, beta, dtype, st);
+}
+
+extern "C" int64_t b200_gemm_f32_scratch_bytes(int64_t batch, int64_t M, int64_t N, int64_t K) {
+  if (!gemm_f32_split_eligible(batch, M, N, K)) return 0;
+  return gemm_f32_split_scratch_bytes(batch, M, N, K);
+}
+
+extern "C" int b200_gemm_f32(const void* A, const void* B, const void* bias, void* C, int64_t batch, int64_t M, int64_t N, int64_t K, int64_t sAb, int64_t sAm, int64_t sAk,
+                             int64_t sBb, int64_t sBk, int64_t sBn, int64_t sbm, int64_t sbn, double alpha, double beta, void* scratch, int64_t scratch_bytes, uint32_t* status,
+                             void* stream) {
+  if (batch < 0 || M < 0 || N < 0 || K < 0) return B200_EINVAL;
+  if (batch == 0 || M == 0 || N == 0) return B200_OK;
+  if (K == 0 || !gemm_f32_split_eligible(batch, M, N, K)) return b200_gemm(A, B, bias, C, batch, M, N, K, sAb, sAm, sAk, sBb, sBk, sBn, sbm, sbn, alpha, beta, B200_F32, status, stream);
+  if (!A || !B || !C) return B200_EINVAL;
+  return gemm_f32_split_dispatch(A, B, bias, C, batch, M, N, K, sAb, sAm, sAk, sBb, sBk, sBn, sbm, sbn, alpha, beta, scratch, scratch_bytes, status, static_cast<cudaStream_t>(stream));
 }

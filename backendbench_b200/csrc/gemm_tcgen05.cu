@@ -143,6 +143,7 @@ struct GemmTcParams {
   int has_bias;
   int tma_store;    // 1 = C goes out through TMA tile stores (N % 8 == 0, aligned), 0 = plain stores
   int col_fastest;  // tile order: 1 = column-block fastest (write-bound shapes), 0 = grouped row-block fastest
+  int split_slabs;  // 0, or K slabs per plane of fp32 operands split into three bf16 planes (see gemm_f32_split_dispatch)
 };
 
 // Tile t of one batch entry -> (row-block, column-block): column-block fastest, or groups of
@@ -160,9 +161,11 @@ __device__ __forceinline__ void tile_coords(int64_t rem, int64_t mt, int64_t nt,
   nb = static_cast<int>(in_g / gm);
 }
 
-template <typename T, int kBN>
+// T: operand type in shared memory (bf16 / f16). TO: type of C and of the bias -- T itself,
+// or float when the operands are the bf16 planes of split fp32 matrices.
+template <typename T, int kBN, typename TO>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c, const T* __restrict__ bias, T* __restrict__ C, GemmTcParams p,
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c, const TO* __restrict__ bias, TO* __restrict__ C, GemmTcParams p,
                     uint32_t* __restrict__ status) {
   constexpr int kStages = TileCfg<kBN>::kStages, kStageBytes = TileCfg<kBN>::kStageBytes, kAccs = TileCfg<kBN>::kAccs;
   extern __shared__ unsigned char smem_raw[];
@@ -205,7 +208,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
   const int64_t mt = (p.M + kBM - 1) / kBM, nt = (p.N + kBN - 1) / kBN;
   const int64_t tiles = p.batch * mt * nt;
-  const int num_kb = static_cast<int>((p.K + kBK - 1) / kBK);
+  // Split operands: plane q of an operand occupies K coordinates [q * Kp, q * Kp + K) of its
+  // tensor map, Kp = 64 * split_slabs. One slab of the product needs the six plane pairs
+  // whose product is not below fp32 resolution: (0,0) (0,1) (1,0) (0,2) (1,1) (2,0).
+  // They are walked pair by pair over all slabs (see the producer).
+  const int num_kb = p.split_slabs ? 6 * p.split_slabs : static_cast<int>((p.K + kBK - 1) / kBK);
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -222,18 +229,27 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
           const uint32_t a_dst = smem_base + stage * kStageBytes, b_dst = a_dst + kABytes;
           mbar_expect_tx(full_bar(stage), kStageBytes);
-          const int k0 = kb * kBK;
+          int ka = kb * kBK, kbb = kb * kBK;
+          if (p.split_slabs) {
+            // pairs (2,0) (1,1) (0,2) (1,0) (0,1) over all slabs first, then (0,0): the tensor
+            // core truncates when it adds into the accumulator, by half a unit in the last
+            // place of the running sum on average, so the small products go in while the sum
+            // is still small and only the K/16 steps of the leading product pay full price
+            const int pair = kb / p.split_slabs, slab = kb - pair * p.split_slabs;
+            ka = (((0x001012 >> (4 * pair)) & 0xf) * p.split_slabs + slab) * kBK;
+            kbb = (((0x010210 >> (4 * pair)) & 0xf) * p.split_slabs + slab) * kBK;
+          }
           if (!p.a_mn_major) {
-            tma_load_3d(a_dst, &map_a, full_bar(stage), k0, m0, static_cast<int>(b));  // box [128 rows][64 k]
+            tma_load_3d(a_dst, &map_a, full_bar(stage), ka, m0, static_cast<int>(b));  // box [128 rows][64 k]
           } else {
 #pragma unroll
-            for (int c = 0; c < kBM / 64; ++c) tma_load_3d(a_dst + c * 8192, &map_a, full_bar(stage), m0 + c * 64, k0, static_cast<int>(b));  // box [64 k][64 m]
+            for (int c = 0; c < kBM / 64; ++c) tma_load_3d(a_dst + c * 8192, &map_a, full_bar(stage), m0 + c * 64, ka, static_cast<int>(b));  // box [64 k][64 m]
           }
           if (!p.b_mn_major) {
-            tma_load_3d(b_dst, &map_b, full_bar(stage), k0, n0, static_cast<int>(b));  // box [256 rows][64 k]
+            tma_load_3d(b_dst, &map_b, full_bar(stage), kbb, n0, static_cast<int>(b));  // box [256 rows][64 k]
           } else {
 #pragma unroll
-            for (int c = 0; c < kBN / 64; ++c) tma_load_3d(b_dst + c * 8192, &map_b, full_bar(stage), n0 + c * 64, k0, static_cast<int>(b));  // box [64 k][64 n]
+            for (int c = 0; c < kBN / 64; ++c) tma_load_3d(b_dst + c * 8192, &map_b, full_bar(stage), n0 + c * 64, kbb, static_cast<int>(b));  // box [64 k][64 n]
           }
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
@@ -291,7 +307,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    const bool vec_ok = (p.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15u) == 0);
+    constexpr int kOutVec = 16 / static_cast<int>(sizeof(TO));  // outputs per 16-byte store
+    const bool vec_ok = (p.N % kOutVec == 0) && ((reinterpret_cast<uintptr_t>(C) & 15u) == 0);
     for (int64_t t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
       const int64_t b = t / (mt * nt), rem = t - b * (mt * nt);
       int mb, nb_blk;
@@ -311,7 +328,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       tc_ld_32x32(t_base, r[0]);
       tc_ld_32x32(t_base + 32, r[0] + 32);
       const bool plain = p.alpha == 1.f && !p.has_bias;  // C = A x B: nothing to do but round
-      const bool bias_vec = p.has_bias && p.sbn == 1 && p.sbm % 8 == 0 && (reinterpret_cast<uintptr_t>(bias) & 15u) == 0;
+      const bool bias_vec = sizeof(TO) == sizeof(T) && p.has_bias && p.sbn == 1 && p.sbm % 8 == 0 && (reinterpret_cast<uintptr_t>(bias) & 15u) == 0;
 #pragma unroll
       for (int c = 0; c < kChunks; ++c) {
         tc_ld_wait();
@@ -345,7 +362,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
               if (bias_vec && m < p.M && n + 8 <= p.N) {
                 // unit-stride bias (a row vector, or a matrix like C): eight values in one load
                 float bv[8];
-                widen<T>(ld_keep(bias + m * p.sbm + n), bv);
+                widen<T>(ld_keep(bias + m * p.sbm + n), bv);  // TO is T on this path
 #pragma unroll
                 for (int e = 0; e < 8; ++e) v[e] = fmaf(p.beta, bv[e], p.alpha * v[e]);
               } else {
@@ -365,7 +382,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             tma_store_commit();
           }
         } else if (m < p.M && nb < p.N) {
-          T* crow = C + (b * p.M + m) * p.N;
+          TO* crow = C + (b * p.M + m) * p.N;
 #pragma unroll
           for (int g = 0; g < 8; ++g) {
             const int64_t n = nb + g * 8;
@@ -376,11 +393,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
               if (p.has_bias && n + e < p.N) v[e] = fmaf(p.beta, to_f32(bias[m * p.sbm + (n + e) * p.sbn]), v[e]);
             }
             if (vec_ok && n + 8 <= p.N) {
-              *reinterpret_cast<uint4*>(crow + n) = narrow<T>(v);
+#pragma unroll
+              for (int h = 0; h < 8 / kOutVec; ++h) *reinterpret_cast<uint4*>(crow + n + h * kOutVec) = narrow<TO>(v + h * kOutVec);
             } else {
 #pragma unroll
               for (int e = 0; e < 8; ++e)
-                if (n + e < p.N) crow[n + e] = from_f32<T>(v[e]);
+                if (n + e < p.N) crow[n + e] = from_f32<TO>(v[e]);
             }
           }
         }
@@ -506,6 +524,7 @@ int gemm_tc_dispatch(const void* A, const void* B, const void* bias, void* C, in
   // write neighbouring column blocks of the same rows (whole DRAM pages); otherwise order
   // tiles for operand reuse in L2
   p.col_fastest = (K + kBK - 1) / kBK <= 4 ? 1 : 0;
+  p.split_slabs = 0;
   // a narrow C takes the 128-wide tile. (Write-bound shapes with few K slabs were measured
   // slower on it: 256-byte row segments instead of 512-byte ones cost more in DRAM than the
   // deeper pipeline gains -- bmm 32x2048x128x2048: 0.162 ms vs 0.116 ms.)
@@ -523,14 +542,182 @@ int gemm_tc_dispatch(const void* A, const void* B, const void* bias, void* C, in
   if (dtype == B200_BF16) {
     const __nv_bfloat16* bt = static_cast<const __nv_bfloat16*>(bias);
     __nv_bfloat16* ct = static_cast<__nv_bfloat16*>(C);
-    rc = narrow ? launch(gemm_tcgen05_kernel<__nv_bfloat16, 128>, bt, ct) : launch(gemm_tcgen05_kernel<__nv_bfloat16, 256>, bt, ct);
+    rc = narrow ? launch(gemm_tcgen05_kernel<__nv_bfloat16, 128, __nv_bfloat16>, bt, ct) : launch(gemm_tcgen05_kernel<__nv_bfloat16, 256, __nv_bfloat16>, bt, ct);
   } else {
     const __half* bt = static_cast<const __half*>(bias);
     __half* ct = static_cast<__half*>(C);
-    rc = narrow ? launch(gemm_tcgen05_kernel<__half, 128>, bt, ct) : launch(gemm_tcgen05_kernel<__half, 256>, bt, ct);
+    rc = narrow ? launch(gemm_tcgen05_kernel<__half, 128, __half>, bt, ct) : launch(gemm_tcgen05_kernel<__half, 256, __half>, bt, ct);
   }
   if (rc) return rc;
   return check_launch();
+}
+
+// ------------------------------------------------------------------ fp32 operands on the tensor cores
+// An fp32 value is the sum of three bf16 values to within 2^-25 of itself (x1 = bf16(x),
+// x2 = bf16(x - x1), x3 = bf16(x - x1 - x2); the subtractions are exact). A product of fp32
+// matrices is therefore, to fp32 accuracy, the sum of the six bf16 products
+// A1B1 + A1B2 + A2B1 + A1B3 + A2B2 + A3B1 (the three left out are below 2^-25 relative) --
+// every one exact in the tensor core's fp32 accumulator. The kernel above runs them as one
+// contraction of depth 6 K: the operands are split once into planes laid side by side along
+// K, and the producer warp walks the six plane pairs of every K slab.
+//
+// split_f32_planes: x [batch, mn, k] (any strides) -> bf16 planes. K-major form (src K
+// stride 1, or neither stride 1): out[b][mn][q * Kp + k]; MN-major form (src MN stride 1):
+// out[b][q * Kp + k][mn]. Kp = K rounded up to 64; the pad [K, Kp) is written as zero.
+// Infinities and NaN stay in plane 0 alone (x - x1 would be NaN); a value whose bf16
+// rounding overflows is truncated instead. An infinity still meets the residual planes of
+// the other operand, whose signs are arbitrary (inf - inf = NaN where fp32 arithmetic gives
+// inf), so the rows of A and columns of B that hold a non-finite value are flagged and
+// gemm_f32_fixup recomputes their outputs in plain fp32 after the tensor-core kernel.
+struct SplitArgs {
+  int64_t batch, mn, k, kp;
+  int64_t s_b, s_mn, s_k;        // source strides, elements
+  int64_t o_b, o_row;            // output batch stride and row pitch, elements
+  int mn_major;                  // output form
+  unsigned char* line_flag;      // [batch * mn]: set where the row of A / column of B holds an infinity or a NaN
+  uint32_t* any_flag;            // set when any line flag is
+};
+__device__ __forceinline__ void split3(float x, __nv_bfloat16& a, __nv_bfloat16& b, __nv_bfloat16& c) {
+  if (!isfinite(x)) { a = __float2bfloat16_rn(x); b = c = __float2bfloat16_rn(0.f); return; }
+  float x1 = __bfloat162float(__float2bfloat16_rn(x));
+  if (!isfinite(x1)) x1 = __uint_as_float(__float_as_uint(x) & 0xffff0000u);
+  const float r1 = x - x1;
+  const float x2 = __bfloat162float(__float2bfloat16_rn(r1));
+  const float r2 = r1 - x2;
+  a = __float2bfloat16_rn(x1);
+  b = __float2bfloat16_rn(x2);
+  c = __float2bfloat16_rn(r2);
+}
+__global__ void __launch_bounds__(256) split_f32_planes(const float* __restrict__ x, __nv_bfloat16* __restrict__ out, SplitArgs A) {
+  // the fast-moving index of a thread block follows the contiguous dimension of the output
+  const int64_t inner = A.mn_major ? A.mn : A.kp, outer = A.mn_major ? A.kp : A.mn;
+  const int64_t per_batch = inner * outer;
+  const int64_t total = A.batch * per_batch;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t b = i / per_batch, r = i - b * per_batch;
+    const int64_t o = r / inner, in = r - o * inner;
+    const int64_t k = A.mn_major ? o : in, mn = A.mn_major ? in : o;
+    __nv_bfloat16 p0, p1, p2;
+    p0 = p1 = p2 = __float2bfloat16_rn(0.f);
+    if (k < A.k) {
+      const float v = x[b * A.s_b + mn * A.s_mn + k * A.s_k];
+      split3(v, p0, p1, p2);
+      if (!isfinite(v)) {
+        A.line_flag[b * A.mn + mn] = 1;
+        *A.any_flag = 1u;
+      }
+    }
+    __nv_bfloat16* ob = out + b * A.o_b;
+    if (A.mn_major) {
+      ob[k * A.o_row + mn] = p0;
+      ob[(A.kp + k) * A.o_row + mn] = p1;
+      ob[(2 * A.kp + k) * A.o_row + mn] = p2;
+    } else {
+      ob[mn * A.o_row + k] = p0;
+      ob[mn * A.o_row + A.kp + k] = p1;
+      ob[mn * A.o_row + 2 * A.kp + k] = p2;
+    }
+  }
+}
+
+// Outputs whose row of A or column of B holds an infinity or a NaN, recomputed as an fp32
+// dot product (one thread per output). Returns at once when nothing was flagged.
+struct FixupArgs {
+  int64_t batch, M, N, K;
+  int64_t sAb, sAm, sAk, sBb, sBk, sBn, sbm, sbn;
+  float alpha, beta;
+  int has_bias;
+};
+__global__ void __launch_bounds__(128) gemm_f32_fixup(const float* __restrict__ A, const float* __restrict__ B, const float* __restrict__ bias, float* __restrict__ C, FixupArgs F,
+                                                      const unsigned char* __restrict__ row_flag, const unsigned char* __restrict__ col_flag, const uint32_t* __restrict__ any_flag) {
+  if (*any_flag == 0u) return;
+  for (int64_t r = blockIdx.x; r < F.batch * F.M; r += gridDim.x) {
+    const int64_t b = r / F.M, m = r - b * F.M;
+    const bool whole_row = row_flag[r] != 0;
+    for (int64_t n = threadIdx.x; n < F.N; n += blockDim.x) {
+      if (!whole_row && col_flag[b * F.N + n] == 0) continue;
+      const float* a = A + b * F.sAb + m * F.sAm;
+      const float* bb = B + b * F.sBb + n * F.sBn;
+      float acc = 0.f;
+      for (int64_t k = 0; k < F.K; ++k) acc = fmaf(a[k * F.sAk], bb[k * F.sBk], acc);
+      acc *= F.alpha;
+      if (F.has_bias) acc = fmaf(F.beta, bias[m * F.sbm + n * F.sbn], acc);
+      C[(b * F.M + m) * F.N + n] = acc;
+    }
+  }
+}
+
+static inline int64_t round_up(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
+
+int64_t gemm_f32_split_scratch_bytes(int64_t batch, int64_t M, int64_t N, int64_t K) {
+  const int64_t kp = round_up(K, kBK);
+  return batch * 3 * kp * (round_up(M, 8) + round_up(N, 8)) * 2 + round_up(batch * (M + N) + 4, 256) + 512;
+}
+
+bool gemm_f32_split_eligible(int64_t batch, int64_t M, int64_t N, int64_t K) {
+  if (batch < 1 || M < 1 || N < 1 || K < 1) return false;
+  if (M > 0x7fffffffLL || N > 0x7fffffffLL || 3 * round_up(K, kBK) > 0x7fffffffLL || batch > 0x7fffffffLL) return false;
+  return encode_fn() != nullptr;
+}
+
+int gemm_f32_split_dispatch(const void* A, const void* B, const void* bias, void* C, int64_t batch, int64_t M, int64_t N, int64_t K, int64_t sAb, int64_t sAm, int64_t sAk, int64_t sBb,
+                            int64_t sBk, int64_t sBn, int64_t sbm, int64_t sbn, double alpha, double beta, void* scratch, int64_t scratch_bytes, uint32_t* status, cudaStream_t st) {
+  if (!gemm_f32_split_eligible(batch, M, N, K)) return B200_EINVAL;
+  if (!scratch || scratch_bytes < gemm_f32_split_scratch_bytes(batch, M, N, K)) return B200_ESCRATCH;
+  const int64_t kp = round_up(K, kBK);
+  // scratch: [any flag (4 bytes) | row flags of A | column flags of B] [planes of A] [planes of B]
+  unsigned char* flags = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(scratch) + 255) & ~static_cast<uintptr_t>(255));
+  const int64_t flag_bytes = round_up(batch * (M + N) + 4, 256);
+  uint32_t* any_flag = reinterpret_cast<uint32_t*>(flags);
+  unsigned char* row_flag = flags + 4;
+  unsigned char* col_flag = row_flag + batch * M;
+  const cudaError_t me = cudaMemsetAsync(flags, 0, static_cast<size_t>(flag_bytes), st);
+  if (me != cudaSuccess) { set_last_cuda_error(me); return B200_ELAUNCH; }
+  auto* pa = reinterpret_cast<__nv_bfloat16*>(flags + flag_bytes);
+  const bool a_mn = sAm == 1 && sAk != 1 && M > 1, b_mn = sBn == 1 && sBk != 1 && N > 1;  // keep the contiguous dimension of each source
+  const int64_t a_row = a_mn ? round_up(M, 8) : 3 * kp, a_rows = a_mn ? 3 * kp : M;
+  const int64_t b_row = b_mn ? round_up(N, 8) : 3 * kp, b_rows = b_mn ? 3 * kp : N;
+  __nv_bfloat16* pb = pa + batch * a_rows * a_row;  // a multiple of 8 elements: stays 16-byte aligned
+  const SplitArgs sa{batch, M, K, kp, sAb, sAm, sAk, a_rows * a_row, a_row, a_mn ? 1 : 0, row_flag, any_flag};
+  const SplitArgs sb{batch, N, K, kp, sBb, sBn, sBk, b_rows * b_row, b_row, b_mn ? 1 : 0, col_flag, any_flag};
+  auto blocks = [](int64_t n) { const int64_t b = (n + 255) / 256; return static_cast<int>(b < 1 ? 1 : (b > kNumSMs * 32LL ? kNumSMs * 32LL : b)); };
+  split_f32_planes<<<blocks(batch * M * kp), 256, 0, st>>>(static_cast<const float*>(A), pa, sa);
+  split_f32_planes<<<blocks(batch * N * kp), 256, 0, st>>>(static_cast<const float*>(B), pb, sb);
+  const cudaError_t se = cudaGetLastError();
+  if (se != cudaSuccess) { set_last_cuda_error(se); return B200_ELAUNCH; }
+
+  // the planes as [rows, 3 Kp] (K-major) or [3 Kp, rows] (MN-major) bf16 operands
+  alignas(64) CUtensorMap map_a, map_b;
+  const int bn = N <= 128 ? 128 : 256;
+  if (!encode_operand(&map_a, pa, B200_BF16, a_mn, M, 3 * kp, a_mn ? 1 : a_row, a_mn ? a_row : 1, a_rows * a_row, batch, kBM)) return B200_EDRIVER;
+  if (!encode_operand(&map_b, pb, B200_BF16, b_mn, N, 3 * kp, b_mn ? 1 : b_row, b_mn ? b_row : 1, b_rows * b_row, batch, bn)) return B200_EDRIVER;
+  GemmTcParams p;
+  p.tma_store = 0;
+  p.M = M; p.N = N; p.K = K; p.batch = batch;
+  p.sbm = sbm; p.sbn = sbn;
+  p.alpha = static_cast<float>(alpha);
+  p.beta = static_cast<float>(beta);
+  p.a_mn_major = a_mn ? 1 : 0;
+  p.b_mn_major = b_mn ? 1 : 0;
+  p.is_bf16 = 1;
+  p.has_bias = (bias != nullptr && p.beta != 0.f) ? 1 : 0;
+  p.split_slabs = static_cast<int>(kp / kBK);
+  p.col_fastest = 6 * p.split_slabs <= 4 ? 1 : 0;
+  const int64_t tiles = batch * ((M + kBM - 1) / kBM) * ((N + bn - 1) / bn);
+  const int grid = static_cast<int>(tiles < kNumSMs ? tiles : kNumSMs);
+  auto launch = [&](auto kernel) -> int {
+    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemmSmem));
+    if (e != cudaSuccess) { set_last_cuda_error(e); return B200_ELAUNCH; }
+    kernel<<<grid, kGemmThreads, kGemmSmem, st>>>(map_a, map_b, map_a, static_cast<const float*>(bias), static_cast<float*>(C), p, status);
+    return B200_OK;
+  };
+  const int rc = bn == 128 ? launch(gemm_tcgen05_kernel<__nv_bfloat16, 128, float>) : launch(gemm_tcgen05_kernel<__nv_bfloat16, 256, float>);
+  if (rc) return rc;
+  const FixupArgs F{batch, M, N, K, sAb, sAm, sAk, sBb, sBk, sBn, sbm, sbn, p.alpha, p.beta, p.has_bias};
+  const int64_t fix_blocks = batch * M < 8LL * kNumSMs ? batch * M : 8LL * kNumSMs;
+  gemm_f32_fixup<<<static_cast<int>(fix_blocks), 128, 0, st>>>(static_cast<const float*>(A), static_cast<const float*>(B), static_cast<const float*>(bias), static_cast<float*>(C), F, row_flag,
+                                                             col_flag, any_flag);
+  return check_launch(4);
 }
 
 }  // namespace b200

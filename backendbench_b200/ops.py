@@ -607,6 +607,8 @@ def scatter_add_default(self: torch.Tensor, dim: int, index: torch.Tensor, src: 
 
 
 # --------------------------------------------------------------------- contraction
+F32_SPLIT_MIN_MACS = 1 << 26  # batch*M*N*K from which an fp32 product takes the split tensor-core path
+
 def _tma_ready(t: torch.Tensor, s_b: int, s_mn: int, s_k: int, batch: int) -> bool:
     """An operand [batch, mn, k] the tensor-core kernel can load as is: one unit stride, the
     other (and the batch stride) a multiple of 8 elements, base 16-byte aligned."""
@@ -661,6 +663,21 @@ def _gemm(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor], batch:
             raise RuntimeError("addmm: self must be broadcastable to a matrix")
         sbm, sbn = bs
         bias_ptr = bias.data_ptr()
+    # Large fp32 products run on the tensor cores too: the operands are split into three bf16
+    # planes each in scratch memory and six plane products are accumulated in fp32, which
+    # keeps fp32 accuracy (see include/b200ops.h). Small ones stay on the CUDA-core kernel.
+    if a.dtype == torch.float32 and batch * M * N * K >= F32_SPLIT_MIN_MACS and K >= 32 and M >= 32 and N >= 32:
+        need = int(lib().b200_gemm_f32_scratch_bytes(batch, M, N, K))
+        if need > 0:
+            scratch = _scratch(a.device, need)
+            check(
+                lib().b200_gemm_f32(
+                    a.data_ptr(), b.data_ptr(), bias_ptr, out.data_ptr(), batch, M, N, K, sa[0], sa[1], sa[2], sb[0], sb[1], sb[2], sbm, sbn,
+                    float(alpha), float(beta), scratch.data_ptr(), need, _status(a.device).data_ptr(), _stream_handle(),
+                ),
+                "b200_gemm_f32",
+            )
+            return out
     check(
         lib().b200_gemm(
             a.data_ptr(), b.data_ptr(), bias_ptr, out.data_ptr(), batch, M, N, K, sa[0], sa[1], sa[2], sb[0], sb[1], sb[2], sbm, sbn,

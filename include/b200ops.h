@@ -222,6 +222,20 @@ int b200_gemm_uses_tensor_cores(int64_t batch, int64_t M, int64_t N, int64_t K, 
                                 int64_t sAm, int64_t sAk, int64_t sBb, int64_t sBk, int64_t sBn,
                                 int dtype, const void* A, const void* B, const void* C);
 
+/* The same contraction for fp32 operands on the tensor cores: A and B are split once into
+ * three bf16 planes each (x = x1 + x2 + x3 to within 2^-25), written to caller scratch, and
+ * the six plane products that matter at fp32 resolution are accumulated in fp32 by the
+ * tcgen05 kernel. The result agrees with an fp32 product to a few units in the last place
+ * of the accumulated magnitude; it pays off when M*N*K is large (the split is one extra
+ * pass over A and B). Any operand strides; C contiguous fp32; bias fp32. Scratch size from
+ * b200_gemm_f32_scratch_bytes. (The reference has one matmul per dtype: eval.py:100-102.) */
+int64_t b200_gemm_f32_scratch_bytes(int64_t batch, int64_t M, int64_t N, int64_t K);
+int b200_gemm_f32(const void* A, const void* B, const void* bias, void* C, int64_t batch,
+                  int64_t M, int64_t N, int64_t K, int64_t sAb, int64_t sAm, int64_t sAk,
+                  int64_t sBb, int64_t sBk, int64_t sBn, int64_t sbias_m, int64_t sbias_n,
+                  double alpha, double beta, void* scratch, int64_t scratch_bytes,
+                  uint32_t* status, void* stream);
+
 /* ------------------------------------------------------------- evaluation path */
 
 /* One pass replacing BackendBench/eval.py:68-90 (`allclose`: torch.testing.assert_close

@@ -102,3 +102,66 @@ def test_large_misaligned_operands_are_repitched_onto_tensor_cores(dtype):
     x, y = _rand((4, 300, 1001), dtype, g, 1001**-0.5), _rand((4, 260, 1001), dtype, g, 1.0).transpose(1, 2)  # K-major B, K = 1001
     _check(ops.bmm_default(x, y), x.double() @ y.double(), dtype)
     ops.check_device_status()
+
+
+def _check32(got, a, b, extra=None, alpha=1.0, beta=1.0):
+    """fp32 result against the fp64 product. The tensor core truncates each of its K/16
+    additions into the accumulator (half a unit in the last place of the running sum on
+    average, always toward zero), so the allowed error is K/16 such units of a running sum
+    as large as the result or four standard deviations of it."""
+    K = a.shape[-1]
+    exact = alpha * (a.double() @ b.double())
+    spread = abs(alpha) * ((a.double() ** 2) @ (b.double() ** 2)).sqrt()
+    if extra is not None:
+        exact = exact + beta * extra.double()
+    err = (got.double() - exact).abs()
+    bound = 2.0**-24 * (K / 16 + 4) * (exact.abs() + 4 * spread) + 1e-30
+    assert got.dtype == torch.float32 and bool((err <= bound).all()), float((err / bound).max())
+
+
+@pytest.mark.parametrize("a_t,b_t", [(False, False), (False, True), (True, False), (True, True)])
+def test_large_fp32_products_take_split_bf16_planes_on_tensor_cores(a_t, b_t):
+    """fp32 mm / addmm / bmm above the size threshold: operands split into three bf16 planes,
+    six plane products accumulated in fp32 by the tcgen05 kernel. Every operand layout, ragged
+    M / N / K (K padded to 64 inside the planes), bias with alpha / beta, batches."""
+    g = torch.Generator(device=DEV).manual_seed(12)
+    for M, N, K in [(512, 512, 512), (446, 2048, 1024), (130, 1000, 1111), (1000, 36, 4099), (33, 8192, 300)]:
+        assert M * N * K >= ops.F32_SPLIT_MIN_MACS
+        a = torch.randn((K, M) if a_t else (M, K), generator=g, device=DEV)
+        b = torch.randn((N, K) if b_t else (K, N), generator=g, device=DEV)
+        a = a.t() if a_t else a
+        b = b.t() if b_t else b
+        _check32(ops.mm_default(a, b), a, b)
+        bias = torch.randn(N, generator=g, device=DEV)
+        _check32(ops.addmm_default(bias, a, b, beta=0.5, alpha=-1.5), a, b, bias.expand(M, N), -1.5, 0.5)
+    B, M, N, K = 4, 200, 264, 640
+    a = torch.randn((B, K, M) if a_t else (B, M, K), generator=g, device=DEV)
+    b = torch.randn((B, N, K) if b_t else (B, K, N), generator=g, device=DEV)
+    a = a.transpose(1, 2) if a_t else a
+    b = b.transpose(1, 2) if b_t else b
+    _check32(ops.bmm_default(a, b), a, b)
+    ops.check_device_status()
+
+
+def test_split_fp32_product_keeps_special_values_and_wide_ranges():
+    g = torch.Generator(device=DEV).manual_seed(13)
+    a = torch.randn(512, 512, generator=g, device=DEV) * torch.logspace(-20, 20, 512, device=DEV)  # columns spanning 40 decades
+    b = torch.randn(512, 512, generator=g, device=DEV) * torch.logspace(20, -20, 512, device=DEV).unsqueeze(1)
+    _check32(ops.mm_default(a, b), a, b)
+    a = torch.randn(512, 512, generator=g, device=DEV)
+    b = torch.randn(512, 512, generator=g, device=DEV)
+    a[3, 7] = float("inf")
+    a[5, 9] = float("nan")
+    a[8, 1] = 3.4e38  # rounds to infinity as bf16: must stay finite
+    b[1] *= 1e-3      # ... and its products stay below the fp32 maximum
+    got, want = ops.mm_default(a, b), a @ b
+    assert bool(torch.isnan(got[5]).all()) and bool(torch.isinf(got[3]).all()) and bool((got[3] == want[3]).all())
+    assert bool(torch.isfinite(got[8]).all()) and bool(((got[8] - want[8]).abs() <= 1e-5 * want[8].abs()).all())
+    b[:, 11] = float("-inf")  # a whole output column: -inf * a, NaN where a is 0 or NaN
+    a[40, :] = 0.0
+    got, want = ops.mm_default(a, b), a @ b
+    assert bool((torch.isnan(got[:, 11]) == torch.isnan(want[:, 11])).all()) and bool((got[:, 11][~torch.isnan(want[:, 11])] == want[:, 11][~torch.isnan(want[:, 11])]).all())
+    rest = [i for i in range(512) if i not in (3, 5, 8)]
+    cols = [j for j in range(512) if j != 11]
+    _check32(got[rest][:, cols], a[rest], b[:, cols])
+    ops.check_device_status()
