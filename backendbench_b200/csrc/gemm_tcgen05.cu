@@ -589,33 +589,60 @@ __device__ __forceinline__ void split3(float x, __nv_bfloat16& a, __nv_bfloat16&
   c = __float2bfloat16_rn(r2);
 }
 __global__ void __launch_bounds__(256) split_f32_planes(const float* __restrict__ x, __nv_bfloat16* __restrict__ out, SplitArgs A) {
-  // the fast-moving index of a thread block follows the contiguous dimension of the output
+  // A thread produces 8 consecutive elements along the contiguous dimension of the output
+  // (k in the K-major form, mn in the MN-major form): two 16-byte loads when the source is
+  // contiguous and aligned there, three 16-byte stores.
   const int64_t inner = A.mn_major ? A.mn : A.kp, outer = A.mn_major ? A.kp : A.mn;
-  const int64_t per_batch = inner * outer;
+  const int64_t groups = (inner + 7) / 8;  // kp is a multiple of 8; a ragged mn tail is a partial group
+  const int64_t per_batch = groups * outer;
   const int64_t total = A.batch * per_batch;
+  const int64_t s_in = A.mn_major ? A.s_mn : A.s_k, s_out = A.mn_major ? A.s_k : A.s_mn;  // source strides along inner / outer
+  const int64_t lim_in = A.mn_major ? A.mn : A.k, lim_out = A.mn_major ? A.k : A.mn;      // where real data ends
+  const bool vec = s_in == 1 && s_out % 4 == 0 && A.s_b % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     const int64_t b = i / per_batch, r = i - b * per_batch;
-    const int64_t o = r / inner, in = r - o * inner;
-    const int64_t k = A.mn_major ? o : in, mn = A.mn_major ? in : o;
-    __nv_bfloat16 p0, p1, p2;
-    p0 = p1 = p2 = __float2bfloat16_rn(0.f);
-    if (k < A.k) {
-      const float v = x[b * A.s_b + mn * A.s_mn + k * A.s_k];
-      split3(v, p0, p1, p2);
-      if (!isfinite(v)) {
-        A.line_flag[b * A.mn + mn] = 1;
-        *A.any_flag = 1u;
+    const int64_t o = r / groups, in0 = (r - o * groups) * 8;
+    float v[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = 0.f;
+    if (o < lim_out) {
+      const float* src = x + b * A.s_b + o * s_out + in0 * s_in;
+      if (vec && in0 + 8 <= lim_in) {
+        const float4 lo = __ldcs(reinterpret_cast<const float4*>(src)), hi = __ldcs(reinterpret_cast<const float4*>(src) + 1);
+        v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w; v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          if (in0 + e < lim_in) v[e] = src[e * s_in];
       }
     }
+    __nv_bfloat16 q0[8], q1[8], q2[8];
+    bool bad = false;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      split3(v[e], q0[e], q1[e], q2[e]);
+      bad |= !isfinite(v[e]);
+    }
+    if (bad) {
+      *A.any_flag = 1u;
+      if (A.mn_major) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          if (!isfinite(v[e])) A.line_flag[b * A.mn + in0 + e] = 1;
+      } else {
+        A.line_flag[b * A.mn + o] = 1;
+      }
+    }
+    // o_row is a multiple of 8 and so are in0 and kp: every store below is 16-byte aligned
     __nv_bfloat16* ob = out + b * A.o_b;
     if (A.mn_major) {
-      ob[k * A.o_row + mn] = p0;
-      ob[(A.kp + k) * A.o_row + mn] = p1;
-      ob[(2 * A.kp + k) * A.o_row + mn] = p2;
+      *reinterpret_cast<uint4*>(ob + o * A.o_row + in0) = *reinterpret_cast<const uint4*>(q0);
+      *reinterpret_cast<uint4*>(ob + (A.kp + o) * A.o_row + in0) = *reinterpret_cast<const uint4*>(q1);
+      *reinterpret_cast<uint4*>(ob + (2 * A.kp + o) * A.o_row + in0) = *reinterpret_cast<const uint4*>(q2);
     } else {
-      ob[mn * A.o_row + k] = p0;
-      ob[mn * A.o_row + A.kp + k] = p1;
-      ob[mn * A.o_row + 2 * A.kp + k] = p2;
+      *reinterpret_cast<uint4*>(ob + o * A.o_row + in0) = *reinterpret_cast<const uint4*>(q0);
+      *reinterpret_cast<uint4*>(ob + o * A.o_row + A.kp + in0) = *reinterpret_cast<const uint4*>(q1);
+      *reinterpret_cast<uint4*>(ob + o * A.o_row + 2 * A.kp + in0) = *reinterpret_cast<const uint4*>(q2);
     }
   }
 }
@@ -681,8 +708,8 @@ int gemm_f32_split_dispatch(const void* A, const void* B, const void* bias, void
   const SplitArgs sa{batch, M, K, kp, sAb, sAm, sAk, a_rows * a_row, a_row, a_mn ? 1 : 0, row_flag, any_flag};
   const SplitArgs sb{batch, N, K, kp, sBb, sBn, sBk, b_rows * b_row, b_row, b_mn ? 1 : 0, col_flag, any_flag};
   auto blocks = [](int64_t n) { const int64_t b = (n + 255) / 256; return static_cast<int>(b < 1 ? 1 : (b > kNumSMs * 32LL ? kNumSMs * 32LL : b)); };
-  split_f32_planes<<<blocks(batch * M * kp), 256, 0, st>>>(static_cast<const float*>(A), pa, sa);
-  split_f32_planes<<<blocks(batch * N * kp), 256, 0, st>>>(static_cast<const float*>(B), pb, sb);
+  split_f32_planes<<<blocks(batch * a_rows * a_row / 24), 256, 0, st>>>(static_cast<const float*>(A), pa, sa);
+  split_f32_planes<<<blocks(batch * b_rows * b_row / 24), 256, 0, st>>>(static_cast<const float*>(B), pb, sb);
   const cudaError_t se = cudaGetLastError();
   if (se != cudaSuccess) { set_last_cuda_error(se); return B200_ELAUNCH; }
 
