@@ -13,6 +13,7 @@ struct GemmArgs {
   int64_t M, N, K;
   int64_t sAb, sAm, sAk, sBb, sBk, sBn, sbm, sbn;
   float alpha, beta;
+  const uint32_t* gate;  // when not NULL: the kernel does its work only if this device word is non-zero
 };
 
 // TM x TN outputs per CTA (256 threads, (TM/16) x (TN/16) per thread), 16-deep K slices.
@@ -23,6 +24,7 @@ template <typename T, int kTM, int kTN>
 __global__ void __launch_bounds__(256) gemm_simt(const T* __restrict__ A, const T* __restrict__ B, const T* __restrict__ bias, T* __restrict__ C, GemmArgs g) {
   __shared__ __align__(16) float As[kTK][kTM + 4];
   __shared__ __align__(16) float Bs[kTK][kTN + 4];
+  if (g.gate && *g.gate == 0u) return;
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
   const int64_t m0 = static_cast<int64_t>(blockIdx.y) * kTM, n0 = static_cast<int64_t>(blockIdx.x) * kTN;
   const int64_t b = blockIdx.z;
@@ -121,8 +123,8 @@ static int launch_simt(const void* A, const void* B, const void* bias, void* C, 
 }
 
 int gemm_simt_dispatch(const void* A, const void* B, const void* bias, void* C, int64_t batch, int64_t M, int64_t N, int64_t K, int64_t sAb, int64_t sAm, int64_t sAk,
-                       int64_t sBb, int64_t sBk, int64_t sBn, int64_t sbm, int64_t sbn, double alpha, double beta, int dtype, cudaStream_t st) {
-  GemmArgs g{M, N, K, sAb, sAm, sAk, sBb, sBk, sBn, sbm, sbn, static_cast<float>(alpha), static_cast<float>(beta)};
+                       int64_t sBb, int64_t sBk, int64_t sBn, int64_t sbm, int64_t sbn, double alpha, double beta, int dtype, cudaStream_t st, const uint32_t* gate) {
+  GemmArgs g{M, N, K, sAb, sAm, sAk, sBb, sBk, sBn, sbm, sbn, static_cast<float>(alpha), static_cast<float>(beta), gate};
   switch (dtype) {
     case B200_F32: return launch_simt<float>(A, B, bias, C, batch, g, st);
     case B200_BF16: return launch_simt<__nv_bfloat16>(A, B, bias, C, batch, g, st);

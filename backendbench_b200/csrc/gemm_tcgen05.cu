@@ -144,6 +144,7 @@ struct GemmTcParams {
   int tma_store;    // 1 = C goes out through TMA tile stores (N % 8 == 0, aligned), 0 = plain stores
   int col_fastest;  // tile order: 1 = column-block fastest (write-bound shapes), 0 = grouped row-block fastest
   int split_slabs;  // 0, or K slabs per plane of fp32 operands split into three bf16 planes (see gemm_f32_split_dispatch)
+  const uint32_t* skip_if_set;  // when not NULL: the kernel returns at once if this device word is non-zero
 };
 
 // Tile t of one batch entry -> (row-block, column-block): column-block fastest, or groups of
@@ -168,6 +169,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c, const TO* __restrict__ bias, TO* __restrict__ C, GemmTcParams p,
                     uint32_t* __restrict__ status) {
   constexpr int kStages = TileCfg<kBN>::kStages, kStageBytes = TileCfg<kBN>::kStageBytes, kAccs = TileCfg<kBN>::kAccs;
+  if (p.skip_if_set && *p.skip_if_set != 0u) return;  // every thread of every CTA reads the same word: a uniform exit before any barrier or TMEM set-up
   extern __shared__ unsigned char smem_raw[];
   // 1024-byte alignment: the 128B swizzle pattern repeats every 8 rows x 128 bytes
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -459,6 +461,9 @@ static OperandLayout operand_layout(int64_t mn, int64_t k, int64_t s_mn, int64_t
   return r;
 }
 
+int gemm_simt_dispatch(const void* A, const void* B, const void* bias, void* C, int64_t batch, int64_t M, int64_t N, int64_t K, int64_t sAb, int64_t sAm, int64_t sAk,
+                       int64_t sBb, int64_t sBk, int64_t sBn, int64_t sbm, int64_t sbn, double alpha, double beta, int dtype, cudaStream_t st, const uint32_t* gate);
+
 bool gemm_tc_eligible(int64_t batch, int64_t M, int64_t N, int64_t K, int64_t sAb, int64_t sAm, int64_t sAk, int64_t sBb, int64_t sBk, int64_t sBn, int dtype, const void* A,
                       const void* B, const void* C) {
   if (dtype != B200_BF16 && dtype != B200_F16) return false;
@@ -525,6 +530,7 @@ int gemm_tc_dispatch(const void* A, const void* B, const void* bias, void* C, in
   // tiles for operand reuse in L2
   p.col_fastest = (K + kBK - 1) / kBK <= 4 ? 1 : 0;
   p.split_slabs = 0;
+  p.skip_if_set = nullptr;
   // a narrow C takes the 128-wide tile. (Write-bound shapes with few K slabs were measured
   // slower on it: 256-byte row segments instead of 512-byte ones cost more in DRAM than the
   // deeper pipeline gains -- bmm 32x2048x128x2048: 0.162 ms vs 0.116 ms.)
@@ -567,15 +573,15 @@ int gemm_tc_dispatch(const void* A, const void* B, const void* bias, void* C, in
 // Infinities and NaN stay in plane 0 alone (x - x1 would be NaN); a value whose bf16
 // rounding overflows is truncated instead. An infinity still meets the residual planes of
 // the other operand, whose signs are arbitrary (inf - inf = NaN where fp32 arithmetic gives
-// inf), so the rows of A and columns of B that hold a non-finite value are flagged and
-// gemm_f32_fixup recomputes their outputs in plain fp32 after the tensor-core kernel.
+// inf), so the split raises a device flag when it meets a non-finite value: the tensor-core
+// kernel returns at once when the flag is up and the CUDA-core kernel, launched behind it
+// and gated the other way, computes that product in plain fp32.
 struct SplitArgs {
   int64_t batch, mn, k, kp;
   int64_t s_b, s_mn, s_k;        // source strides, elements
   int64_t o_b, o_row;            // output batch stride and row pitch, elements
   int mn_major;                  // output form
-  unsigned char* line_flag;      // [batch * mn]: set where the row of A / column of B holds an infinity or a NaN
-  uint32_t* any_flag;            // set when any line flag is
+  uint32_t* any_flag;            // set when the operand holds an infinity or a NaN
 };
 __device__ __forceinline__ void split3(float x, __nv_bfloat16& a, __nv_bfloat16& b, __nv_bfloat16& c) {
   if (!isfinite(x)) { a = __float2bfloat16_rn(x); b = c = __float2bfloat16_rn(0.f); return; }
@@ -623,16 +629,7 @@ __global__ void __launch_bounds__(256) split_f32_planes(const float* __restrict_
       split3(v[e], q0[e], q1[e], q2[e]);
       bad |= !isfinite(v[e]);
     }
-    if (bad) {
-      *A.any_flag = 1u;
-      if (A.mn_major) {
-#pragma unroll
-        for (int e = 0; e < 8; ++e)
-          if (!isfinite(v[e])) A.line_flag[b * A.mn + in0 + e] = 1;
-      } else {
-        A.line_flag[b * A.mn + o] = 1;
-      }
-    }
+    if (bad) *A.any_flag = 1u;
     // o_row is a multiple of 8 and so are in0 and kp: every store below is 16-byte aligned
     __nv_bfloat16* ob = out + b * A.o_b;
     if (A.mn_major) {
@@ -647,38 +644,11 @@ __global__ void __launch_bounds__(256) split_f32_planes(const float* __restrict_
   }
 }
 
-// Outputs whose row of A or column of B holds an infinity or a NaN, recomputed as an fp32
-// dot product (one thread per output). Returns at once when nothing was flagged.
-struct FixupArgs {
-  int64_t batch, M, N, K;
-  int64_t sAb, sAm, sAk, sBb, sBk, sBn, sbm, sbn;
-  float alpha, beta;
-  int has_bias;
-};
-__global__ void __launch_bounds__(128) gemm_f32_fixup(const float* __restrict__ A, const float* __restrict__ B, const float* __restrict__ bias, float* __restrict__ C, FixupArgs F,
-                                                      const unsigned char* __restrict__ row_flag, const unsigned char* __restrict__ col_flag, const uint32_t* __restrict__ any_flag) {
-  if (*any_flag == 0u) return;
-  for (int64_t r = blockIdx.x; r < F.batch * F.M; r += gridDim.x) {
-    const int64_t b = r / F.M, m = r - b * F.M;
-    const bool whole_row = row_flag[r] != 0;
-    for (int64_t n = threadIdx.x; n < F.N; n += blockDim.x) {
-      if (!whole_row && col_flag[b * F.N + n] == 0) continue;
-      const float* a = A + b * F.sAb + m * F.sAm;
-      const float* bb = B + b * F.sBb + n * F.sBn;
-      float acc = 0.f;
-      for (int64_t k = 0; k < F.K; ++k) acc = fmaf(a[k * F.sAk], bb[k * F.sBk], acc);
-      acc *= F.alpha;
-      if (F.has_bias) acc = fmaf(F.beta, bias[m * F.sbm + n * F.sbn], acc);
-      C[(b * F.M + m) * F.N + n] = acc;
-    }
-  }
-}
-
 static inline int64_t round_up(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
 
 int64_t gemm_f32_split_scratch_bytes(int64_t batch, int64_t M, int64_t N, int64_t K) {
   const int64_t kp = round_up(K, kBK);
-  return batch * 3 * kp * (round_up(M, 8) + round_up(N, 8)) * 2 + round_up(batch * (M + N) + 4, 256) + 512;
+  return batch * 3 * kp * (round_up(M, 8) + round_up(N, 8)) * 2 + 256 + 512;
 }
 
 bool gemm_f32_split_eligible(int64_t batch, int64_t M, int64_t N, int64_t K) {
@@ -692,21 +662,19 @@ int gemm_f32_split_dispatch(const void* A, const void* B, const void* bias, void
   if (!gemm_f32_split_eligible(batch, M, N, K)) return B200_EINVAL;
   if (!scratch || scratch_bytes < gemm_f32_split_scratch_bytes(batch, M, N, K)) return B200_ESCRATCH;
   const int64_t kp = round_up(K, kBK);
-  // scratch: [any flag (4 bytes) | row flags of A | column flags of B] [planes of A] [planes of B]
+  // scratch: [flag word, padded to 256 bytes] [planes of A] [planes of B]
   unsigned char* flags = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(scratch) + 255) & ~static_cast<uintptr_t>(255));
-  const int64_t flag_bytes = round_up(batch * (M + N) + 4, 256);
+  const int64_t flag_bytes = 256;
   uint32_t* any_flag = reinterpret_cast<uint32_t*>(flags);
-  unsigned char* row_flag = flags + 4;
-  unsigned char* col_flag = row_flag + batch * M;
-  const cudaError_t me = cudaMemsetAsync(flags, 0, static_cast<size_t>(flag_bytes), st);
+  const cudaError_t me = cudaMemsetAsync(flags, 0, 4, st);
   if (me != cudaSuccess) { set_last_cuda_error(me); return B200_ELAUNCH; }
   auto* pa = reinterpret_cast<__nv_bfloat16*>(flags + flag_bytes);
   const bool a_mn = sAm == 1 && sAk != 1 && M > 1, b_mn = sBn == 1 && sBk != 1 && N > 1;  // keep the contiguous dimension of each source
   const int64_t a_row = a_mn ? round_up(M, 8) : 3 * kp, a_rows = a_mn ? 3 * kp : M;
   const int64_t b_row = b_mn ? round_up(N, 8) : 3 * kp, b_rows = b_mn ? 3 * kp : N;
   __nv_bfloat16* pb = pa + batch * a_rows * a_row;  // a multiple of 8 elements: stays 16-byte aligned
-  const SplitArgs sa{batch, M, K, kp, sAb, sAm, sAk, a_rows * a_row, a_row, a_mn ? 1 : 0, row_flag, any_flag};
-  const SplitArgs sb{batch, N, K, kp, sBb, sBn, sBk, b_rows * b_row, b_row, b_mn ? 1 : 0, col_flag, any_flag};
+  const SplitArgs sa{batch, M, K, kp, sAb, sAm, sAk, a_rows * a_row, a_row, a_mn ? 1 : 0, any_flag};
+  const SplitArgs sb{batch, N, K, kp, sBb, sBn, sBk, b_rows * b_row, b_row, b_mn ? 1 : 0, any_flag};
   auto blocks = [](int64_t n) { const int64_t b = (n + 255) / 256; return static_cast<int>(b < 1 ? 1 : (b > kNumSMs * 32LL ? kNumSMs * 32LL : b)); };
   split_f32_planes<<<blocks(batch * a_rows * a_row / 24), 256, 0, st>>>(static_cast<const float*>(A), pa, sa);
   split_f32_planes<<<blocks(batch * b_rows * b_row / 24), 256, 0, st>>>(static_cast<const float*>(B), pb, sb);
@@ -729,6 +697,7 @@ int gemm_f32_split_dispatch(const void* A, const void* B, const void* bias, void
   p.is_bf16 = 1;
   p.has_bias = (bias != nullptr && p.beta != 0.f) ? 1 : 0;
   p.split_slabs = static_cast<int>(kp / kBK);
+  p.skip_if_set = any_flag;
   p.col_fastest = 6 * p.split_slabs <= 4 ? 1 : 0;
   const int64_t tiles = batch * ((M + kBM - 1) / kBM) * ((N + bn - 1) / bn);
   const int grid = static_cast<int>(tiles < kNumSMs ? tiles : kNumSMs);
@@ -740,11 +709,10 @@ int gemm_f32_split_dispatch(const void* A, const void* B, const void* bias, void
   };
   const int rc = bn == 128 ? launch(gemm_tcgen05_kernel<__nv_bfloat16, 128, float>) : launch(gemm_tcgen05_kernel<__nv_bfloat16, 256, float>);
   if (rc) return rc;
-  const FixupArgs F{batch, M, N, K, sAb, sAm, sAk, sBb, sBk, sBn, sbm, sbn, p.alpha, p.beta, p.has_bias};
-  const int64_t fix_blocks = batch * M < kNumSMs ? batch * M : kNumSMs;  // almost always returns at its first instruction
-  gemm_f32_fixup<<<static_cast<int>(fix_blocks), 128, 0, st>>>(static_cast<const float*>(A), static_cast<const float*>(B), static_cast<const float*>(bias), static_cast<float*>(C), F, row_flag,
-                                                             col_flag, any_flag);
-  return check_launch(4);
+  // the same product on the CUDA cores, run only when the split met an infinity or a NaN
+  const int rs = gemm_simt_dispatch(A, B, bias, C, batch, M, N, K, sAb, sAm, sAk, sBb, sBk, sBn, sbm, sbn, alpha, beta, B200_F32, st, any_flag);
+  if (rs) return rs;
+  return check_launch(3);
 }
 
 }  // namespace b200

@@ -227,7 +227,9 @@ int b200_gemm_uses_tensor_cores(int64_t batch, int64_t M, int64_t N, int64_t K, 
  * the six plane products that matter at fp32 resolution are accumulated in fp32 by the
  * tcgen05 kernel. The result agrees with an fp32 product to a few units in the last place
  * of the accumulated magnitude; it pays off when M*N*K is large (the split is one extra
- * pass over A and B). Any operand strides; C contiguous fp32; bias fp32. Scratch size from
+ * pass over A and B). Operands holding an infinity or a NaN are detected on the device and
+ * that product is computed by the CUDA-core kernel instead (fp32 special-value semantics).
+ * Any operand strides; C contiguous fp32; bias fp32. Scratch size from
  * b200_gemm_f32_scratch_bytes. (The reference has one matmul per dtype: eval.py:100-102.) */
 int64_t b200_gemm_f32_scratch_bytes(int64_t batch, int64_t M, int64_t N, int64_t K);
 int b200_gemm_f32(const void* A, const void* B, const void* bias, void* C, int64_t batch,
