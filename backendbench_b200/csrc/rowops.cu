@@ -558,9 +558,13 @@ static ReducePlan plan_reduce(int64_t outer, int64_t dim, int64_t inner) {
   int64_t ctas = inner == 1 ? outer : outer * ((inner + 255) / 256);
   ReducePlan p{1, dim};
   const int64_t want = 2LL * kNumSMs;
-  if (ctas >= want || dim < 4096) return p;
+  // A row reduction (inner == 1) is worth splitting from 4096 elements, 1024 per split. A
+  // column reduction walks `dim` one row per iteration, every row a coalesced read, and with
+  // few columns it has few threads: split it from 128 rows, 32 per split.
+  const int64_t min_dim = inner == 1 ? 4096 : 128, min_chunk = inner == 1 ? 1024 : 32;
+  if (ctas >= want || dim < min_dim) return p;
   int64_t s = (want + ctas - 1) / ctas;
-  const int64_t max_s = dim / 1024;  // keep >= 1024 elements per split
+  const int64_t max_s = dim / min_chunk;
   if (s > max_s) s = max_s;
   if (s > 1024) s = 1024;
   if (s <= 1) return p;

@@ -637,7 +637,9 @@ def _gemm(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor], batch:
     # 16-bit operands whose layout the tensor-core path cannot load (row pitch or base off the
     # 16-byte grid, e.g. K = 2049) are re-pitched once when the product is large enough for
     # the tensor cores to pay for the extra copy; otherwise the CUDA-core kernel takes them
-    if a.dtype != torch.float32 and M * N * K * batch >= (1 << 24) and K >= 16:
+    # (a long contraction with a small output is re-pitched too: the CUDA-core kernel would
+    # walk all of K in one or two CTAs)
+    if a.dtype != torch.float32 and (M * N * K * batch >= (1 << 24) or K >= 1024) and K >= 16:
         if not _tma_ready(a, sa[0], sa[1], sa[2], batch):
             if sa[1] != 1 or sa[2] == 1:  # keep A K-major unless it is M-major
                 a, (pb, pr) = _repitch(a, batch, M, K, sa[0], sa[1], sa[2])
@@ -666,7 +668,8 @@ def _gemm(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor], batch:
     # Large fp32 products run on the tensor cores too: the operands are split into three bf16
     # planes each in scratch memory and six plane products are accumulated in fp32, which
     # keeps fp32 accuracy (see include/b200ops.h). Small ones stay on the CUDA-core kernel.
-    if a.dtype == torch.float32 and batch * M * N * K >= F32_SPLIT_MIN_MACS and K >= 32 and M >= 32 and N >= 32:
+    macs = batch * M * N * K
+    if a.dtype == torch.float32 and ((macs >= F32_SPLIT_MIN_MACS and K >= 32 and M >= 32 and N >= 32) or (K >= 2048 and macs >= (1 << 22))):
         need = int(lib().b200_gemm_f32_scratch_bytes(batch, M, N, K))
         if need > 0:
             scratch = _scratch(a.device, need)

@@ -165,3 +165,16 @@ def test_split_fp32_product_keeps_special_values_and_wide_ranges():
     cols = [j for j in range(512) if j != 11]
     _check32(got[rest][:, cols], a[rest], b[:, cols])
     ops.check_device_status()
+
+
+def test_long_contractions_with_small_outputs_leave_the_single_cta_path():
+    """K in the thousands with a handful of outputs: 16-bit operands are re-pitched onto the
+    tensor cores whatever their alignment, fp32 operands take the split path."""
+    g = torch.Generator(device=DEV).manual_seed(14)
+    a, b, bias = _rand((32, 4096), torch.bfloat16, g, 4096**-0.5), _rand((4096, 31), torch.bfloat16, g, 1.0), _rand((32, 1), torch.bfloat16, g, 1.0)
+    _check(ops.addmm_default(bias, a, b), a.double() @ b.double() + bias.double(), torch.bfloat16)
+    a32, b32 = torch.randn(16, 8192, generator=g, device=DEV), torch.randn(8192, 40, generator=g, device=DEV)
+    _check32(ops.mm_default(a32, b32), a32, b32)
+    a32, b32 = torch.randn(1, 4096, generator=g, device=DEV), torch.randn(4096, 1024, generator=g, device=DEV)
+    _check32(ops.mm_default(a32, b32), a32, b32)
+    ops.check_device_status()
