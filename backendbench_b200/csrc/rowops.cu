@@ -145,6 +145,94 @@ __global__ void __launch_bounds__(256) softmax_stream(const T* __restrict__ x, v
   }
 }
 
+// ------------------------------------------------------------------ ragged rows, one warp each
+// Rows of 33 ... 32 * NPL elements whose length or base is off the 16-byte grid (the vector
+// kernels cannot take them, and a CTA per row would idle most of its threads): a warp reads
+// its row with coalesced scalar loads, lane l holding elements l, l + 32, ..., in registers,
+// and does the same arithmetic as the resident kernels.
+template <typename T, int NPL, bool IS_LOG>
+__global__ void __launch_bounds__(128) softmax_warp_ragged(const T* __restrict__ x, void* __restrict__ out, int64_t rows, int cols, int dto) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const T* xr = x + row * cols;
+  float f[NPL];
+  float m = -CUDART_INF_F;
+#pragma unroll
+  for (int i = 0; i < NPL; ++i) {
+    const int c = lane + 32 * i;
+    f[i] = c < cols ? to_f32(xr[c]) : -CUDART_INF_F;
+    m = fmaxf(m, f[i]);
+  }
+  m = warp_reduce(m, MaxF{});
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < NPL; ++i) {
+    const float d = f[i] - m;
+    const float ex = lane + 32 * i < cols ? ex2_approx(d * kLog2e) : 0.f;
+    s += ex;
+    f[i] = IS_LOG ? d : ex;
+  }
+  s = warp_reduce(s, SumF{});
+  const float k = IS_LOG ? logf(s) : 1.f / s;
+#pragma unroll
+  for (int i = 0; i < NPL; ++i) {
+    const int c = lane + 32 * i;
+    if (c < cols) store_from_f32(out, row * cols + c, dto, IS_LOG ? f[i] - k : f[i] * k);
+  }
+}
+
+template <typename T, int NPL>
+__global__ void __launch_bounds__(128) layernorm_warp_ragged(const T* __restrict__ x, const void* __restrict__ w, const void* __restrict__ b, T* __restrict__ y, void* __restrict__ mean,
+                                                             void* __restrict__ rstd, int64_t rows, int cols, float eps, int dt_wb, int dt_stat) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const T* xr = x + row * cols;
+  float f[NPL];
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < NPL; ++i) {
+    const int c = lane + 32 * i;
+    f[i] = c < cols ? to_f32(xr[c]) : 0.f;
+    s += f[i];
+  }
+  s = warp_reduce(s, SumF{});
+  float mu = s / static_cast<float>(cols);
+  if (!isfinite(mu)) mu = CUDART_NAN_F;  // same non-finite rule as the resident kernel
+  float q = 0.f;
+#pragma unroll
+  for (int i = 0; i < NPL; ++i) {
+    const float d = lane + 32 * i < cols ? f[i] - mu : 0.f;
+    q = fmaf(d, d, q);
+  }
+  q = warp_reduce(q, SumF{});
+  const float rs = rsqrtf(q / static_cast<float>(cols) + eps);
+  if (lane == 0) {
+    store_from_f32(mean, row, dt_stat, mu);
+    store_from_f32(rstd, row, dt_stat, rs);
+  }
+#pragma unroll
+  for (int i = 0; i < NPL; ++i) {
+    const int c = lane + 32 * i;
+    if (c < cols) {
+      float r = (f[i] - mu) * rs;
+      if (w) r *= load_as_f32(w, c, dt_wb);
+      if (b) r += load_as_f32(b, c, dt_wb);
+      y[row * cols + c] = from_f32<T>(r);
+    }
+  }
+}
+
+// NPL for a ragged row of `cols` elements: 2, 4, ..., 32 elements per lane (cols <= 1024)
+#define B200_DISPATCH_NPL(COLS, BODY)                       \
+  if ((COLS) <= 64) { constexpr int NPL = 2; BODY; }        \
+  else if ((COLS) <= 128) { constexpr int NPL = 4; BODY; }  \
+  else if ((COLS) <= 256) { constexpr int NPL = 8; BODY; }  \
+  else if ((COLS) <= 512) { constexpr int NPL = 16; BODY; } \
+  else { constexpr int NPL = 32; BODY; }
+constexpr int kRaggedMaxCols = 1024;
+
 // ------------------------------------------------------------------ softmax, inner > 1
 template <typename T>
 __global__ void __launch_bounds__(128) softmax_cols(const T* __restrict__ x, void* __restrict__ out, int64_t dim, int64_t inner, int dto, int is_log) {
@@ -672,6 +760,10 @@ static int softmax_T(const void* x, void* out, int64_t outer, int64_t dim, int64
       } else {
         B200_DISPATCH_VPT(c.vpt, MAXV, (softmax_launch<T, VPT, false>(static_cast<unsigned>(outer), c.threads, st, is_log, px, out, outer, static_cast<int>(dim), out_f32)))
       }
+    } else if (dim <= kRaggedMaxCols && outer >= 64) {
+      const unsigned g = grid_for(outer, 4);
+      if (is_log) { B200_DISPATCH_NPL(dim, (softmax_warp_ragged<T, NPL, true><<<g, 128, 0, st>>>(px, out, outer, static_cast<int>(dim), dto))) }
+      else { B200_DISPATCH_NPL(dim, (softmax_warp_ragged<T, NPL, false><<<g, 128, 0, st>>>(px, out, outer, static_cast<int>(dim), dto))) }
     } else {
       if (outer > 0x7fffffffLL) return B200_EINVAL;
       softmax_stream<T><<<static_cast<unsigned>(outer), 256, 0, st>>>(px, out, dim, dto, is_log);
@@ -784,6 +876,16 @@ extern "C" int b200_layer_norm(const void* x, const void* w, const void* b, void
   const bool al = aligned16(x) && aligned16(y) && (!w || aligned16(w)) && (!b || aligned16(b));
   ResidentCfg c{false, false, 1, 128};
   if (cols > 0 && cols % ve == 0 && (dt_wb != B200_F32 || cols % 4 == 0) && al && wb_ok && cols < (1LL << 30)) c = resident_cfg(cols / ve, 32 / ve, ve == 4 ? 4 : 2);
+  if (!c.ok && cols > 0 && cols <= kRaggedMaxCols && rows >= 64) {
+    const unsigned g = grid_for(rows, 4);
+    const int ci = static_cast<int>(cols);
+    switch (dt) {
+      case B200_F32: B200_DISPATCH_NPL(cols, (layernorm_warp_ragged<float, NPL><<<g, 128, 0, st>>>(static_cast<const float*>(x), w, b, static_cast<float*>(y), mean, rstd, rows, ci, e, dt_wb, dt_stat))) break;
+      case B200_BF16: B200_DISPATCH_NPL(cols, (layernorm_warp_ragged<__nv_bfloat16, NPL><<<g, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(x), w, b, static_cast<__nv_bfloat16*>(y), mean, rstd, rows, ci, e, dt_wb, dt_stat))) break;
+      default: B200_DISPATCH_NPL(cols, (layernorm_warp_ragged<__half, NPL><<<g, 128, 0, st>>>(static_cast<const __half*>(x), w, b, static_cast<__half*>(y), mean, rstd, rows, ci, e, dt_wb, dt_stat))) break;
+    }
+    return check_launch();
+  }
   if (!c.ok) {
     layernorm_stream<<<static_cast<unsigned>(rows), 256, 0, st>>>(x, w, b, y, mean, rstd, cols, e, dt, dt_wb, dt_stat);
     return check_launch();

@@ -330,6 +330,25 @@ def test_many_short_rows_and_long_non_last_dims(backend, dtype):
     ops.check_device_status()
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_ragged_mid_size_rows_one_warp_each(backend, dtype):
+    """Rows of 33 ... 1024 elements off the 16-byte grid (odd lengths, or an odd base offset)
+    take the warp-per-row kernels; a row with NaN and an all -inf row behave as in aten."""
+    g = torch.Generator().manual_seed(32)
+    jobs = []
+    for cols in (33, 67, 100, 257, 513, 1000):
+        x = torch.randn(300, cols, generator=g).to(dtype)
+        x[5, 3] = float("nan")
+        x[7, :] = float("-inf")
+        w, b = torch.randn(cols, generator=g).to(dtype), torch.randn(cols, generator=g).to(dtype)
+        jobs += [("_softmax.default", [x, -1, False]), ("_log_softmax.default", [x, -1, False]), ("native_layer_norm.default", [x[8:], [cols], w, b, 1e-5]),
+                 ("native_layer_norm.default", [x[8:], [cols], None, None, 1e-5])]
+    for op_name, args in jobs:
+        got = backend[get_operator(op_name)](*_to_dev(args))
+        _check(op_name, oracle.run(op_name, args, {}), got, (op_name, tuple(args[0].shape)))
+    ops.check_device_status()
+
+
 def test_full_size_argmax_bit_exact(backend):
     c, op, impl, args, kwargs = _full("argmax_f32_8192x32000", backend)
     got = impl(*args, **kwargs)
