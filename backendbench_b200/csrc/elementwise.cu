@@ -186,6 +186,17 @@ __global__ void __launch_bounds__(kEwThreads) copy_strided_bits(const U* x, U* o
   }
 }
 
+// Bit-exact copy between two strided layouts of one shape (source offsets in s0, destination
+// offsets in s1): how a result is written into a caller's non-contiguous `out` / `self`.
+template <typename U>
+__global__ void __launch_bounds__(kEwThreads) copy_between_strided(const U* x, U* out, StridedArgs A) {
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * kEwThreads + threadIdx.x; i < A.n; i += static_cast<int64_t>(gridDim.x) * kEwThreads) {
+    int64_t oa, ob, oc;
+    unravel3(A, i, oa, ob, oc);
+    out[ob] = x[oa];
+  }
+}
+
 // where, strided: cond/x/y offsets in s0/s1/s2. Same-dtype operands are bit-selected;
 // mixed float dtypes go through fp32 (exact: every bf16/f16 value is an fp32 value).
 template <typename U, bool BITS>
@@ -214,6 +225,89 @@ __global__ void __launch_bounds__(kEwThreads) copy_pitched(const U* __restrict__
     out[b * opb + r * opr + c] = x[b * sxb + r * sxr + c * sxc];
   }
 }
+
+// ------------------------------------------------------------------ transposed operands
+// When an operand's unit stride runs along the second-to-last dim of the (coalesced)
+// iteration shape -- a transposed view -- the strided kernel above reads it one 32-byte
+// sector per element. These kernels walk 32 x 32 tiles of the last two dims instead: a
+// transposed operand is read along ITS contiguous direction into shared memory and handed
+// to the thread that needs it; everything else is read in place. Up to one leading batch
+// dim (blockIdx.z).
+struct TiledArgs {
+  int64_t B, R, C;
+  int64_t ab, ar, ac, bb, br, bc;  // element strides of the two operands: batch, row, column
+  int a_t, b_t;                    // operand is read through the transposing tile
+};
+static bool transposed_view(int64_t s_row, int64_t s_col, int64_t rows, int64_t cols) { return s_row == 1 && s_col != 1 && s_col != 0 && rows >= 16 && cols >= 16; }
+
+template <int OP>
+__global__ void __launch_bounds__(256) ew_tiled(const void* a, const void* b, void* out, TiledArgs T, int dta, int dtb, int dto, float alpha) {
+  __shared__ float ta[32][33], tb[32][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int64_t r0 = static_cast<int64_t>(blockIdx.y) * 32, c0 = static_cast<int64_t>(blockIdx.x) * 32, bz = blockIdx.z;
+  constexpr bool kBinary = OP == OP_ADD || OP == OP_MUL;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int64_t r = r0 + tx, c = c0 + ty + 8 * j;  // consecutive threads along the operand's contiguous rows
+    if (r < T.R && c < T.C) {
+      if (T.a_t) ta[ty + 8 * j][tx] = load_as_f32(a, bz * T.ab + r * T.ar + c * T.ac, dta);
+      if (kBinary && T.b_t) tb[ty + 8 * j][tx] = load_as_f32(b, bz * T.bb + r * T.br + c * T.bc, dtb);
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int64_t r = r0 + ty + 8 * j, c = c0 + tx;
+    if (r < T.R && c < T.C) {
+      const float x = T.a_t ? ta[tx][ty + 8 * j] : load_as_f32(a, bz * T.ab + r * T.ar + c * T.ac, dta);
+      float res;
+      if (OP == OP_RELU) res = x <= 0.f ? 0.f : x;
+      else if (OP == OP_COPY) res = x;
+      else if (OP == OP_ADDC) res = x + alpha;
+      else if (OP == OP_MULC) res = x * alpha;
+      else {
+        const float y = T.b_t ? tb[tx][ty + 8 * j] : load_as_f32(b, bz * T.bb + r * T.br + c * T.bc, dtb);
+        res = OP == OP_ADD ? fmaf(alpha, y, x) : x * y;
+      }
+      store_from_f32(out, (bz * T.R + r) * T.C + c, dto, res);
+    }
+  }
+}
+
+template <typename U>
+__global__ void __launch_bounds__(256) copy_tiled_bits(const U* __restrict__ x, U* __restrict__ out, TiledArgs T) {
+  __shared__ U t[32][32 + (sizeof(U) >= 4 ? 1 : (4 / sizeof(U)))];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int64_t r0 = static_cast<int64_t>(blockIdx.y) * 32, c0 = static_cast<int64_t>(blockIdx.x) * 32, bz = blockIdx.z;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int64_t r = r0 + tx, c = c0 + ty + 8 * j;
+    if (r < T.R && c < T.C) t[ty + 8 * j][tx] = x[bz * T.ab + r * T.ar + c * T.ac];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int64_t r = r0 + ty + 8 * j, c = c0 + tx;
+    if (r < T.R && c < T.C) out[(bz * T.R + r) * T.C + c] = t[tx][ty + 8 * j];
+  }
+}
+
+// Fills T and returns true when the iteration shape has 2 or 3 dims and at least one operand
+// is a transposed view of its last two dims (and the grid fits).
+static bool plan_tiled(TiledArgs& T, const StridedArgs& A, bool has_b) {
+  if (A.ndim != 2 && A.ndim != 3) return false;
+  const int dr = A.ndim - 2, dc = A.ndim - 1;
+  T.B = A.ndim == 3 ? A.shape[0] : 1;
+  T.R = A.shape[dr];
+  T.C = A.shape[dc];
+  T.ab = A.ndim == 3 ? A.s0[0] : 0; T.ar = A.s0[dr]; T.ac = A.s0[dc];
+  T.bb = A.ndim == 3 ? A.s1[0] : 0; T.br = A.s1[dr]; T.bc = A.s1[dc];
+  T.a_t = transposed_view(T.ar, T.ac, T.R, T.C) ? 1 : 0;
+  T.b_t = has_b && transposed_view(T.br, T.bc, T.R, T.C) ? 1 : 0;
+  if (!T.a_t && !T.b_t) return false;
+  return T.B <= 65535 && (T.R + 31) / 32 <= 65535 && (T.C + 31) / 32 <= 0x7fffffffLL;
+}
+static dim3 tiled_grid(const TiledArgs& T) { return dim3(static_cast<unsigned>((T.C + 31) / 32), static_cast<unsigned>((T.R + 31) / 32), static_cast<unsigned>(T.B)); }
 
 static int fill_args(StridedArgs& A, int ndim, const int64_t* shape, const int64_t* s0, const int64_t* s1, const int64_t* s2) {
   if (ndim < 0 || ndim > B200_MAX_DIMS || (ndim > 0 && !shape)) return B200_EINVAL;
@@ -282,7 +376,9 @@ static int binary_entry(const void* a, const void* b, void* out, int ndim, const
       default: launch_binary_T<__half, Op>(a, b, out, A.n, mode, op, st); break;
     }
   } else {
-    ew_strided<OPCODE><<<strided_grid(A.n), kEwThreads, 0, st>>>(a, b, out, A, dta, dtb, dto, alpha);
+    TiledArgs T;
+    if (plan_tiled(T, A, true)) ew_tiled<OPCODE><<<tiled_grid(T), 256, 0, st>>>(a, b, out, T, dta, dtb, dto, alpha);
+    else ew_strided<OPCODE><<<strided_grid(A.n), kEwThreads, 0, st>>>(a, b, out, A, dta, dtb, dto, alpha);
   }
   return check_launch();
 }
@@ -299,7 +395,9 @@ extern "C" int b200_relu(const void* x, void* out, int ndim, const int64_t* shap
   if (!x || !out) return B200_EINVAL;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (is_contiguous(ndim, shape, sx) && aligned16(x) && aligned16(out)) return launch_unary_fast(x, out, A.n, dtype, ReluOp{}, st);
-  ew_strided<OP_RELU><<<strided_grid(A.n), kEwThreads, 0, st>>>(x, nullptr, out, A, dtype, dtype, dtype, 0.f);
+  TiledArgs T;
+  if (plan_tiled(T, A, false)) ew_tiled<OP_RELU><<<tiled_grid(T), 256, 0, st>>>(x, nullptr, out, T, dtype, dtype, dtype, 0.f);
+  else ew_strided<OP_RELU><<<strided_grid(A.n), kEwThreads, 0, st>>>(x, nullptr, out, A, dtype, dtype, dtype, 0.f);
   return check_launch();
 }
 
@@ -311,7 +409,9 @@ static int scalar_entry(const void* x, void* out, int ndim, const int64_t* shape
   if (A.n == 0) return B200_OK;
   if (!x || !out) return B200_EINVAL;
   if (dtx == dto && is_contiguous(ndim, shape, sx) && aligned16(x) && aligned16(out)) return launch_unary_fast(x, out, A.n, dtx, op, st);
-  ew_strided<OPCODE><<<strided_grid(A.n), kEwThreads, 0, st>>>(x, nullptr, out, A, dtx, dtx, dto, c);
+  TiledArgs T;
+  if (plan_tiled(T, A, false)) ew_tiled<OPCODE><<<tiled_grid(T), 256, 0, st>>>(x, nullptr, out, T, dtx, dtx, dto, c);
+  else ew_strided<OPCODE><<<strided_grid(A.n), kEwThreads, 0, st>>>(x, nullptr, out, A, dtx, dtx, dto, c);
   return check_launch();
 }
 
@@ -374,6 +474,21 @@ extern "C" int b200_copy_strided(const void* x, void* out, int ndim, const int64
   if (!x || !out) return B200_EINVAL;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int g = strided_grid(A.n);
+  TiledArgs T;
+  if (plan_tiled(T, A, false)) {
+    if (dti != dto) {
+      if (!is_float_dtype(dto)) return B200_EDTYPE;
+      ew_tiled<OP_COPY><<<tiled_grid(T), 256, 0, st>>>(x, nullptr, out, T, dti, dti, dto, 0.f);
+    } else {
+      switch (es) {
+        case 1: copy_tiled_bits<uint8_t><<<tiled_grid(T), 256, 0, st>>>(static_cast<const uint8_t*>(x), static_cast<uint8_t*>(out), T); break;
+        case 2: copy_tiled_bits<uint16_t><<<tiled_grid(T), 256, 0, st>>>(static_cast<const uint16_t*>(x), static_cast<uint16_t*>(out), T); break;
+        case 4: copy_tiled_bits<uint32_t><<<tiled_grid(T), 256, 0, st>>>(static_cast<const uint32_t*>(x), static_cast<uint32_t*>(out), T); break;
+        default: copy_tiled_bits<uint64_t><<<tiled_grid(T), 256, 0, st>>>(static_cast<const uint64_t*>(x), static_cast<uint64_t*>(out), T); break;
+      }
+    }
+    return check_launch();
+  }
   if (dti == dto) {
     switch (es) {
       case 1: copy_strided_bits<uint8_t><<<g, kEwThreads, 0, st>>>(static_cast<const uint8_t*>(x), static_cast<uint8_t*>(out), A); break;
@@ -399,6 +514,23 @@ extern "C" int b200_copy_pitched(const void* x, void* out, int64_t batch, int64_
     case 2: copy_pitched<uint16_t><<<g, kEwThreads, 0, st>>>(static_cast<const uint16_t*>(x), static_cast<uint16_t*>(out), batch, rows, cols, sxb, sxr, sxc, out_batch_pitch, out_row_pitch); break;
     case 4: copy_pitched<uint32_t><<<g, kEwThreads, 0, st>>>(static_cast<const uint32_t*>(x), static_cast<uint32_t*>(out), batch, rows, cols, sxb, sxr, sxc, out_batch_pitch, out_row_pitch); break;
     default: return B200_EDTYPE;
+  }
+  return check_launch();
+}
+
+extern "C" int b200_copy_into(const void* x, void* out, int ndim, const int64_t* shape, const int64_t* sx, const int64_t* so, int elem_size, void* stream) {
+  StridedArgs A;
+  if (int rc = fill_args(A, ndim, shape, sx, so, nullptr)) return rc;
+  if (elem_size != 1 && elem_size != 2 && elem_size != 4 && elem_size != 8) return B200_EDTYPE;
+  if (A.n == 0) return B200_OK;
+  if (!x || !out || !sx || !so) return B200_EINVAL;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int g = strided_grid(A.n);
+  switch (elem_size) {
+    case 1: copy_between_strided<uint8_t><<<g, kEwThreads, 0, st>>>(static_cast<const uint8_t*>(x), static_cast<uint8_t*>(out), A); break;
+    case 2: copy_between_strided<uint16_t><<<g, kEwThreads, 0, st>>>(static_cast<const uint16_t*>(x), static_cast<uint16_t*>(out), A); break;
+    case 4: copy_between_strided<uint32_t><<<g, kEwThreads, 0, st>>>(static_cast<const uint32_t*>(x), static_cast<uint32_t*>(out), A); break;
+    default: copy_between_strided<uint64_t><<<g, kEwThreads, 0, st>>>(static_cast<const uint64_t*>(x), static_cast<uint64_t*>(out), A); break;
   }
   return check_launch();
 }

@@ -207,6 +207,57 @@ static void launch_flat(const void* x, const void* idx, void* out, int64_t outer
   index_select_flat<U><<<capped_grid(total, 256, 16), 256, 0, st>>>(static_cast<const U*>(x), idx, static_cast<U*>(out), outer, dim_size, inner_units, n_idx, idx_i32, status);
 }
 
+// index_select along the LAST dim (inner == 1): every output row is a permutation-with-
+// repeats of one input row of at most 8 KB. A warp copies its input row to shared memory
+// with coalesced loads and builds the output row from there with coalesced stores; the
+// index list is narrowed to int32 once per CTA (-1 = out of range, reported and written as
+// zero). Picking single elements straight from global memory, as the flat kernel does,
+// fetches a 32-byte sector per element.
+constexpr int kLastDimWarps = 8;
+template <typename U>
+__global__ void __launch_bounds__(kLastDimWarps * 32) index_select_lastdim(const U* __restrict__ x, const void* __restrict__ idx, U* __restrict__ out, int64_t outer, int dim, int n_idx, int row_pitch_bytes,
+                                                                           int i32, int vec, uint32_t* status) {
+  extern __shared__ __align__(16) unsigned char sm[];
+  int* sidx = reinterpret_cast<int*>(sm);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  unsigned char* mine = sm + ((n_idx * 4 + 15) & ~15) + warp * row_pitch_bytes;
+  for (int k = tid; k < n_idx; k += blockDim.x) {
+    const int64_t v = load_index(idx, k, i32);
+    const bool ok = v >= 0 && v < dim;
+    if (!ok) flag_oob(status);
+    sidx[k] = ok ? static_cast<int>(v) : -1;
+  }
+  __syncthreads();
+  const U* row_s = reinterpret_cast<const U*>(mine);
+  for (int64_t row = static_cast<int64_t>(blockIdx.x) * kLastDimWarps + warp; row < outer; row += static_cast<int64_t>(gridDim.x) * kLastDimWarps) {
+    const U* xr = x + row * dim;
+    if (vec) {
+      const int nv = dim * static_cast<int>(sizeof(U)) / 16;
+#pragma unroll 4
+      for (int v = lane; v < nv; v += 32) reinterpret_cast<uint4*>(mine)[v] = ld_stream(reinterpret_cast<const uint4*>(xr) + v);
+    } else {
+      for (int c = lane; c < dim; c += 32) reinterpret_cast<U*>(mine)[c] = xr[c];
+    }
+    __syncwarp();
+    U* orow = out + row * n_idx;
+    for (int k = lane; k < n_idx; k += 32) {
+      const int j = sidx[k];
+      orow[k] = j >= 0 ? row_s[j] : zero_of<U>();
+    }
+    __syncwarp();  // the row buffer is rewritten in the next round
+  }
+}
+
+template <typename U>
+static void launch_lastdim(const void* x, const void* idx, void* out, int64_t outer, int64_t dim, int64_t n_idx, int i32, uint32_t* status, cudaStream_t st) {
+  const int pitch = static_cast<int>((dim * sizeof(U) + 15) / 16 * 16);
+  const size_t smem = ((n_idx * 4 + 15) & ~static_cast<size_t>(15)) + static_cast<size_t>(kLastDimWarps) * pitch;
+  const int vec = (dim * sizeof(U)) % 16 == 0 && aligned16(x);
+  cudaFuncSetAttribute(index_select_lastdim<U>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+  index_select_lastdim<U><<<capped_grid(outer, kLastDimWarps, 8), kLastDimWarps * 32, smem, st>>>(static_cast<const U*>(x), idx, static_cast<U*>(out), outer, static_cast<int>(dim), static_cast<int>(n_idx), pitch,
+                                                                                                 i32, vec, status);
+}
+
 static int index_select_bytes(const void* x, const void* idx, void* out, int64_t outer, int64_t dim_size, int64_t inner_bytes, int64_t n_idx, int idx_dtype, uint32_t* status, cudaStream_t st) {
   if (idx_dtype != B200_I32 && idx_dtype != B200_I64) return B200_EDTYPE;
   const int i32 = idx_dtype == B200_I32;
@@ -214,6 +265,15 @@ static int index_select_bytes(const void* x, const void* idx, void* out, int64_t
   const int64_t units = inner_bytes / unit;
   if (outer == 1 && unit == 16 && units >= 64) {
     gather_rows_wide<<<capped_grid(n_idx, 1, 64), 128, 0, st>>>(static_cast<const uint4*>(x), idx, static_cast<uint4*>(out), dim_size, units, n_idx, i32, status);
+    return check_launch();
+  }
+  if (units == 1 && unit <= 8 && dim_size * unit <= 8192 && dim_size >= 32 && n_idx >= 16 && n_idx <= 8192 && outer >= 256) {
+    switch (unit) {
+      case 8: launch_lastdim<uint64_t>(x, idx, out, outer, dim_size, n_idx, i32, status, st); break;
+      case 4: launch_lastdim<uint32_t>(x, idx, out, outer, dim_size, n_idx, i32, status, st); break;
+      case 2: launch_lastdim<uint16_t>(x, idx, out, outer, dim_size, n_idx, i32, status, st); break;
+      default: launch_lastdim<uint8_t>(x, idx, out, outer, dim_size, n_idx, i32, status, st); break;
+    }
     return check_launch();
   }
   switch (unit) {

@@ -197,20 +197,24 @@ def _scalar_value(x) -> float:
 
 
 # --------------------------------------------------------------------- elementwise
-def relu(self: torch.Tensor) -> torch.Tensor:
-    """aten.relu.default -- max(x, 0) with NaN propagated (x <= 0 ? 0 : x)."""
+def relu(self: torch.Tensor, *, _into: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """aten.relu.default -- max(x, 0) with NaN propagated (x <= 0 ? 0 : x). `_into`: a
+    contiguous tensor of the result's shape and dtype to write instead of a fresh one (the
+    in-place overloads pass `self`)."""
     _require_cuda(self)
     if self.dtype not in _FLOATS:
         raise UnsupportedByB200(f"relu: dtype {self.dtype}")
-    out = torch.empty(self.shape, dtype=self.dtype, device=self.device)
+    out = _into if _into is not None else torch.empty(self.shape, dtype=self.dtype, device=self.device)
     if out.numel():
         nd, shp, (sx,) = _iter_layout(self.shape, [self])
         check(lib().b200_relu(self.data_ptr(), out.data_ptr(), nd, shp, sx, _dt(self.dtype), _stream_handle()), "b200_relu")
     return out
 
 
-def _binary(name: str, a, b, alpha: float) -> torch.Tensor:
+def _binary(name: str, a, b, alpha: float, _into: Optional[torch.Tensor] = None) -> torch.Tensor:
     if not isinstance(a, torch.Tensor) or (a.dim() == 0 and not a.is_cuda and isinstance(b, torch.Tensor) and b.is_cuda):
+        if _into is not None:
+            raise UnsupportedByB200(f"{name}: in-place on a wrapped number")
         if name == "mul":
             return _binary(name, b, a, alpha)  # commutative
         if not isinstance(b, torch.Tensor):
@@ -225,7 +229,7 @@ def _binary(name: str, a, b, alpha: float) -> torch.Tensor:
     _require_cuda(a)
     st = _stream_handle()
     if _is_wrapped_scalar(b):
-        out = torch.empty(a.shape, dtype=res_dtype, device=a.device)
+        out = _into if _into is not None else torch.empty(a.shape, dtype=res_dtype, device=a.device)
         if out.numel():
             nd, shp, (sa,) = _iter_layout(a.shape, [a])
             val = _scalar_value(b)
@@ -241,7 +245,7 @@ def _binary(name: str, a, b, alpha: float) -> torch.Tensor:
         shape = a.shape
     else:
         shape = _broadcast_shape(a.shape, b.shape)
-    out = torch.empty(shape, dtype=res_dtype, device=a.device)
+    out = _into if _into is not None else torch.empty(shape, dtype=res_dtype, device=a.device)
     if out.numel():
         nd, shp, (sa, sb) = _iter_layout(shape, [a, b])
         if name == "add":
@@ -669,7 +673,7 @@ def _gemm(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor], batch:
     # planes each in scratch memory and six plane products are accumulated in fp32, which
     # keeps fp32 accuracy (see include/b200ops.h). Small ones stay on the CUDA-core kernel.
     macs = batch * M * N * K
-    if a.dtype == torch.float32 and ((macs >= F32_SPLIT_MIN_MACS and K >= 32 and M >= 32 and N >= 32) or (K >= 2048 and macs >= (1 << 22))):
+    if a.dtype == torch.float32 and ((macs >= F32_SPLIT_MIN_MACS and K >= 32 and M >= 32 and N >= 32) or (K >= 1024 and macs >= (1 << 18))):
         need = int(lib().b200_gemm_f32_scratch_bytes(batch, M, N, K))
         if need > 0:
             scratch = _scratch(a.device, need)

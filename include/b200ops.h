@@ -114,6 +114,13 @@ int b200_copy_pitched(const void* x, void* out, int64_t batch, int64_t rows, int
                       int64_t sx_batch, int64_t sx_row, int64_t sx_col, int64_t out_batch_pitch,
                       int64_t out_row_pitch, int elem_size, void* stream);
 
+/* Bit-exact copy between two strided layouts of one shape (element strides sx -> so): how
+ * the host writes a result into a caller-provided non-contiguous tensor, i.e. the `.out`
+ * and in-place overloads that BackendBench/scripts/op_map.py:7-1148 lists next to each
+ * functional operator. elem_size 1, 2, 4 or 8. Source and destination must not overlap. */
+int b200_copy_into(const void* x, void* out, int ndim, const int64_t* shape, const int64_t* sx,
+                   const int64_t* so, int elem_size, void* stream);
+
 /* ----------------------------------------------------------------- row kernels
  * The input is contiguous and viewed as [outer, dim, inner]; the op runs along `dim`. */
 

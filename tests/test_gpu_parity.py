@@ -197,6 +197,46 @@ def test_full_size_gather_bit_exact(backend):
     ops.check_device_status()
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_elementwise_on_transposed_views_goes_through_tiles(backend, dtype):
+    """Operands whose unit stride runs along the second-to-last dim: 2-D and batched, ragged
+    tile edges, one or both operands transposed, a broadcast partner, and the strided copy."""
+    g = torch.Generator().manual_seed(41)
+    add, mul, relu = backend[torch.ops.aten.add.Tensor], backend[torch.ops.aten.mul.Tensor], backend[torch.ops.aten.relu.default]
+    for shape in [(1000, 70), (33, 1025), (5, 130, 47)]:
+        tshape = shape[:-2] + (shape[-1], shape[-2])
+        a = torch.randn(tshape, generator=g).to(dtype).to(DEV).transpose(-1, -2)
+        b = torch.randn(tshape, generator=g).to(dtype).to(DEV).transpose(-1, -2)
+        c = torch.randn(shape, generator=g).to(dtype).to(DEV)
+        row = torch.randn(shape[-1], generator=g).to(dtype).to(DEV)
+        assert not a.is_contiguous()
+        for got, want in [(add(a, b), a + b), (add(a, c, alpha=2), torch.add(a, c, alpha=2)), (mul(c, b), c * b), (mul(a, row), a * row), (relu(a), torch.relu(a)),
+                          (ops._contig(a), a.contiguous())]:
+            assert bits_equal(want, got), shape
+    ints = torch.randint(-5, 5, (300, 41), generator=g, dtype=torch.int64).to(DEV).t()
+    assert bits_equal(ints.contiguous(), ops._contig(ints))
+
+
+def test_index_select_along_the_last_dim_through_shared_memory(backend):
+    impl = backend[torch.ops.aten.index_select.default]
+    g = torch.Generator().manual_seed(8)
+    for shape, dtype, n_idx in [((1000, 300), torch.float32, 1190), ((513, 77), torch.bfloat16, 40), ((400, 64), torch.int64, 64), ((3, 700, 1024), torch.float16, 16), ((2000, 33), torch.uint8, 100)]:
+        x = (torch.randn(shape, generator=g) * 100).to(dtype).to(DEV)
+        idx = torch.randint(0, shape[-1], (n_idx,), generator=g).to(DEV)
+        assert bits_equal(torch.index_select(x, -1, idx), impl(x, x.dim() - 1, idx))
+        assert bits_equal(torch.index_select(x, -1, idx.int()), impl(x, x.dim() - 1, idx.int()))
+    ops.check_device_status()
+    x = torch.randn(600, 128, device=DEV)
+    idx = torch.randint(0, 128, (64,), device=DEV)
+    idx[5] = 128
+    got = impl(x, 1, idx)
+    with pytest.raises(IndexError):
+        ops.check_device_status()
+    want = torch.index_select(x, 1, idx.clamp(0, 127))
+    want[:, 5] = 0
+    assert bits_equal(want, got)
+
+
 def test_gather_rows_of_self_held_in_shared_memory(backend):
     """dim-0 gather whose source strip fits in shared memory: ragged row counts, row splits,
     a source with a row pitch, and an out-of-range index that must be reported, not read."""
