@@ -2,7 +2,8 @@
 implements (serially or one process per GPU) and print the three summary scores.
 
 Mirrors the hot-path part of BackendBench/scripts/main.py:186-303 with the same flag names
-(`--suite --backend --ops --ops-directory --num-workers --p --log-level --daemon/--no-daemon`).
+(`--suite --backend --ops --ops-directory --num-workers --p --log-level --log-dir
+--daemon/--no-daemon`).
 Suites here are the seeded ones this package can generate offline: `smoke` (one relu case,
 as the reference's smoke suite), `named` (the per-operator configurations throughput is
 quoted on) and `sweep` (the 512-case sharded sweep). Backends: `aten`, `directory`
@@ -96,14 +97,19 @@ def run(suite, backend, backend_ref, num_workers=None, daemon=True, p=1.0, toler
 @click.option("--cases", default=512, type=int, help="Number of cases of the sweep suite")
 @click.option("--dtype-tolerances/--harness-tolerances", default=False, help="Per-dtype tolerances instead of the harness's 1e-2 for everything")
 @click.option("--daemon/--no-daemon", default=True, help="Use daemon worker processes")
-def cli(log_level, suite, backend, ops, ops_directory, num_workers, p, device, cases, dtype_tolerances, daemon):
+@click.option("--log-dir", default=None, type=str, help="Directory for the report artefacts (full_results.json, operator_summary.csv, failed_tests.json, OVERALL_SUMMARY.md); none written when omitted")
+def cli(log_level, suite, backend, ops, ops_directory, num_workers, p, device, cases, dtype_tolerances, daemon, log_dir):
     logging.basicConfig(level=getattr(logging, log_level.upper()), format="[%(asctime)s][%(levelname)s][%(filename)s] %(message)s", datefmt="%Y-%m-%d %H:%M:%S")
     device = device or ("cuda" if torch.cuda.is_available() else "cpu")
     op_filter = [o.strip() for o in ops.split(",")] if ops else None
     test_suite = build_suite(suite, device, op_filter, cases)
     be = make_backend(backend, ops_directory)
     ref = BackendRef(backend, ops_directory if backend == "directory" else None)
-    mean_correctness, geomean_perf, perf_at_p, _ = run(test_suite, be, ref, num_workers, daemon, p, "dtype" if dtype_tolerances else None)
+    mean_correctness, geomean_perf, perf_at_p, (all_c, all_p) = run(test_suite, be, ref, num_workers, daemon, p, "dtype" if dtype_tolerances else None)
+    if log_dir:
+        from ..output import save_results
+
+        save_results(all_c, all_p, log_dir, "python -m backendbench_b200.scripts.main " + " ".join(sys.argv[1:]), mean_correctness, geomean_perf, perf_at_p, p)
     print(f"correctness score (mean pass rate over all operators): {mean_correctness:.2f}")
     print(f"performance score (geomean speedup over all operators): {geomean_perf:.2f}")
     print(f"perf@p score (rate of correct samples with a speedup greater than p, p={p}): {perf_at_p:.2f}")

@@ -27,6 +27,27 @@ def test_cli_sweep_subset_with_two_cpu_workers():
     assert _scores(r.output)[0] == 1.0
 
 
+def test_cli_log_dir_writes_the_four_report_files(tmp_path):
+    """`--log-dir`: the artefacts of BackendBench/output.py:116-196 by name, with the
+    reference's columns first in the operator summary."""
+    import csv
+    import json
+
+    from backendbench_b200.output import EXTRA_COLUMNS, REFERENCE_COLUMNS
+
+    out = tmp_path / "report"
+    r = CliRunner().invoke(cli, ["--suite", "sweep", "--cases", "16", "--backend", "aten", "--device", "cpu", "--ops", "relu,add.Tensor", "--log-dir", str(out)])
+    assert r.exit_code == 0, r.output
+    assert sorted(p.name for p in out.iterdir()) == ["OVERALL_SUMMARY.md", "failed_tests.json", "full_results.json", "operator_summary.csv"]
+    full = json.load(open(out / "full_results.json"))
+    assert full and {"op_name", "args", "test_type"} <= set(full[0]) and full == sorted(full, key=lambda d: (d["op_name"], d["args"]))
+    assert json.load(open(out / "failed_tests.json")) == []
+    rows = list(csv.DictReader(open(out / "operator_summary.csv")))
+    assert list(rows[0]) == REFERENCE_COLUMNS + EXTRA_COLUMNS and {r_["operator"] for r_ in rows} == {"relu.default", "add.Tensor"}
+    assert all(float(r_["correctness_rate"]) == 1.0 for r_ in rows)
+    assert "| Correctness Score | 1.00 |" in open(out / "OVERALL_SUMMARY.md").read()
+
+
 def test_build_suite_filters_and_descriptor_tests():
     s = build_suite("named", "cpu", ["relu", "mm.default"])
     ops = {t.op for t in s}

@@ -74,3 +74,34 @@ def test_reference_eval_accepts_our_result_records(ref):
 
     score, _, cres, _ = ref["eval"].eval_one_op(op, be[op], [Case([torch.randn(4)])], [])
     assert score == 0.0 and "no CPU path" in cres[0].error_msg
+
+
+def test_report_artefacts_match_the_reference_writer(ref, tmp_path):
+    """full_results.json / failed_tests.json are identical, the first thirteen columns of
+    operator_summary.csv carry the reference's values, OVERALL_SUMMARY.md the same scores."""
+    import csv
+    import json
+
+    from BackendBench import output as ref_output
+    from backendbench_b200 import output
+    from backendbench_b200.eval import CorrectnessTestResult, PerformanceTestResult
+
+    cs = [CorrectnessTestResult("relu.default", "a1", True, max_abs_error=0.1, max_rel_error=0.2), CorrectnessTestResult("relu.default", "a0", False, error_msg="boom", error_type="RuntimeError"),
+          CorrectnessTestResult("add.Tensor", "b", True, max_abs_error=1e-3, max_rel_error=2e-3)]
+    ps = [PerformanceTestResult("relu.default", "a1", 2.0, 1.0, 2.0, successfully_ran=True), PerformanceTestResult("relu.default", "a0", 8.0, 0.5, 4.0, successfully_ran=True),
+          PerformanceTestResult("add.Tensor", "b", 0.5, 2.0, 1.0, error_msg="did not run", successfully_ran=False)]
+    rcs = [ref["eval"].CorrectnessTestResult(**vars(c)) for c in cs]
+    rps = [ref["eval"].PerformanceTestResult(**vars(p)) for p in ps]
+    mine, theirs = tmp_path / "mine", tmp_path / "theirs"
+    output.save_results(cs, ps, str(mine), "cmd --x", 0.5, 1.25, 0.3, 1.0, roofline={"relu.default": {"gbs": 5000.0, "frac": 0.77}})
+    ref_output.save_results(rcs, rps, str(theirs), "cmd --x", 0.5, 1.25, 0.3, 1.0)
+    for name in ("full_results.json", "failed_tests.json"):
+        assert json.load(open(mine / name)) == json.load(open(theirs / name))
+    a, b = list(csv.DictReader(open(mine / "operator_summary.csv"))), list(csv.DictReader(open(theirs / "operator_summary.csv")))
+    assert list(a[0])[:13] == list(b[0]) == output.REFERENCE_COLUMNS and len(a) == len(b)
+    for ra, rb in zip(a, b):
+        for k in rb:
+            assert ra[k] == rb[k] or float(ra[k]) == pytest.approx(float(rb[k])), (ra["operator"], k)
+    assert a[0]["achieved_gbs"] == "5000.0" and a[0]["frac_of_measured_peak"] == "0.77"
+    ma, mb = open(mine / "OVERALL_SUMMARY.md").read().splitlines(), open(theirs / "OVERALL_SUMMARY.md").read().splitlines()
+    assert len(ma) == len(mb) and [i for i, (x, y) in enumerate(zip(ma, mb)) if x != y] == [ma.index(next(x for x in ma if x.startswith("- `operator_summary.csv`")))]
