@@ -4,7 +4,8 @@ implements (serially or one process per GPU) and print the three summary scores.
 Mirrors the hot-path part of BackendBench/scripts/main.py:186-303 with the same flag names
 (`--suite --backend --ops --ops-directory --num-workers --p --log-level --log-dir
 --daemon/--no-daemon`).
-Suites here are the seeded ones this package can generate offline: `smoke` (one relu case,
+Suites here are the seeded ones this package can generate offline, plus `torchbench` over a
+LOCAL trace / parquet file (`--alternative-torchbench-data-path`): `smoke` (one relu case,
 as the reference's smoke suite), `named` (the per-operator configurations throughput is
 quoted on) and `sweep` (the 512-case sharded sweep). Backends: `aten`, `directory`
 (`--ops-directory`), `b200` (the kernels shipped with this package).
@@ -87,7 +88,9 @@ def run(suite, backend, backend_ref, num_workers=None, daemon=True, p=1.0, toler
 
 @click.command()
 @click.option("--log-level", default=os.getenv("LOG_LEVEL", "INFO"), type=click.Choice(["DEBUG", "INFO", "WARNING", "ERROR", "CRITICAL"], case_sensitive=False), help="Set the logging level")
-@click.option("--suite", default="smoke", type=click.Choice(["smoke", "named", "sweep"]), help="Which suite to run")
+@click.option("--suite", default="smoke", type=click.Choice(["smoke", "named", "sweep", "torchbench"]), help="Which suite to run")
+@click.option("--alternative-torchbench-data-path", default=None, type=str, help="Local .txt trace or .parquet table for --suite torchbench (nothing is downloaded)")
+@click.option("--topn-inputs", "--topn", default=None, type=int, help="Largest N recorded inputs per operator (torchbench suite)")
 @click.option("--backend", default="aten", type=click.Choice(["aten", "directory", "b200"]), help="Which backend to run")
 @click.option("--ops", default=None, type=str, help="Comma-separated list of ops to run")
 @click.option("--ops-directory", default="generated_kernels", type=str, help="Path to directory containing kernels (directory backend)")
@@ -98,11 +101,18 @@ def run(suite, backend, backend_ref, num_workers=None, daemon=True, p=1.0, toler
 @click.option("--dtype-tolerances/--harness-tolerances", default=False, help="Per-dtype tolerances instead of the harness's 1e-2 for everything")
 @click.option("--daemon/--no-daemon", default=True, help="Use daemon worker processes")
 @click.option("--log-dir", default=None, type=str, help="Directory for the report artefacts (full_results.json, operator_summary.csv, failed_tests.json, OVERALL_SUMMARY.md); none written when omitted")
-def cli(log_level, suite, backend, ops, ops_directory, num_workers, p, device, cases, dtype_tolerances, daemon, log_dir):
+def cli(log_level, suite, alternative_torchbench_data_path, topn_inputs, backend, ops, ops_directory, num_workers, p, device, cases, dtype_tolerances, daemon, log_dir):
     logging.basicConfig(level=getattr(logging, log_level.upper()), format="[%(asctime)s][%(levelname)s][%(filename)s] %(message)s", datefmt="%Y-%m-%d %H:%M:%S")
     device = device or ("cuda" if torch.cuda.is_available() else "cpu")
     op_filter = [o.strip() for o in ops.split(",")] if ops else None
-    test_suite = build_suite(suite, device, op_filter, cases)
+    if suite == "torchbench":
+        if not alternative_torchbench_data_path:
+            raise click.UsageError("--suite torchbench needs --alternative-torchbench-data-path FILE (a local .txt trace or .parquet table; the public dataset is not fetched)")
+        from ..trace_suite import TraceTestSuite
+
+        test_suite = TraceTestSuite("torchbench", alternative_torchbench_data_path, op_filter, topn_inputs)
+    else:
+        test_suite = build_suite(suite, device, op_filter, cases)
     be = make_backend(backend, ops_directory)
     ref = BackendRef(backend, ops_directory if backend == "directory" else None)
     mean_correctness, geomean_perf, perf_at_p, (all_c, all_p) = run(test_suite, be, ref, num_workers, daemon, p, "dtype" if dtype_tolerances else None)

@@ -105,3 +105,30 @@ def test_report_artefacts_match_the_reference_writer(ref, tmp_path):
     assert a[0]["achieved_gbs"] == "5000.0" and a[0]["frac_of_measured_peak"] == "0.77"
     ma, mb = open(mine / "OVERALL_SUMMARY.md").read().splitlines(), open(theirs / "OVERALL_SUMMARY.md").read().splitlines()
     assert len(ma) == len(mb) and [i for i, (x, y) in enumerate(zip(ma, mb)) if x != y] == [ma.index(next(x for x in ma if x.startswith("- `operator_summary.csv`")))]
+
+
+def test_trace_parser_and_ordering_match_the_reference(ref, tmp_path):
+    """The same local trace through the reference's parser / TorchBenchOpTest and through
+    ours: equal records, equal per-operator test order."""
+    import importlib.util
+
+    from BackendBench import data_loaders as ref_loaders
+    from backendbench_b200 import trace_suite
+
+    # the module by path: importing the `suite` package pulls in OpInfo, whose dependencies are not installed here
+    spec = importlib.util.spec_from_file_location("ref_torchbench_suite", os.path.join(REF, "BackendBench", "suite", "torchbench.py"))
+    ref_suite = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ref_suite)
+    TorchBenchOpTest = ref_suite.TorchBenchOpTest
+    from test_trace_suite import TRACE
+
+    path = tmp_path / "trace.txt"
+    path.write_text(TRACE)
+    theirs = ref_loaders._parse_trace_file(str(path))
+    assert trace_suite.load_ops_from_source(str(path)) == theirs
+    assert trace_suite.load_ops_from_source(str(path), filter=["add"]) == ref_loaders._parse_trace_file(str(path), filter=["add"])
+    mine = trace_suite.ops_to_benchmark_dict(trace_suite.load_ops_from_source(str(path)))
+    for op_name, inputs in mine.items():
+        for topn in (None, 1, 2):
+            want = TorchBenchOpTest(op_name, inputs, topn).tests()
+            assert [t.serialized for t in trace_suite.TraceOpTest(op_name, inputs, topn).correctness_tests] == want
