@@ -13,7 +13,8 @@ the device time. `value` = cases all ranks processed / that time.
 
 The JSON line also carries: `e2e` (the same pass through the public plugin call with the
 inputs in pinned HOST memory, H2D copies and the verdict read-back inside the timed
-region), `roofline` (the kernel with the largest share of device time in the sweep),
+region), `roofline` (the operator with the largest share of device time in the sweep, its
+cases classed by the roof that binds them),
 `per_op` (every named operator configuration: GB/s or TFLOP/s against the measured and
 nominal peaks, and the speed-up over aten CUDA), `cpu_baseline` (the reference's aten-CPU
 path on a bounded sample, host cores), `clocks` and `gpu_launches`.
@@ -261,11 +262,12 @@ def per_kernel_profile(prepared):
     for i, p in enumerate(prepared):
         c = p["case"]
         per_case.append((starts[i].elapsed_time(ends[i]), c.label() + (" " + str(dict(c.extra)) if c.extra else "")))
-        d = by_op.setdefault(c.op, {"ms": 0.0, "bytes": 0, "flops": 0, "launches": 0})
+        d = by_op.setdefault(c.op, {"ms": 0.0, "bytes": 0, "flops": 0, "launches": 0, "cases": []})
         d["ms"] += starts[i].elapsed_time(ends[i])
         d["bytes"] += c.algorithmic_bytes()
         d["flops"] += c.flops()
         d["launches"] += 1
+        d["cases"].append((starts[i].elapsed_time(ends[i]), c.algorithmic_bytes(), c.flops()))
     per_case.sort(reverse=True)
     by_op["__slowest__"] = [{"ms": round(ms, 3), "case": label} for ms, label in per_case[:12]]
     by_op["__total_ms__"] = round(sum(ms for ms, _ in per_case), 3)
@@ -423,13 +425,31 @@ def run_b200(args):
         total = sum(d["ms"] for d in by_op.values()) or 1.0
         shares = {op: round(d["ms"] / total, 4) for op, d in sorted(by_op.items(), key=lambda kv: -kv[1]["ms"])}
         top_op, top = max(by_op.items(), key=lambda kv: kv[1]["ms"])
-        if top["flops"] and top_op in ("mm.default", "addmm.default", "bmm.default"):
-            ach = top["flops"] / (top["ms"] * 1e-3) / 1e12
-            roof = {"bound": "tensor", "achieved": round(ach, 2), "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": round(ach / peaks["bf16_tflops"], 4)}
-        else:
-            ach = top["bytes"] / (top["ms"] * 1e-3) / 1e9
-            roof = {"bound": "hbm", "achieved": round(ach, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(ach / peaks["hbm_gbs"], 4)}
-        roof.update({"kernel": top_op, "launches": top["launches"], "avg_launch_ms": round(top["ms"] / top["launches"], 4), "peak_source": peaks["source"], "traffic": None})
+        # The dominant operator's cases are a mix of shapes: each case is bound by whichever
+        # roof it would hit first (its algorithmic bytes at the HBM peak or its FLOP at the
+        # tensor peak). The roofline line describes the class that holds more of the
+        # operator's device time; the other class is listed beside it.
+        classes = {"hbm": {"ms": 0.0, "units": 0.0, "launches": 0}, "tensor": {"ms": 0.0, "units": 0.0, "launches": 0}}
+        for ms, nbytes, flops in top["cases"]:
+            t_hbm, t_tc = nbytes / (peaks["hbm_gbs"] * 1e9), flops / (peaks["bf16_tflops"] * 1e12)
+            k = "tensor" if t_tc > t_hbm else "hbm"
+            classes[k]["ms"] += ms
+            classes[k]["units"] += flops if k == "tensor" else nbytes
+            classes[k]["launches"] += 1
+        bound = max(classes, key=lambda k: classes[k]["ms"])
+
+        def describe(k):
+            c = classes[k]
+            if not c["launches"]:
+                return None
+            scale, peak, unit = (1e12, peaks["bf16_tflops"], "TFLOP/s") if k == "tensor" else (1e9, peaks["hbm_gbs"], "GB/s")
+            ach = c["units"] / (c["ms"] * 1e-3) / scale
+            return {"bound": k, "achieved": round(ach, 2), "peak": peak, "unit": unit, "frac": round(ach / peak, 4), "launches": c["launches"], "avg_launch_ms": round(c["ms"] / c["launches"], 4),
+                    "share_of_op_time": round(c["ms"] / top["ms"], 4)}
+
+        roof = describe(bound)
+        other = describe("hbm" if bound == "tensor" else "tensor")
+        roof.update({"kernel": top_op, "peak_source": peaks["source"], "traffic": None, "other_class": other})
         line["roofline"] = roof
         line["sweep_time_share_by_op"] = shares
         if not args.sweep_only:
