@@ -55,6 +55,7 @@ SIGNATURES = {
     "b200_copy_pitched": (c_int, [c_void_p, c_void_p] + [c_int64] * 8 + [c_int, c_void_p]),
     "b200_copy_into": (c_int, [c_void_p, c_void_p, c_int, I64P, I64P, I64P, c_int, c_void_p]),
     "b200_softmax": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_int, c_void_p]),
+    "b200_softmax_backward": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_int, c_void_p]),
     "b200_reduce_scratch_bytes": (c_int64, [c_int64, c_int64, c_int64]),
     "b200_sum": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_int64, c_void_p]),
     "b200_sum_static": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_void_p]),

@@ -102,6 +102,11 @@ class CaseSpec:
         elif op in ("_softmax.default", "_log_softmax.default"):
             x = transposed(shp) if self.edge == "transposed" and len(shp) == 2 else normal(shp)
             args = [poison(x), self.param("dim", -1), False]
+        elif op in ("_softmax_backward_data.default", "_log_softmax_backward_data.default"):
+            # a forward output of the right kind (rows of a softmax / log_softmax) and a random incoming gradient
+            dim = self.param("dim", -1)
+            y = torch.softmax(normal(shp).float(), dim) if op == "_softmax_backward_data.default" else torch.log_softmax(normal(shp).float(), dim)
+            args = [normal(shp), y.to(dt), dim, dt]
         elif op == "sum.dim_IntList":
             x = transposed(shp) if self.edge == "transposed" and len(shp) == 2 else normal(shp)
             args = [poison(x), list(self.param("dim", (-1,)))]
@@ -182,6 +187,8 @@ class CaseSpec:
             return 3 * n * es + _prod(self.param("cond_shape", self.shape))
         if op in ("_softmax.default", "_log_softmax.default"):
             return 2 * n * es
+        if op in ("_softmax_backward_data.default", "_log_softmax_backward_data.default"):
+            return 3 * n * es  # grad and output in, grad_input out
         if op == "sum.dim_IntList":
             dims = [d % len(self.shape) for d in self.param("dim", (-1,))]
             out = _prod(s for i, s in enumerate(self.shape) if i not in dims)
@@ -268,8 +275,19 @@ def named_cases() -> List[CaseSpec]:
     return c
 
 
+def neighbour_cases() -> List[CaseSpec]:
+    """Configurations of the operators next to the sixteen (the backward neighbours), at the
+    shapes of their forward operators. Not part of the sweep or of the per-op bench table."""
+    c: List[CaseSpec] = []
+    for dtype, shape in (("bf16", (8192, 4096)), ("f32", (65536, 1024))):
+        tag = f"{dtype}_{shape[0]}x{shape[1]}"
+        for name, op in (("softmax_backward", "_softmax_backward_data.default"), ("log_softmax_backward", "_log_softmax_backward_data.default")):
+            c.append(CaseSpec(1000 + len(c), op, dtype, shape, 0, (("dim", -1),), "", "reduce", f"{name}_{tag}"))
+    return c
+
+
 def named_case(name: str) -> CaseSpec:
-    for c in named_cases():
+    for c in named_cases() + neighbour_cases():
         if c.name == name:
             return c
     raise KeyError(name)

@@ -123,6 +123,65 @@ softmax_resident(const T* __restrict__ x, void* __restrict__ out, int64_t rows, 
   softmax_row<T, VPT, WARP, IS_LOG>(x + row * cols, out, row * cols, cols / Vec<T>::N, t, tpr, out_f32, red);
 }
 
+// ------------------------------------------------------------------ softmax / log_softmax backward
+// aten._softmax_backward_data:      gin = (g - sum(g * y)) * y
+// aten._log_softmax_backward_data:  gin = g - exp(y) * sum(g)
+// with y the forward output, along `dim` of [outer, dim, inner]. Resident kernel: the rows
+// of g and y are read once with 16-byte loads and held in registers (one warp or one CTA
+// per row), one reduction, one write -- the forward kernel's geometry with two inputs.
+template <typename T, int VPT, bool WARP, bool IS_LOG>
+__global__ void __launch_bounds__(WARP ? 128 : 1024)
+softmax_bwd_resident(const T* __restrict__ g, const T* __restrict__ y, void* __restrict__ out, int64_t rows, int cols, int out_f32) {
+  constexpr int VE = Vec<T>::N;
+  __shared__ float red[64];
+  const int tpr = WARP ? 32 : blockDim.x;
+  const int t = WARP ? (threadIdx.x & 31) : threadIdx.x;
+  const int64_t row = WARP ? static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5) : blockIdx.x;
+  if (WARP && row >= rows) return;
+  const int nvec = cols / VE;
+  const T* gr = g + row * cols;
+  const T* yr = y + row * cols;
+  float fg[VPT][VE], fy[VPT][VE];
+  float s = 0.f;
+#pragma unroll
+  for (int u = 0; u < VPT; ++u) {
+    const int j = t + u * tpr;
+    if (j < nvec) {
+      widen<T>(ld_stream(gr + j * VE), fg[u]);
+      widen<T>(ld_stream(yr + j * VE), fy[u]);
+#pragma unroll
+      for (int e = 0; e < VE; ++e) s += IS_LOG ? fg[u][e] : fg[u][e] * fy[u][e];
+    }
+  }
+  s = group_reduce<WARP>(s, SumF{}, 0.f, red, 0);
+#pragma unroll
+  for (int u = 0; u < VPT; ++u) {
+    const int j = t + u * tpr;
+    if (j < nvec) {
+#pragma unroll
+      for (int e = 0; e < VE; ++e) fg[u][e] = IS_LOG ? fg[u][e] - ex2_approx(fy[u][e] * kLog2e) * s : (fg[u][e] - s) * fy[u][e];
+      store_row_vec<T>(out, row * cols + static_cast<int64_t>(j) * VE, fg[u], out_f32 != 0);
+    }
+  }
+}
+
+// Any geometry and alignment: one warp per (outer, inner) line, elements `inner` apart,
+// two passes over the line (the second from cache).
+template <typename T, bool IS_LOG>
+__global__ void __launch_bounds__(128) softmax_bwd_lines(const T* __restrict__ g, const T* __restrict__ y, void* __restrict__ out, int64_t outer, int64_t dim, int64_t inner, int dto) {
+  const int lane = threadIdx.x & 31;
+  const int64_t line = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (line >= outer * inner) return;
+  const int64_t o = line / inner, i = line - o * inner, base = o * dim * inner + i;
+  float s = 0.f;
+  for (int64_t k = lane; k < dim; k += 32) s += IS_LOG ? to_f32(g[base + k * inner]) : to_f32(g[base + k * inner]) * to_f32(y[base + k * inner]);
+  s = warp_reduce(s, SumF{});
+  for (int64_t k = lane; k < dim; k += 32) {
+    const float gv = to_f32(g[base + k * inner]), yv = to_f32(y[base + k * inner]);
+    store_from_f32(out, base + k * inner, dto, IS_LOG ? gv - ex2_approx(yv * kLog2e) * s : (gv - s) * yv);
+  }
+}
+
 // ------------------------------------------------------------------ softmax, streaming
 // One CTA per row, three scalar passes (max, sum of exponentials, write); the second
 // and third read come from L2. Any `cols`, any alignment. NaN / inf rows behave as in
@@ -778,6 +837,37 @@ static int softmax_T(const void* x, void* out, int64_t outer, int64_t dim, int64
   return check_launch();
 }
 
+template <typename T>
+static int softmax_bwd_T(const void* g, const void* y, void* out, int64_t outer, int64_t dim, int64_t inner, int dti, int dto, int is_log, cudaStream_t st) {
+  constexpr int VE = Vec<T>::N;
+  constexpr int MAXV = 16 / VE;  // two rows are held: at most 16 fp32 registers of each per thread
+  const T* pg = static_cast<const T*>(g);
+  const T* py = static_cast<const T*>(y);
+  const int out_f32 = dto == B200_F32;
+  const bool out_ok = dto == B200_F32 || dto == dti;  // the vector store writes T or fp32
+  if (inner == 1 && out_ok && dim % VE == 0 && aligned16(g) && aligned16(y) && aligned16(out) && dim < (1LL << 30) && outer <= 0x7fffffffLL) {
+    const ResidentCfg c = resident_cfg(dim / VE, MAXV);
+    if (c.ok) {
+      const int cols = static_cast<int>(dim);
+      if (c.warp) {
+        const unsigned gr = grid_for(outer, 4);
+        if (is_log) { B200_DISPATCH_VPT(c.vpt, MAXV, (softmax_bwd_resident<T, VPT, true, true><<<gr, 128, 0, st>>>(pg, py, out, outer, cols, out_f32))) }
+        else { B200_DISPATCH_VPT(c.vpt, MAXV, (softmax_bwd_resident<T, VPT, true, false><<<gr, 128, 0, st>>>(pg, py, out, outer, cols, out_f32))) }
+      } else {
+        const unsigned gr = static_cast<unsigned>(outer);
+        if (is_log) { B200_DISPATCH_VPT(c.vpt, MAXV, (softmax_bwd_resident<T, VPT, false, true><<<gr, c.threads, 0, st>>>(pg, py, out, outer, cols, out_f32))) }
+        else { B200_DISPATCH_VPT(c.vpt, MAXV, (softmax_bwd_resident<T, VPT, false, false><<<gr, c.threads, 0, st>>>(pg, py, out, outer, cols, out_f32))) }
+      }
+      return check_launch();
+    }
+  }
+  const int64_t lines = outer * inner;
+  if ((lines + 3) / 4 > 0x7fffffffLL) return B200_EINVAL;
+  if (is_log) softmax_bwd_lines<T, true><<<grid_for(lines, 4), 128, 0, st>>>(pg, py, out, outer, dim, inner, dto);
+  else softmax_bwd_lines<T, false><<<grid_for(lines, 4), 128, 0, st>>>(pg, py, out, outer, dim, inner, dto);
+  return check_launch();
+}
+
 template <typename T, typename TW, bool HOLD, bool AFFINE>
 static int layernorm_launch(const T* px, const TW* pw, const TW* pb, T* py, void* mean, void* rstd, int64_t rows, int64_t cols, float eps, int dt_stat, const ResidentCfg& c, cudaStream_t st) {
   constexpr int VE = Vec<T>::N;
@@ -819,6 +909,19 @@ extern "C" int b200_softmax(const void* x, void* out, int64_t outer, int64_t dim
     case B200_F32: return softmax_T<float>(x, out, outer, dim, inner, dto, is_log, st);
     case B200_BF16: return softmax_T<__nv_bfloat16>(x, out, outer, dim, inner, dto, is_log, st);
     default: return softmax_T<__half>(x, out, outer, dim, inner, dto, is_log, st);
+  }
+}
+
+extern "C" int b200_softmax_backward(const void* grad, const void* output, void* grad_input, int64_t outer, int64_t dim, int64_t inner, int dti, int dto, int is_log, void* stream) {
+  if (outer < 0 || dim < 0 || inner < 0) return B200_EINVAL;
+  if (!is_float_dtype(dti) || !is_float_dtype(dto)) return B200_EDTYPE;
+  if (outer == 0 || dim == 0 || inner == 0) return B200_OK;
+  if (!grad || !output || !grad_input) return B200_EINVAL;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (dti) {
+    case B200_F32: return softmax_bwd_T<float>(grad, output, grad_input, outer, dim, inner, dti, dto, is_log, st);
+    case B200_BF16: return softmax_bwd_T<__nv_bfloat16>(grad, output, grad_input, outer, dim, inner, dti, dto, is_log, st);
+    default: return softmax_bwd_T<__half>(grad, output, grad_input, outer, dim, inner, dti, dto, is_log, st);
   }
 }
 

@@ -16,7 +16,7 @@ import json
 import torch
 
 from .backends import B200Backend
-from .cases import named_case, named_cases, scaled_down
+from .cases import named_case, named_cases, neighbour_cases, scaled_down
 from .eval import cuda_bench
 from .opregistry import get_operator
 
@@ -31,7 +31,7 @@ def main():
     ap.add_argument("--list", action="store_true")
     args = ap.parse_args()
     if args.list or not args.case:
-        print("\n".join(c.name for c in named_cases()))
+        print("\n".join(c.name for c in named_cases() + neighbour_cases()))
         return
     case = named_case(args.case)
     if args.scale > 1:

@@ -129,6 +129,17 @@ int b200_copy_into(const void* x, void* out, int ndim, const int64_t* shape, con
 int b200_softmax(const void* x, void* out, int64_t outer, int64_t dim, int64_t inner,
                  int dtype_in, int dtype_out, int log_softmax, void* stream);
 
+/* aten._softmax_backward_data.default / aten._log_softmax_backward_data.default
+ * (grad_output, output, dim, input_dtype), the operators BackendBench/backends/flag_gems.py:196,233
+ * lists next to the forward ones:
+ *   softmax:      grad_input = (grad - sum(grad * output)) * output
+ *   log_softmax:  grad_input = grad - exp(output) * sum(grad)
+ * along `dim` of the contiguous [outer, dim, inner] view; grad and output share dtype_in,
+ * grad_input has dtype_out (= input_dtype); fp32 internal math. */
+int b200_softmax_backward(const void* grad, const void* output, void* grad_input, int64_t outer,
+                          int64_t dim, int64_t inner, int dtype_in, int dtype_out,
+                          int log_softmax, void* stream);
+
 /* Scratch size (bytes, possibly 0) that b200_sum / b200_argmax need for this geometry:
  * when few output elements face a long reduction, the reduction is split across CTAs
  * and per-split partials (fp32 sum, or fp32 value + int64 index) are staged there. */

@@ -166,6 +166,20 @@ def log_softmax(x, dim, half_to_float=False):
     return softmax(x, dim, half_to_float, log=True)
 
 
+def softmax_backward(grad, output, dim, input_dtype, log=False):
+    dim = _norm(dim, grad.dim())
+    g, y = widen(grad), widen(output)
+    out = np.empty_like(g)
+    o, d, i = _split(grad.shape, dim)
+    if g.size:
+        lib().oracle_softmax_backward(_ptr(g), _ptr(y), _ptr(out), c_int64(o), c_int64(d), c_int64(i), c_int(1 if log else 0))
+    return narrow(out, input_dtype).reshape(grad.shape)
+
+
+def log_softmax_backward(grad, output, dim, input_dtype):
+    return softmax_backward(grad, output, dim, input_dtype, log=True)
+
+
 def sum_dims(x, dim=None, keepdim=False, *, dtype=None):
     nd = x.dim()
     dims = list(range(nd)) if dim is None or (isinstance(dim, (list, tuple)) and not dim) else [_norm(d, nd) for d in ([dim] if isinstance(dim, int) else dim)]
@@ -305,6 +319,8 @@ ORACLE = {
     "where.self": where,
     "_softmax.default": softmax,
     "_log_softmax.default": log_softmax,
+    "_softmax_backward_data.default": softmax_backward,
+    "_log_softmax_backward_data.default": log_softmax_backward,
     "sum.dim_IntList": sum_dims,
     "native_layer_norm.default": layer_norm,
     "argmax.default": argmax,

@@ -107,6 +107,23 @@ void oracle_softmax(const float* x, float* out, int64_t outer, int64_t dim, int6
     }
 }
 
+/* aten._softmax_backward_data.default / aten._log_softmax_backward_data.default
+ * (grad_output, output, dim, input_dtype) -- the backward neighbours listed at
+ * BackendBench/backends/flag_gems.py:196,233; evaluated through eval.py:100 like any op.
+ *   softmax:     gin = (g - sum(g * y)) * y        log_softmax: gin = g - exp(y) * sum(g) */
+void oracle_softmax_backward(const float* g, const float* y, float* out, int64_t outer, int64_t dim, int64_t inner, int is_log) {
+  for (int64_t o = 0; o < outer; ++o)
+    for (int64_t i = 0; i < inner; ++i) {
+      const int64_t base = o * dim * inner + i;
+      double s = 0.0;
+      for (int64_t k = 0; k < dim; ++k) s += is_log ? (double)g[base + k * inner] : (double)g[base + k * inner] * (double)y[base + k * inner];
+      for (int64_t k = 0; k < dim; ++k) {
+        const double gv = g[base + k * inner], yv = y[base + k * inner];
+        out[base + k * inner] = (float)(is_log ? gv - exp(yv) * s : (gv - s) * yv);
+      }
+    }
+}
+
 /* aten.sum.dim_IntList over `dim` of [outer, dim, inner]; empty dim sums to 0. eval.py:100. */
 void oracle_sum(const float* x, float* out, int64_t outer, int64_t dim, int64_t inner) {
   for (int64_t o = 0; o < outer; ++o)

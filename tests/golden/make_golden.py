@@ -118,6 +118,18 @@ def tensor_cases():
     out.append(("argmax.default", [ties.clone()], {}, "argmax_flat"))
     out.append(("argmax.default", [rn(5, 6, 7), 1, True], {}, "argmax_dim1_keepdim"))
     out.append(("argmax.default", [rn(20000)], {}, "argmax_long_flat"))
+    # ---- backward neighbours of the row operators (appended last: earlier cases keep their random draws)
+    for dt in (f32, bf, hf):
+        x = rn(37, 96, dtype=dt)
+        out.append(("_softmax_backward_data.default", [rn(37, 96, dtype=dt), torch.softmax(x.float(), -1).to(dt), -1, dt], {}, f"softmax_backward_{dt}"))
+        out.append(("_log_softmax_backward_data.default", [rn(37, 96, dtype=dt), torch.log_softmax(x.float(), -1).to(dt), -1, dt], {}, f"log_softmax_backward_{dt}"))
+    x = rn(6, 33, 5)
+    out.append(("_softmax_backward_data.default", [rn(6, 33, 5), torch.softmax(x, 1), 1, f32], {}, "softmax_backward_dim1"))
+    out.append(("_log_softmax_backward_data.default", [rn(6, 33, 5), torch.log_softmax(x, 0), 0, f32], {}, "log_softmax_backward_dim0"))
+    x = rn(9, 67)
+    out.append(("_softmax_backward_data.default", [rn(9, 67), torch.softmax(x, -1), -1, f32], {}, "softmax_backward_ragged"))
+    out.append(("_log_softmax_backward_data.default", [rn(9, 67), torch.log_softmax(x, -1), -1, f32], {}, "log_softmax_backward_ragged"))
+    out.append(("_softmax_backward_data.default", [torch.empty(0, 7), torch.empty(0, 7), 1, f32], {}, "softmax_backward_empty"))
     return out
 
 

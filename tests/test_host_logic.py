@@ -240,11 +240,12 @@ def test_reference_literal_vectors_on_aten_backend():
 
 # ------------------------------------------------------------------ directory backend
 def test_b200_backend_loads_all_sixteen_overloads_and_their_variants():
+    from backendbench_b200.backward import BACKWARD_TABLE
     from backendbench_b200.variants import VARIANT_TABLE
 
     be = B200Backend()
-    everything = {**OP_TABLE, **VARIANT_TABLE}
-    assert be.name == "b200" and len(OP_TABLE) == 16 and len(be.compiled_kernels) == len(everything) == 37
+    everything = {**OP_TABLE, **VARIANT_TABLE, **BACKWARD_TABLE}
+    assert be.name == "b200" and len(OP_TABLE) == 16 and len(be.compiled_kernels) == len(everything) == 39
     assert set(be.compiled_kernels) == {get_operator(spec) for spec in everything}
     assert get_operator("add_.Tensor") is torch.ops.aten.add_.Tensor and get_operator("sum.IntList_out") is torch.ops.aten.sum.IntList_out
     for spec in everything:

@@ -16,7 +16,7 @@ def _as_tuple(x):
     return tuple(x) if isinstance(x, (tuple, list)) else (x,)
 
 
-def test_golden_covers_all_sixteen_ops(golden_cases):
+def test_golden_covers_every_operator_the_oracle_restates(golden_cases):
     assert {c["op"] for c in golden_cases} == set(oracle.ORACLE)
     assert len(golden_cases) >= 80
 

@@ -31,11 +31,12 @@ def test_reference_directory_backend_loads_our_kernels(ref):
     from backendbench_b200.backends import KERNELS_DIR
     from backendbench_b200.ops import OP_TABLE
 
+    from backendbench_b200.backward import BACKWARD_TABLE
     from backendbench_b200.variants import VARIANT_TABLE
 
     be = ref["DirectoryBackend"](KERNELS_DIR)
-    assert len(be.compiled_kernels) == 16 + len(VARIANT_TABLE)
-    for spec in list(OP_TABLE) + list(VARIANT_TABLE):
+    assert len(be.compiled_kernels) == 16 + len(VARIANT_TABLE) + len(BACKWARD_TABLE)
+    for spec in list(OP_TABLE) + list(VARIANT_TABLE) + list(BACKWARD_TABLE):
         op = ref["utils"].get_pytorch_op(spec)
         assert op in be and callable(be[op])
         assert not ref["utils"].uses_cuda_stream(be[op])  # the reference would refuse to evaluate it otherwise
