@@ -60,6 +60,8 @@ SIGNATURES = {
     "b200_sum": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_int64, c_void_p]),
     "b200_sum_static": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_void_p]),
     "b200_layer_norm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_double, c_int, c_int, c_int, c_void_p]),
+    "b200_layer_norm_backward_scratch_bytes": (c_int64, [c_int64, c_int64]),
+    "b200_layer_norm_backward": (c_int, [c_void_p] * 8 + [c_int64, c_int64, c_int, c_int, c_int, c_void_p, c_int64, c_void_p]),
     "b200_argmax": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p, c_int64, c_void_p]),
     "b200_gather_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p]),
     "b200_index_select": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p]),

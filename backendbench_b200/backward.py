@@ -1,10 +1,10 @@
 """Backward neighbours of the row operators.
 
-BackendBench/backends/flag_gems.py:196,233 lists `_softmax_backward_data` and
-`_log_softmax_backward_data` beside the forward operators, and the reference's
+BackendBench/backends/flag_gems.py:140,196,233 lists `native_layer_norm_backward`,
+`_softmax_backward_data` and `_log_softmax_backward_data` beside the forward operators, and the reference's
 training demo (README.md:40-42) needs them for a model to stay on one backend through a
 backward pass. Same boundary as the forward operators: host wrapper here, kernels behind
-the C-ABI (`b200_softmax_backward`), no aten arithmetic.
+the C-ABI (`b200_softmax_backward`, `b200_layer_norm_backward`), no aten arithmetic.
 """
 
 from __future__ import annotations
@@ -45,8 +45,52 @@ def _log_softmax_backward_data_default(grad_output, output, dim, input_dtype) ->
     return _softmax_backward(grad_output, output, dim, input_dtype, True)
 
 
+def native_layer_norm_backward_default(grad_out, input, normalized_shape, mean, rstd, weight, bias, output_mask):
+    """aten.native_layer_norm_backward.default -> (grad_input, grad_weight, grad_bias), each None
+    where `output_mask` is False. With xhat = (x - mean) * rstd and gy = grad_out * weight:
+    grad_input = rstd * (gy - mean(gy) - xhat * mean(gy * xhat)) over the normalized dims,
+    grad_weight = sum over rows of grad_out * xhat, grad_bias = sum over rows of grad_out."""
+    ops._require_cuda(grad_out, input, mean, rstd)
+    if input.dtype not in ops._FLOATS or grad_out.dtype != input.dtype:
+        raise ops.UnsupportedByB200(f"native_layer_norm_backward: dtypes {grad_out.dtype} / {input.dtype}")
+    normalized_shape = [int(s) for s in normalized_shape]
+    nd = len(normalized_shape)
+    if nd == 0 or list(input.shape[-nd:]) != normalized_shape or grad_out.shape != input.shape:
+        raise RuntimeError(f"native_layer_norm_backward: input {list(input.shape)} / grad {list(grad_out.shape)} do not end with normalized_shape {normalized_shape}")
+    want_dx, want_dw, want_db = (bool(m) for m in output_mask)
+    if weight is not None and (weight.dtype not in ops._FLOATS or list(weight.shape) != normalized_shape):
+        raise RuntimeError("native_layer_norm_backward: weight must be a floating tensor of normalized_shape")
+    if (want_dw or want_db) and weight is None and bias is None:
+        raise ops.UnsupportedByB200("native_layer_norm_backward: parameter gradients requested without parameters")
+    cols = ops._prod(normalized_shape)
+    rows = input.numel() // cols if cols else 0
+    param = weight if weight is not None else bias
+    wb_dtype = param.dtype if param is not None else input.dtype
+    dx = torch.empty(input.shape, dtype=input.dtype, device=input.device) if want_dx else None
+    dw = torch.empty(normalized_shape, dtype=wb_dtype, device=input.device) if want_dw else None
+    db = torch.empty(normalized_shape, dtype=wb_dtype, device=input.device) if want_db else None
+    if cols and (rows or want_dw or want_db):
+        dy, x = ops._contig(grad_out), ops._contig(input)
+        mu, rs = ops._contig(mean), ops._contig(rstd)
+        if mu.numel() != rows or rs.numel() != rows or mu.dtype != rs.dtype or mu.dtype not in ops._FLOATS:
+            raise RuntimeError("native_layer_norm_backward: mean / rstd must hold one floating value per normalized row")
+        w = ops._contig(weight) if weight is not None else None
+        need = int(lib().b200_layer_norm_backward_scratch_bytes(rows, cols)) if (want_dw or want_db) else 0
+        scratch = ops._scratch(input.device, need) if need else None
+        check(
+            lib().b200_layer_norm_backward(
+                dy.data_ptr(), x.data_ptr(), mu.data_ptr(), rs.data_ptr(), w.data_ptr() if w is not None else None, dx.data_ptr() if dx is not None else None,
+                dw.data_ptr() if dw is not None else None, db.data_ptr() if db is not None else None, rows, cols, ops._dt(x.dtype), ops._dt(wb_dtype), ops._dt(mu.dtype),
+                scratch.data_ptr() if scratch is not None else None, need, ops._stream_handle(),
+            ),
+            "b200_layer_norm_backward",
+        )
+    return dx, dw, db
+
+
 # op spec name -> host function, the same form as ops.OP_TABLE
 BACKWARD_TABLE = {
     "_softmax_backward_data.default": _softmax_backward_data_default,
     "_log_softmax_backward_data.default": _log_softmax_backward_data_default,
+    "native_layer_norm_backward.default": native_layer_norm_backward_default,
 }

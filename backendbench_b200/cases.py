@@ -107,6 +107,15 @@ class CaseSpec:
             dim = self.param("dim", -1)
             y = torch.softmax(normal(shp).float(), dim) if op == "_softmax_backward_data.default" else torch.log_softmax(normal(shp).float(), dim)
             args = [normal(shp), y.to(dt), dim, dt]
+        elif op == "native_layer_norm_backward.default":
+            cols = shp[-1]
+            x = normal(shp)
+            w = normal((cols,), std=0.02, mean=1.0)
+            b = normal((cols,), std=0.02)
+            xf = x.float()
+            mean = xf.mean(-1, keepdim=True)  # fp32 statistics, as the CUDA forward returns them
+            rstd = torch.rsqrt(xf.var(-1, unbiased=False, keepdim=True) + 1e-5)
+            args = [normal(shp), x, [cols], mean, rstd, w, b, [True, True, True]]
         elif op == "sum.dim_IntList":
             x = transposed(shp) if self.edge == "transposed" and len(shp) == 2 else normal(shp)
             args = [poison(x), list(self.param("dim", (-1,)))]
@@ -189,6 +198,9 @@ class CaseSpec:
             return 2 * n * es
         if op in ("_softmax_backward_data.default", "_log_softmax_backward_data.default"):
             return 3 * n * es  # grad and output in, grad_input out
+        if op == "native_layer_norm_backward.default":
+            rows = n // max(self.shape[-1], 1)
+            return 3 * n * es + 3 * self.shape[-1] * es + 2 * rows * 4  # dy, x in, dx out; w in, dw, db out; fp32 mean / rstd in
         if op == "sum.dim_IntList":
             dims = [d % len(self.shape) for d in self.param("dim", (-1,))]
             out = _prod(s for i, s in enumerate(self.shape) if i not in dims)
@@ -283,6 +295,7 @@ def neighbour_cases() -> List[CaseSpec]:
         tag = f"{dtype}_{shape[0]}x{shape[1]}"
         for name, op in (("softmax_backward", "_softmax_backward_data.default"), ("log_softmax_backward", "_log_softmax_backward_data.default")):
             c.append(CaseSpec(1000 + len(c), op, dtype, shape, 0, (("dim", -1),), "", "reduce", f"{name}_{tag}"))
+        c.append(CaseSpec(1000 + len(c), "native_layer_norm_backward.default", dtype, shape, 0, (), "", "reduce", f"layer_norm_backward_{tag}"))
     return c
 
 

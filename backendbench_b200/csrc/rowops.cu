@@ -403,6 +403,180 @@ layernorm_resident(const T* __restrict__ x, const TW* __restrict__ w, const TW* 
   }
 }
 
+// ------------------------------------------------------------------ layer norm backward
+// aten.native_layer_norm_backward: with xhat = (x - mean) * rstd and gy = dy * w per row,
+//   dx = rstd * (gy - mean_j(gy) - xhat * mean_j(gy * xhat))
+//   dw = sum_rows dy * xhat,  db = sum_rows dy.
+// Fused kernel (row length a multiple of the 16-byte vector, everything aligned): persistent
+// CTAs, one row at a time per CTA; a thread owns the same columns of every row it sees, so it
+// carries its share of dw / db in registers across rows and writes one partial per CTA at
+// the end (dy and x are read once for all three results). A small second kernel adds the
+// per-CTA partials in order. fp32 arithmetic throughout.
+template <typename T, typename TW, int VPT>
+__global__ void __launch_bounds__(1024)
+layernorm_bwd_fused(const T* __restrict__ dy, const T* __restrict__ x, const TW* __restrict__ w, const void* __restrict__ mean, const void* __restrict__ rstd, T* __restrict__ dx,
+                    float* __restrict__ part_w, float* __restrict__ part_b, int64_t rows, int cols, int dt_stat) {
+  constexpr int VE = Vec<T>::N;
+  __shared__ float red[64];
+  const int t = threadIdx.x, tpr = blockDim.x;
+  const int nvec = cols / VE;
+  const float inv_cols = 1.f / static_cast<float>(cols);
+  float wv[VPT][VE], aw[VPT][VE], ab[VPT][VE];
+#pragma unroll
+  for (int u = 0; u < VPT; ++u) {
+    const int j = t + u * tpr;
+#pragma unroll
+    for (int e = 0; e < VE; ++e) { wv[u][e] = 1.f; aw[u][e] = 0.f; ab[u][e] = 0.f; }
+    if (w && j < nvec) load_weights<VE, TW>(w, j * VE, wv[u]);
+  }
+  // the vectors of the next row are requested before this row is worked on: twice the bytes in flight per thread
+  uint4 ndy[VPT], nx[VPT];
+  if (static_cast<int64_t>(blockIdx.x) < rows) {
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+      const int j = t + u * tpr;
+      if (j < nvec) {
+        ndy[u] = ld_stream(dy + static_cast<int64_t>(blockIdx.x) * cols + j * VE);
+        nx[u] = ld_stream(x + static_cast<int64_t>(blockIdx.x) * cols + j * VE);
+      }
+    }
+  }
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float mu = load_as_f32(mean, row, dt_stat), rs = load_as_f32(rstd, row, dt_stat);
+    float g[VPT][VE], h[VPT][VE];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+      widen<T>(ndy[u], g[u]);
+      widen<T>(nx[u], h[u]);
+    }
+    const int64_t next = row + gridDim.x;
+    if (next < rows) {
+#pragma unroll
+      for (int u = 0; u < VPT; ++u) {
+        const int j = t + u * tpr;
+        if (j < nvec) {
+          ndy[u] = ld_stream(dy + next * cols + j * VE);
+          nx[u] = ld_stream(x + next * cols + j * VE);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+      const int j = t + u * tpr;
+      if (j < nvec) {
+#pragma unroll
+        for (int e = 0; e < VE; ++e) {
+          const float xhat = (h[u][e] - mu) * rs;
+          ab[u][e] += g[u][e];
+          aw[u][e] = fmaf(g[u][e], xhat, aw[u][e]);
+          const float gy = g[u][e] * wv[u][e];
+          s1 += gy;
+          s2 = fmaf(gy, xhat, s2);
+          g[u][e] = gy;
+          h[u][e] = xhat;
+        }
+      }
+    }
+    s1 = block_reduce_once(s1, SumF{}, 0.f, red, 0);
+    s2 = block_reduce_once(s2, SumF{}, 0.f, red, 1);
+    const float c1 = s1 * inv_cols, c2 = s2 * inv_cols;
+    if (dx) {
+#pragma unroll
+      for (int u = 0; u < VPT; ++u) {
+        const int j = t + u * tpr;
+        if (j < nvec) {
+          float o[VE];
+#pragma unroll
+          for (int e = 0; e < VE; ++e) o[e] = rs * (g[u][e] - c1 - h[u][e] * c2);
+          st_stream(dx + row * cols + j * VE, narrow<T>(o));
+        }
+      }
+    }
+  }
+  if (part_w) {
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+      const int j = t + u * tpr;
+      if (j < nvec) {
+        float* pw = part_w + static_cast<int64_t>(blockIdx.x) * cols + j * VE;
+        float* pb = part_b + static_cast<int64_t>(blockIdx.x) * cols + j * VE;
+#pragma unroll
+        for (int e = 0; e < VE; ++e) { pw[e] = aw[u][e]; pb[e] = ab[u][e]; }
+      }
+    }
+  }
+}
+
+// Any row length and alignment. dx: one CTA per row, scalar, three passes (the second and
+// third from cache). dw / db partials: one thread per column walking a chunk of rows
+// (coalesced across columns), one partial row per chunk.
+__global__ void __launch_bounds__(256) layernorm_bwd_dx_lines(const void* __restrict__ dy, const void* __restrict__ x, const void* __restrict__ w, const void* __restrict__ mean,
+                                                              const void* __restrict__ rstd, void* __restrict__ dx, int64_t rows, int64_t cols, int dt, int dt_wb, int dt_stat) {
+  __shared__ float red[64];
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float mu = load_as_f32(mean, row, dt_stat), rs = load_as_f32(rstd, row, dt_stat);
+    const int64_t base = row * cols;
+    float s1 = 0.f, s2 = 0.f;
+    for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) {
+      const float gy = load_as_f32(dy, base + c, dt) * (w ? load_as_f32(w, c, dt_wb) : 1.f);
+      s1 += gy;
+      s2 = fmaf(gy, (load_as_f32(x, base + c, dt) - mu) * rs, s2);
+    }
+    __syncthreads();  // the reduction buffers of the row before are free
+    s1 = block_reduce_once(s1, SumF{}, 0.f, red, 0);
+    s2 = block_reduce_once(s2, SumF{}, 0.f, red, 1);
+    const float c1 = s1 / static_cast<float>(cols), c2 = s2 / static_cast<float>(cols);
+    for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) {
+      const float gy = load_as_f32(dy, base + c, dt) * (w ? load_as_f32(w, c, dt_wb) : 1.f);
+      const float xhat = (load_as_f32(x, base + c, dt) - mu) * rs;
+      store_from_f32(dx, base + c, dt, rs * (gy - c1 - xhat * c2));
+    }
+  }
+}
+__global__ void __launch_bounds__(256) layernorm_bwd_wb_lines(const void* __restrict__ dy, const void* __restrict__ x, const void* __restrict__ mean, const void* __restrict__ rstd,
+                                                              float* __restrict__ part_w, float* __restrict__ part_b, int64_t rows, int64_t cols, int64_t rows_per, int dt, int dt_stat) {
+  const int64_t c = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  const int64_t r0 = static_cast<int64_t>(blockIdx.y) * rows_per, r1 = r0 + rows_per < rows ? r0 + rows_per : rows;
+  float aw = 0.f, ab = 0.f;
+  for (int64_t r = r0; r < r1; ++r) {
+    const float g = load_as_f32(dy, r * cols + c, dt);
+    ab += g;
+    aw = fmaf(g, (load_as_f32(x, r * cols + c, dt) - load_as_f32(mean, r, dt_stat)) * load_as_f32(rstd, r, dt_stat), aw);
+  }
+  part_w[static_cast<int64_t>(blockIdx.y) * cols + c] = aw;
+  part_b[static_cast<int64_t>(blockIdx.y) * cols + c] = ab;
+}
+// dw[c] = sum over the `parts` partial rows, same for db: a CTA takes 32 columns, its 32
+// warps take every 32nd partial row each (coalesced 128-byte reads), and the 32 slice sums
+// of a column are added in slice order -- a fixed order, so the result is reproducible.
+__global__ void __launch_bounds__(1024) layernorm_bwd_finalize(const float* __restrict__ part_w, const float* __restrict__ part_b, void* __restrict__ dw, void* __restrict__ db, int64_t parts,
+                                                               int64_t cols, int dt_wb) {
+  __shared__ float sw[32][33], sb[32][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int64_t c = static_cast<int64_t>(blockIdx.x) * 32 + tx;
+  float aw = 0.f, ab = 0.f;
+  if (c < cols)
+    for (int64_t p = ty; p < parts; p += 32) {
+      aw += part_w[p * cols + c];
+      ab += part_b[p * cols + c];
+    }
+  sw[ty][tx] = aw;
+  sb[ty][tx] = ab;
+  __syncthreads();
+  if (ty == 0 && c < cols) {
+    float tw = 0.f, tb = 0.f;
+#pragma unroll
+    for (int k = 0; k < 32; ++k) {
+      tw += sw[k][tx];
+      tb += sb[k][tx];
+    }
+    if (dw) store_from_f32(dw, c, dt_wb, tw);
+    if (db) store_from_f32(db, c, dt_wb, tb);
+  }
+}
+
 // layer norm, streaming: one CTA per row, three scalar passes (second and third from L2).
 __global__ void __launch_bounds__(256) layernorm_stream(const void* __restrict__ x, const void* __restrict__ w, const void* __restrict__ b, void* __restrict__ y,
                                                         void* __restrict__ mean, void* __restrict__ rstd, int64_t cols, float eps, int dt, int dt_wb, int dt_stat) {
@@ -1003,6 +1177,112 @@ extern "C" int b200_layer_norm(const void* x, const void* w, const void* b, void
       return wf32 ? layernorm_T<__half, float>(x, w, b, y, mean, rstd, rows, cols, e, dt_stat, c, st)
                   : layernorm_T<__half, __half>(x, w, b, y, mean, rstd, rows, cols, e, dt_stat, c, st);
   }
+}
+
+// ---- layer norm backward: host side
+static const int64_t kLnBwdMaxParts = 8LL * kNumSMs;  // partial rows of dw / db in scratch
+
+extern "C" int64_t b200_layer_norm_backward_scratch_bytes(int64_t rows, int64_t cols) {
+  if (rows <= 0 || cols <= 0) return 0;
+  const int64_t parts = rows < kLnBwdMaxParts ? rows : kLnBwdMaxParts;
+  return parts * cols * 2 * 4;
+}
+
+template <typename T, typename TW>
+static int layernorm_bwd_fused_launch(const void* dy, const void* x, const void* w, const void* mean, const void* rstd, void* dx, float* pw, float* pb, int64_t rows, int64_t cols, int dt_stat,
+                                      int threads, int vpt, int grid, cudaStream_t st) {
+  const T* pdy = static_cast<const T*>(dy);
+  const T* px = static_cast<const T*>(x);
+  const TW* pwt = static_cast<const TW*>(w);
+  T* pdx = static_cast<T*>(dx);
+  const int ci = static_cast<int>(cols);
+  switch (vpt) {
+    case 1: layernorm_bwd_fused<T, TW, 1><<<grid, threads, 0, st>>>(pdy, px, pwt, mean, rstd, pdx, pw, pb, rows, ci, dt_stat); break;
+    default: layernorm_bwd_fused<T, TW, 2><<<grid, threads, 0, st>>>(pdy, px, pwt, mean, rstd, pdx, pw, pb, rows, ci, dt_stat); break;
+  }
+  return B200_OK;
+}
+// CTAs of the fused kernel one SM holds at this block size (registers decide).
+template <typename T, typename TW>
+static int layernorm_bwd_fused_per_sm(int threads, int vpt) {
+  int n = 0;
+  const cudaError_t e = vpt == 1 ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, layernorm_bwd_fused<T, TW, 1>, threads, 0)
+                                 : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, layernorm_bwd_fused<T, TW, 2>, threads, 0);
+  return e == cudaSuccess && n > 0 ? n : 1;
+}
+
+extern "C" int b200_layer_norm_backward(const void* dy, const void* x, const void* mean, const void* rstd, const void* w, void* dx, void* dw, void* db, int64_t rows, int64_t cols, int dt,
+                                        int dt_wb, int dt_stat, void* scratch, int64_t scratch_bytes, void* stream) {
+  if (rows < 0 || cols < 0) return B200_EINVAL;
+  if (!is_float_dtype(dt) || !is_float_dtype(dt_stat) || ((w || dw || db) && !is_float_dtype(dt_wb))) return B200_EDTYPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (cols == 0) return B200_OK;
+  if (rows == 0) {  // nothing to sum: the parameter gradients are zero
+    if (dw) fill_zero_typed<<<grid_for(cols, 256), 256, 0, st>>>(dw, cols, dt_wb);
+    if (db) fill_zero_typed<<<grid_for(cols, 256), 256, 0, st>>>(db, cols, dt_wb);
+    return check_launch();
+  }
+  if (!dy || !x || !mean || !rstd) return B200_EINVAL;
+  const bool need_wb = dw || db;
+  const int64_t parts_max = rows < kLnBwdMaxParts ? rows : kLnBwdMaxParts;
+  float* pw = nullptr;
+  float* pb = nullptr;
+  if (need_wb) {
+    if (!scratch || scratch_bytes < b200_layer_norm_backward_scratch_bytes(rows, cols)) return B200_ESCRATCH;
+    pw = static_cast<float*>(scratch);
+    pb = pw + parts_max * cols;
+  }
+  const int ve = 16 / dtype_size(dt);
+  const bool wb_ok = !w || dt_wb == dt || dt_wb == B200_F32;
+  const bool al = aligned16(dy) && aligned16(x) && (!dx || aligned16(dx)) && (!w || aligned16(w));
+  int64_t parts = 0;
+  // a thread keeps five values per owned column in registers (dy, xhat, w, and its share of dw
+  // and db): one 16-byte vector of a 16-bit row, two of an fp32 row -- rows of up to 8192
+  // elements; longer ones would spill
+  const int target = ve == 4 ? 2 : 1;
+  if (cols % ve == 0 && (dt_wb != B200_F32 || !w || cols % 4 == 0) && al && wb_ok && cols / ve <= 1024 * target) {
+    const int64_t nvec = cols / ve;
+    int threads = 32;
+    while (threads < 1024 && threads * target < nvec) threads <<= 1;
+    const int vpt = static_cast<int>((nvec + threads - 1) / threads);
+    const bool wf32 = w && dt_wb == B200_F32;
+    int per_sm = 1;
+    switch (dt) {
+      case B200_F32: per_sm = layernorm_bwd_fused_per_sm<float, float>(threads, vpt); break;
+      case B200_BF16: per_sm = wf32 ? layernorm_bwd_fused_per_sm<__nv_bfloat16, float>(threads, vpt) : layernorm_bwd_fused_per_sm<__nv_bfloat16, __nv_bfloat16>(threads, vpt); break;
+      default: per_sm = wf32 ? layernorm_bwd_fused_per_sm<__half, float>(threads, vpt) : layernorm_bwd_fused_per_sm<__half, __half>(threads, vpt); break;
+    }
+    if (per_sm > 8) per_sm = 8;
+    parts = static_cast<int64_t>(per_sm) * kNumSMs;  // a persistent grid: exactly what the device holds at once
+    if (parts > parts_max) parts = parts_max;
+    const int grid = static_cast<int>(parts);
+    switch (dt) {
+      case B200_F32: layernorm_bwd_fused_launch<float, float>(dy, x, w, mean, rstd, dx, pw, pb, rows, cols, dt_stat, threads, vpt, grid, st); break;
+      case B200_BF16:
+        if (wf32) layernorm_bwd_fused_launch<__nv_bfloat16, float>(dy, x, w, mean, rstd, dx, pw, pb, rows, cols, dt_stat, threads, vpt, grid, st);
+        else layernorm_bwd_fused_launch<__nv_bfloat16, __nv_bfloat16>(dy, x, w, mean, rstd, dx, pw, pb, rows, cols, dt_stat, threads, vpt, grid, st);
+        break;
+      default:
+        if (wf32) layernorm_bwd_fused_launch<__half, float>(dy, x, w, mean, rstd, dx, pw, pb, rows, cols, dt_stat, threads, vpt, grid, st);
+        else layernorm_bwd_fused_launch<__half, __half>(dy, x, w, mean, rstd, dx, pw, pb, rows, cols, dt_stat, threads, vpt, grid, st);
+        break;
+    }
+  } else {
+    if (dx) {
+      const int64_t g = rows < 8LL * kNumSMs ? rows : 8LL * kNumSMs;
+      layernorm_bwd_dx_lines<<<static_cast<int>(g), 256, 0, st>>>(dy, x, w, mean, rstd, dx, rows, cols, dt, dt_wb, dt_stat);
+    }
+    if (need_wb) {
+      parts = parts_max < 64 ? parts_max : 64;
+      const int64_t rows_per = (rows + parts - 1) / parts;
+      parts = (rows + rows_per - 1) / rows_per;
+      const int64_t gx = (cols + 255) / 256;
+      if (gx > 0x7fffffffLL) return B200_EINVAL;
+      layernorm_bwd_wb_lines<<<dim3(static_cast<unsigned>(gx), static_cast<unsigned>(parts)), 256, 0, st>>>(dy, x, mean, rstd, pw, pb, rows, cols, rows_per, dt, dt_stat);
+    }
+  }
+  if (need_wb) layernorm_bwd_finalize<<<grid_for(cols, 32), 1024, 0, st>>>(pw, pb, dw, db, parts, cols, dt_wb);
+  return check_launch(need_wb ? 2 : 1);
 }
 
 // ------------------------------------------------------------------ sum without any allocation

@@ -178,6 +178,18 @@ int b200_layer_norm(const void* x, const void* weight, const void* bias, void* y
                     void* rstd, int64_t rows, int64_t cols, double eps, int dtype,
                     int dtype_wb, int dtype_stat, void* stream);
 
+/* aten.native_layer_norm_backward.default(grad_out, input, normalized_shape, mean, rstd,
+ * weight, bias, output_mask) -- the backward neighbour at BackendBench/backends/flag_gems.py:140.
+ * With xhat = (x - mean) * rstd and gy = dy * weight per row:
+ *   dx = rstd * (gy - mean_j(gy) - xhat * mean_j(gy * xhat)); dw = sum_rows dy * xhat; db = sum_rows dy.
+ * dx / dw / db may each be NULL (output_mask); weight may be NULL. dw / db need
+ * b200_layer_norm_backward_scratch_bytes(rows, cols) bytes of scratch (per-CTA partials). */
+int64_t b200_layer_norm_backward_scratch_bytes(int64_t rows, int64_t cols);
+int b200_layer_norm_backward(const void* dy, const void* x, const void* mean, const void* rstd,
+                             const void* weight, void* dx, void* dw, void* db, int64_t rows,
+                             int64_t cols, int dtype, int dtype_wb, int dtype_stat, void* scratch,
+                             int64_t scratch_bytes, void* stream);
+
 /* aten.argmax.default(self, dim, keepdim): int64 index of the first maximum along
  * `dim`, NaN counts as the maximum (eval.py:100-102). dim must be > 0. */
 int b200_argmax(const void* x, int64_t* out, int64_t outer, int64_t dim, int64_t inner,

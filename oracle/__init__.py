@@ -211,6 +211,24 @@ def layer_norm(x, normalized_shape, weight=None, bias=None, eps=1e-5, stat_dtype
     return narrow(y, x.dtype).reshape(x.shape), narrow(mean, stat_dtype).reshape(stat_shape), narrow(rstd, stat_dtype).reshape(stat_shape)
 
 
+def layer_norm_backward(grad_out, input, normalized_shape, mean, rstd, weight, bias, output_mask):
+    cols = _prod(normalized_shape)
+    rows = input.numel() // max(cols, 1)
+    dy, x = widen(grad_out), widen(input)
+    mu, rs = widen(mean).reshape(-1), widen(rstd).reshape(-1)
+    w = widen(weight) if weight is not None else None
+    dx = np.empty_like(x) if output_mask[0] else None
+    dw = np.empty(cols, dtype=np.float32) if output_mask[1] else None
+    db = np.empty(cols, dtype=np.float32) if output_mask[2] else None
+    if cols:
+        lib().oracle_layer_norm_backward(_ptr(dy), _ptr(x), _ptr(mu), _ptr(rs), _ptr(w) if w is not None else None, _ptr(dx) if dx is not None else None,
+                                         _ptr(dw) if dw is not None else None, _ptr(db) if db is not None else None, c_int64(rows), c_int64(cols))
+    wb_dtype = weight.dtype if weight is not None else input.dtype
+    return (narrow(dx, input.dtype).reshape(input.shape) if dx is not None else None,
+            narrow(dw, wb_dtype).reshape(list(normalized_shape)) if dw is not None else None,
+            narrow(db, wb_dtype).reshape(list(normalized_shape)) if db is not None else None)
+
+
 def argmax(x, dim=None, keepdim=False):
     a = widen(x)
     if dim is None:
@@ -323,6 +341,7 @@ ORACLE = {
     "_log_softmax_backward_data.default": log_softmax_backward,
     "sum.dim_IntList": sum_dims,
     "native_layer_norm.default": layer_norm,
+    "native_layer_norm_backward.default": layer_norm_backward,
     "argmax.default": argmax,
     "embedding.default": embedding,
     "index_select.default": index_select,

@@ -164,6 +164,36 @@ void oracle_layer_norm(const float* x, const float* w, const float* b, float* y,
   }
 }
 
+/* aten.native_layer_norm_backward.default (grad_out, input, normalized_shape, mean, rstd,
+ * weight, bias, output_mask) -- BackendBench/backends/flag_gems.py:140; evaluated through
+ * eval.py:100. w may be NULL; dx / dw / db may be NULL (masked outputs). */
+void oracle_layer_norm_backward(const float* dy, const float* x, const float* mean, const float* rstd, const float* w, float* dx, float* dw, float* db, int64_t rows, int64_t cols) {
+  if (dw) for (int64_t c = 0; c < cols; ++c) dw[c] = 0.f;
+  if (db) for (int64_t c = 0; c < cols; ++c) db[c] = 0.f;
+  double* aw = dw ? (double*)calloc((size_t)(cols > 0 ? cols : 1), sizeof(double)) : NULL;
+  double* ab = db ? (double*)calloc((size_t)(cols > 0 ? cols : 1), sizeof(double)) : NULL;
+  for (int64_t r = 0; r < rows; ++r) {
+    const double mu = mean[r], rs = rstd[r];
+    double s1 = 0.0, s2 = 0.0;
+    for (int64_t c = 0; c < cols; ++c) {
+      const double g = dy[r * cols + c], xhat = ((double)x[r * cols + c] - mu) * rs, gy = g * (w ? (double)w[c] : 1.0);
+      s1 += gy;
+      s2 += gy * xhat;
+      if (aw) aw[c] += g * xhat;
+      if (ab) ab[c] += g;
+    }
+    if (dx) {
+      const double c1 = s1 / (double)cols, c2 = s2 / (double)cols;
+      for (int64_t c = 0; c < cols; ++c) {
+        const double xhat = ((double)x[r * cols + c] - mu) * rs, gy = (double)dy[r * cols + c] * (w ? (double)w[c] : 1.0);
+        dx[r * cols + c] = (float)(rs * (gy - c1 - xhat * c2));
+      }
+    }
+  }
+  if (aw) { for (int64_t c = 0; c < cols; ++c) dw[c] = (float)aw[c]; free(aw); }
+  if (ab) { for (int64_t c = 0; c < cols; ++c) db[c] = (float)ab[c]; free(ab); }
+}
+
 /* aten.argmax.default along `dim` of [outer, dim, inner]: first index of the maximum,
  * NaN counts as the maximum (the first NaN wins). eval.py:100. */
 void oracle_argmax(const float* x, int64_t* out, int64_t outer, int64_t dim, int64_t inner) {

@@ -46,6 +46,11 @@ def tolerance_for_case(op: str, dtype) -> tuple:
     normalisations and contractions (accumulation order differs)."""
     if op in EXACT_OPS:
         return 0.0, 0.0
+    if op == "native_layer_norm_backward.default" and dtype in (torch.bfloat16, torch.float16):
+        # aten CPU, which made the golden vectors, adds the parameter gradients up in the
+        # 16-bit type: its running sums (magnitude ~16 over 37 rows) are rounded to 0.125, so
+        # an element that cancels to ~0 carries that much error; fp32 accumulation does not
+        return 0.25, 1e-2
     if dtype in (torch.bfloat16, torch.float16):
         return 1e-2, 1e-2
     if op.split(".")[0] in ("relu", "add", "mul"):
@@ -54,6 +59,8 @@ def tolerance_for_case(op: str, dtype) -> tuple:
 
 
 def first_dtype(x):
+    if x is None:
+        return None
     if isinstance(x, torch.Tensor):
         return x.dtype
     for y in x:

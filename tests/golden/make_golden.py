@@ -130,6 +130,19 @@ def tensor_cases():
     out.append(("_softmax_backward_data.default", [rn(9, 67), torch.softmax(x, -1), -1, f32], {}, "softmax_backward_ragged"))
     out.append(("_log_softmax_backward_data.default", [rn(9, 67), torch.log_softmax(x, -1), -1, f32], {}, "log_softmax_backward_ragged"))
     out.append(("_softmax_backward_data.default", [torch.empty(0, 7), torch.empty(0, 7), 1, f32], {}, "softmax_backward_empty"))
+    for dt in (f32, bf, hf):
+        x, w, b = rn(37, 96, dtype=dt), rn(96, dtype=dt), rn(96, dtype=dt)
+        _, mean, rstd = torch.ops.aten.native_layer_norm.default(x, [96], w, b, 1e-5)
+        out.append(("native_layer_norm_backward.default", [rn(37, 96, dtype=dt), x, [96], mean, rstd, w, b, [True, True, True]], {}, f"layer_norm_backward_{dt}"))
+    x, w = rn(5, 6, 33), rn(33)
+    _, mean, rstd = torch.ops.aten.native_layer_norm.default(x, [33], w, None, 1e-5)
+    out.append(("native_layer_norm_backward.default", [rn(5, 6, 33), x, [33], mean, rstd, w, None, [True, True, False]], {}, "layer_norm_backward_ragged_no_bias"))
+    x = rn(4, 3, 8, 5)
+    _, mean, rstd = torch.ops.aten.native_layer_norm.default(x, [8, 5], None, None, 1e-5)
+    out.append(("native_layer_norm_backward.default", [rn(4, 3, 8, 5), x, [8, 5], mean, rstd, None, None, [True, False, False]], {}, "layer_norm_backward_two_dims_no_affine"))
+    x, w, b = rn(9, 64), rn(64), rn(64)
+    _, mean, rstd = torch.ops.aten.native_layer_norm.default(x, [64], w, b, 1e-5)
+    out.append(("native_layer_norm_backward.default", [rn(9, 64), x, [64], mean, rstd, w, b, [False, True, True]], {}, "layer_norm_backward_parameters_only"))
     return out
 
 

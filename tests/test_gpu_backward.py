@@ -83,6 +83,70 @@ def test_float_gradients_for_a_half_input(backend):
                 assert ok and got.dtype == dt, (spec, shape, dt, ea, er)
 
 
+LNB = "native_layer_norm_backward.default"
+
+
+def _check_tuple(want, got, atol, rtol, tag):
+    assert len(want) == len(got), tag
+    for i, (w_, g_) in enumerate(zip(want, got)):
+        if w_ is None or g_ is None:
+            assert w_ is None and g_ is None, (tag, i)
+            continue
+        assert w_.shape == g_.shape and w_.dtype == g_.dtype, (tag, i, w_.shape, g_.shape, w_.dtype, g_.dtype)
+        ok, ea, er = compare(w_, g_, atol, rtol)
+        assert ok, (tag, i, ea, er)
+
+
+@pytest.mark.parametrize("name", ["layer_norm_backward_bf16_8192x4096", "layer_norm_backward_f32_65536x1024"])
+def test_full_size_layer_norm_backward(backend, name):
+    c = named_case(name)
+    op = get_operator(c.op)
+    args, kwargs = c.build(DEV)
+    got = backend[op](*args, **kwargs)
+    want = op(*args, **kwargs)
+    # dx to the dtype's tolerance; dw / db are sums over thousands of rows: compare at the size of those sums
+    atol, rtol = _tol(got[0].dtype)
+    _check_tuple(want[:1], got[:1], atol, rtol, name)
+    scale = float(want[1].float().abs().max())
+    _check_tuple(want[1:], got[1:], max(atol, 2e-3 * scale), 1e-2 if got[0].dtype != torch.float32 else 1e-3, name)
+    head = [a[:64].cpu() if isinstance(a, torch.Tensor) and a.dim() == 2 and a.shape[0] == args[0].shape[0] else (a.cpu() if isinstance(a, torch.Tensor) else a) for a in args]
+    head[-1] = [True, False, False]
+    _check_tuple(oracle.run(c.op, head, {})[:1], (got[0][:64].cpu(),), atol, rtol, name + "/oracle")
+    ops.check_device_status()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_layer_norm_backward_geometries_and_masks(backend, dtype):
+    g = torch.Generator(device=DEV).manual_seed(9)
+    atol, rtol = (3e-2, 2e-2) if dtype != torch.float32 else (1e-4, 1e-4)
+    op = get_operator(LNB)
+    for shape, nd in [((300, 67), 1), ((5, 40, 1000), 1), ((6, 8, 5), 2), ((64, 8200), 1), ((3, 16384), 1), ((1, 96), 1), ((2000, 17), 1)]:
+        x = torch.randn(shape, device=DEV, generator=g).to(dtype)
+        dy = torch.randn(shape, device=DEV, generator=g).to(dtype)
+        ns = list(shape[-nd:])
+        w, b = torch.randn(ns, device=DEV, generator=g).to(dtype), torch.randn(ns, device=DEV, generator=g).to(dtype)
+        _, mean, rstd = torch.ops.aten.native_layer_norm.default(x, ns, w, b, 1e-5)
+        for weight, bias, mask in [(w, b, [True, True, True]), (w, None, [True, True, False]), (None, None, [True, False, False]), (w, b, [False, True, True]), (w, b, [True, False, False])]:
+            want = op(dy, x, ns, mean, rstd, weight, bias, mask)
+            got = backend[op](dy, x, ns, mean, rstd, weight, bias, mask)
+            rows = x.numel() // max(1, int(torch.tensor(ns).prod()))
+            _check_tuple(want[:1], got[:1], atol, rtol, (shape, mask))
+            _check_tuple(want[1:], got[1:], atol * max(1.0, rows**0.5), rtol, (shape, mask))
+    # fp32 parameters with 16-bit activations (autocast-style)
+    if dtype != torch.float32:
+        x = torch.randn(128, 512, device=DEV, generator=g).to(dtype)
+        dy = torch.randn(128, 512, device=DEV, generator=g).to(dtype)
+        w32 = torch.randn(512, device=DEV, generator=g)
+        xf = x.float()
+        mean, rstd = xf.mean(-1, keepdim=True), torch.rsqrt(xf.var(-1, unbiased=False, keepdim=True) + 1e-5)
+        got = backend[op](dy, x, [512], mean, rstd, w32, w32, [True, True, True])
+        xhat = (xf - mean) * rstd
+        gy = dy.float() * w32
+        dx = rstd * (gy - gy.mean(-1, keepdim=True) - xhat * (gy * xhat).mean(-1, keepdim=True))
+        _check_tuple((dx.to(dtype), (dy.float() * xhat).sum(0), dy.float().sum(0)), got, 3e-2, 2e-2, "fp32 params")
+    ops.check_device_status()
+
+
 def test_autograd_through_registered_overrides():
     """With the kernels registered through torch.library, a softmax forward + backward of an
     ordinary autograd graph runs on them and matches aten."""
@@ -99,3 +163,16 @@ def test_autograd_through_registered_overrides():
     finally:
         bb.disable()
     torch.testing.assert_close(x.grad, want, rtol=1e-5, atol=1e-6)
+    # layer norm forward + backward, parameters included
+    ln = torch.nn.LayerNorm(512).to(DEV)
+    x.grad = None
+    (ln(x) * w).sum().backward()
+    want = [x.grad.clone(), ln.weight.grad.clone(), ln.bias.grad.clone()]
+    x.grad = ln.weight.grad = ln.bias.grad = None
+    bb.enable()
+    try:
+        (ln(x) * w).sum().backward()
+    finally:
+        bb.disable()
+    for got_t, want_t in zip([x.grad, ln.weight.grad, ln.bias.grad], want):
+        torch.testing.assert_close(got_t, want_t, rtol=1e-4, atol=1e-4)

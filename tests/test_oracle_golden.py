@@ -31,6 +31,9 @@ def test_oracle_matches_golden(golden_cases):
             got = (got[0], got[1].to(ref[1].dtype), got[2].to(ref[2].dtype))
         atol, rtol = tolerance_for_case(c["op"], first_dtype(ref))
         for r, g in zip(_as_tuple(ref), _as_tuple(got)):
+            if r is None or g is None:  # an output masked out (native_layer_norm_backward's output_mask)
+                assert r is None and g is None, c["tag"]
+                continue
             assert r.shape == g.shape and r.dtype == g.dtype, (c["tag"], r.shape, g.shape, r.dtype, g.dtype)
             if c["op"] in EXACT_OPS:
                 if not bits_equal(r, g):
