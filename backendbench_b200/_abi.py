@@ -68,6 +68,8 @@ SIGNATURES = {
     "b200_gather": (c_int, [c_void_p, c_void_p, c_void_p, c_int, I64P, I64P, I64P, c_int64, c_int, c_int, c_void_p, c_void_p]),
     "b200_scatter_add_scratch_bytes": (c_int64, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, I64P, I64P, I64P, I64P, c_int, c_int]),
     "b200_scatter_add": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, I64P, I64P, I64P, I64P, c_int, c_int, c_void_p, c_int64, c_void_p, c_void_p]),
+    "b200_embedding_backward_scratch_bytes": (c_int64, [c_int64, c_int64]),
+    "b200_embedding_backward": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_int64, c_void_p, c_void_p]),
     "b200_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p] + [c_int64] * 12 + [c_double, c_double, c_int, c_void_p, c_void_p]),
     "b200_gemm_uses_tensor_cores": (c_int, [c_int64] * 10 + [c_int, c_void_p, c_void_p, c_void_p]),
     "b200_gemm_f32_scratch_bytes": (c_int64, [c_int64, c_int64, c_int64, c_int64]),

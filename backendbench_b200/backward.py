@@ -1,10 +1,11 @@
 """Backward neighbours of the row operators.
 
-BackendBench/backends/flag_gems.py:140,196,233 lists `native_layer_norm_backward`,
+BackendBench/backends/flag_gems.py:113,140,196,233 lists `embedding_dense_backward`, `native_layer_norm_backward`,
 `_softmax_backward_data` and `_log_softmax_backward_data` beside the forward operators, and the reference's
 training demo (README.md:40-42) needs them for a model to stay on one backend through a
 backward pass. Same boundary as the forward operators: host wrapper here, kernels behind
-the C-ABI (`b200_softmax_backward`, `b200_layer_norm_backward`), no aten arithmetic.
+the C-ABI (`b200_softmax_backward`, `b200_layer_norm_backward`, `b200_embedding_backward`), no aten
+arithmetic.
 """
 
 from __future__ import annotations
@@ -88,9 +89,40 @@ def native_layer_norm_backward_default(grad_out, input, normalized_shape, mean, 
     return dx, dw, db
 
 
+def embedding_dense_backward_default(grad_output, indices, num_weights, padding_idx=-1, scale_grad_by_freq=False) -> torch.Tensor:
+    """aten.embedding_dense_backward.default -> [num_weights, D]: row v is the sum of the rows of
+    grad_output whose index is v (v != padding_idx), added in ascending position in fp32."""
+    ops._require_cuda(grad_output, indices)
+    if scale_grad_by_freq:
+        raise ops.UnsupportedByB200("embedding_dense_backward: scale_grad_by_freq")
+    if grad_output.dtype not in ops._FLOATS:
+        raise ops.UnsupportedByB200(f"embedding_dense_backward: dtype {grad_output.dtype}")
+    if indices.dtype not in (torch.int64, torch.int32):
+        raise RuntimeError(f"Expected tensor for argument 'indices' to have scalar type Long or Int, but got {indices.dtype}")
+    if grad_output.dim() < 1 or list(grad_output.shape[:-1]) != list(indices.shape):
+        raise RuntimeError(f"embedding_dense_backward: grad_output {list(grad_output.shape)} is not indices {list(indices.shape)} + [D]")
+    num_weights = int(num_weights)
+    row_len = int(grad_output.shape[-1])
+    out = torch.empty((num_weights, row_len), dtype=grad_output.dtype, device=grad_output.device)
+    if out.numel():
+        g, idx = ops._contig(grad_output), ops._contig(indices)
+        n = idx.numel()
+        need = int(lib().b200_embedding_backward_scratch_bytes(n, num_weights))
+        scratch = ops._scratch(out.device, need)
+        check(
+            lib().b200_embedding_backward(
+                g.data_ptr(), idx.data_ptr(), out.data_ptr(), n, num_weights, row_len, int(padding_idx), ops._dt(g.dtype), ops._dt(idx.dtype), scratch.data_ptr(), need,
+                ops._status(out.device).data_ptr(), ops._stream_handle(),
+            ),
+            "b200_embedding_backward",
+        )
+    return out
+
+
 # op spec name -> host function, the same form as ops.OP_TABLE
 BACKWARD_TABLE = {
     "_softmax_backward_data.default": _softmax_backward_data_default,
     "_log_softmax_backward_data.default": _log_softmax_backward_data_default,
     "native_layer_norm_backward.default": native_layer_norm_backward_default,
+    "embedding_dense_backward.default": embedding_dense_backward_default,
 }

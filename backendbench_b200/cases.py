@@ -107,6 +107,10 @@ class CaseSpec:
             dim = self.param("dim", -1)
             y = torch.softmax(normal(shp).float(), dim) if op == "_softmax_backward_data.default" else torch.log_softmax(normal(shp).float(), dim)
             args = [normal(shp), y.to(dt), dim, dt]
+        elif op == "embedding_dense_backward.default":
+            rows, cols = shp  # the table whose gradient is produced
+            n_idx = int(self.param("n_idx", 16384))
+            args = [normal((n_idx, cols)), randint(rows, (n_idx,)), rows, -1, False]
         elif op == "native_layer_norm_backward.default":
             cols = shp[-1]
             x = normal(shp)
@@ -201,6 +205,9 @@ class CaseSpec:
         if op == "native_layer_norm_backward.default":
             rows = n // max(self.shape[-1], 1)
             return 3 * n * es + 3 * self.shape[-1] * es + 2 * rows * 4  # dy, x in, dx out; w in, dw, db out; fp32 mean / rstd in
+        if op == "embedding_dense_backward.default":
+            n_idx = int(self.param("n_idx", 16384))
+            return n * es + n_idx * self.shape[-1] * es + n_idx * 8  # the whole table gradient out, the gathered rows and the indices in
         if op == "sum.dim_IntList":
             dims = [d % len(self.shape) for d in self.param("dim", (-1,))]
             out = _prod(s for i, s in enumerate(self.shape) if i not in dims)
@@ -296,6 +303,7 @@ def neighbour_cases() -> List[CaseSpec]:
         for name, op in (("softmax_backward", "_softmax_backward_data.default"), ("log_softmax_backward", "_log_softmax_backward_data.default")):
             c.append(CaseSpec(1000 + len(c), op, dtype, shape, 0, (("dim", -1),), "", "reduce", f"{name}_{tag}"))
         c.append(CaseSpec(1000 + len(c), "native_layer_norm_backward.default", dtype, shape, 0, (), "", "reduce", f"layer_norm_backward_{tag}"))
+    c.append(CaseSpec(1000 + len(c), "embedding_dense_backward.default", "bf16", (128256, 4096), 0, (("n_idx", 16384),), "", "indexing", "embedding_backward_bf16_128256x4096_16384"))
     return c
 
 

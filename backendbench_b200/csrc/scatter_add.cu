@@ -765,6 +765,183 @@ static int launch_bucket(const void* self, const void* index, const void* src, v
   return check_launch(7);
 }
 
+// ------------------------------------------------------------------ embedding_dense_backward
+// out[v, :] = sum over the positions i with indices[i] == v (and v != padding_idx) of
+// grad[i, :], in ascending i, fp32 accumulation, one rounding: the bucket scheme above with
+// whole rows as the unit. count per destination row -> exclusive scan -> fill the row's
+// segment with its source positions (slot order arbitrary) -> replay. A row with at most 32
+// contributions is replayed by one warp, which ranks the positions with shuffles; a heavier
+// row by one CTA, which marks the positions in a shared-memory bitmap (a window of 2^18
+// positions at a time, with a summary word per 32 bitmap words) and walks the bitmap in
+// order -- ascending positions with no sort.
+constexpr int kEmbWindowBits = 1 << 18;
+constexpr int kEmbWindowWords = kEmbWindowBits / 32;
+
+__device__ __forceinline__ int64_t emb_index(const void* idx, int64_t i, int i32) { return i32 ? static_cast<const int32_t*>(idx)[i] : static_cast<const int64_t*>(idx)[i]; }
+
+__global__ void __launch_bounds__(256) emb_count(const void* __restrict__ idx, int i32, int64_t n, int64_t V, int64_t padding_idx, int* __restrict__ cnt, uint32_t* status) {
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t v = emb_index(idx, i, i32);
+    if (v == padding_idx) continue;
+    if (v < 0 || v >= V) { flag_oob(status); continue; }
+    atomicAdd(&cnt[v], 1);
+  }
+}
+__global__ void __launch_bounds__(256) emb_fill(const void* __restrict__ idx, int i32, int64_t n, int64_t V, int64_t padding_idx, int* __restrict__ cursor, int* __restrict__ seg_pos) {
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t v = emb_index(idx, i, i32);
+    if (v == padding_idx || v < 0 || v >= V) continue;
+    seg_pos[atomicAdd(&cursor[v], 1)] = static_cast<int>(i);
+  }
+}
+
+// acc[0..VE) += grad[pos, col .. col + VE) (VE = 16 bytes of T when `vec`, else 1)
+template <typename T, bool VEC>
+__device__ __forceinline__ void emb_add_row(float* acc, const T* __restrict__ grad, int64_t pos, int64_t D, int64_t col) {
+  if (VEC) {
+    float f[Vec<T>::N];
+    widen<T>(ld_stream(grad + pos * D + col), f);
+#pragma unroll
+    for (int e = 0; e < Vec<T>::N; ++e) acc[e] += f[e];
+  } else {
+    acc[0] += to_f32(grad[pos * D + col]);
+  }
+}
+template <typename T, bool VEC>
+__device__ __forceinline__ void emb_store(T* __restrict__ out, int64_t v, int64_t D, int64_t col, const float* acc) {
+  if (VEC) st_stream(out + v * D + col, narrow<T>(acc));
+  else out[v * D + col] = from_f32<T>(acc[0]);
+}
+
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(256) emb_replay(const T* __restrict__ grad, T* __restrict__ out, const int* __restrict__ offs, const int* __restrict__ grand_total, const int* __restrict__ seg_pos,
+                                                  int64_t V, int64_t D, int* __restrict__ heavy_count, int* __restrict__ heavy_list) {
+  constexpr int VE = VEC ? Vec<T>::N : 1;
+  __shared__ int sorted[8][32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t units = D / VE;
+  for (int64_t v = static_cast<int64_t>(blockIdx.x) * 8 + warp; v < V; v += static_cast<int64_t>(gridDim.x) * 8) {
+    const int b = offs[v], e = v + 1 < V ? offs[v + 1] : *grand_total;
+    const int c = e - b;
+    if (c > 32) {
+      if (lane == 0) heavy_list[atomicAdd(heavy_count, 1)] = static_cast<int>(v);
+      continue;
+    }
+    // rank of this lane's position among the row's positions (all distinct)
+    const int p = lane < c ? seg_pos[b + lane] : 0x7fffffff;
+    int rank = 0;
+#pragma unroll
+    for (int k = 0; k < 32; ++k) rank += __shfl_sync(0xffffffffu, p, k) < p ? 1 : 0;
+    __syncwarp();
+    if (lane < c) sorted[warp][rank] = p;
+    __syncwarp();
+    for (int64_t u = lane; u < units; u += 32) {
+      float acc[VE];
+#pragma unroll
+      for (int q = 0; q < VE; ++q) acc[q] = 0.f;
+      for (int k = 0; k < c; ++k) emb_add_row<T, VEC>(acc, grad, sorted[warp][k], D, u * VE);
+      emb_store<T, VEC>(out, v, D, u * VE, acc);
+    }
+  }
+}
+
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(256) emb_replay_heavy(const T* __restrict__ grad, T* __restrict__ out, const int* __restrict__ offs, const int* __restrict__ grand_total,
+                                                        const int* __restrict__ seg_pos, int64_t V, int64_t D, int64_t n, const int* __restrict__ heavy_count, const int* __restrict__ heavy_list) {
+  constexpr int VE = VEC ? Vec<T>::N : 1;
+  __shared__ uint32_t bitmap[kEmbWindowWords];
+  __shared__ uint32_t summary[kEmbWindowWords / 32];
+  const int64_t units = D / VE;
+  for (int h = blockIdx.x; h < *heavy_count; h += gridDim.x) {
+    const int64_t v = heavy_list[h];
+    const int b = offs[v], e = v + 1 < V ? offs[v + 1] : *grand_total;
+    // the row's columns are taken blockDim.x vectors at a time; every pass walks all windows
+    for (int64_t u0 = 0; u0 < units; u0 += blockDim.x) {
+      const int64_t u = u0 + threadIdx.x;
+      float acc[VE];
+#pragma unroll
+      for (int q = 0; q < VE; ++q) acc[q] = 0.f;
+      for (int64_t w0 = 0; w0 < n; w0 += kEmbWindowBits) {
+        __syncthreads();  // the bitmap of the window before has been read by everyone
+        for (int i = threadIdx.x; i < kEmbWindowWords; i += blockDim.x) bitmap[i] = 0u;
+        for (int i = threadIdx.x; i < kEmbWindowWords / 32; i += blockDim.x) summary[i] = 0u;
+        __syncthreads();
+        for (int j = b + threadIdx.x; j < e; j += blockDim.x) {
+          const int64_t rel = static_cast<int64_t>(seg_pos[j]) - w0;
+          if (rel >= 0 && rel < kEmbWindowBits) {
+            atomicOr(&bitmap[rel >> 5], 1u << (rel & 31));
+            atomicOr(&summary[rel >> 10], 1u << ((rel >> 5) & 31));
+          }
+        }
+        __syncthreads();
+        if (u < units) {
+          for (int sw = 0; sw < kEmbWindowWords / 32; ++sw) {
+            uint32_t words = summary[sw];
+            while (words) {
+              const int wi = sw * 32 + __ffs(words) - 1;
+              words &= words - 1;
+              uint32_t bits = bitmap[wi];
+              while (bits) {
+                const int64_t pos = w0 + wi * 32 + __ffs(bits) - 1;
+                bits &= bits - 1;
+                emb_add_row<T, VEC>(acc, grad, pos, D, u * VE);
+              }
+            }
+          }
+        }
+      }
+      if (u < units) emb_store<T, VEC>(out, v, D, u * VE, acc);
+    }
+  }
+}
+
+struct EmbScratch {
+  int64_t offs_bytes, cursor_bytes, pos_bytes, totals_bytes, heavy_bytes, total;
+};
+static EmbScratch emb_scratch(int64_t V, int64_t n) {
+  auto up = [](int64_t b) { return (b + 255) / 256 * 256; };
+  EmbScratch s;
+  s.offs_bytes = up(4 * (V + 1));
+  s.cursor_bytes = up(4 * V);
+  s.pos_bytes = up(4 * n);
+  s.totals_bytes = up(4 * ((V + kScanTile - 1) / kScanTile + 2));
+  s.heavy_bytes = up(4 * (n / 33 + 4));
+  s.total = s.offs_bytes + s.cursor_bytes + s.pos_bytes + s.totals_bytes + s.heavy_bytes;
+  return s;
+}
+
+template <typename T>
+static int launch_embedding_backward(const void* grad, const void* idx, void* out, int64_t n, int64_t V, int64_t D, int64_t padding_idx, int i32, void* scratch, uint32_t* status, cudaStream_t st) {
+  const EmbScratch S = emb_scratch(V, n);
+  char* base = static_cast<char*>(scratch);
+  int* offs = reinterpret_cast<int*>(base);
+  int* cursor = reinterpret_cast<int*>(base + S.offs_bytes);
+  int* seg_pos = reinterpret_cast<int*>(base + S.offs_bytes + S.cursor_bytes);
+  int* totals = reinterpret_cast<int*>(base + S.offs_bytes + S.cursor_bytes + S.pos_bytes);
+  int* heavy = reinterpret_cast<int*>(base + S.offs_bytes + S.cursor_bytes + S.pos_bytes + S.totals_bytes);  // [0] count, [1] grand total, [4..] list
+  cudaError_t e = cudaMemsetAsync(offs, 0, static_cast<size_t>(S.offs_bytes), st);
+  if (e == cudaSuccess) e = cudaMemsetAsync(heavy, 0, 16, st);
+  if (e != cudaSuccess) { set_last_cuda_error(e); return B200_ELAUNCH; }
+  auto grid = [](int64_t items, int per) { int64_t g = (items + per - 1) / per; const int64_t cap = 32LL * kNumSMs; return static_cast<int>(g < 1 ? 1 : (g > cap ? cap : g)); };
+  const int64_t ntiles = (V + kScanTile - 1) / kScanTile;
+  emb_count<<<grid(n, 256), 256, 0, st>>>(idx, i32, n, V, padding_idx, offs, status);
+  scan_tile_totals<<<static_cast<unsigned>(ntiles), kScanBlock, 0, st>>>(offs, totals, V);
+  scan_totals<<<1, 1024, 0, st>>>(totals, ntiles, heavy + 1);
+  scan_apply<<<static_cast<unsigned>(ntiles), kScanBlock, 0, st>>>(offs, cursor, totals, V);
+  emb_fill<<<grid(n, 256), 256, 0, st>>>(idx, i32, n, V, padding_idx, cursor, seg_pos);
+  const T* g = static_cast<const T*>(grad);
+  T* o = static_cast<T*>(out);
+  const bool vec = (D * static_cast<int64_t>(sizeof(T))) % 16 == 0 && aligned16(grad) && aligned16(out);
+  if (vec) {
+    emb_replay<T, true><<<grid(V, 8), 256, 0, st>>>(g, o, offs, heavy + 1, seg_pos, V, D, heavy, heavy + 4);
+    emb_replay_heavy<T, true><<<2 * kNumSMs, 256, 0, st>>>(g, o, offs, heavy + 1, seg_pos, V, D, n, heavy, heavy + 4);
+  } else {
+    emb_replay<T, false><<<grid(V, 8), 256, 0, st>>>(g, o, offs, heavy + 1, seg_pos, V, D, heavy, heavy + 4);
+    emb_replay_heavy<T, false><<<2 * kNumSMs, 256, 0, st>>>(g, o, offs, heavy + 1, seg_pos, V, D, n, heavy, heavy + 4);
+  }
+  return check_launch(7);
+}
+
 template <typename T>
 static int launch_strip(const void* self, const void* index, const void* src, void* out, StripArgs A, uint32_t* status, cudaStream_t st) {
   const int tile_bytes = kTileRows * kStripCols * (8 + static_cast<int>(sizeof(T)));
@@ -1003,4 +1180,27 @@ extern "C" int b200_scatter_add(const void* self, const void* index, const void*
     return b200_copy_strided(acc, out, 1, &n_self, &one, B200_F32, dtype, stream);
   }
   return B200_OK;
+}
+
+extern "C" int64_t b200_embedding_backward_scratch_bytes(int64_t n_indices, int64_t num_weights) {
+  if (n_indices < 0 || num_weights <= 0) return 0;
+  return emb_scratch(num_weights, n_indices).total;
+}
+
+extern "C" int b200_embedding_backward(const void* grad, const void* indices, void* out, int64_t n_indices, int64_t num_weights, int64_t row_len, int64_t padding_idx, int dtype, int idx_dtype,
+                                       void* scratch, int64_t scratch_bytes, uint32_t* status, void* stream) {
+  if (n_indices < 0 || num_weights < 0 || row_len < 0) return B200_EINVAL;
+  if (!is_float_dtype(dtype)) return B200_EDTYPE;
+  if (idx_dtype != B200_I32 && idx_dtype != B200_I64) return B200_EDTYPE;
+  if (num_weights == 0 || row_len == 0) return B200_OK;
+  if (!out || (n_indices > 0 && (!grad || !indices))) return B200_EINVAL;
+  if (n_indices >= 0x7fffffffLL || num_weights >= 0x7fffffffLL) return B200_EINVAL;
+  if (!scratch || scratch_bytes < b200_embedding_backward_scratch_bytes(n_indices, num_weights)) return B200_ESCRATCH;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int i32 = idx_dtype == B200_I32;
+  switch (dtype) {
+    case B200_F32: return launch_embedding_backward<float>(grad, indices, out, n_indices, num_weights, row_len, padding_idx, i32, scratch, status, st);
+    case B200_BF16: return launch_embedding_backward<__nv_bfloat16>(grad, indices, out, n_indices, num_weights, row_len, padding_idx, i32, scratch, status, st);
+    default: return launch_embedding_backward<__half>(grad, indices, out, n_indices, num_weights, row_len, padding_idx, i32, scratch, status, st);
+  }
 }

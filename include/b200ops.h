@@ -235,6 +235,17 @@ int b200_scatter_add(const void* self, const void* index, const void* src, void*
                      int dtype, void* scratch, int64_t scratch_bytes, uint32_t* status,
                      void* stream);
 
+/* aten.embedding_dense_backward.default(grad_output, indices, num_weights, padding_idx,
+ * scale_grad_by_freq = false) -- the backward neighbour at BackendBench/backends/flag_gems.py:113:
+ * out[v, :] = sum of grad[i, :] over the positions i with indices[i] == v, v != padding_idx,
+ * added in ascending i in fp32 and rounded once (reproducible: no floating-point atomics).
+ * grad is [n_indices, row_len], out [num_weights, row_len], both contiguous. */
+int64_t b200_embedding_backward_scratch_bytes(int64_t n_indices, int64_t num_weights);
+int b200_embedding_backward(const void* grad, const void* indices, void* out, int64_t n_indices,
+                            int64_t num_weights, int64_t row_len, int64_t padding_idx, int dtype,
+                            int idx_dtype, void* scratch, int64_t scratch_bytes, uint32_t* status,
+                            void* stream);
+
 /* ------------------------------------------------------------------ contraction
  * aten.mm.default, aten.addmm.default, aten.bmm.default (eval.py:100-102):
  *   C[b] = alpha * A[b] @ B[b] + beta * bias      (fp32 accumulate, one rounding)

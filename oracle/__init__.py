@@ -211,6 +211,21 @@ def layer_norm(x, normalized_shape, weight=None, bias=None, eps=1e-5, stat_dtype
     return narrow(y, x.dtype).reshape(x.shape), narrow(mean, stat_dtype).reshape(stat_shape), narrow(rstd, stat_dtype).reshape(stat_shape)
 
 
+def embedding_backward(grad_output, indices, num_weights, padding_idx=-1, scale_grad_by_freq=False):
+    if scale_grad_by_freq:
+        raise NotImplementedError("scale_grad_by_freq")
+    row_len = grad_output.shape[-1] if grad_output.dim() else 1
+    g = widen(grad_output).reshape(-1, row_len) if grad_output.numel() else np.zeros((0, row_len), dtype=np.float32)
+    idx = np.ascontiguousarray(indices.reshape(-1).to(torch.int64).numpy())
+    out = np.zeros((num_weights, row_len), dtype=np.float32)
+    if out.size:
+        lib().oracle_embedding_backward.restype = c_int64
+        bad = lib().oracle_embedding_backward(_ptr(np.ascontiguousarray(g)), _ptr(idx), _ptr(out), c_int64(idx.size), c_int64(num_weights), c_int64(row_len), c_int64(padding_idx))
+        if bad:
+            raise IndexError("index out of range in embedding_dense_backward")
+    return narrow(out, grad_output.dtype)
+
+
 def layer_norm_backward(grad_out, input, normalized_shape, mean, rstd, weight, bias, output_mask):
     cols = _prod(normalized_shape)
     rows = input.numel() // max(cols, 1)
@@ -342,6 +357,7 @@ ORACLE = {
     "sum.dim_IntList": sum_dims,
     "native_layer_norm.default": layer_norm,
     "native_layer_norm_backward.default": layer_norm_backward,
+    "embedding_dense_backward.default": embedding_backward,
     "argmax.default": argmax,
     "embedding.default": embedding,
     "index_select.default": index_select,

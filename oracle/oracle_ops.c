@@ -164,6 +164,22 @@ void oracle_layer_norm(const float* x, const float* w, const float* b, float* y,
   }
 }
 
+/* aten.embedding_dense_backward.default (grad_output, indices, num_weights, padding_idx,
+ * scale_grad_by_freq = false) -- BackendBench/backends/flag_gems.py:113; evaluated through
+ * eval.py:100. Rows are added in ascending position, fp32 accumulation (the caller rounds
+ * once). Returns the number of out-of-range indices (skipped). */
+int64_t oracle_embedding_backward(const float* grad, const int64_t* idx, float* out, int64_t n, int64_t num_weights, int64_t row_len, int64_t padding_idx) {
+  int64_t bad = 0;
+  for (int64_t k = 0; k < num_weights * row_len; ++k) out[k] = 0.f;
+  for (int64_t i = 0; i < n; ++i) {
+    const int64_t v = idx[i];
+    if (v == padding_idx) continue;
+    if (v < 0 || v >= num_weights) { ++bad; continue; }
+    for (int64_t c = 0; c < row_len; ++c) out[v * row_len + c] += grad[i * row_len + c];
+  }
+  return bad;
+}
+
 /* aten.native_layer_norm_backward.default (grad_out, input, normalized_shape, mean, rstd,
  * weight, bias, output_mask) -- BackendBench/backends/flag_gems.py:140; evaluated through
  * eval.py:100. w may be NULL; dx / dw / db may be NULL (masked outputs). */

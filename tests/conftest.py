@@ -51,6 +51,10 @@ def tolerance_for_case(op: str, dtype) -> tuple:
         # 16-bit type: its running sums (magnitude ~16 over 37 rows) are rounded to 0.125, so
         # an element that cancels to ~0 carries that much error; fp32 accumulation does not
         return 0.25, 1e-2
+    if op == "embedding_dense_backward.default" and dtype in (torch.bfloat16, torch.float16):
+        # same story: aten CPU rounds to the 16-bit type after every added row (sums of ~5
+        # rows reach magnitude 4-8, where a bf16 step is 0.03-0.06)
+        return 0.07, 1e-2
     if dtype in (torch.bfloat16, torch.float16):
         return 1e-2, 1e-2
     if op.split(".")[0] in ("relu", "add", "mul"):

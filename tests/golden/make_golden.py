@@ -143,6 +143,11 @@ def tensor_cases():
     x, w, b = rn(9, 64), rn(64), rn(64)
     _, mean, rstd = torch.ops.aten.native_layer_norm.default(x, [64], w, b, 1e-5)
     out.append(("native_layer_norm_backward.default", [rn(9, 64), x, [64], mean, rstd, w, b, [False, True, True]], {}, "layer_norm_backward_parameters_only"))
+    for dt in (f32, bf, hf):
+        out.append(("embedding_dense_backward.default", [rn(50, 24, dtype=dt), ri(11, 50), 11, -1, False], {}, f"embedding_backward_{dt}"))
+    out.append(("embedding_dense_backward.default", [rn(4, 9, 10), ri(7, 4, 9, dtype=torch.int32), 7, 3, False], {}, "embedding_backward_2d_int32_padding_idx"))
+    out.append(("embedding_dense_backward.default", [rn(300, 6), ri(2, 300), 5, -1, False], {}, "embedding_backward_two_hot_rows"))
+    out.append(("embedding_dense_backward.default", [torch.empty(0, 8), ri(4, 0), 4, -1, False], {}, "embedding_backward_no_indices"))
     return out
 
 

@@ -147,6 +147,51 @@ def test_layer_norm_backward_geometries_and_masks(backend, dtype):
     ops.check_device_status()
 
 
+EMB = "embedding_dense_backward.default"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_embedding_backward_matches_oracle_bit_for_bit_and_aten_closely(backend, dtype):
+    """Rows are added in ascending position in fp32 and rounded once: the CPU oracle does the
+    same, so results agree bit for bit (and run to run); aten CUDA agrees to tolerance."""
+    g = torch.Generator().manual_seed(10)
+    op = get_operator(EMB)
+    impl = backend[op]
+    for n_shape, V, D, hot in [((500,), 97, 64, None), ((40, 50), 300, 257, None), ((5000,), 50, 96, 3), ((70000,), 8, 40, 2), ((3,), 1000, 8, None), ((0,), 10, 16, None)]:
+        idx = torch.randint(0, V, n_shape, generator=g)
+        if hot is not None:  # most positions on a few rows: the many-contributions path
+            idx[torch.rand(n_shape, generator=g) < 0.9] = hot
+        grad = torch.randn(n_shape + (D,), generator=g).to(dtype)
+        pad = 1 if V > 1 else -1
+        got = impl(grad.to(DEV), idx.to(DEV), V, pad, False)
+        want = oracle.embedding_backward(grad, idx, V, pad, False)
+        from conftest import bits_equal
+
+        assert got.shape == (V, D) and got.dtype == dtype and bits_equal(want, got.cpu()), (n_shape, V, D)
+        assert bits_equal(got, impl(grad.to(DEV), idx.to(DEV).int(), V, pad, False))  # int32 indices, and reproducible
+        ref = op(grad.to(DEV), idx.to(DEV), V, pad, False)
+        contributions = max(1, idx.numel() // V if hot is None else idx.numel())
+        ok, ea, er = compare(ref, got, (2e-2 if dtype != torch.float32 else 1e-5) * contributions**0.5, 2e-2 if dtype != torch.float32 else 1e-4)
+        assert ok, (n_shape, V, D, ea, er)
+    ops.check_device_status()
+    idx = torch.tensor([1, 5, 99, 2], device=DEV)
+    impl(torch.randn(4, 8, device=DEV).to(dtype), idx, 10, -1, False)
+    with pytest.raises(IndexError):
+        ops.check_device_status()
+
+
+def test_full_size_embedding_backward(backend):
+    c = named_case("embedding_backward_bf16_128256x4096_16384")
+    op = get_operator(c.op)
+    args, kwargs = c.build(DEV)
+    got, want = backend[op](*args, **kwargs), op(*args, **kwargs)
+    ok, ea, er = compare(want, got, 2e-2, 2e-2)
+    assert ok and got.shape == want.shape and got.dtype == want.dtype, (ea, er)
+    touched = torch.zeros(128256, dtype=torch.bool, device=DEV)
+    touched[args[1]] = True
+    assert float(got[~touched].abs().max()) == 0.0  # rows nobody indexed are exactly zero
+
+
 def test_autograd_through_registered_overrides():
     """With the kernels registered through torch.library, a softmax forward + backward of an
     ordinary autograd graph runs on them and matches aten."""
@@ -176,3 +221,16 @@ def test_autograd_through_registered_overrides():
         bb.disable()
     for got_t, want_t in zip([x.grad, ln.weight.grad, ln.bias.grad], want):
         torch.testing.assert_close(got_t, want_t, rtol=1e-4, atol=1e-4)
+    # embedding forward + backward
+    emb = torch.nn.Embedding(1000, 64).to(DEV)
+    tok = torch.randint(0, 1000, (32, 50), device=DEV)
+    up = torch.randn(32, 50, 64, device=DEV)
+    (emb(tok) * up).sum().backward()
+    want_w = emb.weight.grad.clone()
+    emb.weight.grad = None
+    bb.enable()
+    try:
+        (emb(tok) * up).sum().backward()
+    finally:
+        bb.disable()
+    torch.testing.assert_close(emb.weight.grad, want_w, rtol=1e-5, atol=1e-5)

@@ -245,7 +245,7 @@ def test_b200_backend_loads_all_sixteen_overloads_and_their_variants():
 
     be = B200Backend()
     everything = {**OP_TABLE, **VARIANT_TABLE, **BACKWARD_TABLE}
-    assert be.name == "b200" and len(OP_TABLE) == 16 and len(be.compiled_kernels) == len(everything) == 40
+    assert be.name == "b200" and len(OP_TABLE) == 16 and len(be.compiled_kernels) == len(everything) == 41
     assert set(be.compiled_kernels) == {get_operator(spec) for spec in everything}
     assert get_operator("add_.Tensor") is torch.ops.aten.add_.Tensor and get_operator("sum.IntList_out") is torch.ops.aten.sum.IntList_out
     for spec in everything:
