@@ -1,12 +1,14 @@
 """Generate the golden fixtures in this folder by running the REFERENCE harness.
 
-    PYTHONPATH=/root/reference:. python tests/golden/make_golden.py
+    BACKENDBENCH_REFERENCE=<reference checkout> python tests/golden/make_golden.py
+
+(default: a `reference` folder beside the repository)
 
 Needs the reference checkout (meta-pytorch/BackendBench) importable as `BackendBench`;
 it is only available where the fixtures are made, which is why the outputs are
 committed: `aten_ops_golden.pt` and `harness_golden.json`.
 
-* aten_ops_golden.pt -- for each of the sixteen overloads a handful of small seeded
+* aten_ops_golden.pt -- for each of the sixteen overloads (and their backward neighbours) a handful of small seeded
   cases (inputs and the output of `AtenBackend()[op](*args, **kwargs)` on CPU, i.e. the
   `ref` of BackendBench/eval.py:100), each one passed through the reference's own
   `eval_correctness_test` with the identity backend to make sure the harness accepts it.
@@ -152,7 +154,8 @@ def tensor_cases():
 
 
 def main():
-    ref_root = os.environ.get("BACKENDBENCH_REFERENCE", "/root/reference")
+    repo_root = os.path.dirname(os.path.dirname(HERE))
+    ref_root = os.environ.get("BACKENDBENCH_REFERENCE", os.path.join(os.path.dirname(repo_root), "reference"))
     sys.path.insert(0, ref_root)
     import BackendBench  # noqa: F401  (the reference)
     from BackendBench import eval as ref_eval

@@ -9,7 +9,8 @@ import sys
 import pytest
 import torch
 
-REF = os.environ.get("BACKENDBENCH_REFERENCE", "/root/reference")
+# the reference checkout: named by the environment, else a `reference` folder beside this repository
+REF = os.environ.get("BACKENDBENCH_REFERENCE", os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference"))
 pytestmark = pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "BackendBench")), reason="reference checkout not present")
 
 
