@@ -129,6 +129,43 @@ template <> __device__ __forceinline__ uint4 narrow<__half>(const float* f) {
   return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
+// Mixed-precision add / subtract (sm_100a): one 16-bit operand widened inside the
+// instruction, so a packed row can feed fp32 arithmetic without a separate unpack. The
+// result is that of widening first (the conversion is exact). `w` holds two elements;
+// they are taken low half first, the order `widen` gives them.
+template <typename T> struct Mixed;
+template <> struct Mixed<__nv_bfloat16> {
+  static __device__ __forceinline__ void add2(float& s, uint32_t w) {
+    asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %1;\n\tadd.rn.f32.bf16 %0, lo, %0;\n\tadd.rn.f32.bf16 %0, hi, %0;\n\t}" : "+f"(s) : "r"(w));
+  }
+  static __device__ __forceinline__ void sub2(uint32_t w, float c, float& d0, float& d1) {
+    asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %2;\n\tsub.rn.f32.bf16 %0, lo, %3;\n\tsub.rn.f32.bf16 %1, hi, %3;\n\t}" : "=f"(d0), "=f"(d1) : "r"(w), "f"(c));
+  }
+};
+template <> struct Mixed<__half> {
+  static __device__ __forceinline__ void add2(float& s, uint32_t w) {
+    asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %1;\n\tadd.rn.f32.f16 %0, lo, %0;\n\tadd.rn.f32.f16 %0, hi, %0;\n\t}" : "+f"(s) : "r"(w));
+  }
+  static __device__ __forceinline__ void sub2(uint32_t w, float c, float& d0, float& d1) {
+    asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %2;\n\tsub.rn.f32.f16 %0, lo, %3;\n\tsub.rn.f32.f16 %1, hi, %3;\n\t}" : "=f"(d0), "=f"(d1) : "r"(w), "f"(c));
+  }
+};
+// sum += the elements of a packed vector; d[e] = element e - c
+template <typename T> __device__ __forceinline__ void vec_accumulate(float& s, const uint4& raw) {
+  if constexpr (sizeof(T) == 4) {
+    s += __uint_as_float(raw.x); s += __uint_as_float(raw.y); s += __uint_as_float(raw.z); s += __uint_as_float(raw.w);
+  } else {
+    Mixed<T>::add2(s, raw.x); Mixed<T>::add2(s, raw.y); Mixed<T>::add2(s, raw.z); Mixed<T>::add2(s, raw.w);
+  }
+}
+template <typename T> __device__ __forceinline__ void vec_minus(const uint4& raw, float c, float* d) {
+  if constexpr (sizeof(T) == 4) {
+    d[0] = __uint_as_float(raw.x) - c; d[1] = __uint_as_float(raw.y) - c; d[2] = __uint_as_float(raw.z) - c; d[3] = __uint_as_float(raw.w) - c;
+  } else {
+    Mixed<T>::sub2(raw.x, c, d[0], d[1]); Mixed<T>::sub2(raw.y, c, d[2], d[3]); Mixed<T>::sub2(raw.z, c, d[4], d[5]); Mixed<T>::sub2(raw.w, c, d[6], d[7]);
+  }
+}
+
 // Streaming (evict-first) accesses: the memory-bound kernels touch every byte once.
 __device__ __forceinline__ uint4 ld_stream(const void* p) { return __ldcs(reinterpret_cast<const uint4*>(p)); }
 __device__ __forceinline__ void st_stream(void* p, uint4 v) { __stcs(reinterpret_cast<uint4*>(p), v); }

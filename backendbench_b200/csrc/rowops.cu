@@ -349,11 +349,7 @@ layernorm_resident(const T* __restrict__ x, const TW* __restrict__ w, const TW* 
     }
 #pragma unroll
     for (int u = 0; u < VPT; ++u) {
-      if (t + u * tpr < nvec) {
-        widen<T>(raw[HOLD ? 0 : u], f[0]);
-#pragma unroll
-        for (int e = 0; e < VE; ++e) s += f[0][e];
-      }
+      if (t + u * tpr < nvec) vec_accumulate<T>(s, raw[HOLD ? 0 : u]);
     }
   }
   s = group_reduce<WARP>(s, SumF{}, 0.f, red, 0);
@@ -365,12 +361,15 @@ layernorm_resident(const T* __restrict__ x, const TW* __restrict__ w, const TW* 
 #pragma unroll
   for (int u = 0; u < VPT; ++u) {
     if (t + u * tpr < nvec) {
-      if (!HOLD) widen<T>(raw[HOLD ? 0 : u], f[0]);
+      float d[VE];
+      if (HOLD) {
 #pragma unroll
-      for (int e = 0; e < VE; ++e) {
-        const float d = f[HOLD ? u : 0][e] - mu;
-        q = fmaf(d, d, q);
+        for (int e = 0; e < VE; ++e) d[e] = f[HOLD ? u : 0][e] - mu;
+      } else {
+        vec_minus<T>(raw[HOLD ? 0 : u], mu, d);
       }
+#pragma unroll
+      for (int e = 0; e < VE; ++e) q = fmaf(d[e], d[e], q);
     }
   }
   q = group_reduce<WARP>(q, SumF{}, 0.f, red, 1);
@@ -383,13 +382,18 @@ layernorm_resident(const T* __restrict__ x, const TW* __restrict__ w, const TW* 
   for (int u = 0; u < VPT; ++u) {
     const int j = t + u * tpr;
     if (j < nvec) {
-      float o[VE], wv[VE], bv[VE];
-      if (!HOLD) widen<T>(raw[HOLD ? 0 : u], f[0]);
+      float o[VE], wv[VE], bv[VE], d[VE];
+      if (HOLD) {
+#pragma unroll
+        for (int e = 0; e < VE; ++e) d[e] = f[HOLD ? u : 0][e] - mu;
+      } else {
+        vec_minus<T>(raw[HOLD ? 0 : u], mu, d);
+      }
       if (AFFINE || w) load_weights<VE, TW>(w, j * VE, wv);
       if (AFFINE || b) load_weights<VE, TW>(b, j * VE, bv);
 #pragma unroll
       for (int e = 0; e < VE; ++e) {
-        float r = (f[HOLD ? u : 0][e] - mu) * rs;
+        float r = d[e] * rs;
         if (AFFINE) {
           r = fmaf(r, wv[e], bv[e]);
         } else {
@@ -668,22 +672,25 @@ __global__ void __launch_bounds__(256) reduce_rows(const T* __restrict__ x, void
       for (int u = 0; u < 4; ++u) v[u].raw = ld_stream(xr + (j + u * tpr) * VE);
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-        float fw[VE];
-        widen<T>(v[u].raw, fw);
+        if (ARG) {
+          float fw[VE];
+          widen<T>(v[u].raw, fw);
 #pragma unroll
-        for (int e = 0; e < VE; ++e) {
-          if (ARG) arg_take_ascending(a, fw[e], (j + u * tpr) * VE + e);
-          else s += fw[e];
+          for (int e = 0; e < VE; ++e) arg_take_ascending(a, fw[e], (j + u * tpr) * VE + e);
+        } else {
+          vec_accumulate<T>(s, v[u].raw);  // 16-bit elements are widened inside the add
         }
       }
     }
     for (; j < v1; j += tpr) {
-      float fw[VE];
-      widen<T>(ld_stream(xr + j * VE), fw);
+      const uint4 raw = ld_stream(xr + j * VE);
+      if (ARG) {
+        float fw[VE];
+        widen<T>(raw, fw);
 #pragma unroll
-      for (int e = 0; e < VE; ++e) {
-        if (ARG) arg_take_ascending(a, fw[e], j * VE + e);
-        else s += fw[e];
+        for (int e = 0; e < VE; ++e) arg_take_ascending(a, fw[e], j * VE + e);
+      } else {
+        vec_accumulate<T>(s, raw);
       }
     }
     for (int64_t c = v1 * VE + t; c < c1; c += tpr) {  // ragged end of the last slice
