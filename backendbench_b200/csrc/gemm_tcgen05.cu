@@ -3,7 +3,7 @@
 //   C[b] (M x N, row-major) = alpha * A[b] (M x K) @ B[b] (K x N) + beta * bias
 //
 // One persistent CTA per SM walks 128 x 256 (or 128 x 128) output tiles. Roles by warp:
-//   warp 0   : TMA producer -- one lane issues cp.async.bulk.tensor loads (no multicast)
+//   warp 0   : TMA producer -- one lane issues cp.async.bulk.tensor loads
 //              of a 128 x 64 A slab and a 64 x 256 B slab per pipeline stage into
 //              128-byte-swizzled shared memory, completion on an mbarrier.
 //   warp 1   : owns tensor memory (allocates all 512 TMEM columns = two fp32 accumulators
