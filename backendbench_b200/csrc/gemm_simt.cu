@@ -2,10 +2,16 @@
 // with TF32 off) and for any layout the tensor-core kernel cannot take (odd strides,
 // unaligned bases, K not a multiple of 8). Arbitrary element strides, fp32 accumulate,
 // one rounding. Output tile per CTA chosen by shape (128x128 down to 128x32 / 32x128),
-// 16-deep K slices staged in shared memory.
+// 16-deep K slices staged in shared memory. A product with a long contraction and an output
+// of only a few tiles is split along K over the CTAs of a thread-block cluster, which add
+// their partial tiles through distributed shared memory in rank order (no scratch buffer,
+// no atomics: the result does not depend on scheduling).
+#include <cooperative_groups.h>
+
 #include "b200_common.cuh"
 
 namespace b200 {
+namespace cg = cooperative_groups;
 
 constexpr int kTK = 16;
 
@@ -14,20 +20,31 @@ struct GemmArgs {
   int64_t sAb, sAm, sAk, sBb, sBk, sBn, sbm, sbn;
   float alpha, beta;
   const uint32_t* gate;  // when not NULL: the kernel does its work only if this device word is non-zero
+  int ksplit;            // CTAs per cluster sharing one output tile (KSPLIT kernels), else 1
+  int64_t kchunk;        // K elements per CTA of the cluster, a multiple of kTK
 };
 
 // TM x TN outputs per CTA (256 threads, (TM/16) x (TN/16) per thread), 16-deep K slices.
 // The next slice is fetched from global memory into registers while the current one is
 // multiplied out of shared memory, so one barrier pair per slice is the only serialisation.
 // Tile shapes: 128x128 for large problems, 64x64 / 128x32 / 32x128 when M or N is small.
-template <typename T, int kTM, int kTN>
+// KSPLIT: launched as clusters of g.ksplit CTAs along z; CTA s of a cluster contracts the K
+// range [s * kchunk, (s + 1) * kchunk) of the same output tile, leaves its partial tile in
+// shared memory, and after a cluster barrier every CTA finishes a share of the tile's
+// elements, adding the partials of ranks 0 .. ksplit-1 in that order.
+template <typename T, int kTM, int kTN, bool KSPLIT>
 __global__ void __launch_bounds__(256) gemm_simt(const T* __restrict__ A, const T* __restrict__ B, const T* __restrict__ bias, T* __restrict__ C, GemmArgs g) {
   __shared__ __align__(16) float As[kTK][kTM + 4];
   __shared__ __align__(16) float Bs[kTK][kTN + 4];
-  if (g.gate && *g.gate == 0u) return;
+  __shared__ __align__(16) float part[KSPLIT ? kTM * kTN : 4];
+  if (g.gate && *g.gate == 0u) return;  // the same word for every CTA: whole clusters leave together
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
   const int64_t m0 = static_cast<int64_t>(blockIdx.y) * kTM, n0 = static_cast<int64_t>(blockIdx.x) * kTN;
-  const int64_t b = blockIdx.z;
+  const int nsplit = KSPLIT ? g.ksplit : 1;
+  const int64_t b = KSPLIT ? blockIdx.z / nsplit : blockIdx.z;
+  const int rank = KSPLIT ? static_cast<int>(blockIdx.z % nsplit) : 0;
+  const int64_t k_lo = KSPLIT ? rank * g.kchunk : 0;
+  const int64_t k_hi = KSPLIT ? (k_lo + g.kchunk < g.K ? k_lo + g.kchunk : g.K) : g.K;
   const T* Ab = A + b * g.sAb;
   const T* Bb = B + b * g.sBb;
   const bool a_kfast = g.sAk == 1, b_nfast = g.sBn == 1;
@@ -42,14 +59,14 @@ __global__ void __launch_bounds__(256) gemm_simt(const T* __restrict__ A, const 
       // consecutive threads walk the contiguous direction of the operand
       const int kk = a_kfast ? (e & 15) : (e / kTM), mm = a_kfast ? (e >> 4) : (e % kTM);
       const int64_t m = m0 + mm, k = k0 + kk;
-      pa[q] = (m < g.M && k < g.K) ? to_f32(Ab[m * g.sAm + k * g.sAk]) : 0.f;
+      pa[q] = (m < g.M && k < k_hi) ? to_f32(Ab[m * g.sAm + k * g.sAk]) : 0.f;
     }
 #pragma unroll
     for (int q = 0; q < QB; ++q) {
       const int e = tid + q * 256;
       const int kk = b_nfast ? (e / kTN) : (e & 15), nn = b_nfast ? (e % kTN) : (e >> 4);
       const int64_t n = n0 + nn, k = k0 + kk;
-      pb[q] = (n < g.N && k < g.K) ? to_f32(Bb[k * g.sBk + n * g.sBn]) : 0.f;
+      pb[q] = (n < g.N && k < k_hi) ? to_f32(Bb[k * g.sBk + n * g.sBn]) : 0.f;
     }
   };
   auto stash = [&]() {
@@ -64,11 +81,11 @@ __global__ void __launch_bounds__(256) gemm_simt(const T* __restrict__ A, const 
       Bs[b_nfast ? (e / kTN) : (e & 15)][b_nfast ? (e % kTN) : (e >> 4)] = pb[q];
     }
   };
-  fetch(0);
-  for (int64_t k0 = 0; k0 < g.K; k0 += kTK) {
+  fetch(k_lo);
+  for (int64_t k0 = k_lo; k0 < k_hi; k0 += kTK) {
     stash();
     __syncthreads();
-    if (k0 + kTK < g.K) fetch(k0 + kTK);
+    if (k0 + kTK < k_hi) fetch(k0 + kTK);
 #pragma unroll
     for (int kk = 0; kk < kTK; ++kk) {
       float a[RM], bb[RN];
@@ -84,32 +101,99 @@ __global__ void __launch_bounds__(256) gemm_simt(const T* __restrict__ A, const 
     __syncthreads();
   }
   T* Cb = C + b * g.M * g.N;
+  if (KSPLIT) {
+    cg::cluster_group cluster = cg::this_cluster();
 #pragma unroll
-  for (int i = 0; i < RM; ++i) {
-    const int64_t m = m0 + ty * RM + i;
-    if (m >= g.M) continue;
+    for (int i = 0; i < RM; ++i)
 #pragma unroll
-    for (int j = 0; j < RN; ++j) {
-      const int64_t n = n0 + tx * RN + j;
-      if (n >= g.N) continue;
-      float r = g.alpha * acc[i][j];
-      // beta == 0 drops the bias term entirely (a NaN bias must not leak through)
-      if (bias && g.beta != 0.f) r = fmaf(g.beta, to_f32(bias[m * g.sbm + n * g.sbn]), r);
-      Cb[m * g.N + n] = from_f32<T>(r);
+      for (int j = 0; j < RN; ++j) part[(ty * RM + i) * kTN + tx * RN + j] = acc[i][j];
+    cluster.sync();
+    for (int e = rank * 256 + tid; e < kTM * kTN; e += nsplit * 256) {
+      float sum = 0.f;
+      for (int r = 0; r < nsplit; ++r) sum += cluster.map_shared_rank(part, r)[e];
+      const int64_t m = m0 + e / kTN, n = n0 + e % kTN;
+      if (m < g.M && n < g.N) {
+        float r = g.alpha * sum;
+        // beta == 0 drops the bias term entirely (a NaN bias must not leak through)
+        if (bias && g.beta != 0.f) r = fmaf(g.beta, to_f32(bias[m * g.sbm + n * g.sbn]), r);
+        Cb[m * g.N + n] = from_f32<T>(r);
+      }
+    }
+    cluster.sync();  // nobody leaves while its partial tile may still be read
+  } else {
+#pragma unroll
+    for (int i = 0; i < RM; ++i) {
+      const int64_t m = m0 + ty * RM + i;
+      if (m >= g.M) continue;
+#pragma unroll
+      for (int j = 0; j < RN; ++j) {
+        const int64_t n = n0 + tx * RN + j;
+        if (n >= g.N) continue;
+        float r = g.alpha * acc[i][j];
+        // beta == 0 drops the bias term entirely (a NaN bias must not leak through)
+        if (bias && g.beta != 0.f) r = fmaf(g.beta, to_f32(bias[m * g.sbm + n * g.sbn]), r);
+        Cb[m * g.N + n] = from_f32<T>(r);
+      }
     }
   }
 }
 
-template <typename T, int kTM, int kTN>
-static int launch_simt_tile(const void* A, const void* B, const void* bias, void* C, int64_t batch, const GemmArgs& g, cudaStream_t st) {
+// Few output tiles and a long contraction: how many CTAs share a tile (1 = no split). One
+// CTA walks K at a slice per global-memory round trip, so with under half the SMs busy the
+// time falls with every CTA added (measured: 2 x 2048 x 256 fp32, 192 us unsplit, 41 us
+// at 8); from about one tile per SM on, splitting only adds the exchange (21 x 1024 x 256
+// in 64 batches: 102 us unsplit, 115-140 us split). Each CTA keeps at least four K slices
+// and the cluster stays within the portable size of 8.
+static int pick_ksplit(int64_t tiles, int64_t K) {
+  if (tiles >= kNumSMs / 2 || K < 8 * kTK) return 1;
+  int64_t s = K / (4 * kTK);
+  const int64_t fill = (4 * kNumSMs + tiles - 1) / tiles;
+  if (s > fill) s = fill;
+  if (s > 8) s = 8;
+  return s < 2 ? 1 : static_cast<int>(s);
+}
+
+template <typename T, int kTM, int kTN, bool KSPLIT = false>
+static int launch_simt_tile(const void* A, const void* B, const void* bias, void* C, int64_t batch, GemmArgs g, cudaStream_t st) {
   const int64_t gx = (g.N + kTN - 1) / kTN, gy = (g.M + kTM - 1) / kTM;
   if (gx > 0x7fffffffLL || gy > 65535) return B200_EINVAL;
-  for (int64_t b0 = 0; b0 < batch; b0 += 65535) {
-    const int64_t bn = batch - b0 < 65535 ? batch - b0 : 65535;
-    dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(gy), static_cast<unsigned>(bn));
-    gemm_simt<T, kTM, kTN><<<grid, 256, 0, st>>>(static_cast<const T*>(A) + b0 * g.sAb, static_cast<const T*>(B) + b0 * g.sBb, static_cast<const T*>(bias), static_cast<T*>(C) + b0 * g.M * g.N, g);
+  const int64_t per_launch = 65535 / g.ksplit;  // batches per launch: grid z holds batch x ksplit
+  for (int64_t b0 = 0; b0 < batch; b0 += per_launch) {
+    const int64_t bn = batch - b0 < per_launch ? batch - b0 : per_launch;
+    dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(gy), static_cast<unsigned>(bn * g.ksplit));
+    const T* a = static_cast<const T*>(A) + b0 * g.sAb;
+    const T* b = static_cast<const T*>(B) + b0 * g.sBb;
+    const T* bs = static_cast<const T*>(bias);
+    T* c = static_cast<T*>(C) + b0 * g.M * g.N;
+    if (KSPLIT) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = grid;
+      cfg.blockDim = dim3(256);
+      cfg.stream = st;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = 1;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = static_cast<unsigned>(g.ksplit);
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_simt<T, kTM, kTN, KSPLIT>, a, b, bs, c, g);
+      if (e != cudaSuccess) { set_last_cuda_error(e); return B200_ELAUNCH; }
+    } else {
+      gemm_simt<T, kTM, kTN, KSPLIT><<<grid, 256, 0, st>>>(a, b, bs, c, g);
+    }
   }
   return check_launch();
+}
+
+template <typename T, int kTM, int kTN>
+static int launch_simt_small(const void* A, const void* B, const void* bias, void* C, int64_t batch, GemmArgs g, cudaStream_t st) {
+  const int64_t tiles = batch * ((g.M + kTM - 1) / kTM) * ((g.N + kTN - 1) / kTN);
+  g.ksplit = pick_ksplit(tiles, g.K);
+  if (g.ksplit == 1) return launch_simt_tile<T, kTM, kTN, false>(A, B, bias, C, batch, g, st);
+  const int64_t per = (g.K + g.ksplit - 1) / g.ksplit;
+  g.kchunk = (per + kTK - 1) / kTK * kTK;
+  return launch_simt_tile<T, kTM, kTN, true>(A, B, bias, C, batch, g, st);
 }
 
 template <typename T>
@@ -117,14 +201,14 @@ static int launch_simt(const void* A, const void* B, const void* bias, void* C, 
   // big tiles only when they are mostly full and there are enough of them to fill the GPU
   const int64_t big_tiles = batch * ((g.M + 127) / 128) * ((g.N + 127) / 128);
   if (g.M >= 96 && g.N >= 96 && big_tiles >= kNumSMs) return launch_simt_tile<T, 128, 128>(A, B, bias, C, batch, g, st);
-  if (g.N <= 40 && g.M >= 96) return launch_simt_tile<T, 128, 32>(A, B, bias, C, batch, g, st);
-  if (g.M <= 40 && g.N >= 96) return launch_simt_tile<T, 32, 128>(A, B, bias, C, batch, g, st);
-  return launch_simt_tile<T, 64, 64>(A, B, bias, C, batch, g, st);
+  if (g.N <= 40 && g.M >= 96) return launch_simt_small<T, 128, 32>(A, B, bias, C, batch, g, st);
+  if (g.M <= 40 && g.N >= 96) return launch_simt_small<T, 32, 128>(A, B, bias, C, batch, g, st);
+  return launch_simt_small<T, 64, 64>(A, B, bias, C, batch, g, st);
 }
 
 int gemm_simt_dispatch(const void* A, const void* B, const void* bias, void* C, int64_t batch, int64_t M, int64_t N, int64_t K, int64_t sAb, int64_t sAm, int64_t sAk,
                        int64_t sBb, int64_t sBk, int64_t sBn, int64_t sbm, int64_t sbn, double alpha, double beta, int dtype, cudaStream_t st, const uint32_t* gate) {
-  GemmArgs g{M, N, K, sAb, sAm, sAk, sBb, sBk, sBn, sbm, sbn, static_cast<float>(alpha), static_cast<float>(beta), gate};
+  GemmArgs g{M, N, K, sAb, sAm, sAk, sBb, sBk, sBn, sbm, sbn, static_cast<float>(alpha), static_cast<float>(beta), gate, 1, 0};
   switch (dtype) {
     case B200_F32: return launch_simt<float>(A, B, bias, C, batch, g, st);
     case B200_BF16: return launch_simt<__nv_bfloat16>(A, B, bias, C, batch, g, st);

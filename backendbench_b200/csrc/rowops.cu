@@ -790,87 +790,174 @@ __global__ void __launch_bounds__(256) reduce_finalize(const float* __restrict__
   }
 }
 
+// The same with one warp per output, for many partials of few outputs (a whole-tensor
+// reduction): lanes take partials s = lane, lane + 32, ... and combine by shuffles. The
+// order of the additions is fixed by (lane, shuffle tree), so sums stay run-to-run
+// identical; argmax combines by (NaN, value, index), which is order-free.
+template <bool ARG>
+__global__ void __launch_bounds__(256) reduce_finalize_warp(const float* __restrict__ part_v, const int64_t* __restrict__ part_i, void* __restrict__ out, int64_t n, int splits, int dto) {
+  const int64_t o = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (o >= n) return;
+  if (ARG) {
+    ArgPair a{0.f, -1};
+    for (int s = lane; s < splits; s += 32) {
+      const int64_t i = part_i[s * n + o];
+      if (i >= 0) arg_take(a, part_v[s * n + o], i);
+    }
+    a = arg_warp_reduce(a);
+    if (lane == 0) static_cast<int64_t*>(out)[o] = a.i;
+  } else {
+    float s = 0.f;
+    for (int k = lane; k < splits; k += 32) s += part_v[k * n + o];
+    s = warp_reduce(s, SumF());
+    if (lane == 0) store_from_f32(out, o, dto, s);
+  }
+}
+
 __global__ void fill_zero_typed(void* out, int64_t n, int dto) {
   const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i < n) store_from_f32(out, i, dto, 0.f);
 }
 
 // ------------------------------------------------------------------ very short rows (dim <= 32, inner == 1)
-// Millions of rows of a handful of elements: one THREAD per row, the row in registers. A
-// warp reads 32 consecutive rows, i.e. one contiguous span, so the loads coalesce through L1.
+// Millions of rows of a handful of elements: one THREAD per row, the row in registers (NC
+// slots, the next multiple of 8 above the row length). A CTA owns 256 consecutive rows, one
+// contiguous span of memory, and reaches it in one of two ways.
+//   direct: each thread loads and stores its own row element by element. A warp-wide access
+//     then touches one 32-byte sector per lane, and the load/store unit spends a cycle per
+//     sector: the cost is ~2 x 32 x cols cycles per warp, far above the bytes moved.
+//   staged: the CTA copies the span into shared memory with 16-byte accesses, threads read
+//     and overwrite their rows there, and the span goes back out the same way. Used when the
+//     row stride is not a multiple of 8 bytes (bank conflicts stay at most 2-way) and the
+//     output has the input's element size.
 constexpr int kSmallRow = 32;
+constexpr int kSmallRows = 256;  // rows (threads) per CTA
 enum { SMALL_SOFTMAX = 0, SMALL_LOGSOFTMAX = 1, SMALL_SUM = 2, SMALL_ARGMAX = 3, SMALL_LAYERNORM = 4 };
 
-template <typename T, int OP>
-__global__ void __launch_bounds__(256) rows_small(const T* __restrict__ x, void* __restrict__ out, int64_t rows, int cols, int dto, const void* __restrict__ w, const void* __restrict__ b,
-                                                  int dt_wb, void* __restrict__ mean, void* __restrict__ rstd, int dt_stat, float eps) {
-  const int64_t row = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (row >= rows) return;
-  const T* xr = x + row * cols;
-  float f[kSmallRow];
-#pragma unroll
-  for (int c = 0; c < kSmallRow; ++c) f[c] = c < cols ? to_f32(xr[c]) : 0.f;
-  if (OP == SMALL_SUM) {
-    float s = 0.f;
-#pragma unroll
-    for (int c = 0; c < kSmallRow; ++c) s += c < cols ? f[c] : 0.f;
-    store_from_f32(out, row, dto, s);
-  } else if (OP == SMALL_ARGMAX) {
-    ArgPair a{CUDART_NAN_F, -1};
-#pragma unroll
-    for (int c = 0; c < kSmallRow; ++c)
-      if (c < cols) arg_take_ascending(a, f[c], c);
-    static_cast<int64_t*>(out)[row] = a.i;
-  } else if (OP == SMALL_LAYERNORM) {
-    float s = 0.f;
-#pragma unroll
-    for (int c = 0; c < kSmallRow; ++c) s += c < cols ? f[c] : 0.f;
-    float mu = s / static_cast<float>(cols);
-    if (!isfinite(mu)) mu = CUDART_NAN_F;
-    float q = 0.f;
-#pragma unroll
-    for (int c = 0; c < kSmallRow; ++c) {
-      const float d = f[c] - mu;
-      q = c < cols ? fmaf(d, d, q) : q;
-    }
-    const float rs = rsqrtf(q / static_cast<float>(cols) + eps);
-    store_from_f32(mean, row, dt_stat, mu);
-    store_from_f32(rstd, row, dt_stat, rs);
-#pragma unroll
-    for (int c = 0; c < kSmallRow; ++c)
-      if (c < cols) {
-        float r = (f[c] - mu) * rs;
-        if (w) r *= load_as_f32(w, c, dt_wb);
-        if (b) r += load_as_f32(b, c, dt_wb);
-        store_from_f32(out, row * cols + c, dto, r);
-      }
-  } else {
-    float m = -CUDART_INF_F;
-#pragma unroll
-    for (int c = 0; c < kSmallRow; ++c) m = c < cols ? fmaxf(m, f[c]) : m;
-    float s = 0.f;
-#pragma unroll
-    for (int c = 0; c < kSmallRow; ++c) {
-      const float d = f[c] - m;
-      const float ex = exp2f(d * kLog2e);
-      s += c < cols ? ex : 0.f;
-      f[c] = OP == SMALL_LOGSOFTMAX ? d : ex;
-    }
-    const float k = OP == SMALL_LOGSOFTMAX ? logf(s) : 1.f / s;
-#pragma unroll
-    for (int c = 0; c < kSmallRow; ++c)
-      if (c < cols) store_from_f32(out, row * cols + c, dto, OP == SMALL_LOGSOFTMAX ? f[c] - k : f[c] * k);
+template <typename T, int OP, int NC, bool STAGED>
+__global__ void __launch_bounds__(kSmallRows) rows_small(const T* __restrict__ x, void* __restrict__ out, int64_t rows, int cols, int dto, const void* __restrict__ w,
+                                                         const void* __restrict__ b, int dt_wb, void* __restrict__ mean, void* __restrict__ rstd, int dt_stat, float eps) {
+  extern __shared__ __align__(16) unsigned char small_smem[];
+  constexpr bool WRITES_ROWS = OP == SMALL_SOFTMAX || OP == SMALL_LOGSOFTMAX || OP == SMALL_LAYERNORM;
+  constexpr int VE = 16 / static_cast<int>(sizeof(T));
+  const int tid = threadIdx.x;
+  const int64_t row0 = static_cast<int64_t>(blockIdx.x) * kSmallRows;
+  const int64_t row = row0 + tid;
+  const bool live = row < rows;
+  T* sm = reinterpret_cast<T*>(small_smem);
+  int span = 0;
+  if (STAGED) {
+    const int64_t left = rows - row0;
+    span = static_cast<int>(left < kSmallRows ? left : kSmallRows) * cols;  // elements this CTA owns
+    const T* src = x + row0 * cols;
+    const int nv = span / VE;
+    for (int j = tid; j < nv; j += kSmallRows) reinterpret_cast<uint4*>(sm)[j] = ld_stream(src + static_cast<int64_t>(j) * VE);
+    for (int j = nv * VE + tid; j < span; j += kSmallRows) sm[j] = src[j];
+    __syncthreads();
   }
+  const T* xr = STAGED ? sm + tid * cols : x + row * cols;
+  T* orow = STAGED ? sm + tid * cols : static_cast<T*>(out) + row * cols;  // direct stores go through `put`
+  auto put = [&](int c, float v) {
+    if (STAGED) orow[c] = from_f32<T>(v);
+    else store_from_f32(out, row * cols + c, dto, v);
+  };
+  if (live) {
+    float f[NC];
+#pragma unroll
+    for (int c = 0; c < NC; ++c) f[c] = c < cols ? to_f32(xr[c]) : 0.f;
+    if (OP == SMALL_SUM) {
+      float s = 0.f;
+#pragma unroll
+      for (int c = 0; c < NC; ++c) s += c < cols ? f[c] : 0.f;
+      store_from_f32(out, row, dto, s);
+    } else if (OP == SMALL_ARGMAX) {
+      ArgPair a{CUDART_NAN_F, -1};
+#pragma unroll
+      for (int c = 0; c < NC; ++c)
+        if (c < cols) arg_take_ascending(a, f[c], c);
+      static_cast<int64_t*>(out)[row] = a.i;
+    } else if (OP == SMALL_LAYERNORM) {
+      float s = 0.f;
+#pragma unroll
+      for (int c = 0; c < NC; ++c) s += c < cols ? f[c] : 0.f;
+      float mu = s / static_cast<float>(cols);
+      if (!isfinite(mu)) mu = CUDART_NAN_F;
+      float q = 0.f;
+#pragma unroll
+      for (int c = 0; c < NC; ++c) {
+        const float d = f[c] - mu;
+        q = c < cols ? fmaf(d, d, q) : q;
+      }
+      const float rs = rsqrtf(q / static_cast<float>(cols) + eps);
+      store_from_f32(mean, row, dt_stat, mu);
+      store_from_f32(rstd, row, dt_stat, rs);
+#pragma unroll
+      for (int c = 0; c < NC; ++c)
+        if (c < cols) {
+          float r = (f[c] - mu) * rs;
+          if (w) r *= load_as_f32(w, c, dt_wb);
+          if (b) r += load_as_f32(b, c, dt_wb);
+          put(c, r);
+        }
+    } else {
+      float m = -CUDART_INF_F;
+#pragma unroll
+      for (int c = 0; c < NC; ++c) m = c < cols ? fmaxf(m, f[c]) : m;
+      float s = 0.f;
+#pragma unroll
+      for (int c = 0; c < NC; ++c) {
+        const float d = f[c] - m;
+        const float ex = exp2f(d * kLog2e);
+        s += c < cols ? ex : 0.f;
+        f[c] = OP == SMALL_LOGSOFTMAX ? d : ex;
+      }
+      const float k = OP == SMALL_LOGSOFTMAX ? logf(s) : 1.f / s;
+#pragma unroll
+      for (int c = 0; c < NC; ++c)
+        if (c < cols) put(c, OP == SMALL_LOGSOFTMAX ? f[c] - k : f[c] * k);
+    }
+  }
+  if (STAGED && WRITES_ROWS) {
+    __syncthreads();
+    T* dst = static_cast<T*>(out) + row0 * cols;
+    const int nv = span / VE;
+    for (int j = tid; j < nv; j += kSmallRows) st_stream(dst + static_cast<int64_t>(j) * VE, reinterpret_cast<const uint4*>(sm)[j]);
+    for (int j = nv * VE + tid; j < span; j += kSmallRows) dst[j] = sm[j];
+  }
+}
+
+template <typename T, int OP, int NC>
+static void launch_rows_small_nc(const void* x, void* out, int64_t rows, int cols, int dti, int dto, const void* w, const void* b, int dt_wb, void* mean, void* rstd, int dt_stat, float eps,
+                                 cudaStream_t st) {
+  constexpr bool WRITES_ROWS = OP == SMALL_SOFTMAX || OP == SMALL_LOGSOFTMAX || OP == SMALL_LAYERNORM;
+  const int g = grid_for(rows, kSmallRows);
+  // staged: row stride not a multiple of 8 bytes, 16-byte aligned bases, same-size output
+  const bool staged = (cols * sizeof(T)) % 8 != 0 && aligned16(x) && (!WRITES_ROWS || (dto == dti && aligned16(out)));
+  if (staged) {
+    const size_t smem = (static_cast<size_t>(kSmallRows) * cols * sizeof(T) + 15) / 16 * 16;
+    rows_small<T, OP, NC, true><<<g, kSmallRows, smem, st>>>(static_cast<const T*>(x), out, rows, cols, dto, w, b, dt_wb, mean, rstd, dt_stat, eps);
+  } else {
+    rows_small<T, OP, NC, false><<<g, kSmallRows, 0, st>>>(static_cast<const T*>(x), out, rows, cols, dto, w, b, dt_wb, mean, rstd, dt_stat, eps);
+  }
+}
+
+template <typename T, int OP>
+static void launch_rows_small_T(const void* x, void* out, int64_t rows, int cols, int dti, int dto, const void* w, const void* b, int dt_wb, void* mean, void* rstd, int dt_stat, float eps,
+                                cudaStream_t st) {
+  if (cols <= 8) launch_rows_small_nc<T, OP, 8>(x, out, rows, cols, dti, dto, w, b, dt_wb, mean, rstd, dt_stat, eps, st);
+  else if (cols <= 16) launch_rows_small_nc<T, OP, 16>(x, out, rows, cols, dti, dto, w, b, dt_wb, mean, rstd, dt_stat, eps, st);
+  else if (cols <= 24) launch_rows_small_nc<T, OP, 24>(x, out, rows, cols, dti, dto, w, b, dt_wb, mean, rstd, dt_stat, eps, st);
+  else launch_rows_small_nc<T, OP, 32>(x, out, rows, cols, dti, dto, w, b, dt_wb, mean, rstd, dt_stat, eps, st);
 }
 
 template <int OP>
 static int launch_rows_small(const void* x, void* out, int64_t rows, int cols, int dti, int dto, const void* w, const void* b, int dt_wb, void* mean, void* rstd, int dt_stat, float eps,
                              cudaStream_t st) {
-  const int g = grid_for(rows, 256);
   switch (dti) {
-    case B200_F32: rows_small<float, OP><<<g, 256, 0, st>>>(static_cast<const float*>(x), out, rows, cols, dto, w, b, dt_wb, mean, rstd, dt_stat, eps); break;
-    case B200_BF16: rows_small<__nv_bfloat16, OP><<<g, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), out, rows, cols, dto, w, b, dt_wb, mean, rstd, dt_stat, eps); break;
-    default: rows_small<__half, OP><<<g, 256, 0, st>>>(static_cast<const __half*>(x), out, rows, cols, dto, w, b, dt_wb, mean, rstd, dt_stat, eps); break;
+    case B200_F32: launch_rows_small_T<float, OP>(x, out, rows, cols, dti, dto, w, b, dt_wb, mean, rstd, dt_stat, eps, st); break;
+    case B200_BF16: launch_rows_small_T<__nv_bfloat16, OP>(x, out, rows, cols, dti, dto, w, b, dt_wb, mean, rstd, dt_stat, eps, st); break;
+    default: launch_rows_small_T<__half, OP>(x, out, rows, cols, dti, dto, w, b, dt_wb, mean, rstd, dt_stat, eps, st); break;
   }
   return check_launch();
 }
@@ -944,7 +1031,8 @@ static int launch_reduce_T(const void* x, void* out, int64_t outer, int64_t dim,
     dim3 g(grid_for(inner, 256), static_cast<unsigned>(outer), p.splits);
     reduce_cols<T, ARG><<<g, 256, 0, st>>>(px, out, pv, pi, outer, dim, inner, p.chunk, dto);
   }
-  if (p.splits > 1) reduce_finalize<ARG><<<grid_for(nout, 256), 256, 0, st>>>(pv, pi, out, nout, p.splits, dto);
+  if (p.splits >= 64 && nout <= 8LL * kNumSMs * 8) reduce_finalize_warp<ARG><<<grid_for(nout, 8), 256, 0, st>>>(pv, pi, out, nout, p.splits, dto);
+  else if (p.splits > 1) reduce_finalize<ARG><<<grid_for(nout, 256), 256, 0, st>>>(pv, pi, out, nout, p.splits, dto);
   return check_launch(p.splits > 1 ? 2 : 1);
 }
 

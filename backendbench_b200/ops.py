@@ -671,9 +671,10 @@ def _gemm(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor], batch:
         bias_ptr = bias.data_ptr()
     # Large fp32 products run on the tensor cores too: the operands are split into three bf16
     # planes each in scratch memory and six plane products are accumulated in fp32, which
-    # keeps fp32 accuracy (see include/b200ops.h). Small ones stay on the CUDA-core kernel.
+    # keeps fp32 accuracy (see include/b200ops.h). Small ones stay on the CUDA-core kernel,
+    # which shares a long contraction with few outputs among the CTAs of a cluster.
     macs = batch * M * N * K
-    if a.dtype == torch.float32 and ((macs >= F32_SPLIT_MIN_MACS and K >= 32 and M >= 32 and N >= 32) or (K >= 1024 and macs >= (1 << 18))):
+    if a.dtype == torch.float32 and macs >= F32_SPLIT_MIN_MACS and K >= 32 and M >= 32 and N >= 32:
         need = int(lib().b200_gemm_f32_scratch_bytes(batch, M, N, K))
         if need > 0:
             scratch = _scratch(a.device, need)

@@ -169,7 +169,8 @@ def test_split_fp32_product_keeps_special_values_and_wide_ranges():
 
 def test_long_contractions_with_small_outputs_leave_the_single_cta_path():
     """K in the thousands with a handful of outputs: 16-bit operands are re-pitched onto the
-    tensor cores whatever their alignment, fp32 operands take the split path."""
+    tensor cores whatever their alignment, fp32 operands share K among the CTAs of a cluster
+    (every cluster size from 2 to 8, a K that leaves the last CTAs of the cluster empty)."""
     g = torch.Generator(device=DEV).manual_seed(14)
     a, b, bias = _rand((32, 4096), torch.bfloat16, g, 4096**-0.5), _rand((4096, 31), torch.bfloat16, g, 1.0), _rand((32, 1), torch.bfloat16, g, 1.0)
     _check(ops.addmm_default(bias, a, b), a.double() @ b.double() + bias.double(), torch.bfloat16)
@@ -177,4 +178,19 @@ def test_long_contractions_with_small_outputs_leave_the_single_cta_path():
     _check32(ops.mm_default(a32, b32), a32, b32)
     a32, b32 = torch.randn(1, 4096, generator=g, device=DEV), torch.randn(4096, 1024, generator=g, device=DEV)
     _check32(ops.mm_default(a32, b32), a32, b32)
+    for M, K, N in [(2, 130, 256), (55, 200, 70), (100, 257, 33), (33, 330, 130), (7, 400, 9), (140, 450, 20), (64, 513, 64), (3, 2048, 17), (165, 4096, 32), (44, 2072, 1024)]:
+        a32, b32, bias = torch.randn(M, K, generator=g, device=DEV), torch.randn(K, N, generator=g, device=DEV), torch.randn(M, 1, generator=g, device=DEV)
+        _check32(ops.mm_default(a32, b32), a32, b32)
+        _check32(ops.mm_default(a32.t().contiguous().t(), b32.t().contiguous().t()), a32, b32)  # both operands in the other memory order
+        _check32(ops.addmm_default(bias, a32, b32, beta=2, alpha=0.5), a32, b32, extra=bias.expand(M, N), alpha=0.5, beta=2.0)
+    a3, b3 = torch.randn(5, 21, 1024, generator=g, device=DEV), torch.randn(5, 1024, 40, generator=g, device=DEV)
+    a3[2, 3, 100] = float("inf")
+    b3[4, 7, 5] = float("nan")
+    got, ref = ops.bmm_default(a3, b3), torch.bmm(a3, b3)
+    assert torch.equal(torch.isnan(got), torch.isnan(ref)) and torch.equal(torch.isinf(got), torch.isinf(ref))
+    fin = torch.isfinite(ref)
+    assert torch.allclose(got[fin], ref[fin], atol=1e-3, rtol=1e-4)
+    for dt in (torch.float16, torch.bfloat16):  # 16-bit operands off the 16-byte grid, K below the re-pitch threshold
+        h, w = _rand((9, 1000), dt, g, 1000**-0.5), _rand((1000, 7), dt, g, 1.0)
+        _check(ops.mm_default(h, w), h.double() @ w.double(), dt)
     ops.check_device_status()

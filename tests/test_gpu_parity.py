@@ -374,6 +374,31 @@ def test_many_short_rows_and_long_non_last_dims(backend, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_short_rows_every_length_staged_and_direct(backend, dtype):
+    """Thread-per-row kernels over row lengths on both sides of each register-slot count (8,
+    16, 24, 32), with strides that are and are not multiples of 8 bytes (direct / staged
+    through shared memory), a last CTA holding 3 rows, and a base pointer off the 16-byte grid."""
+    g = torch.Generator().manual_seed(33)
+    jobs = []
+    for cols in (1, 3, 5, 8, 9, 10, 15, 16, 17, 21, 24, 25, 30, 31, 32):
+        x = torch.randn(4099 + 1, cols, generator=g).to(dtype)
+        x[9, cols // 2] = float("nan")
+        x[11, :] = float("-inf")
+        w, b = torch.randn(cols, generator=g).to(dtype), torch.randn(cols, generator=g).to(dtype)
+        xd, wd, bd = x.to(DEV), w.to(DEV), b.to(DEV)
+        for lo, hi in ((1, 4100), (0, 4099)):  # a view keeps its offset on the device: base off / on the 16-byte grid
+            v, vd = x[lo:hi], xd[lo:hi]
+            jobs += [("_softmax.default", [v, -1, False], [vd, -1, False]), ("_log_softmax.default", [v, -1, False], [vd, -1, False]), ("sum.dim_IntList", [v, [-1]], [vd, [-1]]),
+                     ("argmax.default", [v, -1], [vd, -1]), ("native_layer_norm.default", [v[12:], [cols], w, b, 1e-5], [vd[12:], [cols], wd, bd, 1e-5])]
+        if dtype != torch.float32:
+            jobs.append(("_softmax.default", [x[:4099], -1, True], [xd[:4099], -1, True]))  # half_to_float: fp32 output
+    for op_name, args, dev_args in jobs:
+        got = backend[get_operator(op_name)](*dev_args)
+        _check(op_name, oracle.run(op_name, args, {}), got, (op_name, tuple(args[0].shape), args[0].storage_offset()))
+    ops.check_device_status()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
 def test_ragged_mid_size_rows_one_warp_each(backend, dtype):
     """Rows of 33 ... 1024 elements off the 16-byte grid (odd lengths, or an odd base offset)
     take the warp-per-row kernels; a row with NaN and an all -inf row behave as in aten."""
