@@ -21,6 +21,11 @@ namespace b200 {
 
 constexpr float kLog2e = 1.4426950408889634f;
 
+template <typename T> constexpr int dtype_of();
+template <> constexpr int dtype_of<float>() { return B200_F32; }
+template <> constexpr int dtype_of<__nv_bfloat16>() { return B200_BF16; }
+template <> constexpr int dtype_of<__half>() { return B200_F16; }
+
 // ---- group = one warp (WARP) or the whole CTA: reductions over the threads of a row
 template <bool WARP, typename F>
 __device__ __forceinline__ float group_reduce(float v, F f, float identity, float* smem, int phase) {
@@ -201,6 +206,91 @@ __global__ void __launch_bounds__(256) softmax_stream(const T* __restrict__ x, v
   for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) {
     const float d = to_f32(xr[c]) - m;
     store_from_f32(out, row * cols + c, dto, is_log ? d - k : exp2f(d * kLog2e) * k);
+  }
+}
+
+// Long rows (more than the registers of a CTA hold) and rows whose start is off the 16-byte
+// grid, with 16-byte accesses all the same: the CTA walks the aligned span that covers its
+// row -- from `head` elements before the row's first element, inside the first element's
+// own 16-byte block, to the end of the last element's block -- and masks what lies outside
+// the row. Pass 1 keeps a running (max, sum of exponentials relative to it) per thread and
+// merges them over the CTA; pass 2 re-reads the row (from L2 for rows up to some hundreds
+// of KB), writes whole 16-byte vectors inside the row and single elements in the first and
+// last block. The output row must sit at the same offset inside its 16-byte block as the
+// input row and have the input's type. max.NaN makes a NaN element the maximum, hence the
+// whole row NaN, as the three-pass kernel above does through its sum.
+__device__ __forceinline__ float max_nan(float a, float b) {
+  float r;
+  asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+}
+// (m, s): s = sum of 2^((x - m) log2 e) over the elements seen; m = -inf means none yet (s = 0)
+__device__ __forceinline__ void online_merge(float& m, float& s, float m2, float s2) {
+  const float mn = max_nan(m, m2);
+  const float a = m == -CUDART_INF_F ? 0.f : s * ex2_approx((m - mn) * kLog2e);
+  const float b = m2 == -CUDART_INF_F ? 0.f : s2 * ex2_approx((m2 - mn) * kLog2e);
+  m = mn;
+  s = a + b;
+}
+template <typename T, bool IS_LOG>
+__global__ void __launch_bounds__(1024) softmax_stream_vec(const T* __restrict__ x, T* __restrict__ out, int64_t cols) {
+  constexpr int VE = Vec<T>::N;
+  __shared__ float red_m[32], red_s[32];
+  const int64_t row = blockIdx.x;
+  const T* xr = x + row * cols;
+  const int head = static_cast<int>((reinterpret_cast<uintptr_t>(xr) & 15u) / sizeof(T));
+  const T* xa = xr - head;
+  const int64_t nvec = (head + cols + VE - 1) / VE;
+  float m = -CUDART_INF_F, s = 0.f;
+  for (int64_t j = threadIdx.x; j < nvec; j += blockDim.x) {
+    float f[VE];
+    widen<T>(ld_keep(xa + j * VE), f);
+    const int64_t c0 = j * VE - head;
+    if (c0 < 0 || c0 + VE > cols) {
+#pragma unroll
+      for (int e = 0; e < VE; ++e)
+        if (c0 + e < 0 || c0 + e >= cols) f[e] = -CUDART_INF_F;
+    }
+    float lm = f[0];
+#pragma unroll
+    for (int e = 1; e < VE; ++e) lm = max_nan(lm, f[e]);
+    const float mn = max_nan(m, lm);
+    if (mn != m) {  // a new maximum (or a NaN): bring the sum so far onto it; 0 * 2^-inf when there was none
+      s *= ex2_approx((m - mn) * kLog2e);
+      m = mn;
+    }
+    if (m != -CUDART_INF_F) {
+#pragma unroll
+      for (int e = 0; e < VE; ++e) s += ex2_approx((f[e] - m) * kLog2e);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) online_merge(m, s, __shfl_xor_sync(0xffffffffu, m, o), __shfl_xor_sync(0xffffffffu, s, o));
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  if (lane == 0) { red_m[warp] = m; red_s[warp] = s; }
+  __syncthreads();
+  m = lane < nwarps ? red_m[lane] : -CUDART_INF_F;
+  s = lane < nwarps ? red_s[lane] : 0.f;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) online_merge(m, s, __shfl_xor_sync(0xffffffffu, m, o), __shfl_xor_sync(0xffffffffu, s, o));
+  const float k = IS_LOG ? logf(s) : 1.f / s;
+  T* orow = out + row * cols;
+  for (int64_t j = threadIdx.x; j < nvec; j += blockDim.x) {
+    float f[VE];
+    widen<T>(ld_stream(xa + j * VE), f);
+#pragma unroll
+    for (int e = 0; e < VE; ++e) {
+      const float d = f[e] - m;
+      f[e] = IS_LOG ? d - k : ex2_approx(d * kLog2e) * k;
+    }
+    const int64_t c0 = j * VE - head;
+    if (c0 >= 0 && c0 + VE <= cols) {
+      store_row_vec<T>(out, row * cols + c0, f, false);
+    } else {
+#pragma unroll
+      for (int e = 0; e < VE; ++e)
+        if (c0 + e >= 0 && c0 + e < cols) orow[c0 + e] = from_f32<T>(f[e]);
+    }
   }
 }
 
@@ -1094,7 +1184,16 @@ static int softmax_T(const void* x, void* out, int64_t outer, int64_t dim, int64
       else { B200_DISPATCH_NPL(dim, (softmax_warp_ragged<T, NPL, false><<<g, 128, 0, st>>>(px, out, outer, static_cast<int>(dim), dto))) }
     } else {
       if (outer > 0x7fffffffLL) return B200_EINVAL;
-      softmax_stream<T><<<static_cast<unsigned>(outer), 256, 0, st>>>(px, out, dim, dto, is_log);
+      // same type out, and rows of x and out at the same offset inside their 16-byte blocks
+      const bool vec = dto == dtype_of<T>() && ((reinterpret_cast<uintptr_t>(x) ^ reinterpret_cast<uintptr_t>(out)) & 15u) == 0;
+      if (vec) {
+        int64_t th = (dim / VE + 31) / 32 * 32;
+        th = th < 128 ? 128 : (th > 1024 ? 1024 : th);
+        if (is_log) softmax_stream_vec<T, true><<<static_cast<unsigned>(outer), static_cast<unsigned>(th), 0, st>>>(px, static_cast<T*>(out), dim);
+        else softmax_stream_vec<T, false><<<static_cast<unsigned>(outer), static_cast<unsigned>(th), 0, st>>>(px, static_cast<T*>(out), dim);
+      } else {
+        softmax_stream<T><<<static_cast<unsigned>(outer), 256, 0, st>>>(px, out, dim, dto, is_log);
+      }
     }
   } else {
     for (int64_t o0 = 0; o0 < outer; o0 += 65535) {

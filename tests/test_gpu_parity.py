@@ -399,6 +399,28 @@ def test_short_rows_every_length_staged_and_direct(backend, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_long_and_misaligned_rows_take_the_vector_streaming_softmax(backend, dtype):
+    """Rows too long for a CTA's registers (a vocabulary of 50257 or 131072 entries) and long
+    rows that start off the 16-byte grid: two passes of 16-byte accesses over the aligned
+    span around each row. Special rows: a NaN, all -inf, one +inf, -inf everywhere but one."""
+    g = torch.Generator().manual_seed(34)
+    for rows, cols in ((9, 1025), (7, 4099), (6, 33000), (5, 50257), (5, 131072), (6, 70001)):
+        x = (torch.randn(rows + 1, cols, generator=g) * 3).to(dtype)
+        x[1, cols // 3] = float("nan")
+        x[2, :] = float("-inf")
+        x[3, cols - 1] = float("inf")
+        x[4, :] = float("-inf")
+        x[4, 0] = 1.5
+        xd = x.to(DEV)
+        for lo in (0, 1):  # with odd `cols`, the view from row 1 starts off the 16-byte grid
+            v, vd = x[lo:lo + rows], xd[lo:lo + rows]
+            for op_name in ("_softmax.default", "_log_softmax.default"):
+                got = backend[get_operator(op_name)](vd, -1, False)
+                _check(op_name, oracle.run(op_name, [v, -1, False], {}), got, (op_name, rows, cols, lo))
+    ops.check_device_status()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
 def test_ragged_mid_size_rows_one_warp_each(backend, dtype):
     """Rows of 33 ... 1024 elements off the 16-byte grid (odd lengths, or an odd base offset)
     take the warp-per-row kernels; a row with NaN and an all -inf row behave as in aten."""
