@@ -939,29 +939,41 @@ __global__ void fill_zero_typed(void* out, int64_t n, int dto) {
 // ------------------------------------------------------------------ very short rows (dim <= 32, inner == 1)
 // Millions of rows of a handful of elements: one THREAD per row, the row in registers (NC
 // slots, the next multiple of 8 above the row length). A CTA owns 256 consecutive rows, one
-// contiguous span of memory, and reaches it in one of two ways.
+// contiguous span of memory, and reaches it in one of three ways.
 //   direct: each thread loads and stores its own row element by element. A warp-wide access
 //     then touches one 32-byte sector per lane, and the load/store unit spends a cycle per
-//     sector: the cost is ~2 x 32 x cols cycles per warp, far above the bytes moved.
-//   staged: the CTA copies the span into shared memory with 16-byte accesses, threads read
-//     and overwrite their rows there, and the span goes back out the same way. Used when the
-//     row stride is not a multiple of 8 bytes (bank conflicts stay at most 2-way) and the
-//     output has the input's element size.
+//     sector: the cost is ~2 x 32 x cols cycles per warp, far above the bytes moved. Kept
+//     for bases off the 16-byte grid and outputs of another element size.
+//   vector: rows that are whole 16-byte vectors are loaded and stored as such.
+//   staged: any other row length. The CTA copies its span into shared memory with 16-byte
+//     accesses, threads read and overwrite their rows there (the stride is not a multiple of
+//     16 bytes, so at most two lanes of a quarter-warp meet in a bank), and the span goes
+//     back out the same way.
 constexpr int kSmallRow = 32;
 constexpr int kSmallRows = 256;  // rows (threads) per CTA
 enum { SMALL_SOFTMAX = 0, SMALL_LOGSOFTMAX = 1, SMALL_SUM = 2, SMALL_ARGMAX = 3, SMALL_LAYERNORM = 4 };
+enum { SMALL_DIRECT = 0, SMALL_STAGED = 1, SMALL_VECTOR = 2 };
 
-template <typename T, int OP, int NC, bool STAGED>
+template <typename T, int OP, int NC, int MODE>
 __global__ void __launch_bounds__(kSmallRows) rows_small(const T* __restrict__ x, void* __restrict__ out, int64_t rows, int cols, int dto, const void* __restrict__ w,
                                                          const void* __restrict__ b, int dt_wb, void* __restrict__ mean, void* __restrict__ rstd, int dt_stat, float eps) {
   extern __shared__ __align__(16) unsigned char small_smem[];
   constexpr bool WRITES_ROWS = OP == SMALL_SOFTMAX || OP == SMALL_LOGSOFTMAX || OP == SMALL_LAYERNORM;
+  constexpr bool STAGED = MODE == SMALL_STAGED, VECTOR = MODE == SMALL_VECTOR;
   constexpr int VE = 16 / static_cast<int>(sizeof(T));
   const int tid = threadIdx.x;
   const int64_t row0 = static_cast<int64_t>(blockIdx.x) * kSmallRows;
   const int64_t row = row0 + tid;
   const bool live = row < rows;
   T* sm = reinterpret_cast<T*>(small_smem);
+  __shared__ float wb[2 * kSmallRow];  // layer norm: weight and bias as fp32 (1 and 0 when absent)
+  if (OP == SMALL_LAYERNORM) {
+    if (tid < cols) {
+      wb[tid] = w ? load_as_f32(w, tid, dt_wb) : 1.f;
+      wb[kSmallRow + tid] = b ? load_as_f32(b, tid, dt_wb) : 0.f;
+    }
+    if (!STAGED) __syncthreads();
+  }
   int span = 0;
   if (STAGED) {
     const int64_t left = rows - row0;
@@ -973,15 +985,28 @@ __global__ void __launch_bounds__(kSmallRows) rows_small(const T* __restrict__ x
     __syncthreads();
   }
   const T* xr = STAGED ? sm + tid * cols : x + row * cols;
-  T* orow = STAGED ? sm + tid * cols : static_cast<T*>(out) + row * cols;  // direct stores go through `put`
+  T* orow = sm + tid * cols;  // staged results overwrite the row in shared memory
+  float f[NC];
   auto put = [&](int c, float v) {
     if (STAGED) orow[c] = from_f32<T>(v);
+    else if (VECTOR) f[c] = v;  // in place: slot c has been consumed; stored as vectors below
     else store_from_f32(out, row * cols + c, dto, v);
   };
   if (live) {
-    float f[NC];
+    if (VECTOR) {
 #pragma unroll
-    for (int c = 0; c < NC; ++c) f[c] = c < cols ? to_f32(xr[c]) : 0.f;
+      for (int v = 0; v < NC / VE; ++v) {
+        if (v * VE < cols) {
+          widen<T>(ld_stream(xr + v * VE), f + v * VE);
+        } else {
+#pragma unroll
+          for (int e = 0; e < VE; ++e) f[v * VE + e] = 0.f;
+        }
+      }
+    } else {
+#pragma unroll
+      for (int c = 0; c < NC; ++c) f[c] = c < cols ? to_f32(xr[c]) : 0.f;
+    }
     if (OP == SMALL_SUM) {
       float s = 0.f;
 #pragma unroll
@@ -1010,12 +1035,7 @@ __global__ void __launch_bounds__(kSmallRows) rows_small(const T* __restrict__ x
       store_from_f32(rstd, row, dt_stat, rs);
 #pragma unroll
       for (int c = 0; c < NC; ++c)
-        if (c < cols) {
-          float r = (f[c] - mu) * rs;
-          if (w) r *= load_as_f32(w, c, dt_wb);
-          if (b) r += load_as_f32(b, c, dt_wb);
-          put(c, r);
-        }
+        if (c < cols) put(c, (f[c] - mu) * rs * wb[c] + wb[kSmallRow + c]);
     } else {
       float m = -CUDART_INF_F;
 #pragma unroll
@@ -1033,6 +1053,11 @@ __global__ void __launch_bounds__(kSmallRows) rows_small(const T* __restrict__ x
       for (int c = 0; c < NC; ++c)
         if (c < cols) put(c, OP == SMALL_LOGSOFTMAX ? f[c] - k : f[c] * k);
     }
+    if (VECTOR && WRITES_ROWS) {
+#pragma unroll
+      for (int v = 0; v < NC / VE; ++v)
+        if (v * VE < cols) store_row_vec<T>(out, row * cols + v * VE, f + v * VE, false);
+    }
   }
   if (STAGED && WRITES_ROWS) {
     __syncthreads();
@@ -1048,13 +1073,16 @@ static void launch_rows_small_nc(const void* x, void* out, int64_t rows, int col
                                  cudaStream_t st) {
   constexpr bool WRITES_ROWS = OP == SMALL_SOFTMAX || OP == SMALL_LOGSOFTMAX || OP == SMALL_LAYERNORM;
   const int g = grid_for(rows, kSmallRows);
-  // staged: row stride not a multiple of 8 bytes, 16-byte aligned bases, same-size output
-  const bool staged = (cols * sizeof(T)) % 8 != 0 && aligned16(x) && (!WRITES_ROWS || (dto == dti && aligned16(out)));
-  if (staged) {
+  // 16-byte accesses need 16-byte aligned bases and, for row results, an output of the input's type
+  const bool wide = aligned16(x) && (!WRITES_ROWS || (dto == dti && aligned16(out)));
+  const T* px = static_cast<const T*>(x);
+  if (wide && (cols * sizeof(T)) % 16 == 0) {
+    rows_small<T, OP, NC, SMALL_VECTOR><<<g, kSmallRows, 0, st>>>(px, out, rows, cols, dto, w, b, dt_wb, mean, rstd, dt_stat, eps);
+  } else if (wide) {
     const size_t smem = (static_cast<size_t>(kSmallRows) * cols * sizeof(T) + 15) / 16 * 16;
-    rows_small<T, OP, NC, true><<<g, kSmallRows, smem, st>>>(static_cast<const T*>(x), out, rows, cols, dto, w, b, dt_wb, mean, rstd, dt_stat, eps);
+    rows_small<T, OP, NC, SMALL_STAGED><<<g, kSmallRows, smem, st>>>(px, out, rows, cols, dto, w, b, dt_wb, mean, rstd, dt_stat, eps);
   } else {
-    rows_small<T, OP, NC, false><<<g, kSmallRows, 0, st>>>(static_cast<const T*>(x), out, rows, cols, dto, w, b, dt_wb, mean, rstd, dt_stat, eps);
+    rows_small<T, OP, NC, SMALL_DIRECT><<<g, kSmallRows, 0, st>>>(px, out, rows, cols, dto, w, b, dt_wb, mean, rstd, dt_stat, eps);
   }
 }
 

@@ -513,16 +513,30 @@ struct BucketArgs {
 };
 
 __device__ __forceinline__ bool bucket_decode(const BucketArgs& A, int64_t p, const int64_t* __restrict__ index, int64_t& dest, int64_t& so, int& pos, uint32_t* status) {
-  int64_t lin = p, oo = 0, io = 0;
+  int64_t oo = 0, io = 0;
   so = 0;
   pos = 0;
-  for (int d = A.ndim - 1; d >= 0; --d) {
-    const int64_t q = lin / A.shape[d], r = lin - q * A.shape[d];
-    io += r * A.idx_stride[d];
-    so += r * A.src_stride[d];
-    if (d == A.dim) pos = static_cast<int>(r);
-    else oo += r * A.out_stride[d];
-    lin = q;
+  if (A.n_idx <= 0x7fffffffLL) {  // coordinates by 32-bit division (a 64-bit one costs ~5x the instructions)
+    uint32_t lin = static_cast<uint32_t>(p);
+    for (int d = A.ndim - 1; d >= 0; --d) {
+      const uint32_t ext = static_cast<uint32_t>(A.shape[d]);
+      const uint32_t q = lin / ext, r = lin - q * ext;
+      io += r * A.idx_stride[d];
+      so += r * A.src_stride[d];
+      if (d == A.dim) pos = static_cast<int>(r);
+      else oo += r * A.out_stride[d];
+      lin = q;
+    }
+  } else {
+    int64_t lin = p;
+    for (int d = A.ndim - 1; d >= 0; --d) {
+      const int64_t q = lin / A.shape[d], r = lin - q * A.shape[d];
+      io += r * A.idx_stride[d];
+      so += r * A.src_stride[d];
+      if (d == A.dim) pos = static_cast<int>(r);
+      else oo += r * A.out_stride[d];
+      lin = q;
+    }
   }
   const int64_t key = index[io];
   if (key < 0 || key >= A.self_dim_size) {
@@ -594,12 +608,21 @@ __global__ void __launch_bounds__(1024) scan_totals(int* __restrict__ totals, in
 __global__ void __launch_bounds__(kScanBlock) scan_apply(int* __restrict__ cnt_offs, int* __restrict__ cursor, const int* __restrict__ totals, int64_t n) {
   __shared__ int warp_sums[kScanBlock / 32];
   const int64_t base = static_cast<int64_t>(blockIdx.x) * kScanTile + static_cast<int64_t>(threadIdx.x) * kScanItems;
+  // a thread's 16 counters are 64 contiguous, 64-byte aligned bytes: four 16-byte accesses
+  const bool whole = base + kScanItems <= n && ((reinterpret_cast<uintptr_t>(cnt_offs) | reinterpret_cast<uintptr_t>(cursor)) & 15u) == 0;
   int v[kScanItems], s = 0;
+  if (whole) {
 #pragma unroll
-  for (int k = 0; k < kScanItems; ++k) {
-    v[k] = base + k < n ? cnt_offs[base + k] : 0;
-    s += v[k];
+    for (int q = 0; q < kScanItems / 4; ++q) {
+      const int4 t = reinterpret_cast<const int4*>(cnt_offs + base)[q];
+      v[4 * q] = t.x; v[4 * q + 1] = t.y; v[4 * q + 2] = t.z; v[4 * q + 3] = t.w;
+    }
+  } else {
+#pragma unroll
+    for (int k = 0; k < kScanItems; ++k) v[k] = base + k < n ? cnt_offs[base + k] : 0;
   }
+#pragma unroll
+  for (int k = 0; k < kScanItems; ++k) s += v[k];
   int inc = s;
   for (int o = 1; o < 32; o <<= 1) {
     const int y = __shfl_up_sync(0xffffffffu, inc, o);
@@ -609,6 +632,19 @@ __global__ void __launch_bounds__(kScanBlock) scan_apply(int* __restrict__ cnt_o
   __syncthreads();
   int prefix = totals[blockIdx.x] + inc - s;
   for (int w = 0; w < (threadIdx.x >> 5); ++w) prefix += warp_sums[w];
+  if (whole) {
+#pragma unroll
+    for (int q = 0; q < kScanItems / 4; ++q) {
+      int4 t;
+      t.x = prefix; prefix += v[4 * q];
+      t.y = prefix; prefix += v[4 * q + 1];
+      t.z = prefix; prefix += v[4 * q + 2];
+      t.w = prefix; prefix += v[4 * q + 3];
+      reinterpret_cast<int4*>(cnt_offs + base)[q] = t;
+      reinterpret_cast<int4*>(cursor + base)[q] = t;
+    }
+    return;
+  }
 #pragma unroll
   for (int k = 0; k < kScanItems; ++k) {
     if (base + k < n) {
@@ -620,15 +656,14 @@ __global__ void __launch_bounds__(kScanBlock) scan_apply(int* __restrict__ cnt_o
 }
 
 template <typename T>
-__global__ void __launch_bounds__(256) bucket_fill(const int64_t* __restrict__ index, const T* __restrict__ src, int* __restrict__ cursor, int* __restrict__ seg_pos, float* __restrict__ seg_val,
+__global__ void __launch_bounds__(256) bucket_fill(const int64_t* __restrict__ index, const T* __restrict__ src, int* __restrict__ cursor, int2* __restrict__ seg,
                                                    BucketArgs A, uint32_t* status) {
   for (int64_t p = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; p < A.n_idx; p += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     int64_t dest, so;
     int pos;
     if (bucket_decode(A, p, index, dest, so, pos, status)) {
       const int slot = atomicAdd(&cursor[dest], 1);
-      seg_pos[slot] = pos;
-      seg_val[slot] = to_f32(src[so]);
+      seg[slot] = make_int2(pos, __float_as_int(to_f32(src[so])));  // (position, value) in one 8-byte store
     }
   }
 }
@@ -636,7 +671,7 @@ __global__ void __launch_bounds__(256) bucket_fill(const int64_t* __restrict__ i
 // One thread per destination: replay its segment in ascending source position.
 template <typename T>
 __global__ void __launch_bounds__(256) bucket_replay(const T* __restrict__ self, T* __restrict__ out, const int* __restrict__ offs, const int* __restrict__ grand_total,
-                                                     const int* __restrict__ seg_pos, const float* __restrict__ seg_val, int64_t n_self, int* __restrict__ heavy_count,
+                                                     const int2* __restrict__ seg, int64_t n_self, int* __restrict__ heavy_count,
                                                      int* __restrict__ heavy_list) {
   for (int64_t d = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; d < n_self; d += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     const int b = offs[d], e = d + 1 < n_self ? offs[d + 1] : *grand_total;
@@ -650,8 +685,8 @@ __global__ void __launch_bounds__(256) bucket_replay(const T* __restrict__ self,
         int best = 0x7fffffff;
         float bv = 0.f;
         for (int j = b; j < e; ++j) {
-          const int pj = seg_pos[j];
-          if (pj > last && pj < best) { best = pj; bv = seg_val[j]; }
+          const int2 pv = seg[j];
+          if (pv.x > last && pv.x < best) { best = pv.x; bv = __int_as_float(pv.y); }
         }
         acc += bv;
         last = best;
@@ -668,7 +703,7 @@ __global__ void __launch_bounds__(256) bucket_replay(const T* __restrict__ self,
 // the occupied slots are compacted in order with a block scan, and one thread adds them.
 template <typename T>
 __global__ void __launch_bounds__(256) bucket_replay_heavy(const T* __restrict__ self, T* __restrict__ out, const int* __restrict__ offs, const int* __restrict__ grand_total,
-                                                           const int* __restrict__ seg_pos, const float* __restrict__ seg_val, int64_t n_self, int64_t dim_len,
+                                                           const int2* __restrict__ seg, int64_t n_self, int64_t dim_len,
                                                            const int* __restrict__ heavy_count, const int* __restrict__ heavy_list) {
   __shared__ float slot_val[kHeavyWindow];
   __shared__ unsigned char slot_set[kHeavyWindow];
@@ -686,9 +721,10 @@ __global__ void __launch_bounds__(256) bucket_replay_heavy(const T* __restrict__
       for (int i = threadIdx.x; i < kHeavyWindow; i += 256) slot_set[i] = 0;
       __syncthreads();
       for (int j = b + threadIdx.x; j < e; j += 256) {
-        const int64_t pj = seg_pos[j];
+        const int2 pv = seg[j];
+        const int64_t pj = pv.x;
         if (pj >= w0 && pj < w0 + kHeavyWindow) {
-          slot_val[pj - w0] = seg_val[j];
+          slot_val[pj - w0] = __int_as_float(pv.y);
           slot_set[pj - w0] = 1;
         }
       }
@@ -745,8 +781,7 @@ static int launch_bucket(const void* self, const void* index, const void* src, v
   char* base = static_cast<char*>(scratch);
   int* offs = reinterpret_cast<int*>(base);
   int* cursor = reinterpret_cast<int*>(base + S.offs_bytes);
-  int* seg_pos = reinterpret_cast<int*>(base + S.offs_bytes + S.cursor_bytes);
-  float* seg_val = reinterpret_cast<float*>(base + S.offs_bytes + S.cursor_bytes + S.pos_bytes);
+  int2* seg = reinterpret_cast<int2*>(base + S.offs_bytes + S.cursor_bytes);  // (source position, value bits) per contribution: pos_bytes + val_bytes
   int* totals = reinterpret_cast<int*>(base + S.offs_bytes + S.cursor_bytes + S.pos_bytes + S.val_bytes);
   int* heavy = reinterpret_cast<int*>(base + S.offs_bytes + S.cursor_bytes + S.pos_bytes + S.val_bytes + S.totals_bytes);  // [0] count, [1] grand total, [4..] list
   cudaError_t e = cudaMemsetAsync(offs, 0, static_cast<size_t>(S.offs_bytes), st);
@@ -759,9 +794,9 @@ static int launch_bucket(const void* self, const void* index, const void* src, v
   scan_tile_totals<<<static_cast<unsigned>(ntiles), kScanBlock, 0, st>>>(offs, totals, A.n_self);
   scan_totals<<<1, 1024, 0, st>>>(totals, ntiles, heavy + 1);
   scan_apply<<<static_cast<unsigned>(ntiles), kScanBlock, 0, st>>>(offs, cursor, totals, A.n_self);
-  bucket_fill<T><<<grid(A.n_idx, 256), 256, 0, st>>>(pi, static_cast<const T*>(src), cursor, seg_pos, seg_val, A, status);
-  bucket_replay<T><<<grid(A.n_self, 256), 256, 0, st>>>(static_cast<const T*>(self), static_cast<T*>(out), offs, heavy + 1, seg_pos, seg_val, A.n_self, heavy, heavy + 4);
-  bucket_replay_heavy<T><<<2 * kNumSMs, 256, 0, st>>>(static_cast<const T*>(self), static_cast<T*>(out), offs, heavy + 1, seg_pos, seg_val, A.n_self, A.dim_len, heavy, heavy + 4);
+  bucket_fill<T><<<grid(A.n_idx, 256), 256, 0, st>>>(pi, static_cast<const T*>(src), cursor, seg, A, status);
+  bucket_replay<T><<<grid(A.n_self, 256), 256, 0, st>>>(static_cast<const T*>(self), static_cast<T*>(out), offs, heavy + 1, seg, A.n_self, heavy, heavy + 4);
+  bucket_replay_heavy<T><<<2 * kNumSMs, 256, 0, st>>>(static_cast<const T*>(self), static_cast<T*>(out), offs, heavy + 1, seg, A.n_self, A.dim_len, heavy, heavy + 4);
   return check_launch(7);
 }
 
