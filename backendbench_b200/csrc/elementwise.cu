@@ -216,13 +216,24 @@ __global__ void __launch_bounds__(kEwThreads) where_strided(const uint8_t* c, co
 // [batch, rows, cols] gather from arbitrary element strides into a pitched destination
 // (unit column stride): how the host gives a tensor-core GEMM operand a 16-byte-aligned
 // row pitch when the caller's layout has none.
+// One warp per row, lanes along the columns: no per-element index division (a flat index
+// costs two 64-bit divisions per 2-byte element), coalesced on both sides when the source
+// has unit column stride.
 template <typename U>
 __global__ void __launch_bounds__(kEwThreads) copy_pitched(const U* __restrict__ x, U* __restrict__ out, int64_t batch, int64_t rows, int64_t cols, int64_t sxb, int64_t sxr,
                                                            int64_t sxc, int64_t opb, int64_t opr) {
-  const int64_t total = batch * rows * cols;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * kEwThreads + threadIdx.x; i < total; i += static_cast<int64_t>(gridDim.x) * kEwThreads) {
-    const int64_t c = i % cols, r = (i / cols) % rows, b = i / (cols * rows);
-    out[b * opb + r * opr + c] = x[b * sxb + r * sxr + c * sxc];
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = static_cast<int64_t>(gridDim.x) * (kEwThreads / 32);
+  for (int64_t rr = static_cast<int64_t>(blockIdx.x) * (kEwThreads / 32) + (threadIdx.x >> 5); rr < batch * rows; rr += warps) {
+    const int64_t b = rr / rows, r = rr - b * rows;
+    const U* src = x + b * sxb + r * sxr;
+    U* dst = out + b * opb + r * opr;
+    int64_t c = lane;
+    for (; c + 96 < cols; c += 128) {  // four independent loads in flight per lane
+      const U v0 = src[c * sxc], v1 = src[(c + 32) * sxc], v2 = src[(c + 64) * sxc], v3 = src[(c + 96) * sxc];
+      dst[c] = v0; dst[c + 32] = v1; dst[c + 64] = v2; dst[c + 96] = v3;
+    }
+    for (; c < cols; c += 32) dst[c] = src[c * sxc];
   }
 }
 
@@ -509,7 +520,9 @@ extern "C" int b200_copy_pitched(const void* x, void* out, int64_t batch, int64_
   if (batch == 0 || rows == 0 || cols == 0) return B200_OK;
   if (!x || !out) return B200_EINVAL;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int g = strided_grid(batch * rows * cols);
+  int64_t blocks = (batch * rows + kEwThreads / 32 - 1) / (kEwThreads / 32);
+  if (blocks > kNumSMs * 16LL) blocks = kNumSMs * 16LL;
+  const int g = static_cast<int>(blocks);
   switch (elem_size) {
     case 2: copy_pitched<uint16_t><<<g, kEwThreads, 0, st>>>(static_cast<const uint16_t*>(x), static_cast<uint16_t*>(out), batch, rows, cols, sxb, sxr, sxc, out_batch_pitch, out_row_pitch); break;
     case 4: copy_pitched<uint32_t><<<g, kEwThreads, 0, st>>>(static_cast<const uint32_t*>(x), static_cast<uint32_t*>(out), batch, rows, cols, sxb, sxr, sxc, out_batch_pitch, out_row_pitch); break;

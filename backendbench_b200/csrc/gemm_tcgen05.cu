@@ -383,6 +383,34 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             tma_store_3d(&map_c, smem_u32(mine), static_cast<int>(nb), static_cast<int>(m0 + q * 32), static_cast<int>(b));
             tma_store_commit();
           }
+        } else if (sizeof(TO) == 2) {
+          // 16-bit C whose rows are off the 16-byte grid (N not a multiple of 8): a lane owns a
+          // row, so storing from registers would put every lane of a store in another row, one
+          // 32-byte sector per 2-byte element. Park the chunk in the warp's buffer as above and
+          // write it out row by row, 64 contiguous bytes per store.
+          unsigned char* mine = epi_stage + (warp - 2) * kEpiStageBytes;
+          __syncwarp();  // the previous chunk has been read out of the buffer
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            const int64_t n = nb + g * 8;
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              v[e] = p.alpha * __uint_as_float(rc[g * 8 + e]);
+              if (p.has_bias && m < p.M && n + e < p.N) v[e] = fmaf(p.beta, to_f32(bias[m * p.sbm + (n + e) * p.sbn]), v[e]);
+            }
+            *reinterpret_cast<uint4*>(mine + lane * 128 + ((g ^ (lane & 7)) << 4)) = narrow<T>(v);
+          }
+          __syncwarp();
+          const int64_t left = p.N - nb;
+          const int ncols = left < 64 ? static_cast<int>(left) : 64;  // <= 0: the chunk lies right of C
+          for (int rr = 0; rr < 32; ++rr) {
+            const int64_t mr = m0 + q * 32 + rr;
+            if (mr >= p.M) break;
+            TO* crow = C + (b * p.M + mr) * p.N + nb;
+            for (int cc = lane; cc < ncols; cc += 32)
+              crow[cc] = *reinterpret_cast<const TO*>(mine + rr * 128 + (((cc >> 3) ^ (rr & 7)) << 4) + (cc & 7) * 2);
+          }
         } else if (m < p.M && nb < p.N) {
           TO* crow = C + (b * p.M + m) * p.N;
 #pragma unroll

@@ -673,8 +673,12 @@ def _gemm(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor], batch:
     # planes each in scratch memory and six plane products are accumulated in fp32, which
     # keeps fp32 accuracy (see include/b200ops.h). Small ones stay on the CUDA-core kernel,
     # which shares a long contraction with few outputs among the CTAs of a cluster.
+    # A product of only a handful of tensor-core tiles (M below two tiles, few column tiles)
+    # leaves the split path one CTA per tile walking six plane pairs of all of K; the
+    # CUDA-core kernel with K shared among a cluster is faster there.
     macs = batch * M * N * K
-    if a.dtype == torch.float32 and macs >= F32_SPLIT_MIN_MACS and K >= 32 and M >= 32 and N >= 32:
+    tc_tiles = batch * ((M + 127) // 128) * ((N + 255) // 256)
+    if a.dtype == torch.float32 and macs >= F32_SPLIT_MIN_MACS and K >= 32 and M >= 32 and N >= 32 and (tc_tiles >= 8 or macs >= (1 << 30)):
         need = int(lib().b200_gemm_f32_scratch_bytes(batch, M, N, K))
         if need > 0:
             scratch = _scratch(a.device, need)

@@ -167,6 +167,23 @@ def test_split_fp32_product_keeps_special_values_and_wide_ranges():
     ops.check_device_status()
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_odd_output_widths_on_the_tensor_core_path(dtype):
+    """N off the 8-element grid: B is re-pitched, C rows start at odd addresses, and the
+    epilogue writes them row by row from its staging buffer (every column tail length, a
+    ragged last row block, batches, bias and scaling)."""
+    g = torch.Generator(device=DEV).manual_seed(15)
+    for M, N, K in [(300, 513, 192), (1000, 127, 1024), (129, 65, 2048), (4100, 255, 64), (257, 1, 4096), (640, 71, 512)]:
+        a, b = _rand((M, K), dtype, g, K**-0.5), _rand((K, N), dtype, g, 1.0)
+        exact = a.double() @ b.double()
+        _check(ops.mm_default(a, b), exact, dtype)
+        bias = _rand((N,), dtype, g, 1.0)
+        _check(ops.addmm_default(bias, a, b, beta=0.5, alpha=2), 2 * exact + 0.5 * bias.double(), dtype)
+    a3, b3 = _rand((5, 700, 256), dtype, g, 1 / 16), _rand((5, 256, 127), dtype, g, 1.0)
+    _check(ops.bmm_default(a3, b3), a3.double() @ b3.double(), dtype)
+    ops.check_device_status()
+
+
 def test_long_contractions_with_small_outputs_leave_the_single_cta_path():
     """K in the thousands with a handful of outputs: 16-bit operands are re-pitched onto the
     tensor cores whatever their alignment, fp32 operands share K among the CTAs of a cluster
