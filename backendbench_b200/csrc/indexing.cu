@@ -30,6 +30,11 @@ __device__ __forceinline__ uint32_t ld_keep_l2(const uint32_t* p, uint64_t pol) 
   asm volatile("ld.global.nc.L2::cache_hint.u32 %0, [%1], %2;" : "=r"(v) : "l"(p), "l"(pol));
   return v;
 }
+__device__ __forceinline__ uint16_t ld_keep_l2(const uint16_t* p, uint64_t pol) {
+  uint16_t v;
+  asm volatile("ld.global.nc.L2::cache_hint.u16 %0, [%1], %2;" : "=h"(v) : "l"(p), "l"(pol));
+  return v;
+}
 template <typename U> __device__ __forceinline__ U zero_of() { U z; memset(&z, 0, sizeof(U)); return z; }
 
 // One CTA (128 threads) per output row; rows are `nvec` 16-byte vectors.
@@ -82,12 +87,24 @@ struct GatherArgs {
 template <typename U>
 __global__ void __launch_bounds__(256) gather_generic(const U* __restrict__ self, const int64_t* __restrict__ index, U* __restrict__ out, GatherArgs A, uint32_t* status) {
   for (int64_t p = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; p < A.n; p += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    int64_t lin = p, io = 0, so = 0;
-    for (int d = A.ndim - 1; d >= 0; --d) {
-      const int64_t q = lin / A.shape[d], r = lin - q * A.shape[d];
-      io += r * A.idx_stride[d];
-      if (d != A.dim) so += r * A.self_stride[d];
-      lin = q;
+    int64_t io = 0, so = 0;
+    if (A.n <= 0x7fffffffLL) {  // coordinates by 32-bit division (a 64-bit one costs ~5x the instructions)
+      uint32_t lin = static_cast<uint32_t>(p);
+      for (int d = A.ndim - 1; d >= 0; --d) {
+        const uint32_t ext = static_cast<uint32_t>(A.shape[d]);
+        const uint32_t q = lin / ext, r = lin - q * ext;
+        io += r * A.idx_stride[d];
+        if (d != A.dim) so += r * A.self_stride[d];
+        lin = q;
+      }
+    } else {
+      int64_t lin = p;
+      for (int d = A.ndim - 1; d >= 0; --d) {
+        const int64_t q = lin / A.shape[d], r = lin - q * A.shape[d];
+        io += r * A.idx_stride[d];
+        if (d != A.dim) so += r * A.self_stride[d];
+        lin = q;
+      }
     }
     const int64_t k = index[io];
     if (k < 0 || k >= A.self_dim_size) {
@@ -100,35 +117,41 @@ __global__ void __launch_bounds__(256) gather_generic(const U* __restrict__ self
 }
 
 // 2-D, dim 0, contiguous index [R, C] and unit column stride in self (row pitch
-// `self_pitch`): each thread produces 4 adjacent outputs -- two 16-byte index loads,
-// four sector reads, one 16-byte store (4-byte elements). The columns are walked in blocks
-// of `wcols` (blockIdx.y), chosen so that the slice of `self` a block of columns can touch
-// (self_rows x wcols) stays L2-resident while index and output stream past it: every source
-// sector then comes from DRAM once instead of once per eviction.
-__global__ void __launch_bounds__(256) gather_dim0_vec4(const uint32_t* __restrict__ self, const int64_t* __restrict__ index, uint32_t* __restrict__ out,
-                                                        int64_t rows, int64_t cols, int64_t self_pitch, int64_t self_rows, int64_t wcols, uint32_t* status) {
+// `self_pitch`): each thread produces the 16 bytes of adjacent outputs (4 or 8 elements) --
+// 16-byte index loads, one sector read per element, one 16-byte store. The columns are
+// walked in blocks of `wcols` (blockIdx.y), chosen so that the slice of `self` a block of
+// columns can touch (self_rows x wcols) stays L2-resident while index and output stream past
+// it: every source sector then comes from DRAM once instead of once per eviction.
+template <typename U>
+__global__ void __launch_bounds__(256) gather_dim0_vec(const U* __restrict__ self, const int64_t* __restrict__ index, U* __restrict__ out, int64_t rows, int64_t cols,
+                                                       int64_t self_pitch, int64_t self_rows, int64_t wcols, uint32_t* status) {
+  constexpr int VE = 16 / static_cast<int>(sizeof(U));
   const int64_t j0 = static_cast<int64_t>(blockIdx.y) * wcols;
   const int64_t wb = cols - j0 < wcols ? cols - j0 : wcols;
-  const int64_t qpr = wb / 4;  // quads per row inside this column block
-  const int64_t nquad = rows * qpr;
+  const int64_t gpr = wb / VE;  // 16-byte groups per row inside this column block
+  const int64_t ngroup = rows * gpr;
   const uint64_t keep = l2_keep_policy();
-  for (int64_t q = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; q < nquad; q += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int64_t i = q / qpr, col = j0 + (q - i * qpr) * 4;
+  for (int64_t q = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; q < ngroup; q += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t i = q / gpr, col = j0 + (q - i * gpr) * VE;
     const int64_t p = i * cols + col;
-    const longlong2 i01 = __ldcs(reinterpret_cast<const longlong2*>(index + p));
-    const longlong2 i23 = __ldcs(reinterpret_cast<const longlong2*>(index + p + 2));
-    const int64_t k[4] = {i01.x, i01.y, i23.x, i23.y};
-    uint32_t v[4];
+    int64_t k[VE];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
+    for (int h = 0; h < VE / 2; ++h) {
+      const longlong2 t = __ldcs(reinterpret_cast<const longlong2*>(index + p) + h);
+      k[2 * h] = t.x;
+      k[2 * h + 1] = t.y;
+    }
+    __align__(16) U v[VE];
+#pragma unroll
+    for (int e = 0; e < VE; ++e) {
       if (k[e] < 0 || k[e] >= self_rows) {
         flag_oob(status);
-        v[e] = 0;
+        v[e] = zero_of<U>();
       } else {
         v[e] = ld_keep_l2(self + k[e] * self_pitch + col + e, keep);
       }
     }
-    __stcs(reinterpret_cast<uint4*>(out + p), make_uint4(v[0], v[1], v[2], v[3]));
+    __stcs(reinterpret_cast<uint4*>(out + p), *reinterpret_cast<const uint4*>(v));
   }
 }
 
@@ -343,16 +366,20 @@ extern "C" int b200_gather(const void* self, const void* index, void* out, int n
                                                                               index_shape[1], self_strides[0], static_cast<int>(self_dim_size), static_cast<int>(whole), static_cast<int>(tail_split), status);
     return check_launch();
   }
-  if (ndim == 2 && dim == 0 && elem_size == 4 && idx_contig && self_strides[1] == 1 && index_shape[1] % 4 == 0 && aligned16(index) && aligned16(out)) {
-    // column block: about 16 MB of `self` (self_rows x wcols x 4 bytes), a multiple of 4 columns
-    int64_t wcols = (16LL << 20) / (4 * (self_dim_size > 0 ? self_dim_size : 1));
-    wcols = wcols / 4 * 4;
+  const int ve = elem_size == 4 ? 4 : 8;  // outputs per 16 bytes
+  if (ndim == 2 && dim == 0 && (elem_size == 4 || elem_size == 2) && idx_contig && self_strides[1] == 1 && index_shape[1] % ve == 0 && aligned16(index) && aligned16(out)) {
+    // column block: about 16 MB of `self` (self_rows x wcols elements), a multiple of the group width
+    int64_t wcols = (16LL << 20) / (elem_size * (self_dim_size > 0 ? self_dim_size : 1));
+    wcols = wcols / ve * ve;
     if (wcols < 64) wcols = 64;
     if (wcols > index_shape[1]) wcols = index_shape[1];
     const int64_t nblocks = (index_shape[1] + wcols - 1) / wcols;
     if (nblocks <= 65535) {
-      dim3 grid(capped_grid(index_shape[0] * wcols / 4, 256, 32), static_cast<unsigned>(nblocks));
-      gather_dim0_vec4<<<grid, 256, 0, st>>>(static_cast<const uint32_t*>(self), static_cast<const int64_t*>(index), static_cast<uint32_t*>(out), index_shape[0], index_shape[1], self_strides[0], self_dim_size, wcols, status);
+      dim3 grid(capped_grid(index_shape[0] * wcols / ve, 256, 32), static_cast<unsigned>(nblocks));
+      if (elem_size == 4)
+        gather_dim0_vec<uint32_t><<<grid, 256, 0, st>>>(static_cast<const uint32_t*>(self), static_cast<const int64_t*>(index), static_cast<uint32_t*>(out), index_shape[0], index_shape[1], self_strides[0], self_dim_size, wcols, status);
+      else
+        gather_dim0_vec<uint16_t><<<grid, 256, 0, st>>>(static_cast<const uint16_t*>(self), static_cast<const int64_t*>(index), static_cast<uint16_t*>(out), index_shape[0], index_shape[1], self_strides[0], self_dim_size, wcols, status);
       return check_launch();
     }
   }
