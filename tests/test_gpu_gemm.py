@@ -184,6 +184,32 @@ def test_odd_output_widths_on_the_tensor_core_path(dtype):
     ops.check_device_status()
 
 
+def test_many_rows_few_columns_take_the_row_per_thread_kernel():
+    """fp32 (and 16-bit below the re-pitch threshold) products with at most 16 output columns
+    and some hundred thousand rows: both accumulator counts (8, 16), K tails that are not whole
+    16-byte vectors, K longer than one chunk of B, batches, bias and scaling, specials; and
+    the same shapes just outside the kernel's range (19 and 32 columns, few rows)."""
+    g = torch.Generator(device=DEV).manual_seed(16)
+    for M, K, N in [(80000, 256, 8), (76000, 300, 13), (100000, 64, 1), (16384, 1024, 19), (9473, 2060, 32), (12000, 600, 13)]:
+        a32, b32, bias = torch.randn(M, K, generator=g, device=DEV), torch.randn(K, N, generator=g, device=DEV), torch.randn(1, N, generator=g, device=DEV)
+        _check32(ops.mm_default(a32, b32), a32, b32)
+        _check32(ops.addmm_default(bias, a32, b32, beta=2, alpha=0.5), a32, b32, extra=bias.expand(M, N), alpha=0.5, beta=2.0)
+    wide = torch.randn(90000, 132, generator=g, device=DEV)
+    a32, b32 = wide[:, :130], torch.randn(130, 5, generator=g, device=DEV)  # rows 16-byte aligned, K = 130 leaves a tail of 2
+    _check32(ops.mm_default(a32, b32), a32, b32)
+    a3, b3 = torch.randn(16, 8192, 96, generator=g, device=DEV), torch.randn(16, 96, 5, generator=g, device=DEV)
+    a3[3, 100, 7] = float("inf")
+    b3[9, 50, 2] = float("nan")
+    got, ref = ops.bmm_default(a3, b3), torch.bmm(a3, b3)
+    assert torch.equal(torch.isnan(got), torch.isnan(ref)) and torch.equal(torch.isinf(got), torch.isinf(ref))
+    fin = torch.isfinite(ref)
+    assert torch.allclose(got[fin], ref[fin], atol=1e-4, rtol=1e-4)
+    for dt in (torch.bfloat16, torch.float16):
+        h, w = _rand((90000, 64), dt, g, 1 / 8), _rand((64, 6), dt, g, 1.0)
+        _check(ops.mm_default(h, w), h.double() @ w.double(), dt)
+    ops.check_device_status()
+
+
 def test_long_contractions_with_small_outputs_leave_the_single_cta_path():
     """K in the thousands with a handful of outputs: 16-bit operands are re-pitched onto the
     tensor cores whatever their alignment, fp32 operands share K among the CTAs of a cluster
