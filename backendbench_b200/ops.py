@@ -346,8 +346,10 @@ _scratch_cache = {}
 
 
 def _scratch(device: torch.device, nbytes: int) -> torch.Tensor:
-    """A per-device scratch buffer of at least `nbytes` (grown geometrically, reused)."""
-    key = device.index if device.index is not None else torch.cuda.current_device()
+    """A scratch buffer of at least `nbytes` for the current stream of `device` (grown
+    geometrically, reused; per stream, so that operators queued on different streams never
+    share one)."""
+    key = (device.index if device.index is not None else torch.cuda.current_device(), torch.cuda.current_stream().cuda_stream)
     buf = _scratch_cache.get(key)
     if buf is None or buf.numel() < nbytes:
         buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)

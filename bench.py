@@ -145,14 +145,35 @@ def prepare_cases(cases, backend, device):
     return prepared
 
 
-def sweep_enqueue(prepared, records):
-    """Queue one correctness pass (backend launch + fused compare per case); no read-back."""
+def sweep_enqueue(prepared, records, streams=None):
+    """Queue one correctness pass (backend launch + fused compare per case); no read-back.
+    With `streams`, case i goes to streams[i % len(streams)]: the cases are independent (own
+    inputs, own output, own verdict record, per-stream scratch), so their launch chains can
+    run side by side -- most cases are too small to fill the GPU and their cost is the launch
+    gap, not the kernel. The current stream forks to the side streams and joins them again,
+    which under graph capture yields a graph with that many parallel branches."""
     from backendbench_b200.eval import compare_enqueue
 
     structural = []
+    if not streams:
+        for i, p in enumerate(prepared):
+            res = p["impl"](*p["args"], **p["kwargs"])
+            structural.append(compare_enqueue(p["ref"], res, p["atol"], p["rtol"], records[i]))
+        return structural
+    cur = torch.cuda.current_stream()
+    fork = torch.cuda.Event()
+    fork.record(cur)
+    for s in streams:
+        s.wait_event(fork)
     for i, p in enumerate(prepared):
-        res = p["impl"](*p["args"], **p["kwargs"])
-        structural.append(compare_enqueue(p["ref"], res, p["atol"], p["rtol"], records[i]))
+        with torch.cuda.stream(streams[i % len(streams)]):
+            res = p["impl"](*p["args"], **p["kwargs"])
+            structural.append(compare_enqueue(p["ref"], res, p["atol"], p["rtol"], records[i]))
+            del res
+    for s in streams:
+        join = torch.cuda.Event()
+        join.record(s)
+        cur.wait_event(join)
     return structural
 
 
@@ -368,12 +389,15 @@ def run_b200(args):
     # CUDA graph; a timed step replays the graph and reads the verdict records back.
     eager_ms, _ = time_steps(lambda: sweep_pass(prepared, records), 1, max(args.warmup, 2))
     graph, structural = None, None
+    streams = [torch.cuda.Stream(device=device) for _ in range(args.sweep_streams)] if args.sweep_streams > 1 else None
     if not args.no_graph:
         try:
+            if streams:  # one eager multi-stream pass sizes the per-stream scratch buffers
+                sweep_enqueue(prepared, records, streams)
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
-                structural = sweep_enqueue(prepared, records)
+                structural = sweep_enqueue(prepared, records, streams)
             torch.cuda.synchronize()
         except Exception as e:  # capture is an optimisation: fall back to eager launches
             print(f"[bench] CUDA graph capture failed, timing eager launches: {e!r}", file=sys.stderr)
@@ -411,7 +435,7 @@ def run_b200(args):
         "ms_per_step": round(total_ms / args.steps, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32/bf16/f16 (fp32 accumulate)",
         "data": "synthetic", "impl": "b200",
         "config": {"workload": "sharded sweep: 512 seeded (op, shape, dtype) cases over 16 aten overloads, 2^8..2^26 elements, 15% edge cases; one correctness pass per step",
-                   "cases_per_rank": len(prepared), "launches": "one pass captured in a CUDA graph and replayed per step (eager_cases_per_sec: the same pass launched from Python)", "inputs": "resident in HBM, larger than L2 in total (about 10 GB per rank)", "reference_results": "aten CUDA (aten CPU for scatter_add), precomputed, resident",
+                   "cases_per_rank": len(prepared), "launches": f"one pass captured in a CUDA graph of {len(streams) if streams else 1} parallel branch(es) (case i on branch i mod n) and replayed per step (eager_cases_per_sec: the same pass launched from Python on one stream)", "inputs": "resident in HBM, larger than L2 in total (about 10 GB per rank)", "reference_results": "aten CUDA (aten CPU for scatter_add), precomputed, resident",
                    "parallelism": f"{world} independent rank(s), no collective"},
         "sweep_correct": f"{n_ok}/{len(prepared)}", "launch_mode": "cuda_graph_replay" if graph is not None else "eager", "eager_cases_per_sec": round(len(prepared) / (eager_ms * 1e-3), 2), "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
     }
@@ -500,6 +524,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of replaying a CUDA graph of the pass")
+    ap.add_argument("--sweep-streams", type=int, default=8, help="parallel branches of the captured sweep graph (1 = one chain)")
     ap.add_argument("--sweep-only", action="store_true", help="time the sweep only (no e2e pass, per-op table or CPU sample): the short run used for profiler launch lists")
     args = ap.parse_args()
     if args.impl == "reference":
