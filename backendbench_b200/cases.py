@@ -298,7 +298,8 @@ def neighbour_cases() -> List[CaseSpec]:
     """Configurations next to the named ones: the backward neighbours of the sixteen operators
     at the shapes of their forward operators, and softmax / log_softmax over vocabulary-size
     rows (longer than a CTA's registers hold; 50257 is odd, so every second row starts off
-    the 16-byte grid). Not part of the sweep or of the per-op bench table."""
+    the 16-byte grid) and over millions of 17-element rows (a thread per row). Not part of
+    the per-op bench table."""
     c: List[CaseSpec] = []
     for dtype, shape in (("bf16", (8192, 4096)), ("f32", (65536, 1024))):
         tag = f"{dtype}_{shape[0]}x{shape[1]}"
@@ -308,6 +309,7 @@ def neighbour_cases() -> List[CaseSpec]:
     c.append(CaseSpec(1000 + len(c), "embedding_dense_backward.default", "bf16", (128256, 4096), 0, (("n_idx", 16384),), "", "indexing", "embedding_backward_bf16_128256x4096_16384"))
     c.append(CaseSpec(1000 + len(c), "_softmax.default", "bf16", (4096, 128256), 0, (("dim", -1),), "", "reduce", "softmax_bf16_4096x128256"))
     c.append(CaseSpec(1000 + len(c), "_log_softmax.default", "bf16", (4096, 50257), 0, (("dim", -1),), "", "reduce", "log_softmax_bf16_4096x50257"))
+    c.append(CaseSpec(1000 + len(c), "_softmax.default", "f16", (3126099, 17), 0, (("dim", -1),), "", "reduce", "softmax_f16_3126099x17"))
     return c
 
 

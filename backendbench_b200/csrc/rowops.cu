@@ -1044,7 +1044,7 @@ __global__ void __launch_bounds__(kSmallRows) rows_small(const T* __restrict__ x
 #pragma unroll
       for (int c = 0; c < NC; ++c) {
         const float d = f[c] - m;
-        const float ex = exp2f(d * kLog2e);
+        const float ex = ex2_approx(d * kLog2e);
         s += c < cols ? ex : 0.f;
         f[c] = OP == SMALL_LOGSOFTMAX ? d : ex;
       }
