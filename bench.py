@@ -116,6 +116,28 @@ def _dist_env():
     return rank, local, world
 
 
+def _host_memory_allows(bytes_per_rank: int, ranks: int) -> bool:
+    """Whether every rank of this node can hold a pinned host copy of its inputs (plus the
+    pageable staging copy of one tensor at a time), by the free memory the OS reports and by
+    the container's cgroup limit when there is one."""
+    need = 1.3 * bytes_per_rank * max(ranks, 1)
+    try:
+        import psutil
+
+        if psutil.virtual_memory().available < need:
+            return False
+    except Exception:
+        pass
+    for path in ("/sys/fs/cgroup/memory.max", "/sys/fs/cgroup/memory/memory.limit_in_bytes"):
+        try:
+            raw = open(path).read().strip()
+            if raw.isdigit() and int(raw) < need:
+                return False
+        except OSError:
+            pass
+    return True
+
+
 def _bytes_of(args):
     return sum(a.numel() * a.element_size() for a in args if isinstance(a, torch.Tensor))
 
@@ -421,7 +443,10 @@ def run_b200(args):
 
     # ---- end to end: pinned host inputs, H2D inside the timed region
     e2e = None
-    if not args.sweep_only:
+    need_host = sum(_bytes_of(p["args"]) for p in prepared)
+    if not args.sweep_only and not _host_memory_allows(need_host, world):
+        e2e = {"skipped": f"host memory: {world} rank(s) x {need_host} bytes of pinned inputs do not fit what this box offers"}
+    elif not args.sweep_only:
         host_inputs = [[a.cpu().pin_memory() if isinstance(a, torch.Tensor) else a for a in p["args"]] for p in prepared]
         h2d = sum(_bytes_of(h) for h in host_inputs)
         e2e_steps = max(1, min(args.steps, 3))
