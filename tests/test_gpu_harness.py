@@ -41,6 +41,22 @@ def test_device_compare_matches_host_formula():
     assert ev.compare(a, a.clone())[0] is True and math.isnan(ev.compare(a, a.clone())[1])
     assert ev.compare(a, torch.tensor([1.0, 2.0, math.inf, -math.inf, 0.0], device=DEV))[0] is False
     assert ev.compare(torch.tensor([math.inf], device=DEV), torch.tensor([-math.inf], device=DEV))[0] is False
+    for dt in (torch.bfloat16, torch.float16):  # 16-bit vectors that are bit-identical leave the kernel early
+        h = torch.randn(100_003, generator=g, device=DEV).to(dt)
+        assert ev.compare(h, h.clone()) == (True, 0.0, 0.0)
+        one = h.clone()
+        one[50_001] = one[50_001] + 1.0  # a single element inside an otherwise identical tensor
+        ok, mabs, _ = ev.compare(h, one)
+        assert ok is False and mabs == pytest.approx(float((h.float() - one.float()).abs().max()), rel=1e-6)
+        for special in (math.inf, -math.inf, math.nan):  # identical, but inf - inf and NaN make the error NaN, as on the host
+            sp = h.clone()
+            sp[8 * 1234 + 3] = special
+            ok, mabs, mrel = ev.compare(sp, sp.clone())
+            assert ok is True and math.isnan(mabs)
+            habs, _ = utils.compute_errors(sp, sp.clone())
+            assert math.isnan(habs)
+        z = torch.zeros(64, device=DEV, dtype=dt)
+        assert ev.compare(z, -z) == (True, 0.0, 0.0)  # +0 and -0 differ in bits, not in value
     i = torch.arange(100000, device=DEV)
     assert ev.compare(i, i.clone()) == (True, 0.0, 0.0)
     j = i.clone()
