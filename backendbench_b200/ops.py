@@ -345,6 +345,9 @@ def _log_softmax_default(self, dim, half_to_float) -> torch.Tensor:
 _scratch_cache = {}
 
 
+_SCRATCH_MAX_STREAMS = 64
+
+
 def _scratch(device: torch.device, nbytes: int) -> torch.Tensor:
     """A scratch buffer of at least `nbytes` for the current stream of `device` (grown
     geometrically, reused; per stream, so that operators queued on different streams never
@@ -353,7 +356,10 @@ def _scratch(device: torch.device, nbytes: int) -> torch.Tensor:
     buf = _scratch_cache.get(key)
     if buf is None or buf.numel() < nbytes:
         buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _scratch_cache.pop(key, None)
         _scratch_cache[key] = buf
+        while len(_scratch_cache) > _SCRATCH_MAX_STREAMS:  # streams come and go: keep the most recently sized buffers only
+            _scratch_cache.pop(next(iter(_scratch_cache)))
     return buf
 
 
