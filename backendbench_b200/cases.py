@@ -310,6 +310,10 @@ def neighbour_cases() -> List[CaseSpec]:
     c.append(CaseSpec(1000 + len(c), "_softmax.default", "bf16", (4096, 128256), 0, (("dim", -1),), "", "reduce", "softmax_bf16_4096x128256"))
     c.append(CaseSpec(1000 + len(c), "_log_softmax.default", "bf16", (4096, 50257), 0, (("dim", -1),), "", "reduce", "log_softmax_bf16_4096x50257"))
     c.append(CaseSpec(1000 + len(c), "_softmax.default", "f16", (3126099, 17), 0, (("dim", -1),), "", "reduce", "softmax_f16_3126099x17"))
+    # fp32 products off the tensor-core path: a long contraction with few output tiles (K shared
+    # among the CTAs of a cluster) and very many rows with 8 output columns (a row per thread)
+    c.append(CaseSpec(1000 + len(c), "mm.default", "f32", (44, 4096, 1024), 0, (), "", "gemm", "mm_f32_44x4096x1024"))
+    c.append(CaseSpec(1000 + len(c), "bmm.default", "f32", (64, 8192, 256, 8), 0, (), "", "gemm", "bmm_f32_64x8192x256x8"))
     return c
 
 
