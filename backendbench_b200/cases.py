@@ -314,6 +314,8 @@ def neighbour_cases() -> List[CaseSpec]:
     # among the CTAs of a cluster) and very many rows with 8 output columns (a row per thread)
     c.append(CaseSpec(1000 + len(c), "mm.default", "f32", (44, 4096, 1024), 0, (), "", "gemm", "mm_f32_44x4096x1024"))
     c.append(CaseSpec(1000 + len(c), "bmm.default", "f32", (64, 8192, 256, 8), 0, (), "", "gemm", "bmm_f32_64x8192x256x8"))
+    # an elementwise operator over a transposed view (read through 32 x 32 shared-memory tiles)
+    c.append(CaseSpec(1000 + len(c), "add.Tensor", "f32", (39934, 1024), 0, (), "transposed", "elementwise", "add_f32_39934x1024_transposed"))
     return c
 
 

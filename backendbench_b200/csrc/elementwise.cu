@@ -285,6 +285,69 @@ __global__ void __launch_bounds__(256) ew_tiled(const void* a, const void* b, vo
   }
 }
 
+// The same 32 x 32 walk for operands and result of one type T. The generic kernel above
+// decides the element type per access and rebuilds every address from three 64-bit products
+// (92 instructions per element in the profile of a transposed fp32 add); here the type is a
+// template parameter and the offsets advance by additions.
+template <typename T, int OP>
+__global__ void __launch_bounds__(256) ew_tiled_typed(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out, TiledArgs A, float alpha) {
+  constexpr bool kBinary = OP == OP_ADD || OP == OP_MUL;
+  __shared__ float ta[32][33];
+  __shared__ float tb[kBinary ? 32 : 1][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int64_t r0 = static_cast<int64_t>(blockIdx.y) * 32, c0 = static_cast<int64_t>(blockIdx.x) * 32, bz = blockIdx.z;
+  const T* ap = a + bz * A.ab;
+  const T* bp = kBinary ? b + bz * A.bb : nullptr;
+  {
+    const int64_t r = r0 + tx;  // consecutive threads along the transposed operand's contiguous direction
+    int64_t c = c0 + ty;
+    int64_t oa = r * A.ar + c * A.ac, ob = kBinary ? r * A.br + c * A.bc : 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j, c += 8, oa += 8 * A.ac, ob += 8 * A.bc) {
+      if (r < A.R && c < A.C) {
+        if (A.a_t) ta[ty + 8 * j][tx] = to_f32(ap[oa]);
+        if (kBinary && A.b_t) tb[kBinary ? ty + 8 * j : 0][tx] = to_f32(bp[ob]);
+      }
+    }
+  }
+  __syncthreads();
+  const int64_t c = c0 + tx;
+  int64_t r = r0 + ty;
+  int64_t oa = r * A.ar + c * A.ac, ob = kBinary ? r * A.br + c * A.bc : 0;
+  T* op = out + (bz * A.R + r) * A.C + c;
+#pragma unroll
+  for (int j = 0; j < 4; ++j, r += 8, oa += 8 * A.ar, ob += 8 * A.br, op += 8 * A.C) {
+    if (r < A.R && c < A.C) {
+      const float x = A.a_t ? ta[tx][ty + 8 * j] : to_f32(ap[oa]);
+      float res;
+      if (OP == OP_RELU) res = x <= 0.f ? 0.f : x;
+      else if (OP == OP_COPY) res = x;
+      else if (OP == OP_ADDC) res = x + alpha;
+      else if (OP == OP_MULC) res = x * alpha;
+      else {
+        const float y = A.b_t ? tb[kBinary ? tx : 0][ty + 8 * j] : to_f32(bp[ob]);
+        res = OP == OP_ADD ? fmaf(alpha, y, x) : x * y;
+      }
+      *op = from_f32<T>(res);
+    }
+  }
+}
+
+template <int OP>
+static void launch_tiled(const void* a, const void* b, void* out, const TiledArgs& T, int dta, int dtb, int dto, float alpha, cudaStream_t st) {
+  constexpr bool kBinary = OP == OP_ADD || OP == OP_MUL;
+  const dim3 g(static_cast<unsigned>((T.C + 31) / 32), static_cast<unsigned>((T.R + 31) / 32), static_cast<unsigned>(T.B));
+  if (dta == dto && (!kBinary || dtb == dto)) {
+    switch (dto) {
+      case B200_F32: ew_tiled_typed<float, OP><<<g, 256, 0, st>>>(static_cast<const float*>(a), static_cast<const float*>(b), static_cast<float*>(out), T, alpha); return;
+      case B200_BF16: ew_tiled_typed<__nv_bfloat16, OP><<<g, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(b), static_cast<__nv_bfloat16*>(out), T, alpha); return;
+      case B200_F16: ew_tiled_typed<__half, OP><<<g, 256, 0, st>>>(static_cast<const __half*>(a), static_cast<const __half*>(b), static_cast<__half*>(out), T, alpha); return;
+      default: break;
+    }
+  }
+  ew_tiled<OP><<<g, 256, 0, st>>>(a, b, out, T, dta, dtb, dto, alpha);
+}
+
 template <typename U>
 __global__ void __launch_bounds__(256) copy_tiled_bits(const U* __restrict__ x, U* __restrict__ out, TiledArgs T) {
   __shared__ U t[32][32 + (sizeof(U) >= 4 ? 1 : (4 / sizeof(U)))];
@@ -388,7 +451,7 @@ static int binary_entry(const void* a, const void* b, void* out, int ndim, const
     }
   } else {
     TiledArgs T;
-    if (plan_tiled(T, A, true)) ew_tiled<OPCODE><<<tiled_grid(T), 256, 0, st>>>(a, b, out, T, dta, dtb, dto, alpha);
+    if (plan_tiled(T, A, true)) launch_tiled<OPCODE>(a, b, out, T, dta, dtb, dto, alpha, st);
     else ew_strided<OPCODE><<<strided_grid(A.n), kEwThreads, 0, st>>>(a, b, out, A, dta, dtb, dto, alpha);
   }
   return check_launch();
@@ -407,7 +470,7 @@ extern "C" int b200_relu(const void* x, void* out, int ndim, const int64_t* shap
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (is_contiguous(ndim, shape, sx) && aligned16(x) && aligned16(out)) return launch_unary_fast(x, out, A.n, dtype, ReluOp{}, st);
   TiledArgs T;
-  if (plan_tiled(T, A, false)) ew_tiled<OP_RELU><<<tiled_grid(T), 256, 0, st>>>(x, nullptr, out, T, dtype, dtype, dtype, 0.f);
+  if (plan_tiled(T, A, false)) launch_tiled<OP_RELU>(x, nullptr, out, T, dtype, dtype, dtype, 0.f, st);
   else ew_strided<OP_RELU><<<strided_grid(A.n), kEwThreads, 0, st>>>(x, nullptr, out, A, dtype, dtype, dtype, 0.f);
   return check_launch();
 }
@@ -421,7 +484,7 @@ static int scalar_entry(const void* x, void* out, int ndim, const int64_t* shape
   if (!x || !out) return B200_EINVAL;
   if (dtx == dto && is_contiguous(ndim, shape, sx) && aligned16(x) && aligned16(out)) return launch_unary_fast(x, out, A.n, dtx, op, st);
   TiledArgs T;
-  if (plan_tiled(T, A, false)) ew_tiled<OPCODE><<<tiled_grid(T), 256, 0, st>>>(x, nullptr, out, T, dtx, dtx, dto, c);
+  if (plan_tiled(T, A, false)) launch_tiled<OPCODE>(x, nullptr, out, T, dtx, dtx, dto, c, st);
   else ew_strided<OPCODE><<<strided_grid(A.n), kEwThreads, 0, st>>>(x, nullptr, out, A, dtx, dtx, dto, c);
   return check_launch();
 }
@@ -489,7 +552,7 @@ extern "C" int b200_copy_strided(const void* x, void* out, int ndim, const int64
   if (plan_tiled(T, A, false)) {
     if (dti != dto) {
       if (!is_float_dtype(dto)) return B200_EDTYPE;
-      ew_tiled<OP_COPY><<<tiled_grid(T), 256, 0, st>>>(x, nullptr, out, T, dti, dti, dto, 0.f);
+      launch_tiled<OP_COPY>(x, nullptr, out, T, dti, dti, dto, 0.f, st);
     } else {
       switch (es) {
         case 1: copy_tiled_bits<uint8_t><<<tiled_grid(T), 256, 0, st>>>(static_cast<const uint8_t*>(x), static_cast<uint8_t*>(out), T); break;
