@@ -141,6 +141,18 @@ struct StridedArgs {
 
 __device__ __forceinline__ void unravel3(const StridedArgs& A, int64_t lin, int64_t& o0, int64_t& o1, int64_t& o2) {
   o0 = o1 = o2 = 0;
+  if (A.n <= 0x7fffffffLL) {  // coordinates by 32-bit division (a 64-bit one costs ~5x the instructions)
+    uint32_t l = static_cast<uint32_t>(lin);
+    for (int d = A.ndim - 1; d >= 0; --d) {
+      const uint32_t ext = static_cast<uint32_t>(A.shape[d]);
+      const uint32_t q = l / ext, r = l - q * ext;
+      o0 += r * A.s0[d];
+      o1 += r * A.s1[d];
+      o2 += r * A.s2[d];
+      l = q;
+    }
+    return;
+  }
   for (int d = A.ndim - 1; d >= 0; --d) {
     const int64_t q = lin / A.shape[d];
     const int64_t r = lin - q * A.shape[d];
