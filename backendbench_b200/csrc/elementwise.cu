@@ -439,6 +439,82 @@ static void launch_binary_T(const void* a, const void* b, void* out, int64_t n, 
   else ew_binary_vec<T, Op, 2><<<g, kEwThreads, 0, st>>>(pa, pb, po, n, op);
 }
 
+// ------------------------------------------------------------------ rows with a broadcast partner
+// out[r, c] = f(a[r, c], b[r, c]) over a contiguous [R, C] result, where each operand is
+// either contiguous along c (column stride 1, any row stride, 0 included: a bias vector) or
+// constant along c (column stride 0: one value per row). The bias add and the per-row scale
+// of ordinary model code; the generic strided kernel would pay an index decomposition per
+// element. A thread produces 16 bytes of a row (VEC: rows, bases and C on the 16-byte grid)
+// or one element; one 32-bit division per thread and trip finds its row.
+struct Rows2dArgs {
+  int64_t R, C;
+  int64_t ar, br;  // row strides, elements
+  int a_c, b_c;    // column stride: 1 or 0
+};
+template <typename T, int OP, bool VEC>
+__global__ void __launch_bounds__(256) ew_rows2d(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out, Rows2dArgs A, float alpha) {
+  constexpr int VE = VEC ? 16 / static_cast<int>(sizeof(T)) : 1;
+  const int64_t per_row = A.C / VE, total = A.R * per_row;
+  const bool small = total <= 0x7fffffffLL;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    int64_t r, g;
+    if (small) {
+      const uint32_t q = static_cast<uint32_t>(i) / static_cast<uint32_t>(per_row);
+      r = q;
+      g = static_cast<uint32_t>(i) - q * static_cast<uint32_t>(per_row);
+    } else {
+      r = i / per_row;
+      g = i - r * per_row;
+    }
+    const int64_t c = g * VE;
+    float x[VE], y[VE], res[VE];
+    if (VEC) {
+      if (A.a_c) widen<T>(ld_stream(a + r * A.ar + c), x);
+      if (A.b_c) widen<T>(ld_stream(b + r * A.br + c), y);
+    } else {
+      if (A.a_c) x[0] = to_f32(a[r * A.ar + c]);
+      if (A.b_c) y[0] = to_f32(b[r * A.br + c]);
+    }
+    if (!A.a_c) {
+      const float v = to_f32(a[r * A.ar]);
+#pragma unroll
+      for (int e = 0; e < VE; ++e) x[e] = v;
+    }
+    if (!A.b_c) {
+      const float v = to_f32(b[r * A.br]);
+#pragma unroll
+      for (int e = 0; e < VE; ++e) y[e] = v;
+    }
+#pragma unroll
+    for (int e = 0; e < VE; ++e) res[e] = OP == OP_ADD ? fmaf(alpha, y[e], x[e]) : x[e] * y[e];
+    if (VEC) st_stream(out + r * A.C + c, narrow<T>(res));
+    else out[r * A.C + c] = from_f32<T>(res[0]);
+  }
+}
+
+// Classifies one operand of an N-d elementwise call against a contiguous [R, C] result
+// (C = the last extent): contiguous, a last-dim vector (all other strides 0), or -- for 2-d
+// calls -- a column (one value per row). Returns false for anything else.
+static bool rows2d_operand(int ndim, const int64_t* shape, const int64_t* s, int64_t C, int64_t& row_stride, int& col_stride) {
+  if (is_contiguous(ndim, shape, s)) { row_stride = C; col_stride = 1; return true; }
+  bool lead_zero = true;
+  for (int d = 0; d + 1 < ndim; ++d) lead_zero = lead_zero && (s[d] == 0 || shape[d] == 1);
+  if (lead_zero && (s[ndim - 1] == 1 || shape[ndim - 1] == 1)) { row_stride = 0; col_stride = 1; return true; }
+  if (ndim == 2 && s[1] == 0) { row_stride = shape[0] == 1 ? 0 : s[0]; col_stride = 0; return true; }
+  if (ndim == 2 && s[1] == 1 && s[0] >= shape[1]) { row_stride = s[0]; col_stride = 1; return true; }  // a row-pitched matrix
+  return false;
+}
+template <typename T, int OP>
+static void launch_rows2d_T(const void* a, const void* b, void* out, const Rows2dArgs& A, float alpha, cudaStream_t st) {
+  constexpr int VE = 16 / static_cast<int>(sizeof(T));
+  const bool a_ok = !A.a_c || (aligned16(a) && A.ar % VE == 0), b_ok = !A.b_c || (aligned16(b) && A.br % VE == 0);
+  const bool vec = A.C % VE == 0 && aligned16(out) && a_ok && b_ok;
+  const int64_t work = A.R * (vec ? A.C / VE : A.C);
+  const int g = strided_grid(work);
+  if (vec) ew_rows2d<T, OP, true><<<g, 256, 0, st>>>(static_cast<const T*>(a), static_cast<const T*>(b), static_cast<T*>(out), A, alpha);
+  else ew_rows2d<T, OP, false><<<g, 256, 0, st>>>(static_cast<const T*>(a), static_cast<const T*>(b), static_cast<T*>(out), A, alpha);
+}
+
 template <typename Op, int OPCODE>
 static int binary_entry(const void* a, const void* b, void* out, int ndim, const int64_t* shape, const int64_t* sa, const int64_t* sb, int dta, int dtb, int dto, Op op, float alpha, cudaStream_t st) {
   StridedArgs A;
@@ -463,8 +539,20 @@ static int binary_entry(const void* a, const void* b, void* out, int ndim, const
     }
   } else {
     TiledArgs T;
-    if (plan_tiled(T, A, true)) launch_tiled<OPCODE>(a, b, out, T, dta, dtb, dto, alpha, st);
-    else ew_strided<OPCODE><<<strided_grid(A.n), kEwThreads, 0, st>>>(a, b, out, A, dta, dtb, dto, alpha);
+    Rows2dArgs R2;
+    R2.C = ndim > 0 ? shape[ndim - 1] : 1;
+    R2.R = R2.C > 0 ? A.n / R2.C : 0;
+    if (same && ndim >= 1 && R2.C > 0 && rows2d_operand(ndim, shape, sa, R2.C, R2.ar, R2.a_c) && rows2d_operand(ndim, shape, sb, R2.C, R2.br, R2.b_c)) {
+      switch (dto) {
+        case B200_F32: launch_rows2d_T<float, OPCODE>(a, b, out, R2, alpha, st); break;
+        case B200_BF16: launch_rows2d_T<__nv_bfloat16, OPCODE>(a, b, out, R2, alpha, st); break;
+        default: launch_rows2d_T<__half, OPCODE>(a, b, out, R2, alpha, st); break;
+      }
+    } else if (plan_tiled(T, A, true)) {
+      launch_tiled<OPCODE>(a, b, out, T, dta, dtb, dto, alpha, st);
+    } else {
+      ew_strided<OPCODE><<<strided_grid(A.n), kEwThreads, 0, st>>>(a, b, out, A, dta, dtb, dto, alpha);
+    }
   }
   return check_launch();
 }

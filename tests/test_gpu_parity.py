@@ -374,6 +374,27 @@ def test_many_short_rows_and_long_non_last_dims(backend, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_add_mul_with_a_bias_vector_or_a_value_per_row(backend, dtype):
+    """x + bias[C], x * scale[R, 1], either operand first, 2-d and 3-d, row lengths on and off the
+    16-byte grid, a row-pitched matrix view, alpha: bit-identical to aten on the same tensors
+    (one fp32 operation and one rounding per element)."""
+    g = torch.Generator(device=DEV).manual_seed(35)
+    add, mul = backend[get_operator("add.Tensor")], backend[get_operator("mul.Tensor")]
+    for R, C in ((1109, 8195), (300, 4096), (70000, 12), (5, 1), (1, 777)):
+        x = torch.randn(R, C, generator=g, device=DEV).to(dtype)
+        bias, col = torch.randn(C, generator=g, device=DEV).to(dtype), torch.randn(R, 1, generator=g, device=DEV).to(dtype)
+        wide = torch.randn(R, C + 8, generator=g, device=DEV).to(dtype)[:, :C]  # rows with a pitch
+        for a, b in ((x, bias), (bias, x), (x, col), (col, x), (wide, bias), (wide, col), (col, bias), (x, wide)):
+            assert bits_equal(torch.add(a, b), add(a, b)), (R, C, a.shape, b.shape)
+            assert bits_equal(torch.mul(a, b), mul(a, b)), (R, C, a.shape, b.shape)
+        assert bits_equal(torch.add(x, bias, alpha=0.5), add(x, bias, alpha=0.5))
+    x3 = torch.randn(7, 33, 256, generator=g, device=DEV).to(dtype)
+    b3 = torch.randn(256, generator=g, device=DEV).to(dtype)
+    assert bits_equal(torch.add(x3, b3), add(x3, b3)) and bits_equal(torch.mul(b3, x3), mul(b3, x3))
+    ops.check_device_status()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
 def test_short_rows_every_length_staged_and_direct(backend, dtype):
     """Thread-per-row kernels over row lengths on both sides of each register-slot count (8,
     16, 24, 32), with strides that are and are not multiples of 8 bytes (direct / staged
