@@ -1109,7 +1109,7 @@ static int launch_rows_small(const void* x, void* out, int64_t rows, int cols, i
 // ------------------------------------------------------------------ host-side planning
 struct ReducePlan {
   int splits;
-  int64_t chunk;  // elements of `dim` per split (multiple of 64)
+  int64_t chunk;  // elements of `dim` per split (a multiple of 64 for rows, of 16 for columns)
 };
 
 static ReducePlan plan_reduce(int64_t outer, int64_t dim, int64_t inner) {
@@ -1119,8 +1119,9 @@ static ReducePlan plan_reduce(int64_t outer, int64_t dim, int64_t inner) {
   const int64_t want = 2LL * kNumSMs;
   // A row reduction (inner == 1) is worth splitting from 4096 elements, 1024 per split. A
   // column reduction walks `dim` one row per iteration, every row a coalesced read, and with
-  // few columns it has few threads: split it from 128 rows, 32 per split.
-  const int64_t min_dim = inner == 1 ? 4096 : 128, min_chunk = inner == 1 ? 1024 : 32;
+  // few columns it has few threads: split it from 64 rows, 16 per split (argmax over 112
+  // rows of 6144 columns: 24 CTAs unsplit).
+  const int64_t min_dim = inner == 1 ? 4096 : 64, min_chunk = inner == 1 ? 1024 : 16;
   if (ctas >= want || dim < min_dim) return p;
   int64_t s = (want + ctas - 1) / ctas;
   const int64_t max_s = dim / min_chunk;
@@ -1128,7 +1129,8 @@ static ReducePlan plan_reduce(int64_t outer, int64_t dim, int64_t inner) {
   if (s > 1024) s = 1024;
   if (s <= 1) return p;
   int64_t chunk = (dim + s - 1) / s;
-  chunk = (chunk + 63) / 64 * 64;
+  const int64_t gran = inner == 1 ? 64 : 16;  // row chunks stay on the 16-byte grid of any element type
+  chunk = (chunk + gran - 1) / gran * gran;
   p.splits = static_cast<int>((dim + chunk - 1) / chunk);
   p.chunk = chunk;
   return p;
