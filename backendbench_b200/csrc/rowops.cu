@@ -886,6 +886,73 @@ __global__ void __launch_bounds__(256) reduce_cols(const T* __restrict__ x, void
   }
 }
 
+// Column reduction with at most 32 columns (the bias-gradient shape: many rows, few columns):
+// a thread per column would leave most lanes of a warp without work, so the lanes of a warp
+// tile rows x columns instead -- W = the next power of two above `inner` columns, 32 / W rows
+// per warp and trip, i.e. a warp reads 32 consecutive elements when inner == W -- and the
+// row-lanes are folded by shuffles, the CTA's 8 warps through shared memory, in a fixed order.
+template <typename T, bool ARG>
+__global__ void __launch_bounds__(256) reduce_cols_narrow(const T* __restrict__ x, void* __restrict__ out, float* __restrict__ part_v, int64_t* __restrict__ part_i,
+                                                          int64_t outer, int64_t dim, int inner, int W, int64_t chunk, int dto) {
+  __shared__ float sh_v[8][32];
+  __shared__ int64_t sh_i[ARG ? 8 : 1][32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int col = lane & (W - 1), rsub = lane / W, rpw = 32 / W;
+  const int64_t o = blockIdx.y;
+  const int64_t k0 = static_cast<int64_t>(blockIdx.z) * chunk;
+  const int64_t k1 = k0 + chunk < dim ? k0 + chunk : dim;
+  const T* p = x + o * dim * inner + col;
+  const int64_t step = 8 * rpw;
+  float s0 = 0.f, s1 = 0.f;
+  ArgPair a{0.f, -1};
+  if (col < inner) {
+    int64_t k = k0 + warp * rpw + rsub;
+    if (!ARG) {
+      for (; k + step < k1; k += 2 * step) {
+        s0 += to_f32(p[k * inner]);
+        s1 += to_f32(p[(k + step) * inner]);
+      }
+    }
+    for (; k < k1; k += step) {
+      const float fv = to_f32(p[k * inner]);
+      if (ARG) arg_take(a, fv, k);
+      else s0 += fv;
+    }
+  }
+  float s = s0 + s1;
+  for (int off = W; off < 32; off <<= 1) {  // fold the row-lanes of the warp onto lanes 0 .. W-1
+    if (ARG) {
+      const float v = __shfl_xor_sync(0xffffffffu, a.v, off);
+      const int64_t i = __shfl_xor_sync(0xffffffffu, a.i, off);
+      if (i >= 0) arg_take(a, v, i);
+    } else {
+      s += __shfl_xor_sync(0xffffffffu, s, off);
+    }
+  }
+  if (lane < W) {
+    sh_v[warp][lane] = ARG ? a.v : s;
+    if (ARG) sh_i[warp][lane] = a.i;
+  }
+  __syncthreads();
+  if (warp == 0 && lane < inner) {
+    float t = 0.f;
+    ArgPair b{0.f, -1};
+    for (int w = 0; w < 8; ++w) {
+      if (ARG) { if (sh_i[w][lane] >= 0) arg_take(b, sh_v[w][lane], sh_i[w][lane]); }
+      else t += sh_v[w][lane];
+    }
+    const int64_t oi = o * inner + lane;
+    if (gridDim.z > 1) {
+      const int64_t slot = static_cast<int64_t>(blockIdx.z) * outer * inner + oi;
+      if (ARG) { part_v[slot] = b.v; part_i[slot] = b.i; }
+      else part_v[slot] = t;
+    } else {
+      if (ARG) static_cast<int64_t*>(out)[oi] = b.i;
+      else store_from_f32(out, oi, dto, t);
+    }
+  }
+}
+
 // Second stage of a split reduction: n outputs, `splits` partials each, ascending split
 // order (so the earliest index wins argmax ties and sums are run-to-run identical).
 template <bool ARG>
@@ -1174,8 +1241,15 @@ static int launch_reduce_T(const void* x, void* out, int64_t outer, int64_t dim,
       }
       return check_launch();
     }
-    dim3 g(grid_for(inner, 256), static_cast<unsigned>(outer), p.splits);
-    reduce_cols<T, ARG><<<g, 256, 0, st>>>(px, out, pv, pi, outer, dim, inner, p.chunk, dto);
+    if (inner <= 32 && dim >= 64) {
+      int W = 1;
+      while (W < inner) W <<= 1;
+      dim3 g(1, static_cast<unsigned>(outer), p.splits);
+      reduce_cols_narrow<T, ARG><<<g, 256, 0, st>>>(px, out, pv, pi, outer, dim, static_cast<int>(inner), W, p.chunk, dto);
+    } else {
+      dim3 g(grid_for(inner, 256), static_cast<unsigned>(outer), p.splits);
+      reduce_cols<T, ARG><<<g, 256, 0, st>>>(px, out, pv, pi, outer, dim, inner, p.chunk, dto);
+    }
   }
   if (p.splits >= 64 && nout <= 8LL * kNumSMs * 8) reduce_finalize_warp<ARG><<<grid_for(nout, 8), 256, 0, st>>>(pv, pi, out, nout, p.splits, dto);
   else if (p.splits > 1) reduce_finalize<ARG><<<grid_for(nout, 256), 256, 0, st>>>(pv, pi, out, nout, p.splits, dto);

@@ -374,6 +374,26 @@ def test_many_short_rows_and_long_non_last_dims(backend, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_reductions_over_rows_of_a_narrow_matrix(backend, dtype):
+    """sum / argmax over dim 0 of [rows, 2 .. 32 columns] (the bias-gradient shape): the lanes of
+    a warp tile rows x columns; ties go to the first row, a NaN wins, batches reduce apart."""
+    g = torch.Generator().manual_seed(36)
+    jobs = []
+    for cols in (2, 7, 16, 17, 32):
+        x = torch.randn(5003, cols, generator=g).to(dtype)
+        x[100, 0] = x[4000, 0] = 50.0  # a tie: the earlier row
+        x[77, cols - 1] = float("nan")
+        jobs += [("sum.dim_IntList", [x[:, : cols - 1].contiguous() if cols > 2 else x[:, :1].contiguous(), [0]]), ("sum.dim_IntList", [x.nan_to_num(0.0), [0], True]),
+                 ("argmax.default", [x, 0]), ("argmax.default", [x.nan_to_num(0.0), 0, True])]
+    xb = torch.randn(6, 700, 12, generator=g).to(dtype)
+    jobs += [("sum.dim_IntList", [xb, [1]]), ("argmax.default", [xb, 1])]
+    for op_name, args in jobs:
+        got = backend[get_operator(op_name)](*_to_dev(args))
+        _check(op_name, oracle.run(op_name, args, {}), got, (op_name, tuple(args[0].shape)))
+    ops.check_device_status()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
 def test_add_mul_with_a_bias_vector_or_a_value_per_row(backend, dtype):
     """x + bias[C], x * scale[R, 1], either operand first, 2-d and 3-d, row lengths on and off the
     16-byte grid, a row-pitched matrix view, alpha: bit-identical to aten on the same tensors
