@@ -72,6 +72,7 @@ SIGNATURES = {
     "b200_embedding_backward": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_int64, c_void_p, c_void_p]),
     "b200_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p] + [c_int64] * 12 + [c_double, c_double, c_int, c_void_p, c_void_p]),
     "b200_gemm_uses_tensor_cores": (c_int, [c_int64] * 10 + [c_int, c_void_p, c_void_p, c_void_p]),
+    "b200_gemm_wait_probe": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int64, c_void_p, c_void_p]),
     "b200_gemm_f32_scratch_bytes": (c_int64, [c_int64, c_int64, c_int64, c_int64]),
     "b200_gemm_f32": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p] + [c_int64] * 12 + [c_double, c_double, c_void_p, c_int64, c_void_p, c_void_p]),
     "b200_allclose": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_double, c_double, c_void_p, c_int, c_void_p]),

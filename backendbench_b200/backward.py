@@ -25,7 +25,7 @@ def _softmax_backward(grad_output: torch.Tensor, output: torch.Tensor, dim: int,
     if grad_output.dtype not in ops._FLOATS or input_dtype not in ops._FLOATS:
         raise ops.UnsupportedByB200(f"softmax backward: dtypes {grad_output.dtype} -> {input_dtype}")
     dim = ops._norm_dim(dim, grad_output.dim())
-    out = torch.empty(grad_output.shape, dtype=input_dtype, device=grad_output.device)
+    out = ops._new(grad_output.shape, input_dtype, grad_output.device)
     if out.numel():
         outer, d, inner = ops._split_at(list(grad_output.shape) or [1], dim)
         g, y = ops._contig(grad_output), ops._contig(output)
@@ -67,9 +67,9 @@ def native_layer_norm_backward_default(grad_out, input, normalized_shape, mean, 
     rows = input.numel() // cols if cols else 0
     param = weight if weight is not None else bias
     wb_dtype = param.dtype if param is not None else input.dtype
-    dx = torch.empty(input.shape, dtype=input.dtype, device=input.device) if want_dx else None
-    dw = torch.empty(normalized_shape, dtype=wb_dtype, device=input.device) if want_dw else None
-    db = torch.empty(normalized_shape, dtype=wb_dtype, device=input.device) if want_db else None
+    dx = ops._new(input.shape, input.dtype, input.device) if want_dx else None
+    dw = ops._new(normalized_shape, wb_dtype, input.device) if want_dw else None
+    db = ops._new(normalized_shape, wb_dtype, input.device) if want_db else None
     if cols and (rows or want_dw or want_db):
         dy, x = ops._contig(grad_out), ops._contig(input)
         mu, rs = ops._contig(mean), ops._contig(rstd)
@@ -103,7 +103,7 @@ def embedding_dense_backward_default(grad_output, indices, num_weights, padding_
         raise RuntimeError(f"embedding_dense_backward: grad_output {list(grad_output.shape)} is not indices {list(indices.shape)} + [D]")
     num_weights = int(num_weights)
     row_len = int(grad_output.shape[-1])
-    out = torch.empty((num_weights, row_len), dtype=grad_output.dtype, device=grad_output.device)
+    out = ops._new((num_weights, row_len), grad_output.dtype, grad_output.device)
     if out.numel():
         g, idx = ops._contig(grad_output), ops._contig(indices)
         n = idx.numel()

@@ -83,14 +83,20 @@ __global__ void __launch_bounds__(256) allclose_kernel(const T* __restrict__ ref
   }
 }
 
-// Integer / bool tensors: exact comparison in int64 (|a-b| <= 1e-2 means a == b), error
-// magnitudes after conversion to fp32 as the host formula does.
+// Integer / bool tensors: the same band as for floating point, |ref - res| <= atol + rtol * |res|,
+// evaluated in double (assert_close applies its tolerances to integers too: 5000 and 5001 are
+// close under the harness's 1e-2); atol = rtol = 0 makes the comparison exact. Error magnitudes
+// after conversion to fp32 as the host formula does.
 template <typename T>
-__global__ void __launch_bounds__(256) allclose_int_kernel(const T* __restrict__ ref, const T* __restrict__ res, int64_t n, b200_close_record* rec) {
+__global__ void __launch_bounds__(256) allclose_int_kernel(const T* __restrict__ ref, const T* __restrict__ res, int64_t n, double rtol, double atol, b200_close_record* rec) {
   CloseAcc a{0ull, 0.f, 0.f, 0u};
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     const T r = ref[i], s = res[i];
-    if (r != s) ++a.bad;
+    if (r != s) {  // zero tolerances: unequal is a mismatch, whatever double makes of the difference
+      const double ds = static_cast<double>(s);
+      const bool inside = (rtol > 0.0 || atol > 0.0) && fabs(static_cast<double>(r) - ds) <= atol + rtol * fabs(ds);
+      if (!inside) ++a.bad;
+    }
     const float fr = static_cast<float>(r), fs = static_cast<float>(s);
     const float diff = fabsf(fr - fs);
     a.max_abs = fmaxf(a.max_abs, diff);
@@ -137,11 +143,11 @@ extern "C" int b200_allclose(const void* ref, const void* res, int64_t n, int dt
     case B200_F32: allclose_kernel<float><<<g, 256, 0, st>>>(static_cast<const float*>(ref), static_cast<const float*>(res), n, rt, at, rec, vec_ok); break;
     case B200_BF16: allclose_kernel<__nv_bfloat16><<<g, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(ref), static_cast<const __nv_bfloat16*>(res), n, rt, at, rec, vec_ok); break;
     case B200_F16: allclose_kernel<__half><<<g, 256, 0, st>>>(static_cast<const __half*>(ref), static_cast<const __half*>(res), n, rt, at, rec, vec_ok); break;
-    case B200_I64: allclose_int_kernel<int64_t><<<g, 256, 0, st>>>(static_cast<const int64_t*>(ref), static_cast<const int64_t*>(res), n, rec); break;
-    case B200_I32: allclose_int_kernel<int32_t><<<g, 256, 0, st>>>(static_cast<const int32_t*>(ref), static_cast<const int32_t*>(res), n, rec); break;
-    case B200_I16: allclose_int_kernel<int16_t><<<g, 256, 0, st>>>(static_cast<const int16_t*>(ref), static_cast<const int16_t*>(res), n, rec); break;
-    case B200_I8: allclose_int_kernel<int8_t><<<g, 256, 0, st>>>(static_cast<const int8_t*>(ref), static_cast<const int8_t*>(res), n, rec); break;
-    case B200_BOOL: case B200_U8: allclose_int_kernel<uint8_t><<<g, 256, 0, st>>>(static_cast<const uint8_t*>(ref), static_cast<const uint8_t*>(res), n, rec); break;
+    case B200_I64: allclose_int_kernel<int64_t><<<g, 256, 0, st>>>(static_cast<const int64_t*>(ref), static_cast<const int64_t*>(res), n, rtol, atol, rec); break;
+    case B200_I32: allclose_int_kernel<int32_t><<<g, 256, 0, st>>>(static_cast<const int32_t*>(ref), static_cast<const int32_t*>(res), n, rtol, atol, rec); break;
+    case B200_I16: allclose_int_kernel<int16_t><<<g, 256, 0, st>>>(static_cast<const int16_t*>(ref), static_cast<const int16_t*>(res), n, rtol, atol, rec); break;
+    case B200_I8: allclose_int_kernel<int8_t><<<g, 256, 0, st>>>(static_cast<const int8_t*>(ref), static_cast<const int8_t*>(res), n, rtol, atol, rec); break;
+    case B200_BOOL: case B200_U8: allclose_int_kernel<uint8_t><<<g, 256, 0, st>>>(static_cast<const uint8_t*>(ref), static_cast<const uint8_t*>(res), n, rtol, atol, rec); break;
     default: return B200_EDTYPE;
   }
   return check_launch();

@@ -8,7 +8,8 @@ int gemm_simt_dispatch(const void* A, const void* B, const void* bias, void* C, 
 bool gemm_tc_eligible(int64_t batch, int64_t M, int64_t N, int64_t K, int64_t sAb, int64_t sAm, int64_t sAk, int64_t sBb, int64_t sBk, int64_t sBn, int dtype,
                       const void* A, const void* B, const void* C);
 int gemm_tc_dispatch(const void* A, const void* B, const void* bias, void* C, int64_t batch, int64_t M, int64_t N, int64_t K, int64_t sAb, int64_t sAm, int64_t sAk,
-                     int64_t sBb, int64_t sBk, int64_t sBn, int64_t sbm, int64_t sbn, double alpha, double beta, int dtype, uint32_t* status, cudaStream_t st);
+                     int64_t sBb, int64_t sBk, int64_t sBn, int64_t sbm, int64_t sbn, double alpha, double beta, int dtype, uint32_t* status, cudaStream_t st,
+                     uint64_t wait_probe_limit_ns = 0);
 
 int64_t gemm_f32_split_scratch_bytes(int64_t batch, int64_t M, int64_t N, int64_t K);
 bool gemm_f32_split_eligible(int64_t batch, int64_t M, int64_t N, int64_t K);
@@ -49,6 +50,14 @@ extern "C" int b200_gemm(const void* A, const void* B, const void* bias, void* C
   if (gemm_tc_eligible(batch, M, N, K, sAb, sAm, sAk, sBb, sBk, sBn, dtype, A, B, C))
     return gemm_tc_dispatch(A, B, bias, C, batch, M, N, K, sAb, sAm, sAk, sBb, sBk, sBn, sbm, sbn, alpha, beta, dtype, status, st);
   return gemm_simt_dispatch(A, B, bias, C, batch, M, N, K, sAb, sAm, sAk, sBb, sBk, sBn, sbm, sbn, alpha, beta, dtype, st);
+}
+
+extern "C" int b200_gemm_wait_probe(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int dtype, int64_t wait_limit_us, uint32_t* status, void* stream) {
+  if (M < 1 || N < 1 || K < 1 || !A || !B || !C || !status) return B200_EINVAL;
+  if (wait_limit_us < 50 || wait_limit_us > 100000) return B200_EINVAL;  // 50 us .. 0.1 s
+  // row-major A [M, K] and B [K, N], the tensor-core path or nothing
+  if (!gemm_tc_eligible(1, M, N, K, 0, K, 1, 0, N, 1, dtype, A, B, C)) return B200_EALIGN;
+  return gemm_tc_dispatch(A, B, nullptr, C, 1, M, N, K, 0, K, 1, 0, N, 1, 0, 0, 1.0, 0.0, dtype, status, static_cast<cudaStream_t>(stream), static_cast<uint64_t>(wait_limit_us) * 1000ull);
 }
 
 extern "C" int64_t b200_gemm_f32_scratch_bytes(int64_t batch, int64_t M, int64_t N, int64_t K) {

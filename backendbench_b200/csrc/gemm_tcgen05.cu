@@ -72,15 +72,15 @@ __device__ __forceinline__ uint64_t global_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-// Bounded wait: false when kWaitLimitNs ran out or another role already aborted.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
+// Bounded wait: false when `limit_ns` ran out or another role already aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, uint64_t limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = global_ns();
   for (uint32_t i = 0;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 7u) == 7u) {
       if (*abort_flag) return false;
-      if (global_ns() - t0 > kWaitLimitNs) return false;
+      if (global_ns() - t0 > limit_ns) return false;
     }
   }
 }
@@ -145,6 +145,8 @@ struct GemmTcParams {
   int col_fastest;  // tile order: 1 = column-block fastest (write-bound shapes), 0 = grouped row-block fastest
   int split_slabs;  // 0, or K slabs per plane of fp32 operands split into three bf16 planes (see gemm_f32_split_dispatch)
   const uint32_t* skip_if_set;  // when not NULL: the kernel returns at once if this device word is non-zero
+  uint64_t wait_limit_ns;       // every mbarrier wait gives up after this long (kWaitLimitNs in ordinary calls)
+  int withhold_first_slab;      // wait probe only: the producer never loads the first K slab of a CTA's first tile
 };
 
 // Tile t of one batch entry -> (row-block, column-block): column-block fastest, or groups of
@@ -228,8 +230,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         tile_coords(rem, mt, nt, mb, nb, p.col_fastest);
         const int m0 = mb * kBM, n0 = nb * kBN;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.wait_limit_ns)) { ok = false; break; }
           const uint32_t a_dst = smem_base + stage * kStageBytes, b_dst = a_dst + kABytes;
+          if (p.withhold_first_slab && t == blockIdx.x && kb == 0) {
+            // wait probe: this stage is never armed and never filled, so the MMA warp's wait on
+            // it must run into its limit; the producer carries on until it needs the stage back
+            if (++stage == kStages) { stage = 0; phase ^= 1u; }
+            continue;
+          }
           mbar_expect_tx(full_bar(stage), kStageBytes);
           int ka = kb * kBK, kbb = kb * kBK;
           if (p.split_slabs) {
@@ -276,11 +284,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
       for (int64_t t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
-        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.wait_limit_ns)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kBN);
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(full_bar(stage), phase, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.wait_limit_ns)) { ok = false; break; }
           tc_fence_after();
           const uint32_t a_addr = smem_base + stage * kStageBytes, b_addr = a_addr + kABytes;
 #pragma unroll
@@ -317,7 +325,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       tile_coords(rem, mt, nt, mb, nb_blk, p.col_fastest);
       const int64_t m0 = static_cast<int64_t>(mb) * kBM, n0 = static_cast<int64_t>(nb_blk) * kBN + chalf * (kBN / 2);
       int got = 0;
-      if (lane == 0) got = mbar_wait(tfull_bar(acc), acc_phase, abort_flag) ? 1 : 0;
+      if (lane == 0) got = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.wait_limit_ns) ? 1 : 0;
       got = __shfl_sync(0xffffffffu, got, 0);
       if (!got) { ok = false; break; }
       tc_fence_after();
@@ -461,15 +469,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+static EncodeTiledFn lookup_encode_fn() {
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess) return reinterpret_cast<EncodeTiledFn>(p);
+  return nullptr;
+}
 static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess) fn = reinterpret_cast<EncodeTiledFn>(p);
-  }
+  static const EncodeTiledFn fn = lookup_encode_fn();  // initialised once, thread-safe (C++11 static)
   return fn;
 }
 
@@ -522,7 +529,7 @@ static bool encode_operand(CUtensorMap* map, const void* base, int dtype, bool m
 }
 
 int gemm_tc_dispatch(const void* A, const void* B, const void* bias, void* C, int64_t batch, int64_t M, int64_t N, int64_t K, int64_t sAb, int64_t sAm, int64_t sAk, int64_t sBb,
-                     int64_t sBk, int64_t sBn, int64_t sbm, int64_t sbn, double alpha, double beta, int dtype, uint32_t* status, cudaStream_t st) {
+                     int64_t sBk, int64_t sBn, int64_t sbm, int64_t sbn, double alpha, double beta, int dtype, uint32_t* status, cudaStream_t st, uint64_t wait_probe_limit_ns) {
   const OperandLayout la = operand_layout(M, K, sAm, sAk, sAb, batch, A);
   const OperandLayout lb = operand_layout(N, K, sBn, sBk, sBb, batch, B);
   if (!la.ok || !lb.ok || !encode_fn()) return B200_EALIGN;
@@ -559,6 +566,8 @@ int gemm_tc_dispatch(const void* A, const void* B, const void* bias, void* C, in
   p.col_fastest = (K + kBK - 1) / kBK <= 4 ? 1 : 0;
   p.split_slabs = 0;
   p.skip_if_set = nullptr;
+  p.wait_limit_ns = wait_probe_limit_ns ? wait_probe_limit_ns : kWaitLimitNs;
+  p.withhold_first_slab = wait_probe_limit_ns ? 1 : 0;
   // a narrow C takes the 128-wide tile. (Write-bound shapes with few K slabs were measured
   // slower on it: 256-byte row segments instead of 512-byte ones cost more in DRAM than the
   // deeper pipeline gains -- bmm 32x2048x128x2048: 0.162 ms vs 0.116 ms.)
@@ -726,6 +735,8 @@ int gemm_f32_split_dispatch(const void* A, const void* B, const void* bias, void
   p.has_bias = (bias != nullptr && p.beta != 0.f) ? 1 : 0;
   p.split_slabs = static_cast<int>(kp / kBK);
   p.skip_if_set = any_flag;
+  p.wait_limit_ns = kWaitLimitNs;
+  p.withhold_first_slab = 0;
   p.col_fastest = 6 * p.split_slabs <= 4 ? 1 : 0;
   const int64_t tiles = batch * ((M + kBM - 1) / kBM) * ((N + bn - 1) / bn);
   const int grid = static_cast<int>(tiles < kNumSMs ? tiles : kNumSMs);

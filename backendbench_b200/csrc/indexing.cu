@@ -348,11 +348,9 @@ extern "C" int b200_gather(const void* self, const void* index, void* out, int n
   if (ndim == 2 && dim == 0 && elem_size == 4 && idx_contig && self_strides[1] == 1 && index_shape[1] % kStripW == 0 && self_strides[0] % 4 == 0 && aligned16(self) && aligned16(index) &&
       aligned16(out) && self_dim_size > 0 && self_dim_size * kStripW * 4 <= kStripMaxSelfBytes && index_shape[0] >= 512 && index_shape[0] * 2 >= self_dim_size && index_shape[1] / kStripW >= kNumSMs) {
     const size_t smem = static_cast<size_t>(self_dim_size) * kStripW * 4;
-    static bool allowed = false;
-    if (!allowed) {
+    {  // the attribute belongs to the current device: set it on every launch, as the other large-shared-memory kernels do
       const cudaError_t e = cudaFuncSetAttribute(gather_dim0_strip, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kStripMaxSelfBytes));
       if (e != cudaSuccess) { set_last_cuda_error(e); return B200_ELAUNCH; }
-      allowed = true;
     }
     const int64_t strips = index_shape[1] / kStripW;
     const int64_t tail = strips % kNumSMs;

@@ -243,6 +243,28 @@ def _first_dtype(x):
     return None
 
 
+def _first_cuda_device(x):
+    if isinstance(x, torch.Tensor):
+        return x.device if x.is_cuda else None
+    if isinstance(x, (list, tuple)):
+        for y in x:
+            d = _first_cuda_device(y)
+            if d is not None:
+                return d
+    return None
+
+
+def _raise_device_status(res) -> None:
+    """Read (and clear) the status word of the device a CUDA result lives on; raises what
+    `ops.check_device_status` raises (IndexError for an out-of-range index). The comparison
+    before it has already synchronised, so this costs one 4-byte read."""
+    dev = _first_cuda_device(res)
+    if dev is not None:
+        from .ops import check_device_status
+
+        check_device_status(dev)
+
+
 # ------------------------------------------------------------------ correctness
 def eval_correctness_test(op, impl, test, tolerances=None) -> CorrectnessTestResult:
     """Run `impl` on the test's arguments and compare with `op` on the same arguments.
@@ -259,6 +281,7 @@ def eval_correctness_test(op, impl, test, tolerances=None) -> CorrectnessTestRes
         else:
             atol, rtol = tolerances
         ok, abs_err, rel_err = compare(ref, res, atol, rtol)
+        _raise_device_status(res)  # a kernel that zero-filled on a bad index fails THIS test, with the reason
         return CorrectnessTestResult(op_name=op_name, args=serialize_args(args, kwargs), is_correct=ok, max_abs_error=abs_err, max_rel_error=rel_err)
     except Exception as e:
         tb = traceback.format_exc()
@@ -376,6 +399,7 @@ def eval_performance(op, impl, tests, tolerances=None) -> Tuple[float, List[Perf
             else:
                 atol, rtol = tolerances
             ok, abs_err, rel_err = compare(ref, res, atol, rtol)
+            _raise_device_status(res)
             if not ok:
                 raise ValueError(f"Reference and result tensors are not close: max absolute error {abs_err}, max relative error {rel_err}")
             t = bench(lambda: impl(*args, **kwargs))
@@ -389,11 +413,26 @@ def eval_performance(op, impl, tests, tolerances=None) -> Tuple[float, List[Perf
     return speedups.log().mean().exp().float(), results
 
 
+_stream_screen = {}
+
+
+def _creates_streams(impl) -> bool:
+    """`uses_cuda_stream(impl)`, remembered per callable (reading and parsing the source of
+    the same function for each of thousands of per-case tasks is pure overhead)."""
+    try:
+        return _stream_screen[impl]
+    except KeyError:
+        verdict = _stream_screen[impl] = uses_cuda_stream(impl)
+        return verdict
+    except TypeError:  # unhashable callable
+        return uses_cuda_stream(impl)
+
+
 def eval_one_op(op, impl, correctness_tests, performance_tests, tolerances=None):
     """(correctness score, performance score, correctness results, performance results).
     Implementations whose source creates CUDA streams are not evaluated (score 0 / 1.0)."""
     op_name = getattr(op, "__name__", str(op))
-    if uses_cuda_stream(impl):
+    if _creates_streams(impl):
         logger.warning(f"Skipping {op_name} because it uses CUDA stream")
         why = "Skipped: uses CUDA stream"
         cres = [CorrectnessTestResult(op_name=op_name, args=serialize_args(t.args, t.kwargs), is_correct=False, error_msg=why) for t in correctness_tests]

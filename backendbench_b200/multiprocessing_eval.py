@@ -20,6 +20,13 @@ What is different, because the machine is 8 GPUs with 180 GB each rather than on
 * Queues block with a timeout instead of 0.1 s sleep-polling, the parent watches
   `Process.is_alive()` so a hard crash (segfault, SIGKILL, `os._exit`) cannot stall
   `get_results` forever, and a per-task wall-clock limit bounds a wedged worker.
+* The parent knows which task every worker holds (workers post `TaskStarted` the moment
+  they take one), so a lost task is booked exactly once and only for a worker that held
+  one: a worker that dies idle costs nothing, and a death signal that arrives after the
+  liveness check already replaced its sender restarts nobody.
+* Workers post `WorkerReady` once their CUDA context and the kernel library are loaded;
+  `timeline()` reports start-up, steady-state rate and per-worker busy time, which is
+  what the sharded-sweep figure of the benchmark is made of.
 """
 
 from __future__ import annotations
@@ -69,6 +76,25 @@ class ProcessDeathSignal:
     worker_id: int
     error_msg: str
     task_id: int = -1
+    pid: int = -1
+
+
+@dataclass
+class TaskStarted:
+    """Posted by a worker the moment it takes a task off the queue."""
+
+    worker_id: int
+    task_id: int
+    pid: int = -1
+
+
+@dataclass
+class WorkerReady:
+    """Posted once per worker process when its device and the backend library are usable."""
+
+    worker_id: int
+    pid: int
+    seconds: float  # from process entry to ready (imports, CUDA context, library load)
 
 
 @dataclass(frozen=True)
@@ -180,10 +206,17 @@ def _resolve_impl(impl, op, backends_cache):
     return impl
 
 
-def _worker_process(worker_id, task_queue, result_queue, poll_s=0.5):
+def _worker_process(worker_id, task_queue, result_queue, poll_s=0.5, warm_backend=None):
+    t_entry = time.perf_counter()
+    pid = os.getpid()
     backends_cache = {}
     try:
         own_device = _worker_device(worker_id)
+        if warm_backend is not None:  # load the kernel table (and the shared library) before the first task
+            from .backends import make_backend
+
+            backends_cache[warm_backend] = make_backend(warm_backend.name, warm_backend.ops_directory)
+        result_queue.put(WorkerReady(worker_id, pid, time.perf_counter() - t_entry))
         while True:
             try:
                 task = task_queue.get(timeout=poll_s)
@@ -192,6 +225,7 @@ def _worker_process(worker_id, task_queue, result_queue, poll_s=0.5):
             if task is None:
                 logger.info(f"Worker {worker_id} received shutdown signal")
                 break
+            result_queue.put(TaskStarted(worker_id, task.task_id, pid))
             t0 = time.perf_counter()
             op = task.op
             try:
@@ -204,17 +238,22 @@ def _worker_process(worker_id, task_queue, result_queue, poll_s=0.5):
                 ctests = (test_to_device(t, torch.device(device)) for t in task.correctness_tests)
                 ptests = (test_to_device(t, torch.device(device)) for t in task.performance_tests)
                 cs, ps, cr, pr = eval_one_op(op, impl, ctests, ptests, task.tolerances)
+                error = None
                 if device.startswith("cuda"):
+                    # backstop: the per-test check in eval_correctness_test normally clears the word
                     from .ops import check_device_status
 
-                    check_device_status(torch.device(device))
-                result = EvalResult(task.task_id, float(cs), float(ps), cr, pr, None, worker_id, time.perf_counter() - t0)
+                    try:
+                        check_device_status(torch.device(device))
+                    except IndexError as e:
+                        error = f"device status after the task: {e}"
+                result = EvalResult(task.task_id, float(cs), float(ps), cr, pr, error, worker_id, time.perf_counter() - t0)
             except Exception as e:
                 msg = f"Error in eval_one_op: {e}\n{traceback.format_exc()}"
                 logger.warning(f"Worker {worker_id} task {task.task_id} failed: {msg}")
                 if "cuda" in str(e).lower():
                     # a CUDA error may have poisoned the context: die and let the parent restart us
-                    result_queue.put(ProcessDeathSignal(worker_id, f"Worker {worker_id} CUDA error: {msg}", task.task_id))
+                    result_queue.put(ProcessDeathSignal(worker_id, f"Worker {worker_id} CUDA error: {msg}", task.task_id, pid))
                     break
                 name = getattr(op, "__name__", str(op))
                 result = EvalResult(
@@ -225,7 +264,7 @@ def _worker_process(worker_id, task_queue, result_queue, poll_s=0.5):
                 )
             result_queue.put(result)
     except Exception as e:
-        result_queue.put(ProcessDeathSignal(worker_id, f"Worker {worker_id} fatal error: {e}\n{traceback.format_exc()}"))
+        result_queue.put(ProcessDeathSignal(worker_id, f"Worker {worker_id} fatal error: {e}\n{traceback.format_exc()}", -1, pid))
     finally:
         if torch.cuda.is_available():
             try:
@@ -251,8 +290,19 @@ class MultiprocessingEvaluator:
         self.backend = backend
         self.task_timeout_s = task_timeout_s
         self.restarts = 0
+        self.lost_tasks: List[int] = []  # task ids that died with their worker (no result)
         self._worker_target = worker_target or _worker_process
         self._last_progress = time.monotonic()
+        self._holding = {}  # worker id -> task id it took and has not answered yet
+        self._accounted = set()  # task ids already counted as completed
+        # timeline (time.monotonic): start of evaluation, per-worker ready, first / last result
+        self._t_start = None
+        self._t_ready = {}
+        self._t_spawn = {}
+        self._startup_s = {}
+        self._t_results: List[float] = []
+        self._busy_s = {}
+        self._tasks_by_worker = {}
 
     # ---------------------------------------------------------------- submission
     def submit_task(self, op, impl, correctness_tests, performance_tests, tolerances=None) -> int:
@@ -285,7 +335,11 @@ class MultiprocessingEvaluator:
 
     # ---------------------------------------------------------------- workers
     def _start_worker(self, worker_id):
-        p = self.mp_context.Process(target=self._worker_target, args=(worker_id, self.task_queue, self.result_queue), daemon=self.daemon)
+        args = (worker_id, self.task_queue, self.result_queue)
+        if self._worker_target is _worker_process:
+            args = args + (0.5, self.backend)
+        p = self.mp_context.Process(target=self._worker_target, args=args, daemon=self.daemon)
+        self._t_spawn[worker_id] = time.monotonic()
         p.start()
         self.workers[worker_id] = p
         logger.info(f"Started worker {worker_id} (PID: {p.pid}, GPU: {worker_id})")
@@ -296,52 +350,148 @@ class MultiprocessingEvaluator:
             if old.is_alive():
                 old.terminate()
             old.join(timeout=5)
+        self._holding.pop(worker_id, None)
         self.restarts += 1
         self._start_worker(worker_id)
         logger.warning(f"Restarted worker {worker_id}")
 
     def start_evaluation(self) -> None:
         self._last_progress = time.monotonic()
+        self._t_start = time.monotonic()
         for i in range(self.num_workers):
             self._start_worker(i)
 
+    # ---------------------------------------------------------------- accounting
+    def _account(self, task_id, lost=False) -> bool:
+        """Count `task_id` as completed, once. Returns False when it was counted before."""
+        if task_id is None or task_id < 0 or task_id in self._accounted:
+            return False
+        self._accounted.add(task_id)
+        self.completed_tasks += 1
+        if lost:
+            self.lost_tasks.append(task_id)
+        return True
+
+    def _is_current(self, worker_id, pid) -> bool:
+        """Whether a message's sender is the process that now owns `worker_id` (a message of a
+        process that was already replaced must not touch its successor)."""
+        p = self.workers.get(worker_id)
+        return p is not None and (pid is None or pid < 0 or p.pid == pid)
+
+    def _handle(self, item, results) -> None:
+        now = time.monotonic()
+        self._last_progress = now
+        if isinstance(item, WorkerReady):
+            if self._is_current(item.worker_id, item.pid):
+                self._t_ready.setdefault(item.worker_id, now)
+                # spawn -> ready as the parent sees it: interpreter start, imports, CUDA context, library load
+                self._startup_s.setdefault(item.worker_id, now - self._t_spawn.get(item.worker_id, now))
+        elif isinstance(item, TaskStarted):
+            if self._is_current(item.worker_id, item.pid) and item.task_id not in self._accounted:
+                self._holding[item.worker_id] = item.task_id
+        elif isinstance(item, ProcessDeathSignal):
+            logger.error(f"Worker {item.worker_id} died: {item.error_msg}")
+            task_id = item.task_id if item.task_id >= 0 else (self._holding.get(item.worker_id) if self._is_current(item.worker_id, item.pid) else None)
+            self._account(task_id, lost=True)  # the task that killed the worker yields no result
+            if self._is_current(item.worker_id, item.pid):
+                self._restart_worker(item.worker_id)
+        elif isinstance(item, EvalResult):
+            if self._account(item.task_id):
+                results.append(item)
+                self._t_results.append(now)
+                self._busy_s[item.worker_id] = self._busy_s.get(item.worker_id, 0.0) + item.seconds
+                self._tasks_by_worker[item.worker_id] = self._tasks_by_worker.get(item.worker_id, 0) + 1
+            if self._holding.get(item.worker_id) == item.task_id:
+                del self._holding[item.worker_id]
+            if item.error:
+                logger.warning(f"Task {item.task_id} completed with error: {item.error}")
+
+    def _drain(self, results, wait_s=0.05) -> None:
+        """Handle every message already in the result queue (a worker that posted and then
+        exited may be seen dead before its last message is read)."""
+        while True:
+            try:
+                item = self.result_queue.get(timeout=wait_s)
+            except queue.Empty:
+                return
+            self._handle(item, results)
+
     # ---------------------------------------------------------------- results
     def get_results(self):
+        """Block until every submitted task is accounted for; results sorted by task id. May be
+        called again after further `submit_task` calls: the workers stay up in between."""
         results = []
+        if self._t_start is None:
+            self._t_start = time.monotonic()
         while self.completed_tasks < self.total_tasks:
             try:
                 item = self.result_queue.get(timeout=0.2)
             except queue.Empty:
-                self._check_liveness()
+                self._check_liveness(results)
                 continue
-            self._last_progress = time.monotonic()
-            if isinstance(item, ProcessDeathSignal):
-                self.completed_tasks += 1  # the task that killed the worker yields no result
-                logger.error(f"Worker {item.worker_id} died: {item.error_msg}")
-                self._restart_worker(item.worker_id)
-            elif isinstance(item, EvalResult):
-                results.append(item)
-                self.completed_tasks += 1
-                if item.error:
-                    logger.warning(f"Task {item.task_id} completed with error: {item.error}")
+            self._handle(item, results)
         results.sort(key=lambda r: r.task_id)
         return results
 
-    def _check_liveness(self):
-        """A worker that vanished without a signal took one task with it: account for the
-        task and restart the worker. A worker silent for `task_timeout_s` is replaced too."""
-        for wid, p in list(self.workers.items()):
-            if not p.is_alive() and self.completed_tasks < self.total_tasks:
-                logger.error(f"Worker {wid} exited unexpectedly (exit code {p.exitcode})")
-                self.completed_tasks += 1
-                self._last_progress = time.monotonic()
-                self._restart_worker(wid)
-        if time.monotonic() - self._last_progress > self.task_timeout_s:
-            logger.error(f"No result for {self.task_timeout_s} s: restarting all workers")
-            self.completed_tasks += len(self.workers)
+    def _check_liveness(self, results):
+        """A worker that vanished without a signal took the task it held (if any) with it:
+        book that task once and restart the worker. When nothing at all has arrived for
+        `task_timeout_s`, the tasks in flight are booked as lost and their workers replaced."""
+        dead = [wid for wid, p in self.workers.items() if not p.is_alive()]
+        if dead:
+            self._drain(results)  # their last messages first
+        for wid in dead:
+            p = self.workers.get(wid)
+            if p is None or p.is_alive():
+                continue  # replaced while draining
+            logger.error(f"Worker {wid} exited unexpectedly (exit code {p.exitcode})")
+            self._account(self._holding.pop(wid, None), lost=True)
             self._last_progress = time.monotonic()
-            for wid in list(self.workers):
+            if self.completed_tasks < self.total_tasks:
                 self._restart_worker(wid)
+            else:
+                self.workers.pop(wid, None)
+        if time.monotonic() - self._last_progress > self.task_timeout_s:
+            logger.error(f"No message for {self.task_timeout_s} s: replacing the workers that hold a task")
+            held = list(self._holding.items())
+            for wid, task_id in held:
+                self._account(task_id, lost=True)
+                self._restart_worker(wid)
+            if not held:
+                # nothing is known to be in flight, yet tasks are missing (one vanished between a
+                # worker's queue read and its TaskStarted message): give up on the remainder
+                missing = [t for t in range(self.next_task_id) if t not in self._accounted]
+                logger.error(f"Giving up on tasks nobody holds: {missing}")
+                for t in missing:
+                    self._account(t, lost=True)
+            self._last_progress = time.monotonic()
+
+    def timeline(self) -> dict:
+        """Wall-clock anatomy of the evaluation so far (seconds, `time.monotonic` of the parent)."""
+        t0 = self._t_start
+        if t0 is None or not self._t_results:
+            return {}
+        ready = sorted(self._t_ready.values())
+        last = max(self._t_results)
+        first = min(self._t_results)
+        all_ready = ready[-1] if len(ready) >= self.num_workers else None
+        out = {
+            "wall_s": last - t0,
+            "first_result_s": first - t0,
+            "first_worker_ready_s": (ready[0] - t0) if ready else None,
+            "all_workers_ready_s": (all_ready - t0) if all_ready is not None else None,
+            "worker_startup_s": {int(k): round(v, 3) for k, v in sorted(self._startup_s.items())},
+            "per_worker_busy_s": {int(k): round(v, 3) for k, v in sorted(self._busy_s.items())},
+            "per_worker_tasks": {int(k): v for k, v in sorted(self._tasks_by_worker.items())},
+            "results": len(self._t_results),
+            "lost_tasks": list(self.lost_tasks),
+            "restarts": self.restarts,
+        }
+        if all_ready is not None:
+            after = [t for t in self._t_results if t >= all_ready]
+            out["results_after_all_ready"] = len(after)
+            out["steady_s"] = (last - all_ready) if after else 0.0
+        return out
 
     # ---------------------------------------------------------------- shutdown
     def shutdown(self) -> None:

@@ -64,6 +64,18 @@ def _require_cuda(*tensors: torch.Tensor) -> torch.device:
     return dev
 
 
+# Every output and scratch buffer of the host wrappers is allocated here. `_allocator` is a
+# hook for the guard-band tests (a callable (shape, dtype, device) -> tensor that places the
+# tensor between sentinel bands); None means PyTorch's caching allocator.
+_allocator = None
+
+
+def _new(shape, dtype, device) -> torch.Tensor:
+    if _allocator is not None:
+        return _allocator(shape, dtype, device)
+    return torch.empty(shape, dtype=dtype, device=device)
+
+
 def _stream_handle() -> int:
     return torch.cuda.current_stream().cuda_stream
 
@@ -174,7 +186,7 @@ def _contig(t: torch.Tensor) -> torch.Tensor:
     """`t` itself when contiguous, else a contiguous copy made by the strided-copy kernel."""
     if t.is_contiguous():
         return t
-    out = torch.empty(t.shape, dtype=t.dtype, device=t.device)
+    out = _new(t.shape, t.dtype, t.device)
     if out.numel():
         nd, shp, (st,) = _iter_layout(t.shape, [t])
         check(lib().b200_copy_strided(t.data_ptr(), out.data_ptr(), nd, shp, st, _dt(t.dtype), _dt(t.dtype), _stream_handle()), "b200_copy_strided")
@@ -204,7 +216,7 @@ def relu(self: torch.Tensor, *, _into: Optional[torch.Tensor] = None) -> torch.T
     _require_cuda(self)
     if self.dtype not in _FLOATS:
         raise UnsupportedByB200(f"relu: dtype {self.dtype}")
-    out = _into if _into is not None else torch.empty(self.shape, dtype=self.dtype, device=self.device)
+    out = _into if _into is not None else _new(self.shape, self.dtype, self.device)
     if out.numel():
         nd, shp, (sx,) = _iter_layout(self.shape, [self])
         check(lib().b200_relu(self.data_ptr(), out.data_ptr(), nd, shp, sx, _dt(self.dtype), _stream_handle()), "b200_relu")
@@ -229,7 +241,7 @@ def _binary(name: str, a, b, alpha: float, _into: Optional[torch.Tensor] = None)
     _require_cuda(a)
     st = _stream_handle()
     if _is_wrapped_scalar(b):
-        out = _into if _into is not None else torch.empty(a.shape, dtype=res_dtype, device=a.device)
+        out = _into if _into is not None else _new(a.shape, res_dtype, a.device)
         if out.numel():
             nd, shp, (sa,) = _iter_layout(a.shape, [a])
             val = _scalar_value(b)
@@ -245,7 +257,7 @@ def _binary(name: str, a, b, alpha: float, _into: Optional[torch.Tensor] = None)
         shape = a.shape
     else:
         shape = _broadcast_shape(a.shape, b.shape)
-    out = _into if _into is not None else torch.empty(shape, dtype=res_dtype, device=a.device)
+    out = _into if _into is not None else _new(shape, res_dtype, a.device)
     if out.numel():
         nd, shp, (sa, sb) = _iter_layout(shape, [a, b])
         if name == "add":
@@ -281,7 +293,7 @@ def where_self(condition: torch.Tensor, self, other) -> torch.Tensor:
     x, y = as_dev(self), as_dev(other)
     _require_cuda(condition, x, y)
     shape = _broadcast_shape(condition.shape, x.shape, y.shape)
-    out = torch.empty(shape, dtype=res_dtype, device=dev)
+    out = _new(shape, res_dtype, dev)
     if out.numel():
         if x.dtype != y.dtype and not (x.dtype in _FLOATS and y.dtype in _FLOATS):
             raise UnsupportedByB200(f"where: mixed dtypes {x.dtype}/{y.dtype}")
@@ -313,7 +325,7 @@ def _softmax_impl(self: torch.Tensor, dim: int, half_to_float: bool, log: bool) 
         raise RuntimeError("conversion is supported for Half type only")
     dim = _norm_dim(dim, self.dim())
     out_dtype = torch.float32 if half_to_float else self.dtype
-    out = torch.empty(self.shape, dtype=out_dtype, device=self.device)
+    out = _new(self.shape, out_dtype, self.device)
     if out.numel():
         outer, d, inner = _split_at(list(self.shape) or [1], dim)
         if inner > 1 and d >= 128 and outer * ((inner + 127) // 128) < 592:
@@ -321,7 +333,7 @@ def _softmax_impl(self: torch.Tensor, dim: int, half_to_float: bool, log: bool) 
             # column kernel. Move the dim last with the strided-copy kernel, run the row
             # kernel, and copy the result back through the inverse permutation.
             xt = _contig(self.movedim(dim, -1))
-            tmp = torch.empty(xt.shape, dtype=out_dtype, device=self.device)
+            tmp = _new(xt.shape, out_dtype, self.device)
             check(lib().b200_softmax(xt.data_ptr(), tmp.data_ptr(), xt.numel() // d, d, 1, _dt(xt.dtype), _dt(out_dtype), 1 if log else 0, _stream_handle()), "b200_softmax")
             back = tmp.movedim(-1, dim)  # a view with out's shape
             nd, shp, (st,) = _iter_layout(out.shape, [back])
@@ -355,7 +367,7 @@ def _scratch(device: torch.device, nbytes: int) -> torch.Tensor:
     key = (device.index if device.index is not None else torch.cuda.current_device(), torch.cuda.current_stream().cuda_stream)
     buf = _scratch_cache.get(key)
     if buf is None or buf.numel() < nbytes:
-        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        buf = _new(max(nbytes, 1 << 20), torch.uint8, device)
         _scratch_cache.pop(key, None)
         _scratch_cache[key] = buf
         while len(_scratch_cache) > _SCRATCH_MAX_STREAMS:  # streams come and go: keep the most recently sized buffers only
@@ -393,7 +405,7 @@ def sum_dim_IntList(self: torch.Tensor, dim=None, keepdim: bool = False, *, dtyp
     if nd == 0:
         dims = []
     out_shape = [(1 if d in dims else s) for d, s in enumerate(self.shape)] if keepdim else [s for d, s in enumerate(self.shape) if d not in dims]
-    out = torch.empty(out_shape, dtype=out_dtype, device=self.device)
+    out = _new(out_shape, out_dtype, self.device)
     if out.numel() == 0:
         return out
     if not dims:  # 0-dim input: the sum of one element
@@ -433,9 +445,9 @@ def native_layer_norm_default(input: torch.Tensor, normalized_shape, weight=None
     lead = list(input.shape[: input.dim() - k])
     rows, cols = _prod(lead), _prod(ns)
     stat_shape = lead + [1] * k
-    out = torch.empty(input.shape, dtype=input.dtype, device=input.device)
-    mean = torch.empty(stat_shape, dtype=LAYER_NORM_STAT_DTYPE_CUDA, device=input.device)
-    rstd = torch.empty(stat_shape, dtype=LAYER_NORM_STAT_DTYPE_CUDA, device=input.device)
+    out = _new(input.shape, input.dtype, input.device)
+    mean = _new(stat_shape, LAYER_NORM_STAT_DTYPE_CUDA, input.device)
+    rstd = _new(stat_shape, LAYER_NORM_STAT_DTYPE_CUDA, input.device)
     if rows:
         x = _contig(input)
         w = _contig(weight) if weight is not None else None
@@ -471,7 +483,7 @@ def argmax_default(self: torch.Tensor, dim=None, keepdim: bool = False) -> torch
         x = _contig(self)
         outer, d, inner = _split_at(shape, dim)
         out_shape = [(1 if i == dim else s) for i, s in enumerate(self.shape)] if keepdim else [s for i, s in enumerate(self.shape) if i != dim]
-    out = torch.empty(out_shape, dtype=torch.int64, device=self.device)
+    out = _new(out_shape, torch.int64, self.device)
     if out.numel():
         L = lib()
         need = L.b200_reduce_scratch_bytes(outer, d, inner)
@@ -495,7 +507,7 @@ def embedding_default(weight: torch.Tensor, indices: torch.Tensor, padding_idx: 
     if weight.dim() < 1:
         raise RuntimeError("'weight' must be at least 1-D")
     idt = _index_dtype(indices, "embedding")
-    out = torch.empty(list(indices.shape) + list(weight.shape[1:]), dtype=weight.dtype, device=weight.device)
+    out = _new(list(indices.shape) + list(weight.shape[1:]), weight.dtype, weight.device)
     if out.numel():
         w, idx = _contig(weight), _contig(indices)
         row_bytes = _prod(w.shape[1:]) * w.element_size()
@@ -520,7 +532,7 @@ def index_select_default(self: torch.Tensor, dim: int, index: torch.Tensor) -> t
         out_shape[dim] = n_idx
     elif n_idx != 1:
         raise IndexError("index_select(): Index to scalar can have only 1 value")
-    out = torch.empty(out_shape, dtype=self.dtype, device=self.device)
+    out = _new(out_shape, self.dtype, self.device)
     if out.numel():
         x, idx = _contig(self), _contig(index)
         outer, d, inner = _split_at(shape, dim)
@@ -555,7 +567,7 @@ def gather_default(self: torch.Tensor, dim: int, index: torch.Tensor, *, sparse_
     """aten.gather.default -- out[p] = self[p with p[dim] = index[p]] (bit copy)."""
     _require_cuda(self, index)
     dim = _norm_dim(int(dim), self.dim())
-    out = torch.empty(index.shape, dtype=self.dtype, device=self.device)
+    out = _new(index.shape, self.dtype, self.device)
     if index.numel() == 0:
         return out
     _check_gather_shapes(self, dim, index)
@@ -585,7 +597,7 @@ def scatter_add_default(self: torch.Tensor, dim: int, index: torch.Tensor, src: 
     if src.dtype != self.dtype:
         raise RuntimeError("scatter(): Expected self.dtype to be equal to src.dtype")
     dim = _norm_dim(int(dim), self.dim())
-    out = torch.empty(self.shape, dtype=self.dtype, device=self.device)
+    out = _new(self.shape, self.dtype, self.device)
     if out.numel() == 0:
         return out
     if index.numel():
@@ -633,7 +645,7 @@ def _repitch(t: torch.Tensor, batch: int, rows: int, cols: int, s_b: int, s_r: i
     """Copy a [batch, rows, cols] view into a fresh buffer whose row pitch is a multiple of 8
     elements (pad columns stay uninitialised: the tensor map's extents exclude them)."""
     pitch = (cols + 7) // 8 * 8
-    buf = torch.empty((batch, rows, pitch), dtype=t.dtype, device=t.device)
+    buf = _new((batch, rows, pitch), t.dtype, t.device)
     check(lib().b200_copy_pitched(t.data_ptr(), buf.data_ptr(), batch, rows, cols, s_b, s_r, s_c, rows * pitch, pitch, t.element_size(), _stream_handle()), "b200_copy_pitched")
     return buf, (rows * pitch, pitch)
 
@@ -643,7 +655,7 @@ def _gemm(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor], batch:
         raise RuntimeError(f"expected m1 and m2 to have the same dtype, but got: {a.dtype} != {b.dtype}")
     if a.dtype not in _FLOATS:
         raise UnsupportedByB200(f"matmul: dtype {a.dtype}")
-    out = torch.empty(out_shape, dtype=a.dtype, device=a.device)
+    out = _new(out_shape, a.dtype, a.device)
     if out.numel() == 0:
         return out
     # 16-bit operands whose layout the tensor-core path cannot load (row pitch or base off the

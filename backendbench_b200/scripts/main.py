@@ -27,6 +27,7 @@ from ..backends import make_backend
 from ..cases import named_cases, sweep_cases
 from ..multiprocessing_eval import BackendRef, MultiprocessingEvaluator, SpecTest
 from ..opregistry import get_operator
+from ..sharding import estimated_seconds
 from ..suite import OpTest, TestSuite, make_smoke_suite
 
 logger = logging.getLogger(__name__)
@@ -51,6 +52,32 @@ def build_suite(name: str, device: str, ops=None, n_cases: int = 512) -> TestSui
     return TestSuite(name, optests)
 
 
+def task_units(suite, backend):
+    """(op, correctness tests, performance tests) per task for the multi-worker run. An
+    operator whose tests are all `SpecTest` descriptors is cut into one task per CASE and
+    the tasks of all operators are ordered longest first (estimated from the case's bytes
+    and FLOP), so the shared queue balances the GPUs; other operators stay one task each,
+    at the front (their cost is unknown), as BackendBench/scripts/main.py:266-287 submits them."""
+    whole, units = [], []
+    for test in suite:
+        if test.op not in backend:
+            continue
+        ctests, ptests = list(test.correctness_tests), list(test.performance_tests)
+        if ctests and all(isinstance(t, SpecTest) for t in ctests + ptests):
+            timed = {t.spec for t in ptests}
+            seen = set()
+            for t in ctests:
+                seen.add(t.spec)
+                units.append((estimated_seconds(t.spec) * (50 if t.spec in timed else 1), test.op, [t], [t] if t.spec in timed else []))
+            for t in ptests:
+                if t.spec not in seen:
+                    units.append((estimated_seconds(t.spec) * 50, test.op, [], [t]))
+        else:
+            whole.append((test.op, ctests, ptests))
+    units.sort(key=lambda u: -u[0])
+    return whole + [(op, c, q) for _, op, c, q in units]
+
+
 def run(suite, backend, backend_ref, num_workers=None, daemon=True, p=1.0, tolerances=None):
     """Evaluate `suite` on `backend`; returns (mean correctness, geomean perf, perf@p, results)."""
     overall_correctness, overall_performance, all_c, all_p = [], [], [], []
@@ -65,17 +92,28 @@ def run(suite, backend, backend_ref, num_workers=None, daemon=True, p=1.0, toler
             all_p.extend(pres)
     else:
         with MultiprocessingEvaluator(num_workers, daemon=daemon, backend=backend_ref) as evaluator:
-            for test in suite:
-                if test.op not in backend:
-                    continue
-                evaluator.submit_task(test.op, backend_ref if backend_ref is not None else backend[test.op], test.correctness_tests, test.performance_tests, tolerances)
+            op_of_task = {}
+            for op, ctests, ptests in task_units(suite, backend):
+                tid = evaluator.submit_task(op, backend_ref if backend_ref is not None else backend[op], ctests, ptests, tolerances)
+                op_of_task[tid] = op
             evaluator.start_evaluation()
             results = evaluator.get_results()
-        for r in results:
-            overall_correctness.append(all(c.is_correct for c in r.correctness_results))
-            overall_performance.append(float(r.performance_score))
-            all_c.extend(r.correctness_results)
-            all_p.extend(r.performance_results)
+        by_op = {}
+        for r in results:  # one task per CASE for descriptor suites: put the operator back together
+            by_op.setdefault(op_of_task[r.task_id], []).append(r)
+        for op, rs in by_op.items():
+            cres = [c for r in rs for c in r.correctness_results]
+            pres = [q for r in rs for q in r.performance_results]
+            overall_correctness.append(all(c.is_correct for c in cres))
+            if len(rs) == 1:
+                overall_performance.append(float(rs[0].performance_score))
+            elif pres:  # as eval_performance scores an operator: geomean over its cases, a failed case counts 1.0
+                sp = torch.tensor([float(q.speedup) if (q.successfully_ran and q.speedup) else 1.0 for q in pres], dtype=torch.float64)
+                overall_performance.append(float(sp.log().mean().exp()))
+            else:
+                overall_performance.append(float("nan"))
+            all_c.extend(cres)
+            all_p.extend(pres)
     if not overall_correctness:
         return 0.0, 1.0, 0.0, (all_c, all_p)
     mean_correctness = torch.tensor(overall_correctness).float().mean().item()

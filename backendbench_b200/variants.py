@@ -39,26 +39,57 @@ def _copy_into(dst: torch.Tensor, src: torch.Tensor) -> torch.Tensor:
     return dst
 
 
-def _deliver(result: torch.Tensor, out: torch.Tensor, what: str) -> torch.Tensor:
-    """aten's `out=` contract: dtype must match, a wrong shape is resized, then filled."""
+_TYPE_NAMES = {torch.float32: "Float", torch.bfloat16: "BFloat16", torch.float16: "Half", torch.float64: "Double", torch.int64: "Long", torch.int32: "Int", torch.int16: "Short", torch.int8: "Char", torch.uint8: "Byte", torch.bool: "Bool"}
+
+
+def _as_dtype(result: torch.Tensor, dtype: torch.dtype, what: str) -> torch.Tensor:
+    """`result` in the target's dtype, the way aten treats a result whose type differs from
+    the `out=` / in-place target: allowed when `torch.can_cast(result type, target type)`
+    (then the full-precision result is rounded ONCE into the target type -- `bf16.add_(f32)`
+    adds in fp32 and rounds to bf16), an error with aten's message otherwise. The conversion
+    runs in the library's converting copy kernel (floating types)."""
+    if result.dtype == dtype:
+        return result
+    if not torch.can_cast(result.dtype, dtype):
+        raise RuntimeError(f"result type {_TYPE_NAMES.get(result.dtype, result.dtype)} can't be cast to the desired output type {_TYPE_NAMES.get(dtype, dtype)}")
+    if result.dtype not in ops._FLOATS or dtype not in ops._FLOATS:
+        raise ops.UnsupportedByB200(f"{what}: converting a {result.dtype} result into a {dtype} target")
+    out = ops._new(result.shape, dtype, result.device)
+    if out.numel():
+        nd, shp, (st,) = ops._iter_layout(result.shape, [result])
+        check(lib().b200_copy_strided(result.data_ptr(), out.data_ptr(), nd, shp, st, ops._dt(result.dtype), ops._dt(dtype), _stream_handle()), "b200_copy_strided")
+    return out
+
+
+def _deliver(result: torch.Tensor, out: torch.Tensor, what: str, cast: bool = False) -> torch.Tensor:
+    """aten's `out=` contract: a wrong shape is resized, then the tensor is filled. The out
+    tensor's dtype must equal the result's, except for the TensorIterator operators
+    (`cast=True`: add, mul, sum), which accept any type the result type can be cast to."""
     if out is result:
         return out
     if not out.is_cuda:
         raise ops.UnsupportedByB200(f"{what}: out tensor on {out.device}")
-    if out.dtype != result.dtype:
+    if cast:
+        result = _as_dtype(result, out.dtype, what)
+    elif out.dtype != result.dtype:
         raise RuntimeError(f"Expected out tensor to have dtype {result.dtype}, but got {out.dtype} instead")
     if out.shape != result.shape:
         out.resize_(result.shape)  # storage management only; aten warns when the old shape was non-empty
     return _copy_into(out, result)
 
 
-def _in_place(self: torch.Tensor, result: torch.Tensor, what: str) -> torch.Tensor:
-    """aten's in-place contract: the result must already fit `self` (no resize, no cast)."""
+def _in_place(self: torch.Tensor, result: torch.Tensor, what: str, cast: bool = False) -> torch.Tensor:
+    """aten's in-place contract: the result must already have `self`'s shape (no resize); its
+    type must be `self`'s, or (`cast=True`: add_, mul_) one that can be cast to it."""
     if result.shape != self.shape:
         raise RuntimeError(f"output with shape {list(self.shape)} doesn't match the broadcast shape {list(result.shape)}")
-    if result.dtype != self.dtype:
-        raise RuntimeError(f"result type {result.dtype} can't be cast to the desired output type {self.dtype}")
-    return _copy_into(self, result) if result is not self else self
+    if result is self:
+        return self
+    if cast:
+        result = _as_dtype(result, self.dtype, what)
+    elif result.dtype != self.dtype:
+        raise RuntimeError(f"result type {_TYPE_NAMES.get(result.dtype, result.dtype)} can't be cast to the desired output type {_TYPE_NAMES.get(self.dtype, self.dtype)}")
+    return _copy_into(self, result)
 
 
 def _direct_target(self: torch.Tensor, others, shape, dtype) -> Optional[torch.Tensor]:
@@ -96,24 +127,24 @@ def add__Tensor(self: torch.Tensor, other, *, alpha=1) -> torch.Tensor:
     """aten.add_.Tensor"""
     shape, dtype = _result_shape_dtype(self, other)
     target = _direct_target(self, (other,), shape, dtype)
-    return _in_place(self, ops._binary("add", self, other, float(alpha), _into=target), "add_")
+    return _in_place(self, ops._binary("add", self, other, float(alpha), _into=target), "add_", cast=True)
 
 
 def mul__Tensor(self: torch.Tensor, other) -> torch.Tensor:
     """aten.mul_.Tensor"""
     shape, dtype = _result_shape_dtype(self, other)
     target = _direct_target(self, (other,), shape, dtype)
-    return _in_place(self, ops._binary("mul", self, other, 1.0, _into=target), "mul_")
+    return _in_place(self, ops._binary("mul", self, other, 1.0, _into=target), "mul_", cast=True)
 
 
 def add_out(self, other, *, alpha=1, out: torch.Tensor) -> torch.Tensor:
     """aten.add.out"""
-    return _deliver(ops.add_Tensor(self, other, alpha=alpha), out, "add.out")
+    return _deliver(ops.add_Tensor(self, other, alpha=alpha), out, "add.out", cast=True)
 
 
 def mul_out(self, other, *, out: torch.Tensor) -> torch.Tensor:
     """aten.mul.out"""
-    return _deliver(ops.mul_Tensor(self, other), out, "mul.out")
+    return _deliver(ops.mul_Tensor(self, other), out, "mul.out", cast=True)
 
 
 def where_self_out(condition, self, other, *, out: torch.Tensor) -> torch.Tensor:
@@ -134,7 +165,7 @@ def _log_softmax_out(self, dim, half_to_float, *, out: torch.Tensor) -> torch.Te
 
 def sum_IntList_out(self, dim=None, keepdim=False, *, dtype=None, out: torch.Tensor) -> torch.Tensor:
     """aten.sum.IntList_out"""
-    return _deliver(ops.sum_dim_IntList(self, dim, keepdim, dtype=dtype), out, "sum.IntList_out")
+    return _deliver(ops.sum_dim_IntList(self, dim, keepdim, dtype=dtype), out, "sum.IntList_out", cast=True)
 
 
 def native_layer_norm_out(input, normalized_shape, weight, bias, eps, *, out0: torch.Tensor, out1: torch.Tensor, out2: torch.Tensor):

@@ -263,6 +263,18 @@ int b200_gemm_uses_tensor_cores(int64_t batch, int64_t M, int64_t N, int64_t K, 
                                 int64_t sAm, int64_t sAk, int64_t sBb, int64_t sBk, int64_t sBn,
                                 int dtype, const void* A, const void* B, const void* C);
 
+/* Failure-detection probe of the tcgen05 kernel's bounded waits (no counterpart in the
+ * reference, whose only failure path is a worker that dies on a CUDA error,
+ * multiprocessing_eval.py:130-138): runs the tensor-core kernel on row-major bf16/f16
+ * A [M, K], B [K, N] with the producer WITHHOLDING the first K slab of every CTA's first
+ * tile and with every mbarrier wait limited to `wait_limit_us` (50 .. 100000). Nothing can
+ * complete that tile, so the waits run out: the kernel ORs B200_DEV_WAIT_TIMEOUT into
+ * *status, frees its tensor memory and returns by itself within a few limits; C is left
+ * undefined. The context stays usable and the next b200_gemm is unaffected. Returns
+ * B200_EALIGN when the operands would not take the tensor-core path. */
+int b200_gemm_wait_probe(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                         int dtype, int64_t wait_limit_us, uint32_t* status, void* stream);
+
 /* The same contraction for fp32 operands on the tensor cores: A and B are split once into
  * three bf16 planes each (x = x1 + x2 + x3 to within 2^-25), written to caller scratch, and
  * the six plane products that matter at fp32 resolution are accumulated in fp32 by the

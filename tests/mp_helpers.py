@@ -47,3 +47,13 @@ def gloo_shard_worker(rank, world, port, out_dir):
         json.dump({"rank": rank, "n_weak": len(mine), "strong_ids": [c.case_id for c in strong], "weak_seeds": [c.seed for c in mine][:4], "max_ms": worst, "total_units": total}, fh)
     dist.barrier()
     dist.destroy_process_group()
+
+
+def worker_one_dies_idle(worker_id, task_queue, result_queue):
+    """Worker target for the liveness test: worker 1 vanishes before it ever takes a task
+    (a crash during start-up); every other worker is the ordinary loop."""
+    if worker_id == 1:
+        os._exit(23)
+    from backendbench_b200.multiprocessing_eval import _worker_process
+
+    _worker_process(worker_id, task_queue, result_queue)

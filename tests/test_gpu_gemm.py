@@ -237,3 +237,32 @@ def test_long_contractions_with_small_outputs_leave_the_single_cta_path():
         h, w = _rand((9, 1000), dt, g, 1000**-0.5), _rand((1000, 7), dt, g, 1.0)
         _check(ops.mm_default(h, w), h.double() @ w.double(), dt)
     ops.check_device_status()
+
+
+def test_a_wait_that_cannot_complete_ends_in_a_status_not_a_hang():
+    """The failure-detection form this kernel has: every mbarrier wait carries a time limit.
+    The probe entry withholds one K slab (so the MMA warp's wait for it can never complete)
+    with a 1 ms limit; the kernel must come back by itself, report B200_DEV_WAIT_TIMEOUT in
+    the status word, and leave the context and the tensor memory usable for the next product."""
+    import time
+
+    g = torch.Generator(device=DEV).manual_seed(9)
+    a = _rand((512, 1024), torch.bfloat16, g, 1024**-0.5)
+    b = _rand((1024, 768), torch.bfloat16, g, 1.0)
+    c = torch.empty(512, 768, dtype=torch.bfloat16, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    rc = _abi.lib().b200_gemm_wait_probe(a.data_ptr(), b.data_ptr(), c.data_ptr(), 512, 768, 1024, _abi.BF16, 1000, status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, rc
+    torch.cuda.synchronize()
+    took = time.perf_counter() - t0
+    assert int(status.item()) & _abi.DEV_WAIT_TIMEOUT
+    assert took < 1.0, took  # a handful of 1 ms limits, not the 2 s of an ordinary call
+    # limits outside 50 us .. 0.1 s are refused, as are operands that would not reach the kernel
+    assert _abi.lib().b200_gemm_wait_probe(a.data_ptr(), b.data_ptr(), c.data_ptr(), 512, 768, 1024, _abi.BF16, 5_000_000, status.data_ptr(), 0) < 0
+    assert _abi.lib().b200_gemm_wait_probe(a.data_ptr(), b.data_ptr(), c.data_ptr(), 512, 768, 1024, _abi.F32, 1000, status.data_ptr(), 0) < 0
+    # the same context, the same tensor memory: an ordinary product right behind it is correct
+    got = ops.mm_default(a, b)
+    ops.check_device_status()
+    _check(got, a.double() @ b.double(), torch.bfloat16)

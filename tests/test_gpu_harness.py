@@ -150,3 +150,96 @@ def test_one_worker_sweep_with_descriptor_tasks():
     failed = [f for f in failed if not f[0].startswith("scatter_add")]
     assert not failed, failed
     assert any(r.performance_results for r in results)
+
+
+def test_two_workers_share_one_queue_of_per_case_tasks():
+    """Worker i on GPU i, one shared queue, per-case tasks longest first
+    (BackendBench/multiprocessing_eval.py:226-395 has only ever run with one worker)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two visible GPUs")
+    from backendbench_b200.sharding import lpt_order
+
+    cases = lpt_order([c for c in sweep_cases(96, seed=3, max_log2=20)][:48])
+    ref = BackendRef("b200")
+    with MultiprocessingEvaluator(2, backend=ref) as evaluator:
+        for c in cases:
+            evaluator.submit_task(c.op, ref, [SpecTest(c, "cuda")], [], "dtype")
+        evaluator.start_evaluation()
+        results = evaluator.get_results()
+        tl = evaluator.timeline()
+    assert len(results) == len(cases) and tl["lost_tasks"] == [] and tl["restarts"] == 0
+    assert {r.worker_id for r in results} == {0, 1} and sum(tl["per_worker_tasks"].values()) == len(cases)
+    assert tl["all_workers_ready_s"] is not None and tl["wall_s"] >= tl["first_result_s"] > 0
+    failed = [cases[r.task_id].label() for r in results if r.correctness_score != 1.0 and not cases[r.task_id].op.startswith("scatter_add")]
+    assert not failed, failed
+
+
+def test_integer_results_get_the_harness_tolerance_band():
+    """assert_close applies atol + rtol * |expected| to integers as well: 5000 and 5001 are
+    close under the harness's 1e-2 and differ under zero tolerances."""
+    a = torch.tensor([5000, 7, -3, 1 << 60], device=DEV)
+    b = torch.tensor([5001, 7, -3, 1 << 60], device=DEV)
+    assert ev.compare(a, b)[0] is True and ev.compare(a, b, 0.0, 0.0)[0] is False
+    assert ev.compare(a.cpu(), b.cpu())[0] is True  # same verdict as the host path
+    c = torch.tensor([5000, 9, -3, 1 << 60], device=DEV)
+    assert ev.compare(a, c)[0] is False  # |7 - 9| > 1e-2 + 1e-2 * 9
+    big = torch.tensor([(1 << 60) + 1], device=DEV)
+    assert ev.compare(torch.tensor([1 << 60], device=DEV), big, 0.0, 0.0)[0] is False  # exact means exact beyond 2^53 too
+
+
+def test_out_of_range_index_fails_its_own_test_only():
+    """A kernel that zero-filled rows for a bad index reports it through the status word; the
+    evaluation reads the word per test, so exactly that test fails, with the reason."""
+    emb = torch.ops.aten.embedding.default
+    impl = B200Backend()[emb]
+    table = torch.randn(32, 8, device=DEV)
+
+    class Lying:  # the reference side gets valid indices, the implementation a bad one
+        def __init__(self, bad):
+            self.bad = bad
+
+        def __call__(self, w, idx, *a, **k):
+            return impl(w, torch.tensor([1, 99, 3], device=DEV) if self.bad else idx, *a, **k)
+
+    good = Case([table, torch.tensor([1, 2, 3], device=DEV)])
+    r_bad = ev.eval_correctness_test(emb, Lying(True), good)
+    r_ok = ev.eval_correctness_test(emb, Lying(False), good)
+    assert r_bad.is_correct is False and "IndexError" in r_bad.error_type and "index out of range" in r_bad.error_msg
+    assert r_ok.is_correct is True and r_ok.error_msg == ""
+    ops.check_device_status()  # the word was cleared by the failing test
+
+
+def test_trace_replay_through_the_cli_on_the_gpu(tmp_path):
+    """TorchBench-format ingestion end to end (BackendBench/suite/torchbench.py:45-105): a local
+    trace in the documented grammar becomes device tests and runs through `--suite torchbench
+    --backend b200`. Made-up shapes; the public dataset is not reproduced."""
+    from click.testing import CliRunner
+
+    from backendbench_b200.scripts.main import cli
+    from backendbench_b200.trace_suite import TraceTestSuite
+
+    trace = tmp_path / "trace.txt"
+    trace.write_text(
+        "Operator: aten.relu.default\n"
+        "cnt: 3, ((T([64, 128], f16),), {})\n"
+        "cnt: 1, ((T([4, 16], f32),), {})\n"
+        "Operator: aten.add.Tensor\n"
+        "cnt: 7, ((T([8, 32], f32), T([32], f32)), {})\n"
+        "cnt: 2, ((T([8, 32], bf16), T([8, 32], bf16)), {'alpha': 2})\n"
+        "Operator: aten.mm.default\n"
+        "cnt: 1, ((T([16, 24], f32), T([24, 8], f32, [1, 24])), {})\n"
+        "Operator: aten._softmax.default\n"
+        "cnt: 4, ((T([32, 1000], f16), -1, False), {})\n"
+    )
+    suite = TraceTestSuite("torchbench", str(trace), None, None)
+    backend = B200Backend()
+    for optest in suite:
+        assert optest.op in backend
+        score, _, cres, _ = ev.eval_one_op(optest.op, backend[optest.op], optest.correctness_tests, [], "dtype")
+        assert score == 1.0, (optest.op, [c.error_msg[:200] for c in cres if not c.is_correct])
+        assert all(c.args.startswith("((T(") for c in cres)
+    out = tmp_path / "report"
+    r = CliRunner().invoke(cli, ["--suite", "torchbench", "--alternative-torchbench-data-path", str(trace), "--backend", "b200", "--log-dir", str(out)])
+    assert r.exit_code == 0, r.output
+    assert "correctness score (mean pass rate over all operators): 1.00" in r.output
+    assert (out / "full_results.json").exists() and (out / "operator_summary.csv").exists()

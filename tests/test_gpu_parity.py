@@ -543,3 +543,19 @@ def test_unsupported_requests_fail_loudly(backend):
         backend[torch.ops.aten.mm.default](torch.randn(4, 4, device=DEV, dtype=torch.float64), torch.randn(4, 4, device=DEV, dtype=torch.float64))
     with pytest.raises(RuntimeError):
         backend[torch.ops.aten.mm.default](torch.randn(4, 5, device=DEV), torch.randn(4, 5, device=DEV))
+
+
+def test_strip_gather_on_a_second_device_in_one_process(backend):
+    """The strip kernel asks for 128 KB of dynamic shared memory, an opt-in that belongs to
+    the device: the same process must be able to run it on cuda:0 and then on cuda:1."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two visible GPUs")
+    gather = backend[torch.ops.aten.gather.default]
+    for dev in ("cuda:0", "cuda:1"):
+        with torch.cuda.device(dev):
+            g = torch.Generator(device=dev).manual_seed(5)
+            src = torch.randn(2048, 2048, device=dev, generator=g)
+            idx = torch.randint(0, 2048, (2048, 2048), device=dev, generator=g)
+            got = gather(src, 0, idx)
+            assert bits_equal(got, torch.gather(src, 0, idx)), dev
+            ops.check_device_status(torch.device(dev))

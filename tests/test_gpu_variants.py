@@ -152,3 +152,36 @@ def test_registered_overrides_serve_in_place_and_out_calls():
     finally:
         bb.disable()
     assert bits_equal(want_relu, a) and bits_equal(want_add, out)
+
+
+def test_mixed_precision_targets_follow_aten(backend):
+    """add_/mul_ and add.out / mul.out / sum.out accept any target type the result type can be
+    cast to (aten rounds the full-precision result once into the target); the other overloads
+    insist on the exact type, with aten's message."""
+    g = torch.Generator(device=DEV).manual_seed(11)
+    xb = torch.randn(129, 65, device=DEV, generator=g).to(torch.bfloat16)
+    yf = torch.randn(129, 65, device=DEV, generator=g)
+    for spec, aten_fn in (("add_.Tensor", torch.Tensor.add_), ("mul_.Tensor", torch.Tensor.mul_)):
+        mine, ref = xb.clone(), xb.clone()
+        ret = _impl(backend, spec)(mine, yf)
+        assert ret is mine and mine.dtype == torch.bfloat16 and bits_equal(aten_fn(ref, yf), mine), spec
+    mine, ref = xb.clone(), xb.clone()
+    _impl(backend, "add_.Tensor")(mine, yf, alpha=0.5)
+    assert bits_equal(ref.add_(yf, alpha=0.5), mine)
+    out_m, out_r = torch.empty(129, 65, device=DEV, dtype=torch.bfloat16), torch.empty(129, 65, device=DEV, dtype=torch.bfloat16)
+    _impl(backend, "add.out")(yf, yf * 3, out=out_m)
+    torch.add(yf, yf * 3, out=out_r)
+    assert bits_equal(out_r, out_m)
+    _impl(backend, "mul.out")(yf, xb, out=out_m)
+    torch.mul(yf, xb, out=out_r)
+    assert bits_equal(out_r, out_m)
+    s_m, s_r = torch.empty(129, device=DEV, dtype=torch.bfloat16), torch.empty(129, device=DEV, dtype=torch.bfloat16)
+    _impl(backend, "sum.IntList_out")(yf, [-1], out=s_m)
+    torch.sum(yf, [-1], out=s_r)
+    assert torch.allclose(s_m.float(), s_r.float(), rtol=1e-2, atol=1e-2)
+    with pytest.raises(RuntimeError, match="can't be cast to the desired output type Long"):
+        _impl(backend, "add.out")(yf, yf, out=torch.empty(129, 65, device=DEV, dtype=torch.int64))
+    with pytest.raises(RuntimeError, match="Expected out tensor to have dtype"):
+        _impl(backend, "mm.out")(yf, yf.t().contiguous(), out=torch.empty(129, 129, device=DEV, dtype=torch.bfloat16))
+    with pytest.raises(RuntimeError, match="Expected out tensor to have dtype"):
+        _impl(backend, "relu.out")(yf, out=torch.empty(129, 65, device=DEV, dtype=torch.bfloat16))

@@ -122,3 +122,50 @@ def test_gloo_world_size_two_sharding_and_reductions(tmp_path):
     assert r0["total_units"] == r1["total_units"] == 64.0  # units all ranks processed
     assert r0["n_weak"] == r1["n_weak"] == 32 and r0["weak_seeds"] != r1["weak_seeds"]
     assert sorted(r0["strong_ids"] + r1["strong_ids"]) == list(range(32))
+
+
+def test_worker_that_dies_idle_costs_no_task():
+    """Only a worker that HELD a task takes one with it. Worker 1 exits during start-up,
+    over and over (it is restarted while tasks remain); every task must still be answered
+    by worker 0 and none may be booked as lost."""
+    with MultiprocessingEvaluator(2, worker_target=mp_helpers.worker_one_dies_idle) as ev:
+        for v in (1.0, 2.0, 3.0, 4.0):
+            ev.submit_task(RELU, RELU, [Case([torch.tensor([-v, v])], {})], [])
+        ev.start_evaluation()
+        results = ev.get_results()
+        lost, restarts = list(ev.lost_tasks), ev.restarts
+    assert [r.task_id for r in results] == [0, 1, 2, 3] and all(r.correctness_score == 1.0 for r in results)
+    assert lost == [] and restarts >= 0  # (restarted only if the parent looked while tasks were still open)
+    assert {r.worker_id for r in results} == {0}
+
+
+def test_fatal_task_is_booked_once_and_timeline_reports_the_run():
+    with MultiprocessingEvaluator(1) as ev:
+        ev.submit_task(mp_helpers.raises_injected_cuda_error, RELU, [Case([torch.tensor([1.0])], {})], [])
+        for v in (1.0, 2.0, 3.0):
+            ev.submit_task(RELU, RELU, [Case([torch.tensor([-v, v])], {})], [])
+        ev.start_evaluation()
+        results = ev.get_results()
+        assert ev.lost_tasks == [0] and ev.restarts == 1 and ev.completed_tasks == ev.total_tasks == 4
+        # a second batch on the same (restarted) worker: get_results can be called again
+        ev.submit_task(RELU, RELU, [Case([torch.tensor([5.0])], {})], [])
+        more = ev.get_results()
+        tl = ev.timeline()
+    assert [r.task_id for r in results] == [1, 2, 3] and [r.task_id for r in more] == [4]
+    assert tl["results"] == 4 and tl["lost_tasks"] == [0] and tl["wall_s"] > 0 and tl["per_worker_tasks"] == {0: 4}
+    assert tl["first_worker_ready_s"] is not None and tl["worker_startup_s"][0] > 0
+
+
+def test_sweep_tasks_are_per_case_and_longest_first():
+    from backendbench_b200.backends import AtenBackend as Aten
+    from backendbench_b200.scripts.main import build_suite, task_units
+    from backendbench_b200.sharding import estimated_seconds, lpt_order
+
+    cases = sweep_cases(64, seed=0)
+    order = lpt_order(cases)
+    costs = [estimated_seconds(c) for c in order]
+    assert costs == sorted(costs, reverse=True) and sorted(c.case_id for c in order) == list(range(64))
+    units = task_units(build_suite("sweep", "cpu", None, 64), Aten())
+    assert sum(len(c) for _, c, _ in units) == 64 and all(len(c) <= 1 for _, c, _ in units)  # one case per task
+    untimed = [estimated_seconds(c[0].spec) for _, c, q in units if c and not q]
+    assert untimed == sorted(untimed, reverse=True)
