@@ -28,6 +28,7 @@ def main():
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--rotate", action="store_true", help="time back-to-back launches over rotating input sets larger than L2 instead of flushing L2 before every launch")
+    ap.add_argument("--compare", action="store_true", help="time the fused compare kernel on (aten result, backend result) of the case instead of the operator")
     ap.add_argument("--list", action="store_true")
     args = ap.parse_args()
     if args.list or not args.case:
@@ -38,6 +39,17 @@ def main():
         case = scaled_down(case, args.scale)
     op = get_operator(case.op)
     impl = B200Backend()[op]
+    if args.compare:
+        from .eval import compare_enqueue
+
+        a, kw = case.build("cuda")
+        ref, res = op(*a, **kw), impl(*a, **kw)
+        rec = torch.zeros(8, dtype=torch.int32, device="cuda")
+        ms = cuda_bench(lambda: compare_enqueue(ref, res, 1e-4, 1e-4, rec), warmup=args.warmup, reps=args.reps)
+        first = ref[0] if isinstance(ref, (tuple, list)) else ref
+        nbytes = 2 * first.numel() * first.element_size()
+        print(json.dumps({"case": case.label(), "kernel": "compare", "ms": round(ms, 5), "algorithmic_bytes": nbytes, "gbs": round(nbytes / ms / 1e6, 1)}))
+        return
     if args.rotate:
         from dataclasses import replace
 

@@ -60,8 +60,10 @@ def test_device_compare_matches_host_formula():
     i = torch.arange(100000, device=DEV)
     assert ev.compare(i, i.clone()) == (True, 0.0, 0.0)
     j = i.clone()
-    j[777] += 3
-    assert ev.compare(i, j)[0] is False and ev.compare(i, j)[1] == 3.0
+    j[777] += 3  # inside the harness band (1e-2 + 1e-2 * 780), which assert_close applies to integers too
+    assert ev.compare(i, j)[0] is True and ev.compare(i, j, 0.0, 0.0)[0] is False and ev.compare(i, j)[1] == 3.0
+    j[777] += 30
+    assert ev.compare(i, j)[0] is False and ev.compare(i, j)[1] == 33.0
     assert ev.compare((a, i), (a.clone(), i.clone()))[0] is True  # tuples accumulate into one record
     assert ev.allclose(a, a.double()) is False and ev.allclose(a, a[:3]) is False  # dtype / shape
     assert ev.compare(i.view(400, 250).t(), i.view(400, 250).t().clone())[0] is True  # strided inputs
