@@ -36,6 +36,39 @@ __device__ __forceinline__ void close_step(CloseAcc& a, float r, float s, float 
   }
 }
 
+__device__ __forceinline__ void warp_merge(CloseAcc& a) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    a.bad += __shfl_xor_sync(0xffffffffu, a.bad, o);
+    a.max_abs = fmaxf(a.max_abs, __shfl_xor_sync(0xffffffffu, a.max_abs, o));
+    a.max_rel = fmaxf(a.max_rel, __shfl_xor_sync(0xffffffffu, a.max_rel, o));
+    a.nan_seen |= __shfl_xor_sync(0xffffffffu, a.nan_seen, o);
+  }
+}
+
+// Merge the CTA's accumulators (256 threads) and fold them into the record with at most one
+// atomic per field per CTA, and only where the CTA's value can still change the record: every
+// atomic of every CTA goes to the same 32 bytes, so they queue up behind one another in L2
+// (one set per WARP cost more time than reading 128 MiB of operands). Non-negative floats
+// order like their bit patterns.
+__device__ __forceinline__ void publish(CloseAcc a, b200_close_record* rec) {
+  __shared__ CloseAcc part[8];
+  warp_merge(a);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) part[warp] = a;
+  __syncthreads();
+  if (warp != 0) return;
+  a = lane < 8 ? part[lane] : CloseAcc{0ull, 0.f, 0.f, 0u};
+  warp_merge(a);
+  if (lane != 0) return;
+  if (a.bad) atomicAdd(reinterpret_cast<unsigned long long*>(&rec->mismatches), a.bad);
+  volatile unsigned* cur_abs = reinterpret_cast<volatile unsigned*>(&rec->max_abs);
+  volatile unsigned* cur_rel = reinterpret_cast<volatile unsigned*>(&rec->max_rel);
+  if (a.max_abs > 0.f && __float_as_uint(a.max_abs) > *cur_abs) atomicMax(reinterpret_cast<unsigned*>(&rec->max_abs), __float_as_uint(a.max_abs));
+  if (a.max_rel > 0.f && __float_as_uint(a.max_rel) > *cur_rel) atomicMax(reinterpret_cast<unsigned*>(&rec->max_rel), __float_as_uint(a.max_rel));
+  if (a.nan_seen && *reinterpret_cast<volatile unsigned*>(&rec->nan_seen) == 0u) atomicOr(&rec->nan_seen, 1u);
+}
+
 // exponent field of both halves of a packed pair of 16-bit floats
 template <typename T> struct kExpMask16 { static constexpr uint32_t value = 0u; };
 template <> struct kExpMask16<__nv_bfloat16> { static constexpr uint32_t value = 0x7f807f80u; };
@@ -82,19 +115,7 @@ __global__ void __launch_bounds__(256) allclose_kernel(const T* __restrict__ ref
     done = nvec * VE;
   }
   for (int64_t i = done + t0; i < n; i += stride) close_step(a, to_f32(ref[i]), to_f32(res[i]), rtol, atol);
-  // warp, then one set of atomics per warp (non-negative floats order like their bit patterns)
-  for (int o = 16; o > 0; o >>= 1) {
-    a.bad += __shfl_xor_sync(0xffffffffu, a.bad, o);
-    a.max_abs = fmaxf(a.max_abs, __shfl_xor_sync(0xffffffffu, a.max_abs, o));
-    a.max_rel = fmaxf(a.max_rel, __shfl_xor_sync(0xffffffffu, a.max_rel, o));
-    a.nan_seen |= __shfl_xor_sync(0xffffffffu, a.nan_seen, o);
-  }
-  if ((threadIdx.x & 31) == 0) {
-    if (a.bad) atomicAdd(reinterpret_cast<unsigned long long*>(&rec->mismatches), a.bad);
-    if (a.max_abs > 0.f) atomicMax(reinterpret_cast<unsigned*>(&rec->max_abs), __float_as_uint(a.max_abs));
-    if (a.max_rel > 0.f) atomicMax(reinterpret_cast<unsigned*>(&rec->max_rel), __float_as_uint(a.max_rel));
-    if (a.nan_seen) atomicOr(&rec->nan_seen, 1u);
-  }
+  publish(a, rec);
 }
 
 // Integer / bool tensors: the same band as for floating point, |ref - res| <= atol + rtol * |res|,
@@ -116,16 +137,7 @@ __global__ void __launch_bounds__(256) allclose_int_kernel(const T* __restrict__
     a.max_abs = fmaxf(a.max_abs, diff);
     take_rel(a, diff, fabsf(fr) + 1e-10f);
   }
-  for (int o = 16; o > 0; o >>= 1) {
-    a.bad += __shfl_xor_sync(0xffffffffu, a.bad, o);
-    a.max_abs = fmaxf(a.max_abs, __shfl_xor_sync(0xffffffffu, a.max_abs, o));
-    a.max_rel = fmaxf(a.max_rel, __shfl_xor_sync(0xffffffffu, a.max_rel, o));
-  }
-  if ((threadIdx.x & 31) == 0) {
-    if (a.bad) atomicAdd(reinterpret_cast<unsigned long long*>(&rec->mismatches), a.bad);
-    if (a.max_abs > 0.f) atomicMax(reinterpret_cast<unsigned*>(&rec->max_abs), __float_as_uint(a.max_abs));
-    if (a.max_rel > 0.f) atomicMax(reinterpret_cast<unsigned*>(&rec->max_rel), __float_as_uint(a.max_rel));
-  }
+  publish(a, rec);
 }
 
 __global__ void __launch_bounds__(256) l2_flush_kernel(uint4* __restrict__ p, int64_t nvec) {

@@ -21,11 +21,23 @@
 // instruction descriptors, nothing is copied or transposed. Ragged M / N / K edges rely on
 // TMA zero fill for loads and predicated stores.
 //
+// CTA pairs (kPair): two CTAs of a 2-CTA cluster, on the two SMs of one TPC, share a 256 x 256
+// tile. Each keeps the accumulator of ITS 128 rows in its own tensor memory and loads its own
+// 128 x 64 A slab and HALF of the 64 x 256 B slab (32 KB per stage instead of 48, six stages);
+// one thread of the even CTA issues tcgen05.mma.cta_group::2 (M256 N256 K16), which reads A
+// from both shared memories and each half of B from its own. The odd CTA's copies complete on
+// the even CTA's barrier, and tcgen05.commit.cta_group::2 hands stages and accumulators back
+// to both. Per FLOP a third fewer operand bytes cross the L2-to-SM fabric, which is what the
+// single-CTA kernel waits on at large shapes. No cluster multicast is used anywhere: every
+// CTA fetches its own tiles.
+//
 // Every mbarrier wait is bounded: when a wait gives up the CTA sets an abort flag, ORs
 // B200_DEV_WAIT_TIMEOUT into the caller's status word, lets outstanding copies land, frees
 // its tensor memory and returns -- a protocol bug can produce a wrong result plus an error
 // status, never a hung GPU.
 #include <cuda.h>
+
+#include <cstdlib>
 
 #include "b200_common.cuh"
 
@@ -36,10 +48,12 @@ constexpr int kABytes = kBM * kBK * 2;                  // 16 KB
 constexpr int kTmemCols = 512;                          // 512 / BN fp32 accumulators of 128 lanes x BN columns
 // BN = 256: 48 KB stages x 4, two accumulators (compute-bound shapes).
 // BN = 128: 32 KB stages x 6, four accumulators, for C no wider than 128 columns.
-template <int BN> struct TileCfg {
-  static constexpr int kBBytes = BN * kBK * 2;
+// A CTA of a pair holds half of the B slab: 32 KB stages x 6, two accumulators.
+template <int BN, bool PAIR = false> struct TileCfg {
+  static constexpr int kBRows = PAIR ? BN / 2 : BN;      // rows (N) of the B slab in THIS CTA's shared memory
+  static constexpr int kBBytes = kBRows * kBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = BN == 256 ? 4 : 6;
+  static constexpr int kStages = kStageBytes == 49152 ? 4 : 6;
   static constexpr int kAccs = kTmemCols / BN;
 };
 constexpr int kGemmThreads = 320;                       // TMA warp, MMA warp, 8 epilogue warps
@@ -90,6 +104,30 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
                : "memory");
 }
 
+// The same load issued by a CTA of a pair: the destination is this CTA's shared memory, the
+// mbarrier (a shared::cluster address) may be the peer CTA's.
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst), "l"(map), "r"(bar_cluster), "r"(c0),
+               "r"(c1), "r"(c2)
+               : "memory");
+}
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the location `addr` (a shared::cta address) in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster) { asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory"); }
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 // Tiled store shared -> global through the copy engine; clips at the tensor's edges.
 __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2) {
   asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2) : "memory");
@@ -108,6 +146,17 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uin
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// pair forms: the barrier address is a shared::cluster address (own or peer CTA)
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar_cluster) { asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster) : "memory"); }
+__device__ __forceinline__ void tc_mma_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  const uint32_t z = 0u;  // no output lane is disabled
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(z)
       : "memory");
 }
 __device__ __forceinline__ void tc_ld_32x32(uint32_t taddr, uint32_t* r) {
@@ -151,26 +200,29 @@ struct GemmTcParams {
 
 // Tile t of one batch entry -> (row-block, column-block): column-block fastest, or groups of
 // kGroupM row-blocks with the row-block fastest inside a group.
-__device__ __forceinline__ void tile_coords(int64_t rem, int64_t mt, int64_t nt, int& mb, int& nb, int col_fastest) {
+__device__ __forceinline__ void tile_coords(int64_t rem, int64_t mt, int64_t nt, int& mb, int& nb, int col_fastest, int group_m = kGroupM) {
   if (col_fastest) {
     mb = static_cast<int>(rem / nt);
     nb = static_cast<int>(rem - static_cast<int64_t>(mb) * nt);
     return;
   }
-  const int64_t per_group = static_cast<int64_t>(kGroupM) * nt;
+  const int64_t per_group = static_cast<int64_t>(group_m) * nt;
   const int64_t g = rem / per_group, in_g = rem - g * per_group;
-  const int64_t gm = (mt - g * kGroupM) < kGroupM ? (mt - g * kGroupM) : kGroupM;  // the last group may be short
-  mb = static_cast<int>(g * kGroupM + in_g % gm);
+  const int64_t gm = (mt - g * group_m) < group_m ? (mt - g * group_m) : group_m;  // the last group may be short
+  mb = static_cast<int>(g * group_m + in_g % gm);
   nb = static_cast<int>(in_g / gm);
 }
 
 // T: operand type in shared memory (bf16 / f16). TO: type of C and of the bias -- T itself,
 // or float when the operands are the bf16 planes of split fp32 matrices.
-template <typename T, int kBN, typename TO>
+template <typename T, int kBN, typename TO, bool kPair = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c, const TO* __restrict__ bias, TO* __restrict__ C, GemmTcParams p,
                     uint32_t* __restrict__ status) {
-  constexpr int kStages = TileCfg<kBN>::kStages, kStageBytes = TileCfg<kBN>::kStageBytes, kAccs = TileCfg<kBN>::kAccs;
+  using Cfg = TileCfg<kBN, kPair>;
+  constexpr int kStages = Cfg::kStages, kStageBytes = Cfg::kStageBytes, kAccs = Cfg::kAccs, kBRows = Cfg::kBRows;
+  constexpr int kTileM = kPair ? 2 * kBM : kBM;  // rows of C one tile covers (both CTAs of a pair)
+  static_assert(!kPair || kBN == 256, "CTA pairs work on 256 x 256 tiles");
   if (p.skip_if_set && *p.skip_if_set != 0u) return;  // every thread of every CTA reads the same word: a uniform exit before any barrier or TMEM set-up
   extern __shared__ unsigned char smem_raw[];
   // 1024-byte alignment: the 128B swizzle pattern repeats every 8 rows x 128 bytes
@@ -189,29 +241,39 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
   auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + kAccs + a); };
 
+  // pair: rank of this CTA in its 2-CTA cluster (0 = the CTA that issues the MMAs), and the
+  // shared::cluster addresses of the even CTA's barriers that both CTAs signal
+  const uint32_t cta_rank = kPair ? cluster_ctarank() : 0u;
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(full_bar(s), 1);
-      mbar_init(empty_bar(s), 1);
+      mbar_init(full_bar(s), 1);   // pair: only the even CTA's is used (its producer arms it for both CTAs' bytes)
+      mbar_init(empty_bar(s), 1);  // one tcgen05.commit per use (pair: the even CTA commits to both CTAs')
     }
     for (int a = 0; a < kAccs; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), 8);  // one arrival per epilogue warp
+      mbar_init(tempty_bar(a), kPair ? 16 : 8);  // one arrival per epilogue warp (pair: of both CTAs, on the even CTA's)
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_base_slot)), "r"(kTmemCols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (kPair) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_base_slot)), "r"(kTmemCols) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_base_slot)), "r"(kTmemCols) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (kPair) cluster_sync_all();  // the peer's barriers exist before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
 
-  const int64_t mt = (p.M + kBM - 1) / kBM, nt = (p.N + kBN - 1) / kBN;
+  const int64_t mt = (p.M + kTileM - 1) / kTileM, nt = (p.N + kBN - 1) / kBN;
   const int64_t tiles = p.batch * mt * nt;
+  const int64_t tile_first = kPair ? (blockIdx.x >> 1) : blockIdx.x, tile_step = kPair ? (gridDim.x >> 1) : gridDim.x;
   // Split operands: plane q of an operand occupies K coordinates [q * Kp, q * Kp + K) of its
   // tensor map, Kp = 64 * split_slabs. One slab of the product needs the six plane pairs
   // whose product is not below fp32 resolution: (0,0) (0,1) (1,0) (0,2) (1,1) (2,0).
@@ -224,21 +286,30 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int64_t t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+      for (int64_t t = tile_first; t < tiles && ok; t += tile_step) {
         const int64_t b = t / (mt * nt), rem = t - b * (mt * nt);
         int mb, nb;
-        tile_coords(rem, mt, nt, mb, nb, p.col_fastest);
-        const int m0 = mb * kBM, n0 = nb * kBN;
+        tile_coords(rem, mt, nt, mb, nb, p.col_fastest, kPair ? kGroupM / 2 : kGroupM);
+        // pair: this CTA's 128 rows of A and its half of the B slab's 256 rows
+        const int m0 = mb * kTileM + static_cast<int>(cta_rank) * kBM, n0 = nb * kBN + static_cast<int>(cta_rank) * (kPair ? kBRows : 0);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.wait_limit_ns)) { ok = false; break; }
           const uint32_t a_dst = smem_base + stage * kStageBytes, b_dst = a_dst + kABytes;
-          if (p.withhold_first_slab && t == blockIdx.x && kb == 0) {
+          if (!kPair && p.withhold_first_slab && t == blockIdx.x && kb == 0) {
             // wait probe: this stage is never armed and never filled, so the MMA warp's wait on
             // it must run into its limit; the producer carries on until it needs the stage back
             if (++stage == kStages) { stage = 0; phase ^= 1u; }
             continue;
           }
-          mbar_expect_tx(full_bar(stage), kStageBytes);
+          // pair: every copy of both CTAs completes on the even CTA's barrier, which its
+          // producer arms for the bytes of both
+          const uint32_t fbar = kPair ? map_to_cta(full_bar(stage), 0u) : full_bar(stage);
+          if (!kPair) mbar_expect_tx(full_bar(stage), kStageBytes);
+          else if (cta_rank == 0u) mbar_expect_tx(full_bar(stage), 2 * kStageBytes);
+          auto load = [&](uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2) {
+            if (kPair) tma_load_3d_pair(dst, map, fbar, c0, c1, c2);
+            else tma_load_3d(dst, map, fbar, c0, c1, c2);
+          };
           int ka = kb * kBK, kbb = kb * kBK;
           if (p.split_slabs) {
             // pairs (2,0) (1,1) (0,2) (1,0) (0,1) over all slabs first, then (0,0): the tensor
@@ -250,17 +321,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             kbb = (((0x010210 >> (4 * pair)) & 0xf) * p.split_slabs + slab) * kBK;
           }
           if (!p.a_mn_major) {
-            tma_load_3d(a_dst, &map_a, full_bar(stage), ka, m0, static_cast<int>(b));  // box [128 rows][64 k]
+            load(a_dst, &map_a, ka, m0, static_cast<int>(b));  // box [128 rows][64 k]
           } else {
 #pragma unroll
-            for (int c = 0; c < kBM / 64; ++c) tma_load_3d(a_dst + c * 8192, &map_a, full_bar(stage), m0 + c * 64, ka, static_cast<int>(b));  // box [64 k][64 m]
+            for (int c = 0; c < kBM / 64; ++c) load(a_dst + c * 8192, &map_a, m0 + c * 64, ka, static_cast<int>(b));  // box [64 k][64 m]
           }
           if (!p.b_mn_major) {
-            tma_load_3d(b_dst, &map_b, full_bar(stage), kbb, n0, static_cast<int>(b));  // box [256 rows][64 k]
+            load(b_dst, &map_b, kbb, n0, static_cast<int>(b));  // box [kBRows rows][64 k]
           } else {
 #pragma unroll
-            for (int c = 0; c < kBN / 64; ++c) tma_load_3d(b_dst + c * 8192, &map_b, full_bar(stage), n0 + c * 64, kbb, static_cast<int>(b));  // box [64 k][64 n]
+            for (int c = 0; c < kBRows / 64; ++c) load(b_dst + c * 8192, &map_b, n0 + c * 64, kbb, static_cast<int>(b));  // box [64 k][64 n]
           }
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (kPair && ok) {
+        // tail: the even CTA's commits arrive on THIS CTA's empty barriers from afar; wait for
+        // the ones still outstanding so that none lands after this CTA's shared memory is gone
+        for (int i = 0; i < kStages && ok; ++i) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.wait_limit_ns)) ok = false;
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
       }
@@ -272,18 +351,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     __syncwarp();  // lanes 1..31 rejoin lane 0 before the CTA-wide barrier below
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    if (lane == 0 && cta_rank == 0u) {  // pair: the even CTA issues for both
       // instruction descriptor: fp32 accumulate, A/B format, majors, N >> 3, M >> 4
       const uint32_t fmt = p.is_bf16 ? 1u : 0u;
       const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(p.a_mn_major) << 15) | (static_cast<uint32_t>(p.b_mn_major) << 16) |
-                             (static_cast<uint32_t>(kBN >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);
+                             (static_cast<uint32_t>(kBN >> 3) << 17) | (static_cast<uint32_t>(kTileM >> 4) << 24);
       // per-UMMA (K = 16) advance of the start address and the two byte offsets per layout
       const uint32_t a_adv = p.a_mn_major ? 2048u : 32u, b_adv = p.b_mn_major ? 2048u : 32u;
       const uint32_t a_lbo = p.a_mn_major ? 8192u : 16u, b_lbo = p.b_mn_major ? 8192u : 16u;
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
-      for (int64_t t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+      for (int64_t t = tile_first; t < tiles && ok; t += tile_step) {
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.wait_limit_ns)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kBN);
@@ -295,13 +374,26 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           for (int k = 0; k < kBK / 16; ++k) {
             const uint64_t da = smem_desc(a_addr + k * a_adv, a_lbo, 1024u);
             const uint64_t db = smem_desc(b_addr + k * b_adv, b_lbo, 1024u);
-            tc_mma_f16(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+            if (kPair) tc_mma_f16_pair(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+            else tc_mma_f16(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
           }
-          tc_commit(empty_bar(stage));  // the stage is free once these MMAs have read it
+          // the stage is free once these MMAs have read it (pair: in both CTAs)
+          if (kPair) {
+            tc_commit_pair(map_to_cta(empty_bar(stage), 0u));
+            tc_commit_pair(map_to_cta(empty_bar(stage), 1u));
+          } else {
+            tc_commit(empty_bar(stage));
+          }
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
-        tc_commit(tfull_bar(acc));  // accumulator complete
+        // accumulator complete (pair: each CTA's epilogue waits on its own barrier)
+        if (kPair) {
+          tc_commit_pair(map_to_cta(tfull_bar(acc), 0u));
+          tc_commit_pair(map_to_cta(tfull_bar(acc), 1u));
+        } else {
+          tc_commit(tfull_bar(acc));
+        }
         if (++acc == kAccs) { acc = 0; acc_phase ^= 1u; }
       }
       if (!ok) {
@@ -319,11 +411,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     bool ok = true;
     constexpr int kOutVec = 16 / static_cast<int>(sizeof(TO));  // outputs per 16-byte store
     const bool vec_ok = (p.N % kOutVec == 0) && ((reinterpret_cast<uintptr_t>(C) & 15u) == 0);
-    for (int64_t t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+    const uint32_t tempty_target = kPair ? map_to_cta(tempty_bar(0), 0u) : 0u;  // the even CTA's tmem_empty[0]
+    for (int64_t t = tile_first; t < tiles && ok; t += tile_step) {
       const int64_t b = t / (mt * nt), rem = t - b * (mt * nt);
       int mb, nb_blk;
-      tile_coords(rem, mt, nt, mb, nb_blk, p.col_fastest);
-      const int64_t m0 = static_cast<int64_t>(mb) * kBM, n0 = static_cast<int64_t>(nb_blk) * kBN + chalf * (kBN / 2);
+      tile_coords(rem, mt, nt, mb, nb_blk, p.col_fastest, kPair ? kGroupM / 2 : kGroupM);
+      const int64_t m0 = static_cast<int64_t>(mb) * kTileM + static_cast<int64_t>(cta_rank) * kBM, n0 = static_cast<int64_t>(nb_blk) * kBN + chalf * (kBN / 2);
       int got = 0;
       if (lane == 0) got = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.wait_limit_ns) ? 1 : 0;
       got = __shfl_sync(0xffffffffu, got, 0);
@@ -349,7 +442,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           // every value of the accumulator is in registers: hand it back to the MMA warp now
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(tempty_bar(acc));
+          if (lane == 0) {
+            if (kPair) mbar_arrive_cluster(tempty_target + 8u * acc);
+            else mbar_arrive(tempty_bar(acc));
+          }
         }
         const uint32_t* rc = r[c & 1];
         const int64_t nb = n0 + c * 64;
@@ -460,8 +556,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     for (int i = 0; i < 64; ++i) __nanosleep(1000);
     __syncthreads();
   }
+  if (kPair) cluster_sync_all();  // neither CTA leaves while the other may still signal its barriers or read its operands
   if (warp == 1) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    if (kPair) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
   }
 }
 
@@ -528,6 +626,16 @@ static bool encode_operand(CUtensorMap* map, const void* base, int dtype, bool m
   return r == CUDA_SUCCESS;
 }
 
+// CTA pairs can be switched off with B200_GEMM_PAIR=0 in the environment (read once): the
+// single-CTA kernel then serves every shape, which is how the two are compared.
+static bool pair_launch_ok() {
+  static const bool on = []() {
+    const char* e = getenv("B200_GEMM_PAIR");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
 int gemm_tc_dispatch(const void* A, const void* B, const void* bias, void* C, int64_t batch, int64_t M, int64_t N, int64_t K, int64_t sAb, int64_t sAm, int64_t sAk, int64_t sBb,
                      int64_t sBk, int64_t sBn, int64_t sbm, int64_t sbn, double alpha, double beta, int dtype, uint32_t* status, cudaStream_t st, uint64_t wait_probe_limit_ns) {
   const OperandLayout la = operand_layout(M, K, sAm, sAk, sAb, batch, A);
@@ -535,7 +643,12 @@ int gemm_tc_dispatch(const void* A, const void* B, const void* bias, void* C, in
   if (!la.ok || !lb.ok || !encode_fn()) return B200_EALIGN;
   alignas(64) CUtensorMap map_a, map_b;
   if (!encode_operand(&map_a, A, dtype, la.mn_major, M, K, sAm, sAk, sAb, batch, kBM)) return B200_EDRIVER;
-  const int bn_box = N <= 128 ? 128 : 256;  // must match the tile shape chosen below
+  // CTA pairs on 256 x 256 tiles whenever C has more than one 128-row block and is not narrow;
+  // the wait probe stays on the single-CTA kernel
+  // (with four K slabs or fewer the kernel is bound by writing C and the pair is slower:
+  // bmm 32 x 2048 x 128 x 2048 0.087 ms against 0.061 ms)
+  const bool pair = M > kBM && N > 128 && (K + kBK - 1) / kBK > 4 && wait_probe_limit_ns == 0 && pair_launch_ok();
+  const int bn_box = (N <= 128 || pair) ? 128 : 256;  // rows of the B box: must match the tile shape chosen below
   if (!encode_operand(&map_b, B, dtype, lb.mn_major, N, K, sBn, sBk, sBb, batch, bn_box)) return B200_EDRIVER;
   alignas(64) CUtensorMap map_c;
   const bool tma_store = (N % 8 == 0) && aligned16(C);
@@ -573,23 +686,44 @@ int gemm_tc_dispatch(const void* A, const void* B, const void* bias, void* C, in
   // deeper pipeline gains -- bmm 32x2048x128x2048: 0.162 ms vs 0.116 ms.)
   const bool narrow = N <= 128;
   const int bn = narrow ? 128 : 256;
-  const int64_t tiles = batch * ((M + kBM - 1) / kBM) * ((N + bn - 1) / bn);
-  const int grid = static_cast<int>(tiles < kNumSMs ? tiles : kNumSMs);
+  const int tile_m = pair ? 2 * kBM : kBM;
+  const int64_t tiles = batch * ((M + tile_m - 1) / tile_m) * ((N + bn - 1) / bn);
+  const int64_t slots = pair ? kNumSMs / 2 : kNumSMs;  // persistent: one CTA (or CTA pair) per SM (or TPC)
+  const int grid = static_cast<int>(tiles < slots ? tiles : slots) * (pair ? 2 : 1);
   auto launch = [&](auto kernel, auto* bias_t, auto* c_t) -> int {
     const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemmSmem));
     if (e != cudaSuccess) { set_last_cuda_error(e); return B200_ELAUNCH; }
-    kernel<<<grid, kGemmThreads, kGemmSmem, st>>>(map_a, map_b, map_c, bias_t, c_t, p, status);
+    if (!pair) {
+      kernel<<<grid, kGemmThreads, kGemmSmem, st>>>(map_a, map_b, map_c, bias_t, c_t, p, status);
+      return B200_OK;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+    cfg.blockDim = dim3(kGemmThreads, 1, 1);
+    cfg.dynamicSmemBytes = kGemmSmem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t le = cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, map_c, bias_t, c_t, p, status);
+    if (le != cudaSuccess) { set_last_cuda_error(le); return B200_ELAUNCH; }
     return B200_OK;
   };
   int rc;
   if (dtype == B200_BF16) {
     const __nv_bfloat16* bt = static_cast<const __nv_bfloat16*>(bias);
     __nv_bfloat16* ct = static_cast<__nv_bfloat16*>(C);
-    rc = narrow ? launch(gemm_tcgen05_kernel<__nv_bfloat16, 128, __nv_bfloat16>, bt, ct) : launch(gemm_tcgen05_kernel<__nv_bfloat16, 256, __nv_bfloat16>, bt, ct);
+    rc = pair ? launch(gemm_tcgen05_kernel<__nv_bfloat16, 256, __nv_bfloat16, true>, bt, ct)
+              : narrow ? launch(gemm_tcgen05_kernel<__nv_bfloat16, 128, __nv_bfloat16>, bt, ct) : launch(gemm_tcgen05_kernel<__nv_bfloat16, 256, __nv_bfloat16>, bt, ct);
   } else {
     const __half* bt = static_cast<const __half*>(bias);
     __half* ct = static_cast<__half*>(C);
-    rc = narrow ? launch(gemm_tcgen05_kernel<__half, 128, __half>, bt, ct) : launch(gemm_tcgen05_kernel<__half, 256, __half>, bt, ct);
+    rc = pair ? launch(gemm_tcgen05_kernel<__half, 256, __half, true>, bt, ct)
+              : narrow ? launch(gemm_tcgen05_kernel<__half, 128, __half>, bt, ct) : launch(gemm_tcgen05_kernel<__half, 256, __half>, bt, ct);
   }
   if (rc) return rc;
   return check_launch();

@@ -782,23 +782,6 @@ __global__ void __launch_bounds__(256) reduce_rows(const T* __restrict__ x, void
     // chunk is a multiple of VE, so every slice starts on a vector boundary
     const int64_t v0 = c0 / VE, v1 = c1 / VE;
     int64_t j = v0 + t;
-    if (!ARG) {
-      // sums: eight 16-byte loads in flight per thread and two independent accumulators -- a
-      // warp that owns an 8 KB row makes two trips to memory instead of four, and a row of
-      // 16-bit elements is no longer one chain of dependent adds
-      float s2 = 0.f;
-      for (; j + 7 * tpr < v1; j += 8 * tpr) {
-        Vec<T> v[8];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) v[u].raw = ld_stream(xr + (j + u * tpr) * VE);
-#pragma unroll
-        for (int u = 0; u < 8; u += 2) {
-          vec_accumulate<T>(s, v[u].raw);
-          vec_accumulate<T>(s2, v[u + 1].raw);
-        }
-      }
-      s += s2;
-    }
     for (; j + 3 * tpr < v1; j += 4 * tpr) {
       Vec<T> v[4];
 #pragma unroll
