@@ -14,7 +14,9 @@ import os
 from ctypes import POINTER, c_char_p, c_double, c_int, c_int64, c_uint32, c_void_p
 
 CSRC_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "csrc")
-LIB_PATH = os.path.join(CSRC_DIR, "libb200ops.so")
+# B200OPS_LIB names another build of the same library (same ABI version), e.g. one compiled
+# with other tuning constants, without touching the in-tree one
+LIB_PATH = os.environ.get("B200OPS_LIB") or os.path.join(CSRC_DIR, "libb200ops.so")
 
 ABI_VERSION = 1
 MAX_DIMS = 8

@@ -2,6 +2,8 @@
 // harness asks about a (reference, result) pair -- "are they close?" (assert_close with
 // equal_nan) and "how far apart?" (max abs / max rel error) -- plus the L2 flush used
 // between timed repetitions. One read of each tensor, one 32-byte record back.
+#include <math_constants.h>
+
 #include "b200_common.cuh"
 
 namespace b200 {
@@ -20,20 +22,23 @@ __device__ __forceinline__ void take_rel(CloseAcc& a, float diff, float den) {
   if (diff > a.max_rel * den * 0.999999f) a.max_rel = fmaxf(a.max_rel, diff / den);
 }
 
+// One element pair. The kernel runs a dozen instructions per pair on the common path, which
+// is what bounds it next to the loads (the first version spent about thirty and ran at half
+// the issue rate of the SM with a third of its warps resident):
+//  * closeness, as torch.isclose(actual = reference output, expected = backend output) with
+//    equal_nan: equal (covers equal infinities), or a finite difference inside the band
+//    atol + rtol * |expected|; a pair that fails both is a mismatch unless both are NaN --
+//    that last test sits on the rare path;
+//  * error magnitudes follow `(ref - res).abs().max()`: fmaxf drops a NaN operand, so the
+//    running maximum needs no guard, and a NaN difference only raises the flag.
 __device__ __forceinline__ void close_step(CloseAcc& a, float r, float s, float rtol, float atol) {
-  const bool rn = r != r, sn = s != s;
   const float diff = fabsf(r - s);
-  // closeness: equal (covers equal infinities), both NaN, or inside the tolerance band
-  // around the second operand, as torch.isclose(actual, expected) does with
-  // actual = reference output and expected = backend output.
-  const bool close = (r == s) || (rn && sn) || (!rn && !sn && isfinite(diff) && diff <= atol + rtol * fabsf(s));
-  if (!close) ++a.bad;
-  // error magnitudes follow `(ref - res).abs().max()`: any NaN difference makes the max NaN
+  const float band = fmaf(rtol, fabsf(s), atol);
+  const bool close = (r == s) || (diff <= band && diff != CUDART_INF_F);  // NaN compares false everywhere
+  if (!close && !(r != r && s != s)) ++a.bad;
   if (diff != diff) a.nan_seen = 1;
-  else {
-    a.max_abs = fmaxf(a.max_abs, diff);
-    take_rel(a, diff, fabsf(r) + 1e-10f);
-  }
+  a.max_abs = fmaxf(a.max_abs, diff);
+  take_rel(a, diff, fabsf(r) + 1e-10f);
 }
 
 __device__ __forceinline__ void warp_merge(CloseAcc& a) {
@@ -75,7 +80,7 @@ template <> struct kExpMask16<__nv_bfloat16> { static constexpr uint32_t value =
 template <> struct kExpMask16<__half> { static constexpr uint32_t value = 0x7c007c00u; };
 
 template <typename T>
-__global__ void __launch_bounds__(256) allclose_kernel(const T* __restrict__ ref, const T* __restrict__ res, int64_t n, float rtol, float atol, b200_close_record* rec, int vec_ok) {
+__global__ void __launch_bounds__(256, 4) allclose_kernel(const T* __restrict__ ref, const T* __restrict__ res, int64_t n, float rtol, float atol, b200_close_record* rec, int vec_ok) {
   constexpr int VE = Vec<T>::N;
   CloseAcc a{0ull, 0.f, 0.f, 0u};
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
@@ -97,9 +102,8 @@ __global__ void __launch_bounds__(256) allclose_kernel(const T* __restrict__ ref
 #pragma unroll
       for (int e = 0; e < VE; ++e) close_step(a, fr[e], fs[e], rtol, atol);
     };
-    // four vector pairs (eight 16-byte loads) in flight per thread: with one pair per trip the
-    // kernel waits on memory latency (3.6 TB/s on 128 MiB operands), not on bandwidth
-    constexpr int U = 4;
+    // two vector pairs (four 16-byte loads) in flight per thread and four CTAs per SM
+    constexpr int U = 2;
     int64_t j = t0;
     for (; j + (U - 1) * stride < nvec; j += U * stride) {
       uint4 vr[U], vs[U];

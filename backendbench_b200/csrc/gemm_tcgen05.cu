@@ -626,6 +626,33 @@ static bool encode_operand(CUtensorMap* map, const void* base, int dtype, bool m
   return r == CUDA_SUCCESS;
 }
 
+// One launch of the kernel: a plain grid, or 2-CTA clusters for the pair variant.
+template <typename Kernel, typename TB, typename TC>
+static int launch_tc(Kernel kernel, bool pair, int grid, cudaStream_t st, const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_c, const TB* bias_t, TC* c_t,
+                     const GemmTcParams& p, uint32_t* status) {
+  const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemmSmem));
+  if (e != cudaSuccess) { set_last_cuda_error(e); return B200_ELAUNCH; }
+  if (!pair) {
+    kernel<<<grid, kGemmThreads, kGemmSmem, st>>>(map_a, map_b, map_c, bias_t, c_t, p, status);
+    return B200_OK;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+  cfg.blockDim = dim3(kGemmThreads, 1, 1);
+  cfg.dynamicSmemBytes = kGemmSmem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t le = cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, map_c, bias_t, c_t, p, status);
+  if (le != cudaSuccess) { set_last_cuda_error(le); return B200_ELAUNCH; }
+  return B200_OK;
+}
+
 // CTA pairs can be switched off with B200_GEMM_PAIR=0 in the environment (read once): the
 // single-CTA kernel then serves every shape, which is how the two are compared.
 static bool pair_launch_ok() {
@@ -690,29 +717,7 @@ int gemm_tc_dispatch(const void* A, const void* B, const void* bias, void* C, in
   const int64_t tiles = batch * ((M + tile_m - 1) / tile_m) * ((N + bn - 1) / bn);
   const int64_t slots = pair ? kNumSMs / 2 : kNumSMs;  // persistent: one CTA (or CTA pair) per SM (or TPC)
   const int grid = static_cast<int>(tiles < slots ? tiles : slots) * (pair ? 2 : 1);
-  auto launch = [&](auto kernel, auto* bias_t, auto* c_t) -> int {
-    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemmSmem));
-    if (e != cudaSuccess) { set_last_cuda_error(e); return B200_ELAUNCH; }
-    if (!pair) {
-      kernel<<<grid, kGemmThreads, kGemmSmem, st>>>(map_a, map_b, map_c, bias_t, c_t, p, status);
-      return B200_OK;
-    }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
-    cfg.blockDim = dim3(kGemmThreads, 1, 1);
-    cfg.dynamicSmemBytes = kGemmSmem;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    const cudaError_t le = cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, map_c, bias_t, c_t, p, status);
-    if (le != cudaSuccess) { set_last_cuda_error(le); return B200_ELAUNCH; }
-    return B200_OK;
-  };
+  auto launch = [&](auto kernel, auto* bias_t, auto* c_t) -> int { return launch_tc(kernel, pair, grid, st, map_a, map_b, map_c, bias_t, c_t, p, status); };
   int rc;
   if (dtype == B200_BF16) {
     const __nv_bfloat16* bt = static_cast<const __nv_bfloat16*>(bias);
@@ -855,8 +860,9 @@ int gemm_f32_split_dispatch(const void* A, const void* B, const void* bias, void
   // the planes as [rows, 3 Kp] (K-major) or [3 Kp, rows] (MN-major) bf16 operands
   alignas(64) CUtensorMap map_a, map_b;
   const int bn = N <= 128 ? 128 : 256;
+  const bool pair = M > kBM && N > 128 && pair_launch_ok();  // the contraction is six planes deep: never write-bound
   if (!encode_operand(&map_a, pa, B200_BF16, a_mn, M, 3 * kp, a_mn ? 1 : a_row, a_mn ? a_row : 1, a_rows * a_row, batch, kBM)) return B200_EDRIVER;
-  if (!encode_operand(&map_b, pb, B200_BF16, b_mn, N, 3 * kp, b_mn ? 1 : b_row, b_mn ? b_row : 1, b_rows * b_row, batch, bn)) return B200_EDRIVER;
+  if (!encode_operand(&map_b, pb, B200_BF16, b_mn, N, 3 * kp, b_mn ? 1 : b_row, b_mn ? b_row : 1, b_rows * b_row, batch, pair ? 128 : bn)) return B200_EDRIVER;
   GemmTcParams p;
   p.tma_store = 0;
   p.M = M; p.N = N; p.K = K; p.batch = batch;
@@ -872,15 +878,13 @@ int gemm_f32_split_dispatch(const void* A, const void* B, const void* bias, void
   p.wait_limit_ns = kWaitLimitNs;
   p.withhold_first_slab = 0;
   p.col_fastest = 6 * p.split_slabs <= 4 ? 1 : 0;
-  const int64_t tiles = batch * ((M + kBM - 1) / kBM) * ((N + bn - 1) / bn);
-  const int grid = static_cast<int>(tiles < kNumSMs ? tiles : kNumSMs);
-  auto launch = [&](auto kernel) -> int {
-    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemmSmem));
-    if (e != cudaSuccess) { set_last_cuda_error(e); return B200_ELAUNCH; }
-    kernel<<<grid, kGemmThreads, kGemmSmem, st>>>(map_a, map_b, map_a, static_cast<const float*>(bias), static_cast<float*>(C), p, status);
-    return B200_OK;
-  };
-  const int rc = bn == 128 ? launch(gemm_tcgen05_kernel<__nv_bfloat16, 128, float>) : launch(gemm_tcgen05_kernel<__nv_bfloat16, 256, float>);
+  const int tile_m = pair ? 2 * kBM : kBM;
+  const int64_t tiles = batch * ((M + tile_m - 1) / tile_m) * ((N + bn - 1) / bn);
+  const int64_t slots = pair ? kNumSMs / 2 : kNumSMs;
+  const int grid = static_cast<int>(tiles < slots ? tiles : slots) * (pair ? 2 : 1);
+  auto launch = [&](auto kernel) -> int { return launch_tc(kernel, pair, grid, st, map_a, map_b, map_a, static_cast<const float*>(bias), static_cast<float*>(C), p, status); };
+  const int rc = pair ? launch(gemm_tcgen05_kernel<__nv_bfloat16, 256, float, true>)
+                      : bn == 128 ? launch(gemm_tcgen05_kernel<__nv_bfloat16, 128, float>) : launch(gemm_tcgen05_kernel<__nv_bfloat16, 256, float>);
   if (rc) return rc;
   // the same product on the CUDA cores, run only when the split met an infinity or a NaN
   const int rs = gemm_simt_dispatch(A, B, bias, C, batch, M, N, K, sAb, sAm, sAk, sBb, sBk, sBn, sbm, sbn, alpha, beta, B200_F32, st, any_flag);

@@ -356,13 +356,14 @@ def _f32_pairs(ref, res, out):
 
 
 def compare_kernel_roofline(prepared, peaks, repeats=5):
-    """Roofline of the kernel that holds the largest share of the sweep's device time, the
-    fused fp32 compare (`allclose_kernel<float>`: 17.8 % of one pass in the profiler's launch
-    list, ahead of every operator kernel). Every fp32 (reference, result) pair of one pass is
-    compared back to back between one pair of CUDA events on the launching stream -- its
-    launches exactly as the sweep makes them, 2.8 GB of operands in total so nothing stays in
-    L2 from one launch to the next; median of `repeats`. Algorithmic bytes of a launch: both
-    operands read once, 2 x 4 x numel (the 32-byte verdict record is noise)."""
+    """Roofline of the kernel that holds the largest share of the sweep's device time: the fused
+    fp32 compare (`allclose_kernel<float>`, ahead of every operator kernel in the profiler's
+    launch list of one pass). Every fp32 (reference, result) pair of one pass is compared back
+    to back -- its launches exactly as the sweep makes them, gigabytes of operands in total, so
+    nothing stays in L2 from one launch to the next. The launches are captured in a CUDA graph
+    (as the timed step is) and the replay is bracketed by one pair of CUDA events on the
+    launching stream; median of `repeats`. Algorithmic bytes of a launch: both operands read
+    once, 2 x 4 x numel (the 32-byte verdict record is noise)."""
     from backendbench_b200 import _abi
     from backendbench_b200.eval import compare_enqueue
 
@@ -373,41 +374,43 @@ def compare_kernel_roofline(prepared, peaks, repeats=5):
     if not pairs:
         return None
     rec = torch.zeros(8, dtype=torch.int32, device=pairs[0][0].device)
-    nbytes = sum(2 * 4 * r.numel() for r, _ in pairs)
-    times, launches = [], 0
-    for rep in range(repeats + 1):
-        n0 = _abi.lib().b200_launch_count()
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        for r, s in pairs:
+
+    def timed(subset):
+        for r, s in subset:  # warm-up, and the launch count
             compare_enqueue(r, s, 1e-4, 1e-4, rec)
-        end.record()
         torch.cuda.synchronize()
+        n0 = _abi.lib().b200_launch_count()
+        side = torch.cuda.Stream()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for r, s in subset:
+                compare_enqueue(r, s, 1e-4, 1e-4, rec)
         launches = _abi.lib().b200_launch_count() - n0
-        if rep:  # the first pass is the warm-up
+        times = []
+        for _ in range(repeats + 1):
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            graph.replay()
+            end.record()
+            torch.cuda.synchronize()
             times.append(start.elapsed_time(end))
-    ms = statistics.median(times)
+        return statistics.median(times[1:]), launches
+
+    nbytes = sum(2 * 4 * r.numel() for r, _ in pairs)
+    ms, launches = timed(pairs)
     ach = nbytes / (ms * 1e-3) / 1e9
-    big = [(r, s) for r, s in pairs if 2 * 4 * r.numel() >= (32 << 20)]
     per_launch = nbytes / max(launches, 1)
     roof = {"bound": "hbm", "kernel": "b200::allclose_kernel<float>", "achieved": round(ach, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(ach / peaks["hbm_gbs"], 4),
             "peak_source": peaks["source"], "launches": int(launches), "avg_launch_ms": round(ms / max(launches, 1), 5), "algorithmic_bytes_per_launch": int(per_launch),
             "traffic": (int(per_launch * ALLCLOSE_F32_DRAM_PER_ALGORITHMIC_BYTE) if ALLCLOSE_F32_DRAM_PER_ALGORITHMIC_BYTE else None),
-            "timing": f"one CUDA-event pair around all {launches} launches of one pass, median of {repeats}"}
+            "timing": f"all {launches} fp32 compare launches of one pass replayed from a CUDA graph between one CUDA-event pair, median of {repeats}"}
+    big = [(r, s) for r, s in pairs if 2 * 4 * r.numel() >= (32 << 20)]
     if big:  # the launches large enough to be bound by HBM rather than by launch latency, on their own
         bb = sum(2 * 4 * r.numel() for r, _ in big)
-        ts = []
-        for rep in range(repeats + 1):
-            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            start.record()
-            for r, s in big:
-                compare_enqueue(r, s, 1e-4, 1e-4, rec)
-            end.record()
-            torch.cuda.synchronize()
-            if rep:
-                ts.append(start.elapsed_time(end))
-        g = bb / (statistics.median(ts) * 1e-3) / 1e9
-        roof["launches_of_32MiB_or_more"] = {"launches": len(big), "achieved": round(g, 1), "frac": round(g / peaks["hbm_gbs"], 4), "share_of_bytes": round(bb / nbytes, 4)}
+        bms, bl = timed(big)
+        g = bb / (bms * 1e-3) / 1e9
+        roof["launches_of_32MiB_or_more"] = {"launches": int(bl), "achieved": round(g, 1), "frac": round(g / peaks["hbm_gbs"], 4), "share_of_bytes": round(bb / nbytes, 4),
+                                             "avg_launch_ms": round(bms / max(bl, 1), 5)}
     return roof
 
 
