@@ -167,7 +167,7 @@ __global__ void __launch_bounds__(256) gather_dim0_vec(const U* __restrict__ sel
 // row ranges each (blockIdx.x >= whole_strips), so that the wave's work spreads over all
 // SMs instead of leaving most of them idle.
 constexpr int kStripW = 8;
-constexpr int kStripThreads = 512;  // 128 registers per thread: two trips of index loads stay in registers
+constexpr int kStripThreads = 1024;
 constexpr int64_t kStripMaxSelfBytes = 200 * 1024;
 __global__ void __launch_bounds__(kStripThreads, 1) gather_dim0_strip(const uint32_t* __restrict__ self, const int64_t* __restrict__ index, uint32_t* __restrict__ out,
                                                                       int64_t rows, int64_t cols, int64_t self_pitch, int self_rows, int whole_strips, int tail_split, uint32_t* status) {
@@ -186,19 +186,19 @@ __global__ void __launch_bounds__(kStripThreads, 1) gather_dim0_strip(const uint
   __syncthreads();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int rsub = lane >> 2, cp = (lane & 3) * 2;  // a warp covers 8 rows x 8 columns per load
+  // Four index segments in flight per thread and no more: keeping the next trip's segments
+  // in flight as well (with 1024, 768 or 512 threads) was measured 12-19 % SLOWER (62 -> 70-74
+  // us at 4096 x 4096) -- the 64-byte segments of different rows lie in different DRAM pages,
+  // and more of them outstanding at once cost more in page misses than the latency they hid.
   constexpr int U = 4;
   constexpr int kWarps = kStripThreads / 32;
-  // The index segments of the NEXT trip are requested before this trip's look-ups and stores,
-  // so a warp always has loads in flight (with one trip at a time the kernel sat at half the
-  // DRAM rate, waiting for its index loads).
-  auto fetch = [&](int64_t r0, longlong2 (&k)[U]) {
+  for (int64_t r0 = r_begin + warp * (8 * U); r0 < r_end; r0 += kWarps * (8 * U)) {
+    longlong2 k[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int64_t row = r0 + u * 8 + rsub;
       if (row < r_end) k[u] = __ldcs(reinterpret_cast<const longlong2*>(index + row * cols + c0 + cp));
     }
-  };
-  auto emit = [&](int64_t r0, const longlong2 (&k)[U]) {
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int64_t row = r0 + u * 8 + rsub;
@@ -210,18 +210,6 @@ __global__ void __launch_bounds__(kStripThreads, 1) gather_dim0_strip(const uint
         else v.y = strip[static_cast<int>(k[u].y) * kStripW + cp + 1];
         __stcs(reinterpret_cast<uint2*>(out + row * cols + c0 + cp), v);
       }
-    }
-  };
-  constexpr int64_t kStep = static_cast<int64_t>(kWarps) * (8 * U);
-  longlong2 ka[U], kb[U];
-  int64_t r0 = r_begin + warp * (8 * U);
-  if (r0 < r_end) fetch(r0, ka);
-  for (; r0 < r_end; r0 += 2 * kStep) {
-    if (r0 + kStep < r_end) fetch(r0 + kStep, kb);
-    emit(r0, ka);
-    if (r0 + kStep < r_end) {
-      if (r0 + 2 * kStep < r_end) fetch(r0 + 2 * kStep, ka);
-      emit(r0 + kStep, kb);
     }
   }
 }
