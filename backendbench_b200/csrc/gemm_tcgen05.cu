@@ -196,6 +196,7 @@ struct GemmTcParams {
   const uint32_t* skip_if_set;  // when not NULL: the kernel returns at once if this device word is non-zero
   uint64_t wait_limit_ns;       // every mbarrier wait gives up after this long (kWaitLimitNs in ordinary calls)
   int withhold_first_slab;      // wait probe only: the producer never loads the first K slab of a CTA's first tile
+  int group_m;                  // row-blocks per rasterisation group (see tile_coords)
 };
 
 // Tile t of one batch entry -> (row-block, column-block): column-block fastest, or groups of
@@ -289,7 +290,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       for (int64_t t = tile_first; t < tiles && ok; t += tile_step) {
         const int64_t b = t / (mt * nt), rem = t - b * (mt * nt);
         int mb, nb;
-        tile_coords(rem, mt, nt, mb, nb, p.col_fastest, kPair ? kGroupM / 2 : kGroupM);
+        tile_coords(rem, mt, nt, mb, nb, p.col_fastest, p.group_m);
         // pair: this CTA's 128 rows of A and its half of the B slab's 256 rows
         const int m0 = mb * kTileM + static_cast<int>(cta_rank) * kBM, n0 = nb * kBN + static_cast<int>(cta_rank) * (kPair ? kBRows : 0);
         for (int kb = 0; kb < num_kb; ++kb) {
@@ -415,7 +416,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     for (int64_t t = tile_first; t < tiles && ok; t += tile_step) {
       const int64_t b = t / (mt * nt), rem = t - b * (mt * nt);
       int mb, nb_blk;
-      tile_coords(rem, mt, nt, mb, nb_blk, p.col_fastest, kPair ? kGroupM / 2 : kGroupM);
+      tile_coords(rem, mt, nt, mb, nb_blk, p.col_fastest, p.group_m);
       const int64_t m0 = static_cast<int64_t>(mb) * kTileM + static_cast<int64_t>(cta_rank) * kBM, n0 = static_cast<int64_t>(nb_blk) * kBN + chalf * (kBN / 2);
       int got = 0;
       if (lane == 0) got = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.wait_limit_ns) ? 1 : 0;
@@ -626,6 +627,22 @@ static bool encode_operand(CUtensorMap* map, const void* base, int dtype, bool m
   return r == CUDA_SUCCESS;
 }
 
+// Rows of C per rasterisation group: the CTAs that run together walk the column blocks of one
+// group of row blocks, so the group's A panel (rows x K 16-bit values) stays in L2 while B
+// streams past it once per group. The panel is sized to a fraction of the 126 MB L2; fewer
+// groups mean fewer passes over B (at 8192 x 4096 x 11008 groups of 2048 rows read B four
+// times: 441 MB of DRAM reads for 157 MB of operands).
+#ifndef B200_GEMM_PANEL_MB
+#define B200_GEMM_PANEL_MB 32
+#endif
+static int group_rows_for(int64_t k_elems) {
+  int64_t rows = (static_cast<int64_t>(B200_GEMM_PANEL_MB) << 20) / (2 * (k_elems > 0 ? k_elems : 1));
+  rows = rows / 256 * 256;
+  if (rows < 2048) rows = 2048;    // never smaller than the groups the kernel always used
+  if (rows > 65536) rows = 65536;
+  return static_cast<int>(rows);
+}
+
 // One launch of the kernel: a plain grid, or 2-CTA clusters for the pair variant.
 template <typename Kernel, typename TB, typename TC>
 static int launch_tc(Kernel kernel, bool pair, int grid, cudaStream_t st, const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_c, const TB* bias_t, TC* c_t,
@@ -708,6 +725,7 @@ int gemm_tc_dispatch(const void* A, const void* B, const void* bias, void* C, in
   p.skip_if_set = nullptr;
   p.wait_limit_ns = wait_probe_limit_ns ? wait_probe_limit_ns : kWaitLimitNs;
   p.withhold_first_slab = wait_probe_limit_ns ? 1 : 0;
+  p.group_m = group_rows_for(K) / (pair ? 2 * kBM : kBM);
   // a narrow C takes the 128-wide tile. (Write-bound shapes with few K slabs were measured
   // slower on it: 256-byte row segments instead of 512-byte ones cost more in DRAM than the
   // deeper pipeline gains -- bmm 32x2048x128x2048: 0.162 ms vs 0.116 ms.)
@@ -878,6 +896,7 @@ int gemm_f32_split_dispatch(const void* A, const void* B, const void* bias, void
   p.wait_limit_ns = kWaitLimitNs;
   p.withhold_first_slab = 0;
   p.col_fastest = 6 * p.split_slabs <= 4 ? 1 : 0;
+  p.group_m = group_rows_for(3 * kp) / (pair ? 2 * kBM : kBM);
   const int tile_m = pair ? 2 * kBM : kBM;
   const int64_t tiles = batch * ((M + tile_m - 1) / tile_m) * ((N + bn - 1) / bn);
   const int64_t slots = pair ? kNumSMs / 2 : kNumSMs;

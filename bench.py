@@ -60,8 +60,8 @@ FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1590.0
 WORKLOAD = "sharded sweep: 512 seeded (op, shape, dtype) cases over 16 aten overloads, 2^8..2^26 elements, 15% edge cases; one correctness pass over all 512 cases per step"
 # DRAM bytes moved per algorithmic byte by the fp32 compare kernel, from its profiler capture
-# (profiles/allclose_f32_*.md); None until a capture exists
-ALLCLOSE_F32_DRAM_PER_ALGORITHMIC_BYTE = None
+# (profiles/allclose_f32_4096x4096.md: 134.2 MB read + 4.1 MB written for 134.2 MB of operands)
+ALLCLOSE_F32_DRAM_PER_ALGORITHMIC_BYTE = 1.031
 EXACT_VS_CPU = ("scatter_add.default",)  # aten CUDA scatter_add is order-nondeterministic: its reference comes from aten CPU
 
 
@@ -398,20 +398,22 @@ def compare_kernel_roofline(prepared, peaks, repeats=5):
 
     nbytes = sum(2 * 4 * r.numel() for r, _ in pairs)
     ms, launches = timed(pairs)
-    ach = nbytes / (ms * 1e-3) / 1e9
-    per_launch = nbytes / max(launches, 1)
-    roof = {"bound": "hbm", "kernel": "b200::allclose_kernel<float>", "achieved": round(ach, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(ach / peaks["hbm_gbs"], 4),
-            "peak_source": peaks["source"], "launches": int(launches), "avg_launch_ms": round(ms / max(launches, 1), 5), "algorithmic_bytes_per_launch": int(per_launch),
-            "traffic": (int(per_launch * ALLCLOSE_F32_DRAM_PER_ALGORITHMIC_BYTE) if ALLCLOSE_F32_DRAM_PER_ALGORITHMIC_BYTE else None),
-            "timing": f"all {launches} fp32 compare launches of one pass replayed from a CUDA graph between one CUDA-event pair, median of {repeats}"}
-    big = [(r, s) for r, s in pairs if 2 * 4 * r.numel() >= (32 << 20)]
-    if big:  # the launches large enough to be bound by HBM rather than by launch latency, on their own
-        bb = sum(2 * 4 * r.numel() for r, _ in big)
-        bms, bl = timed(big)
-        g = bb / (bms * 1e-3) / 1e9
-        roof["launches_of_32MiB_or_more"] = {"launches": int(bl), "achieved": round(g, 1), "frac": round(g / peaks["hbm_gbs"], 4), "share_of_bytes": round(bb / nbytes, 4),
-                                             "avg_launch_ms": round(bms / max(bl, 1), 5)}
-    return roof
+    everything = {"launches": int(launches), "achieved": round(nbytes / (ms * 1e-3) / 1e9, 1), "frac": round(nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
+                  "avg_launch_ms": round(ms / max(launches, 1), 5), "algorithmic_bytes_per_launch": int(nbytes / max(launches, 1)),
+                  "note": "most of these launches move under a megabyte and cost a launch, not bandwidth"}
+    # The launch class the roofline line describes: operands of 32 MiB or more in total, the
+    # launches that hold nine tenths of the kernel's bytes and are bound by HBM, not by launch latency
+    big = [(r, s) for r, s in pairs if 2 * 4 * r.numel() >= (32 << 20)] or pairs
+    bb = sum(2 * 4 * r.numel() for r, _ in big)
+    bms, bl = timed(big)
+    ach = bb / (bms * 1e-3) / 1e9
+    per_launch = bb / max(bl, 1)
+    return {"bound": "hbm", "kernel": "b200::allclose_kernel<float>", "launch_class": "fp32 operand pairs of 32 MiB or more", "achieved": round(ach, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+            "frac": round(ach / peaks["hbm_gbs"], 4), "peak_source": peaks["source"], "launches": int(bl), "avg_launch_ms": round(bms / max(bl, 1), 5),
+            "algorithmic_bytes_per_launch": int(per_launch), "traffic": int(per_launch * ALLCLOSE_F32_DRAM_PER_ALGORITHMIC_BYTE) if ALLCLOSE_F32_DRAM_PER_ALGORITHMIC_BYTE else None,
+            "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one captured launch (128 MiB of operands) scaled by the bytes of the average launch of the class",
+            "share_of_kernel_bytes": round(bb / nbytes, 4), "share_of_kernel_time": round(bms / ms, 4),
+            "timing": f"the {bl} launches of the class replayed from a CUDA graph between one CUDA-event pair, median of {repeats}", "all_launches": everything}
 
 
 def cpu_bench_bounded(fn, budget_s=2.0):
