@@ -432,6 +432,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       tc_ld_32x32(t_base, r[0]);
       tc_ld_32x32(t_base + 32, r[0] + 32);
       const bool plain = p.alpha == 1.f && !p.has_bias;  // C = A x B: nothing to do but round
+      const bool unit_scales = p.alpha == 1.f && p.beta == 1.f;
       const bool bias_vec = sizeof(TO) == sizeof(T) && p.has_bias && p.sbn == 1 && p.sbm % 8 == 0 && (reinterpret_cast<uintptr_t>(bias) & 15u) == 0;
 #pragma unroll
       for (int c = 0; c < kChunks; ++c) {
@@ -470,8 +471,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 // unit-stride bias (a row vector, or a matrix like C): eight values in one load
                 float bv[8];
                 widen<T>(ld_keep(bias + m * p.sbm + n), bv);  // TO is T on this path
+                if (unit_scales) {  // addmm as models call it: one add per value
 #pragma unroll
-                for (int e = 0; e < 8; ++e) v[e] = fmaf(p.beta, bv[e], p.alpha * v[e]);
+                  for (int e = 0; e < 8; ++e) v[e] += bv[e];
+                } else {
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) v[e] = fmaf(p.beta, bv[e], p.alpha * v[e]);
+                }
               } else {
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {

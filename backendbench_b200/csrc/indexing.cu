@@ -190,6 +190,8 @@ __global__ void __launch_bounds__(kStripThreads, 1) gather_dim0_strip(const uint
   // in flight as well (with 1024, 768 or 512 threads) was measured 12-19 % SLOWER (62 -> 70-74
   // us at 4096 x 4096) -- the 64-byte segments of different rows lie in different DRAM pages,
   // and more of them outstanding at once cost more in page misses than the latency they hid.
+  // Holding neighbouring strips in lockstep (clusters of 2 / 4 / 8 CTAs, a cluster barrier per
+  // trip) did not help either: 68 -> 76 / 84 / 90 us on the same box.
   constexpr int U = 4;
   constexpr int kWarps = kStripThreads / 32;
   for (int64_t r0 = r_begin + warp * (8 * U); r0 < r_end; r0 += kWarps * (8 * U)) {

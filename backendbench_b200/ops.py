@@ -76,7 +76,15 @@ def _new(shape, dtype, device) -> torch.Tensor:
     return torch.empty(shape, dtype=dtype, device=device)
 
 
+try:  # the raw handle of the current stream without building a torch.cuda.Stream object (about 2 us less per call)
+    _raw_stream = torch._C._cuda_getCurrentRawStream
+except AttributeError:  # pragma: no cover - older / newer torch without the private accessor
+    _raw_stream = None
+
+
 def _stream_handle() -> int:
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -171,15 +179,36 @@ def _contiguous_strides(shape: Sequence[int]) -> List[int]:
     return st
 
 
+_array_memo = {}
+
+
+def _memo_array(values: tuple):
+    """`i64_array(values)`, remembered: the kernels only read these arrays, and a sweep asks
+    for the same few shapes and strides over and over."""
+    arr = _array_memo.get(values)
+    if arr is None:
+        if len(_array_memo) > 8192:
+            _array_memo.clear()
+        arr = _array_memo[values] = i64_array(values)
+    return arr
+
+
 def _iter_layout(out_shape: Sequence[int], operands: Sequence[torch.Tensor]):
     """(ndim, shape array, [stride arrays]) for a contiguous output of `out_shape`."""
+    if all(t.shape == out_shape and t.is_contiguous() for t in operands):
+        # the common case: everything contiguous and of the output's shape is one flat run
+        n = 1
+        for d in out_shape:
+            n *= d
+        one = _memo_array((1,))
+        return 1, _memo_array((n,)), [one] * len(operands)
     shape = list(out_shape)
     strides = [_expanded_strides(t, shape) for t in operands]
     strides.append(_contiguous_strides(shape))  # the output constrains merging too
     shape, strides = _coalesce(shape, strides)
     if len(shape) > _abi.MAX_DIMS:
         raise UnsupportedByB200(f"more than {_abi.MAX_DIMS} non-mergeable dimensions")
-    return len(shape), i64_array(shape), [i64_array(s) for s in strides[:-1]]
+    return len(shape), _memo_array(tuple(shape)), [_memo_array(tuple(st)) for st in strides[:-1]]
 
 
 def _contig(t: torch.Tensor) -> torch.Tensor:

@@ -28,6 +28,7 @@ def main():
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--rotate", action="store_true", help="time back-to-back launches over rotating input sets larger than L2 instead of flushing L2 before every launch")
+    ap.add_argument("--graph", action="store_true", help="with --rotate: capture the loop in a CUDA graph and time the replay (device time without the host's launch cost)")
     ap.add_argument("--compare", action="store_true", help="time the fused compare kernel on (aten result, backend result) of the case instead of the operator")
     ap.add_argument("--list", action="store_true")
     args = ap.parse_args()
@@ -57,7 +58,7 @@ def main():
 
         nsets = max(2, min(8, -(-2 * (126 << 20) // max(case.algorithmic_bytes(), 1))))
         sets = [replace(case, seed=case.seed + i).build("cuda") for i in range(nsets)]
-        ms = cuda_bench_rotating([(lambda a=a, k=k: impl(*a, **k)) for a, k in sets], reps=max(args.reps, 20))
+        ms = cuda_bench_rotating([(lambda a=a, k=k: impl(*a, **k)) for a, k in sets], reps=max(args.reps, 20), graph=args.graph)
     else:
         a, kw = case.build("cuda")
         ms = cuda_bench(lambda: impl(*a, **kw), warmup=args.warmup, reps=args.reps)

@@ -438,7 +438,8 @@ def named_config_table(backend, device, peaks, reps, with_cpu=False):
     """Throughput of every named operator configuration, next to aten CUDA on the same
     tensors. Each configuration is instantiated several times (different seeds) until the
     input sets exceed twice the L2 size; `reps` back-to-back launches rotate through the
-    sets between one pair of CUDA events. With `with_cpu`, the aten CPU operator is timed on a
+    sets, captured in a CUDA graph whose replay is timed between one pair of CUDA events (`ms`,
+    `aten_cuda_ms`: device time of both); `eager_ms` is the same loop launched from Python. With `with_cpu`, the aten CPU operator is timed on a
     host copy of the first input set by the harness's cpu_bench protocol (all host threads)."""
     from dataclasses import replace
 
@@ -454,13 +455,15 @@ def named_config_table(backend, device, peaks, reps, with_cpu=False):
         nsets = max(2, min(8, -(-2 * l2_bytes // max(c.algorithmic_bytes(), 1))))
         try:
             sets = [replace(c, seed=c.seed + i).build(device) for i in range(nsets)]
-            ms = cuda_bench_rotating([(lambda a=a, k=k: impl(*a, **k)) for a, k in sets], reps=reps)
-            aten_ms = cuda_bench_rotating([(lambda a=a, k=k: op(*a, **k)) for a, k in sets], reps=reps)
+            ms = cuda_bench_rotating([(lambda a=a, k=k: impl(*a, **k)) for a, k in sets], reps=reps, graph=True)
+            aten_ms = cuda_bench_rotating([(lambda a=a, k=k: op(*a, **k)) for a, k in sets], reps=reps, graph=True)
+            eager_ms = cuda_bench_rotating([(lambda a=a, k=k: impl(*a, **k)) for a, k in sets], reps=reps)
         except Exception as e:  # a failing configuration must not hide the others
             rows.append({"name": c.name, "error": repr(e)[:200]})
             continue
         tensor_bound = c.op in ("mm.default", "addmm.default")
-        row = {"name": c.name, "ms": round(ms, 5), "aten_cuda_ms": round(aten_ms, 5), "speedup_vs_aten_cuda": round(aten_ms / ms, 4), "bound": "tensor" if tensor_bound else "hbm", "input_sets": nsets}
+        row = {"name": c.name, "ms": round(ms, 5), "aten_cuda_ms": round(aten_ms, 5), "speedup_vs_aten_cuda": round(aten_ms / ms, 4), "eager_ms": round(eager_ms, 5),
+               "bound": "tensor" if tensor_bound else "hbm", "input_sets": nsets}
         gbs = c.algorithmic_bytes() / (ms * 1e-3) / 1e9
         row["gbs"] = round(gbs, 1)
         if c.flops():
