@@ -15,9 +15,11 @@ quoted on) and `sweep` (the 512-case sharded sweep). Backends: `aten`, `director
 
 from __future__ import annotations
 
+import json
 import logging
 import os
 import sys
+from dataclasses import asdict
 
 import click
 import torch
@@ -78,42 +80,109 @@ def task_units(suite, backend):
     return whole + [(op, c, q) for _, op, c, q in units]
 
 
-def run(suite, backend, backend_ref, num_workers=None, daemon=True, p=1.0, tolerances=None):
-    """Evaluate `suite` on `backend`; returns (mean correctness, geomean perf, perf@p, results)."""
+def _unit_key(op, ctests, ptests) -> str:
+    """What identifies a unit of work across runs: the operator and its test descriptors."""
+    def one(t):
+        if isinstance(t, SpecTest):
+            return f"{t.spec.label()}#{t.spec.seed}"
+        return getattr(t, "serialized", None) or repr(type(t).__name__)
+
+    name = getattr(op, "__name__", str(op))
+    return name + "|" + ";".join(one(t) for t in ctests) + "|" + ";".join(one(t) for t in ptests)
+
+
+class Checkpoint:
+    """One JSON line per finished unit of work (an operator, or one case of a descriptor
+    suite): its key, the operator's name and its result records. The reference writes its
+    results once, at the end of the run (BackendBench/scripts/main.py:315); a 512-case sweep on
+    eight GPUs that dies at case 500 should not start over. `--resume` reads the file back and
+    evaluates only the units that are not in it."""
+
+    def __init__(self, path, resume=False):
+        self.path = path
+        self.done = {}
+        if resume and path and os.path.exists(path):
+            with open(path) as fh:
+                for line in fh:
+                    line = line.strip()
+                    if not line:
+                        continue
+                    try:
+                        row = json.loads(line)
+                    except ValueError:  # a line cut short by the crash that made the resume necessary
+                        continue
+                    self.done[row["key"]] = row
+        elif path:
+            os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
+            open(path, "w").close()
+
+    def record(self, key, op_name, performance_score, cres, pres):
+        row = {"key": key, "op": op_name, "performance_score": performance_score, "correctness": [asdict(c) for c in cres], "performance": [asdict(q) for q in pres]}
+        self.done[key] = row
+        if self.path:
+            with open(self.path, "a") as fh:
+                fh.write(json.dumps(row, default=str) + "\n")
+
+    @staticmethod
+    def results_of(row):
+        cres = [evaluation.CorrectnessTestResult(**c) for c in row["correctness"]]
+        pres = [evaluation.PerformanceTestResult(**q) for q in row["performance"]]
+        return row["performance_score"], cres, pres
+
+
+def run(suite, backend, backend_ref, num_workers=None, daemon=True, p=1.0, tolerances=None, checkpoint=None):
+    """Evaluate `suite` on `backend`; returns (mean correctness, geomean perf, perf@p, results).
+    With a `Checkpoint`, finished units are appended to its file as they come in and units
+    already in it (a resumed run) are not evaluated again."""
     overall_correctness, overall_performance, all_c, all_p = [], [], [], []
+    ck = checkpoint or Checkpoint(None)
+    by_op = {}  # operator -> [(performance score, correctness results, performance results)]
     if num_workers is None:
         for test in suite:
             if test.op not in backend:
                 continue
-            _, perf, cres, pres = evaluation.eval_one_op(test.op, backend[test.op], test.correctness_tests, test.performance_tests, tolerances)
-            overall_correctness.append(all(r.is_correct for r in cres))
-            overall_performance.append(float(perf))
-            all_c.extend(cres)
-            all_p.extend(pres)
+            ctests, ptests = list(test.correctness_tests), list(test.performance_tests)
+            key = _unit_key(test.op, ctests, ptests)
+            if key in ck.done:
+                by_op.setdefault(test.op, []).append(Checkpoint.results_of(ck.done[key]))
+                continue
+            _, perf, cres, pres = evaluation.eval_one_op(test.op, backend[test.op], ctests, ptests, tolerances)
+            ck.record(key, getattr(test.op, "__name__", str(test.op)), float(perf), cres, pres)
+            by_op.setdefault(test.op, []).append((float(perf), cres, pres))
     else:
-        with MultiprocessingEvaluator(num_workers, daemon=daemon, backend=backend_ref) as evaluator:
-            op_of_task = {}
-            for op, ctests, ptests in task_units(suite, backend):
-                tid = evaluator.submit_task(op, backend_ref if backend_ref is not None else backend[op], ctests, ptests, tolerances)
-                op_of_task[tid] = op
-            evaluator.start_evaluation()
-            results = evaluator.get_results()
-        by_op = {}
-        for r in results:  # one task per CASE for descriptor suites: put the operator back together
-            by_op.setdefault(op_of_task[r.task_id], []).append(r)
-        for op, rs in by_op.items():
-            cres = [c for r in rs for c in r.correctness_results]
-            pres = [q for r in rs for q in r.performance_results]
-            overall_correctness.append(all(c.is_correct for c in cres))
-            if len(rs) == 1:
-                overall_performance.append(float(rs[0].performance_score))
-            elif pres:  # as eval_performance scores an operator: geomean over its cases, a failed case counts 1.0
-                sp = torch.tensor([float(q.speedup) if (q.successfully_ran and q.speedup) else 1.0 for q in pres], dtype=torch.float64)
-                overall_performance.append(float(sp.log().mean().exp()))
+        units = task_units(suite, backend)
+        pending = []
+        for op, ctests, ptests in units:
+            key = _unit_key(op, ctests, ptests)
+            if key in ck.done:
+                by_op.setdefault(op, []).append(Checkpoint.results_of(ck.done[key]))
             else:
-                overall_performance.append(float("nan"))
-            all_c.extend(cres)
-            all_p.extend(pres)
+                pending.append((key, op, ctests, ptests))
+        if pending:
+            with MultiprocessingEvaluator(num_workers, daemon=daemon, backend=backend_ref) as evaluator:
+                unit_of_task = {}
+                for key, op, ctests, ptests in pending:
+                    tid = evaluator.submit_task(op, backend_ref if backend_ref is not None else backend[op], ctests, ptests, tolerances)
+                    unit_of_task[tid] = (key, op)
+                evaluator.start_evaluation()
+                results = evaluator.get_results()
+            for r in results:  # one task per CASE for descriptor suites: put the operator back together
+                key, op = unit_of_task[r.task_id]
+                ck.record(key, getattr(op, "__name__", str(op)), float(r.performance_score), r.correctness_results, r.performance_results)
+                by_op.setdefault(op, []).append((float(r.performance_score), r.correctness_results, r.performance_results))
+    for op, rs in by_op.items():
+        cres = [c for _, cs, _ in rs for c in cs]
+        pres = [q for _, _, ps in rs for q in ps]
+        overall_correctness.append(all(c.is_correct for c in cres))
+        if len(rs) == 1:
+            overall_performance.append(float(rs[0][0]))
+        elif pres:  # as eval_performance scores an operator: geomean over its cases, a failed case counts 1.0
+            sp = torch.tensor([float(q.speedup) if (q.successfully_ran and q.speedup) else 1.0 for q in pres], dtype=torch.float64)
+            overall_performance.append(float(sp.log().mean().exp()))
+        else:
+            overall_performance.append(float("nan"))
+        all_c.extend(cres)
+        all_p.extend(pres)
     if not overall_correctness:
         return 0.0, 1.0, 0.0, (all_c, all_p)
     mean_correctness = torch.tensor(overall_correctness).float().mean().item()
@@ -139,7 +208,9 @@ def run(suite, backend, backend_ref, num_workers=None, daemon=True, p=1.0, toler
 @click.option("--dtype-tolerances/--harness-tolerances", default=False, help="Per-dtype tolerances instead of the harness's 1e-2 for everything")
 @click.option("--daemon/--no-daemon", default=True, help="Use daemon worker processes")
 @click.option("--log-dir", default=None, type=str, help="Directory for the report artefacts (full_results.json, operator_summary.csv, failed_tests.json, OVERALL_SUMMARY.md); none written when omitted")
-def cli(log_level, suite, alternative_torchbench_data_path, topn_inputs, backend, ops, ops_directory, num_workers, p, device, cases, dtype_tolerances, daemon, log_dir):
+@click.option("--checkpoint", default=None, type=str, help="Append one JSON line per finished unit of work to this file (with --resume and --log-dir the default is <log-dir>/results.jsonl)")
+@click.option("--resume/--no-resume", default=False, help="Skip the units already recorded in the checkpoint file and merge their results")
+def cli(log_level, suite, alternative_torchbench_data_path, topn_inputs, backend, ops, ops_directory, num_workers, p, device, cases, dtype_tolerances, daemon, log_dir, checkpoint, resume):
     logging.basicConfig(level=getattr(logging, log_level.upper()), format="[%(asctime)s][%(levelname)s][%(filename)s] %(message)s", datefmt="%Y-%m-%d %H:%M:%S")
     device = device or ("cuda" if torch.cuda.is_available() else "cpu")
     op_filter = [o.strip() for o in ops.split(",")] if ops else None
@@ -153,7 +224,12 @@ def cli(log_level, suite, alternative_torchbench_data_path, topn_inputs, backend
         test_suite = build_suite(suite, device, op_filter, cases)
     be = make_backend(backend, ops_directory)
     ref = BackendRef(backend, ops_directory if backend == "directory" else None)
-    mean_correctness, geomean_perf, perf_at_p, (all_c, all_p) = run(test_suite, be, ref, num_workers, daemon, p, "dtype" if dtype_tolerances else None)
+    if checkpoint is None and log_dir and resume:
+        checkpoint = os.path.join(log_dir, "results.jsonl")
+    ck = Checkpoint(checkpoint, resume) if checkpoint else None
+    if ck is not None and resume:
+        print(f"resuming: {len(ck.done)} finished unit(s) found in {checkpoint}")
+    mean_correctness, geomean_perf, perf_at_p, (all_c, all_p) = run(test_suite, be, ref, num_workers, daemon, p, "dtype" if dtype_tolerances else None, ck)
     if log_dir:
         from ..output import save_results
 

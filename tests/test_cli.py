@@ -68,3 +68,40 @@ def test_cli_sweep_with_b200_backend_on_gpu():
     correctness, geomean, _ = _scores(r.output)
     # scatter_add is compared with aten CUDA here (unordered atomics): tolerance-level agreement only
     assert correctness >= 0.9 and geomean > 0.05
+
+
+def test_checkpoint_and_resume(tmp_path):
+    """One JSON line per finished unit; a resumed run evaluates only what is missing and ends
+    with the same scores (the reference writes results once, at the end: scripts/main.py:315)."""
+    import json
+
+    from backendbench_b200.backends import AtenBackend
+    from backendbench_b200.scripts import main as cli_main
+
+    ck_path = str(tmp_path / "results.jsonl")
+    suite = cli_main.build_suite("sweep", "cpu", ["relu", "add"], 48)
+    full = cli_main.run(suite, AtenBackend(), None, None, True, 1.0, None, cli_main.Checkpoint(ck_path))
+    rows = [json.loads(line) for line in open(ck_path)]
+    assert len(rows) == len(list(suite)) and all(r["correctness"] for r in rows)
+    # drop the last unit (and leave a torn line behind, as a crash would) and resume
+    with open(ck_path, "w") as fh:
+        for r in rows[:-1]:
+            fh.write(json.dumps(r) + "\n")
+        fh.write('{"key": "torn')
+    calls = {"n": 0}
+    real = cli_main.evaluation.eval_one_op
+
+    def counting(*a, **k):
+        calls["n"] += 1
+        return real(*a, **k)
+
+    cli_main.evaluation.eval_one_op = counting
+    try:
+        ck = cli_main.Checkpoint(ck_path, resume=True)
+        assert len(ck.done) == len(rows) - 1
+        again = cli_main.run(suite, AtenBackend(), None, None, True, 1.0, None, ck)
+    finally:
+        cli_main.evaluation.eval_one_op = real
+    assert calls["n"] == 1  # only the missing unit was evaluated
+    assert again[0] == full[0] and len(again[3][0]) == len(full[3][0])
+    assert len([line for line in open(ck_path) if line.strip().endswith("}")]) == len(rows)
