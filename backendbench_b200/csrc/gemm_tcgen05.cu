@@ -40,6 +40,7 @@
 #include <cstdlib>
 
 #include "b200_common.cuh"
+#include "tma_common.cuh"
 
 namespace b200 {
 
@@ -63,42 +64,7 @@ constexpr int kEpiWarps = 8;
 constexpr int kEpiStageBytes = 32 * 128;                // per epilogue warp: 32 rows x 64 16-bit outputs, TMA-store staging
 constexpr size_t kGemmSmem = static_cast<size_t>(4) * (kABytes + 256 * kBK * 2) + kEpiWarps * kEpiStageBytes + 1024 /*align*/ + 256 /*barriers*/;  // same for both tile shapes (6 x 32 KB = 4 x 48 KB)
 
-// ------------------------------------------------------------------ PTX wrappers
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count)); }
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) { asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory"); }
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
-// One probe of the barrier phase; the hardware may park the thread for at most ~1 us.
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(1000u)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ uint64_t global_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-// Bounded wait: false when `limit_ns` ran out or another role already aborted.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, uint64_t limit_ns) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = global_ns();
-  for (uint32_t i = 0;; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 7u) == 7u) {
-      if (*abort_flag) return false;
-      if (global_ns() - t0 > limit_ns) return false;
-    }
-  }
-}
-
+// ------------------------------------------------------------------ PTX wrappers (mbarrier and timer helpers: tma_common.cuh)
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2) {
   asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
                : "memory");
@@ -571,20 +537,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 }
 
 // ------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn lookup_encode_fn() {
-  void* p = nullptr;
-  cudaDriverEntryPointQueryResult q;
-  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess) return reinterpret_cast<EncodeTiledFn>(p);
-  return nullptr;
-}
-static EncodeTiledFn encode_fn() {
-  static const EncodeTiledFn fn = lookup_encode_fn();  // initialised once, thread-safe (C++11 static)
-  return fn;
-}
-
 struct OperandLayout {
   bool ok, mn_major;
 };

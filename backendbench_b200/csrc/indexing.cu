@@ -8,7 +8,10 @@
 // An index outside [0, size) never faults: the element/row is written as zero and
 // B200_DEV_INDEX_OOB is OR-ed into the caller's status word. Negative indices are out of
 // range here, as they are for the aten CPU kernels.
+#include <cstdlib>
+
 #include "b200_common.cuh"
+#include "tma_common.cuh"
 
 namespace b200 {
 
@@ -169,9 +172,12 @@ __global__ void __launch_bounds__(256) gather_dim0_vec(const U* __restrict__ sel
 constexpr int kStripW = 8;
 constexpr int kStripThreads = 1024;
 constexpr int64_t kStripMaxSelfBytes = 200 * 1024;
-__global__ void __launch_bounds__(kStripThreads, 1) gather_dim0_strip(const uint32_t* __restrict__ self, const int64_t* __restrict__ index, uint32_t* __restrict__ out,
-                                                                      int64_t rows, int64_t cols, int64_t self_pitch, int self_rows, int whole_strips, int tail_split, uint32_t* status) {
-  extern __shared__ __align__(16) uint32_t strip[];  // [self_rows][kStripW]
+// Which strip and which rows this CTA works on (the strips of the last partial wave are cut
+// into `tail_split` row ranges).
+struct StripWork {
+  int64_t c0, r_begin, r_end;
+};
+__device__ __forceinline__ StripWork strip_work(int64_t rows, int whole_strips, int tail_split) {
   int64_t s = blockIdx.x, r_begin = 0, r_end = rows;
   if (static_cast<int>(blockIdx.x) >= whole_strips) {
     const int q = (blockIdx.x - whole_strips) / tail_split, piece = (blockIdx.x - whole_strips) % tail_split;
@@ -180,39 +186,94 @@ __global__ void __launch_bounds__(kStripThreads, 1) gather_dim0_strip(const uint
     r_begin = piece * per;
     r_end = r_begin + per < rows ? r_begin + per : rows;
   }
-  const int64_t c0 = s * kStripW;
+  return StripWork{s * kStripW, r_begin, r_end};
+}
+
+// Four index segments in flight per thread and no more: keeping the next trip's segments
+// in flight as well (with 1024, 768 or 512 threads) was measured 12-19 % SLOWER (62 -> 70-74
+// us at 4096 x 4096) -- the 64-byte segments of different rows lie in different DRAM pages,
+// and more of them outstanding at once cost more in page misses than the latency they hid.
+// Holding neighbouring strips in lockstep (clusters of 2 / 4 / 8 CTAs, a cluster barrier per
+// trip) did not help either: 68 -> 76 / 84 / 90 us on the same box.
+constexpr int kStripU = 4;
+constexpr int64_t kStripTrip = static_cast<int64_t>(kStripThreads / 32) * (8 * kStripU);  // rows one trip of the CTA covers
+
+__device__ __forceinline__ void strip_fetch(const int64_t* __restrict__ index, int64_t cols, const StripWork& w, int64_t r0, int rsub, int cp, longlong2 (&k)[kStripU]) {
+#pragma unroll
+  for (int u = 0; u < kStripU; ++u) {
+    const int64_t row = r0 + u * 8 + rsub;
+    if (row < w.r_end) k[u] = __ldcs(reinterpret_cast<const longlong2*>(index + row * cols + w.c0 + cp));
+  }
+}
+__device__ __forceinline__ void strip_emit(const uint32_t* strip, uint32_t* __restrict__ out, int64_t cols, const StripWork& w, int64_t r0, int rsub, int cp, int self_rows,
+                                           const longlong2 (&k)[kStripU], uint32_t* status) {
+#pragma unroll
+  for (int u = 0; u < kStripU; ++u) {
+    const int64_t row = r0 + u * 8 + rsub;
+    if (row < w.r_end) {
+      uint2 v = make_uint2(0u, 0u);
+      if (k[u].x < 0 || k[u].x >= self_rows) flag_oob(status);
+      else v.x = strip[static_cast<int>(k[u].x) * kStripW + cp];
+      if (k[u].y < 0 || k[u].y >= self_rows) flag_oob(status);
+      else v.y = strip[static_cast<int>(k[u].y) * kStripW + cp + 1];
+      __stcs(reinterpret_cast<uint2*>(out + row * cols + w.c0 + cp), v);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kStripThreads, 1) gather_dim0_strip(const uint32_t* __restrict__ self, const int64_t* __restrict__ index, uint32_t* __restrict__ out,
+                                                                      int64_t rows, int64_t cols, int64_t self_pitch, int self_rows, int whole_strips, int tail_split, uint32_t* status) {
+  extern __shared__ __align__(128) uint32_t strip[];  // [self_rows][kStripW]
+  const StripWork w = strip_work(rows, whole_strips, tail_split);
   for (int h = threadIdx.x; h < self_rows * 2; h += kStripThreads)  // half-rows: 16 bytes each
-    reinterpret_cast<uint4*>(strip)[h] = ld_keep(self + static_cast<int64_t>(h >> 1) * self_pitch + c0 + (h & 1) * 4);
+    reinterpret_cast<uint4*>(strip)[h] = ld_keep(self + static_cast<int64_t>(h >> 1) * self_pitch + w.c0 + (h & 1) * 4);
   __syncthreads();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int rsub = lane >> 2, cp = (lane & 3) * 2;  // a warp covers 8 rows x 8 columns per load
-  // Four index segments in flight per thread and no more: keeping the next trip's segments
-  // in flight as well (with 1024, 768 or 512 threads) was measured 12-19 % SLOWER (62 -> 70-74
-  // us at 4096 x 4096) -- the 64-byte segments of different rows lie in different DRAM pages,
-  // and more of them outstanding at once cost more in page misses than the latency they hid.
-  // Holding neighbouring strips in lockstep (clusters of 2 / 4 / 8 CTAs, a cluster barrier per
-  // trip) did not help either: 68 -> 76 / 84 / 90 us on the same box.
-  constexpr int U = 4;
-  constexpr int kWarps = kStripThreads / 32;
-  for (int64_t r0 = r_begin + warp * (8 * U); r0 < r_end; r0 += kWarps * (8 * U)) {
-    longlong2 k[U];
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int64_t row = r0 + u * 8 + rsub;
-      if (row < r_end) k[u] = __ldcs(reinterpret_cast<const longlong2*>(index + row * cols + c0 + cp));
-    }
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int64_t row = r0 + u * 8 + rsub;
-      if (row < r_end) {
-        uint2 v = make_uint2(0u, 0u);
-        if (k[u].x < 0 || k[u].x >= self_rows) flag_oob(status);
-        else v.x = strip[static_cast<int>(k[u].x) * kStripW + cp];
-        if (k[u].y < 0 || k[u].y >= self_rows) flag_oob(status);
-        else v.y = strip[static_cast<int>(k[u].y) * kStripW + cp + 1];
-        __stcs(reinterpret_cast<uint2*>(out + row * cols + c0 + cp), v);
-      }
-    }
+  for (int64_t r0 = w.r_begin + warp * (8 * kStripU); r0 < w.r_end; r0 += kStripTrip) {
+    longlong2 k[kStripU];
+    strip_fetch(index, cols, w, r0, rsub, cp, k);
+    strip_emit(strip, out, cols, w, r0, rsub, cp, self_rows, k, status);
+  }
+}
+
+// The same kernel with the strip brought in by the copy engine: one thread issues a tiled TMA
+// load per 256 source rows (box 8 columns x 256 rows = 8 KB, rows beyond the source read as
+// zero), all of them completing on one mbarrier, and every thread requests the index
+// segments of its first trip BEFORE it waits for the strip -- the strip load costs the 1024
+// threads no issue slots and overlaps the first index loads instead of preceding them. The
+// wait is bounded: when it runs out the CTA raises B200_DEV_WAIT_TIMEOUT and leaves.
+constexpr int kStripBoxRows = 256;
+constexpr int kStripBoxBytes = kStripBoxRows * kStripW * 4;
+__global__ void __launch_bounds__(kStripThreads, 1) gather_dim0_strip_tma(const __grid_constant__ CUtensorMap map_self, const int64_t* __restrict__ index, uint32_t* __restrict__ out, int64_t rows,
+                                                                          int64_t cols, int self_rows, int whole_strips, int tail_split, uint32_t* status) {
+  extern __shared__ __align__(128) uint32_t strip[];  // [boxes * 256][kStripW]
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ uint32_t gave_up;
+  const StripWork w = strip_work(rows, whole_strips, tail_split);
+  const int boxes = (self_rows + kStripBoxRows - 1) / kStripBoxRows;
+  if (threadIdx.x == 0) {
+    gave_up = 0u;
+    mbar_init(smem_u32(&bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    mbar_expect_tx(smem_u32(&bar), static_cast<uint32_t>(boxes) * kStripBoxBytes);
+    for (int b = 0; b < boxes; ++b) tma_load_2d(smem_u32(strip) + b * kStripBoxBytes, &map_self, smem_u32(&bar), static_cast<int>(w.c0), b * kStripBoxRows);
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int rsub = lane >> 2, cp = (lane & 3) * 2;
+  int64_t r0 = w.r_begin + warp * (8 * kStripU);
+  longlong2 k[kStripU];
+  if (r0 < w.r_end) strip_fetch(index, cols, w, r0, rsub, cp, k);  // in flight while the strip lands
+  __syncthreads();                                                  // the barrier is initialised for everybody
+  if (!mbar_wait(smem_u32(&bar), 0u, &gave_up, 2000000000ull)) {
+    gave_up = 1u;
+    if (status) atomicOr(status, B200_DEV_WAIT_TIMEOUT);
+    return;
+  }
+  while (r0 < w.r_end) {
+    strip_emit(strip, out, cols, w, r0, rsub, cp, self_rows, k, status);
+    r0 += kStripTrip;
+    if (r0 < w.r_end) strip_fetch(index, cols, w, r0, rsub, cp, k);
   }
 }
 
@@ -333,6 +394,15 @@ extern "C" int b200_index_select(const void* x, const void* idx, void* out, int6
   return index_select_bytes(x, idx, out, outer, dim_size, inner * elem_size, n_idx, idx_dtype, status, static_cast<cudaStream_t>(stream));
 }
 
+// B200_GATHER_TMA=0 in the environment (read once) keeps the strip on plain loads: how the two are compared.
+static bool strip_tma_enabled() {
+  static const bool on = []() {
+    const char* e = getenv("B200_GATHER_TMA");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
 extern "C" int b200_gather(const void* self, const void* index, void* out, int ndim, const int64_t* index_shape, const int64_t* self_strides, const int64_t* index_strides, int64_t self_dim_size, int dim, int elem_size, uint32_t* status, void* stream) {
   if (ndim < 1 || ndim > B200_MAX_DIMS || dim < 0 || dim >= ndim || !index_shape || !self_strides || !index_strides) return B200_EINVAL;
   GatherArgs A;
@@ -366,6 +436,25 @@ extern "C" int b200_gather(const void* self, const void* index, void* out, int n
     const int64_t whole = tail_split > 1 ? strips - tail : strips;
     const int64_t grid = whole + (strips - whole) * tail_split;
     if (grid > 0x7fffffffLL) return B200_EINVAL;
+    // the strip through the copy engine when a tensor map over `self` can be built (this GPU's own memory, no multicast)
+    alignas(64) CUtensorMap map_self;
+    bool tma = encode_fn() != nullptr && strip_tma_enabled();
+    if (tma) {
+      cuuint64_t dims[2] = {static_cast<cuuint64_t>(index_shape[1]), static_cast<cuuint64_t>(self_dim_size)};  // the columns this launch may touch x all source rows
+      cuuint64_t strides[1] = {static_cast<cuuint64_t>(self_strides[0]) * 4};
+      cuuint32_t box[2] = {kStripW, kStripBoxRows};
+      cuuint32_t estr[2] = {1, 1};
+      tma = encode_fn()(&map_self, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(self), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    }
+    if (tma) {
+      const size_t smem_tma = static_cast<size_t>((self_dim_size + kStripBoxRows - 1) / kStripBoxRows) * kStripBoxBytes;
+      const cudaError_t e2 = cudaFuncSetAttribute(gather_dim0_strip_tma, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kStripMaxSelfBytes));
+      if (e2 != cudaSuccess) { set_last_cuda_error(e2); return B200_ELAUNCH; }
+      gather_dim0_strip_tma<<<static_cast<unsigned>(grid), kStripThreads, smem_tma, st>>>(map_self, static_cast<const int64_t*>(index), static_cast<uint32_t*>(out), index_shape[0], index_shape[1],
+                                                                                        static_cast<int>(self_dim_size), static_cast<int>(whole), static_cast<int>(tail_split), status);
+      return check_launch();
+    }
     gather_dim0_strip<<<static_cast<unsigned>(grid), kStripThreads, smem, st>>>(static_cast<const uint32_t*>(self), static_cast<const int64_t*>(index), static_cast<uint32_t*>(out), index_shape[0],
                                                                               index_shape[1], self_strides[0], static_cast<int>(self_dim_size), static_cast<int>(whole), static_cast<int>(tail_split), status);
     return check_launch();
