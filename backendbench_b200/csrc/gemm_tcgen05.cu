@@ -77,22 +77,9 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap
                "r"(c1), "r"(c2)
                : "memory");
 }
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-// shared::cluster address of the location `addr` (a shared::cta address) in CTA `rank` of the cluster
-__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
-  return r;
-}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) { return map_to_cta_addr(addr, rank); }
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster) { asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory"); }
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
+__device__ __forceinline__ void cluster_sync_all() { cluster_barrier(); }
 
 // Tiled store shared -> global through the copy engine; clips at the tensor's edges.
 __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2) {
