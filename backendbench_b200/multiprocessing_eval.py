@@ -185,12 +185,29 @@ test_to_device.__test__ = False  # not a pytest test despite the name
 
 
 def _worker_device(worker_id: int) -> str:
-    if torch.cuda.is_available():
-        torch.cuda.set_device(worker_id)
+    """Bind this worker to GPU `worker_id` (the reference: `torch.cuda.set_device(worker_id)`,
+    BackendBench/multiprocessing_eval.py:82). When CUDA has not been initialised in this
+    process yet -- the normal case in a freshly spawned worker -- the binding is made by
+    narrowing CUDA_VISIBLE_DEVICES to that one GPU first: the driver then enumerates one device
+    instead of every GPU of the node while N workers start at once, and the worker cannot touch
+    a neighbour's GPU by accident. The GPU is then `cuda:0` in this process."""
+    narrowed = False
+    if not torch.cuda.is_initialized():  # a Python-side flag: no driver call yet, so the variable still counts
+        visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+        ids = [v.strip() for v in visible.split(",") if v.strip()] if visible else None
+        if ids is None or worker_id < len(ids):
+            os.environ["CUDA_VISIBLE_DEVICES"] = ids[worker_id] if ids else str(worker_id)
+            narrowed = True
+    if not torch.cuda.is_available():
+        return "cpu"
+    if narrowed:
+        torch.cuda.set_device(0)
         torch.cuda.synchronize()
-        torch.cuda.empty_cache()
-        return f"cuda:{worker_id}"
-    return "cpu"
+        return "cuda:0"
+    torch.cuda.set_device(worker_id)
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+    return f"cuda:{worker_id}"
 
 
 def _resolve_impl(impl, op, backends_cache):
