@@ -737,7 +737,10 @@ def run_b200(args):
     # ---- end to end: pinned host inputs, H2D inside the timed region
     e2e = None
     need_host = sum(_bytes_of(p["args"]) for p in prepared)
-    if not args.sweep_only and not _host_memory_allows(need_host, world):
+    # one decision for all ranks (each looks at the free memory at a slightly different moment;
+    # a split decision would leave some ranks alone in the collectives of the timed passes)
+    host_ok = args.sweep_only or sum_over_ranks(1.0 if _host_memory_allows(need_host, world) else 0.0) == float(world)
+    if not args.sweep_only and not host_ok:
         e2e = {"skipped": f"host memory: {world} rank(s) x {need_host} bytes of pinned inputs do not fit what this box offers"}
     elif not args.sweep_only:
         host_inputs = [[a.cpu().pin_memory() if isinstance(a, torch.Tensor) else a for a in p["args"]] for p in prepared]
