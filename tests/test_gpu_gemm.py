@@ -266,3 +266,43 @@ def test_a_wait_that_cannot_complete_ends_in_a_status_not_a_hang():
     got = ops.mm_default(a, b)
     ops.check_device_status()
     _check(got, a.double() @ b.double(), torch.bfloat16)
+
+
+PAIR_SHAPES = [(256, 256, 320), (300, 520, 640), (1000, 1000, 1000), (129, 130, 4096), (2048, 384, 512), (513, 257, 328)]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("a_t,b_t", [(False, False), (False, True), (True, False), (True, True)])
+def test_cta_pair_tiles_every_layout_and_ragged_edge(dtype, a_t, b_t):
+    """Products of more than 128 rows and columns with more than four K slabs run on CTA pairs
+    (256 x 256 tiles, tcgen05 cta_group::2): rows that end in the first or in the second CTA of
+    the last pair, columns that end in either half of B, K off the 64 grid, all four operand
+    layouts -- against the fp64 product, and bit for bit against the single-CTA kernel's rule
+    (fp32 accumulation, one rounding) through the tolerance of `_check`."""
+    g = torch.Generator(device=DEV).manual_seed(21)
+    for M, N, K in PAIR_SHAPES:
+        Mp, Kp, Np = (M + 7) // 8 * 8, (K + 7) // 8 * 8, (N + 7) // 8 * 8
+        a = _rand((Kp, Mp), dtype, g, K**-0.5).t()[:M, :K] if a_t else _rand((Mp, Kp), dtype, g, K**-0.5)[:M, :K]
+        b = _rand((Np, Kp), dtype, g, 1.0).t()[:K, :N] if b_t else _rand((Kp, Np), dtype, g, 1.0)[:K, :N]
+        got = ops.mm_default(a, b)
+        ops.check_device_status()
+        assert got.shape == (M, N) and got.dtype == dtype
+        _check(got, a.double() @ b.double(), dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_cta_pair_epilogue_and_batches(dtype):
+    g = torch.Generator(device=DEV).manual_seed(22)
+    M, N, K = 300, 520, 704
+    a, b = _rand((M, K), dtype, g, K**-0.5), _rand((K, N), dtype, g, 1.0)
+    exact = a.double() @ b.double()
+    for bias_shape in [(N,), (M, N), (1, N), (M, 1), ()]:
+        bias = _rand(bias_shape, dtype, g, 1.0)
+        _check(ops.addmm_default(bias, a, b), exact + bias.double(), dtype)  # alpha = beta = 1: the single-add epilogue
+        _check(ops.addmm_default(bias, a, b, beta=0.5, alpha=2), 2 * exact + 0.5 * bias.double(), dtype)
+    for B, M, K, N in [(3, 256, 384, 256), (5, 200, 520, 136), (2, 640, 1024, 300)]:
+        x, y = _rand((B, M, K), dtype, g, K**-0.5), _rand((B, K, N), dtype, g, 1.0)
+        _check(ops.bmm_default(x, y), x.double() @ y.double(), dtype)
+        yt = _rand((B, N, K), dtype, g, 1.0).transpose(1, 2)
+        _check(ops.bmm_default(x, yt), x.double() @ yt.double(), dtype)
+    ops.check_device_status()
