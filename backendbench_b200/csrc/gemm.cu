@@ -9,7 +9,7 @@ bool gemm_tc_eligible(int64_t batch, int64_t M, int64_t N, int64_t K, int64_t sA
                       const void* A, const void* B, const void* C);
 int gemm_tc_dispatch(const void* A, const void* B, const void* bias, void* C, int64_t batch, int64_t M, int64_t N, int64_t K, int64_t sAb, int64_t sAm, int64_t sAk,
                      int64_t sBb, int64_t sBk, int64_t sBn, int64_t sbm, int64_t sbn, double alpha, double beta, int dtype, uint32_t* status, cudaStream_t st,
-                     uint64_t wait_probe_limit_ns = 0);
+                     uint64_t wait_probe_limit_ns = 0, bool allow_pair = true);
 
 int64_t gemm_f32_split_scratch_bytes(int64_t batch, int64_t M, int64_t N, int64_t K);
 bool gemm_f32_split_eligible(int64_t batch, int64_t M, int64_t N, int64_t K);

@@ -626,7 +626,8 @@ static bool pair_launch_ok() {
 }
 
 int gemm_tc_dispatch(const void* A, const void* B, const void* bias, void* C, int64_t batch, int64_t M, int64_t N, int64_t K, int64_t sAb, int64_t sAm, int64_t sAk, int64_t sBb,
-                     int64_t sBk, int64_t sBn, int64_t sbm, int64_t sbn, double alpha, double beta, int dtype, uint32_t* status, cudaStream_t st, uint64_t wait_probe_limit_ns) {
+                     int64_t sBk, int64_t sBn, int64_t sbm, int64_t sbn, double alpha, double beta, int dtype, uint32_t* status, cudaStream_t st, uint64_t wait_probe_limit_ns,
+                     bool allow_pair) {
   const OperandLayout la = operand_layout(M, K, sAm, sAk, sAb, batch, A);
   const OperandLayout lb = operand_layout(N, K, sBn, sBk, sBb, batch, B);
   if (!la.ok || !lb.ok || !encode_fn()) return B200_EALIGN;
@@ -636,7 +637,7 @@ int gemm_tc_dispatch(const void* A, const void* B, const void* bias, void* C, in
   // the wait probe stays on the single-CTA kernel
   // (with four K slabs or fewer the kernel is bound by writing C and the pair is slower:
   // bmm 32 x 2048 x 128 x 2048 0.087 ms against 0.061 ms)
-  const bool pair = M > kBM && N > 128 && (K + kBK - 1) / kBK > 4 && wait_probe_limit_ns == 0 && pair_launch_ok();
+  const bool pair = allow_pair && M > kBM && N > 128 && (K + kBK - 1) / kBK > 4 && wait_probe_limit_ns == 0 && pair_launch_ok();
   const int bn_box = (N <= 128 || pair) ? 128 : 256;  // rows of the B box: must match the tile shape chosen below
   if (!encode_operand(&map_b, B, dtype, lb.mn_major, N, K, sBn, sBk, sBb, batch, bn_box)) return B200_EDRIVER;
   alignas(64) CUtensorMap map_c;
@@ -692,6 +693,12 @@ int gemm_tc_dispatch(const void* A, const void* B, const void* bias, void* C, in
     __half* ct = static_cast<__half*>(C);
     rc = pair ? launch(gemm_tcgen05_kernel<__half, 256, __half, true>, bt, ct)
               : narrow ? launch(gemm_tcgen05_kernel<__half, 128, __half>, bt, ct) : launch(gemm_tcgen05_kernel<__half, 256, __half>, bt, ct);
+  }
+  if (rc == B200_ELAUNCH && pair) {
+    // the cluster launch was refused (a device or a partition without thread-block clusters):
+    // the same product on single CTAs
+    (void)cudaGetLastError();
+    return gemm_tc_dispatch(A, B, bias, C, batch, M, N, K, sAb, sAm, sAk, sBb, sBk, sBn, sbm, sbn, alpha, beta, dtype, status, st, wait_probe_limit_ns, false);
   }
   if (rc) return rc;
   return check_launch();

@@ -268,6 +268,7 @@ __global__ void __launch_bounds__(kStripThreads, 1) gather_dim0_strip_tma(const 
   if (!mbar_wait(smem_u32(&bar), 0u, &gave_up, 2000000000ull)) {
     gave_up = 1u;
     if (status) atomicOr(status, B200_DEV_WAIT_TIMEOUT);
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);  // copies still under way may land before this CTA's shared memory is handed on
     return;
   }
   while (r0 < w.r_end) {
