@@ -65,11 +65,6 @@ constexpr int kEpiStageBytes = 32 * 128;                // per epilogue warp: 32
 constexpr size_t kGemmSmem = static_cast<size_t>(4) * (kABytes + 256 * kBK * 2) + kEpiWarps * kEpiStageBytes + 1024 /*align*/ + 256 /*barriers*/;  // same for both tile shapes (6 x 32 KB = 4 x 48 KB)
 
 // ------------------------------------------------------------------ PTX wrappers (mbarrier and timer helpers: tma_common.cuh)
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2) {
-  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
-               : "memory");
-}
-
 // The same load issued by a CTA of a pair: the destination is this CTA's shared memory, the
 // mbarrier (a shared::cluster address) may be the peer CTA's.
 __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster, int c0, int c1, int c2) {

@@ -31,6 +31,7 @@
 #include <type_traits>
 
 #include "b200_common.cuh"
+#include "tma_common.cuh"
 
 namespace b200 {
 
@@ -238,10 +239,18 @@ scatter_add_strip(const T* __restrict__ self, const int64_t* __restrict__ index,
 // The strip kernel again, for destinations of at most 4096 rows, sized for the memory
 // system instead of for occupancy. A CTA owns EIGHT columns (its fp32 strip is 128 KB at
 // 4096 rows: one CTA per SM), so every source row contributes a 64-byte index segment and
-// a 32-byte (fp32) value segment -- whole sectors, fetched with 16-byte asynchronous copies
-// and no transposition. Each of the eight warps owns one column and walks a tile 32 source
-// rows at a time, lane = source row; the 16-byte chunks of a staged row are XOR-swizzled
-// by the row number so that the 32 rows of one column spread over the banks.
+// a 32-byte (fp32) value segment -- whole sectors.
+// Source rows arrive in tiles of 128 rows through a ring filled by the copy engine: a ninth
+// warp issues two tiled TMA loads per tile (index box 8 x 128 int64 with the 64-byte swizzle,
+// value box 8 x 128 with the 32-byte swizzle: the 16-byte chunks of a staged row are XORed
+// with the row number, so the 32 rows a warp reads of one column spread over the banks) onto
+// the tile's `full` mbarrier, as soon as the eight compute warps have released the slot on its
+// `empty` mbarrier. The compute warps never meet at a CTA-wide barrier inside a strip: each
+// owns one column, waits for a tile, walks it 32 source rows at a time (lane = source row) and
+// releases it, so a warp that met more clashes than its neighbours falls behind by a few
+// tiles instead of holding all of them up, and the next strip's first tiles load while this
+// strip is written back. Every wait is bounded (a wait that runs out raises
+// B200_DEV_WAIT_TIMEOUT, and the CTA finishes its barriers and leaves).
 // With one or two warps per scheduler the kernel runs at the speed of its dependent
 // instruction chain, so the step is kept to a couple of dozen instructions: every offset
 // that depends only on the lane is computed once, row-bound tests exist only for the
@@ -250,162 +259,195 @@ scatter_add_strip(const T* __restrict__ self, const int64_t* __restrict__ index,
 // for the strip value it read ahead, keys, values and tags of step st + 1 are under way.
 constexpr int kWideCols = 8;
 constexpr int kWideTileRows = 128;
-constexpr int kWideThreads = 256;     // eight warps: one column each; all of them stage tiles
-constexpr int kWideTagSlots = 4096;   // one table per warp, exact up to 4096 destinations
-constexpr int kWideStages = 5;        // 12 KB tiles (fp32): 48 KB of source rows in flight per SM
+constexpr int kWideComputeThreads = 256;  // eight warps: one column each
+constexpr int kWideThreads = 288;         // ... and the warp that feeds the ring
+constexpr int kWideTagSlots = 4096;       // one table per warp, exact up to 4096 destinations
+constexpr int kWideStages = 5;            // 12 KB tiles (fp32): 48 KB of source rows in flight per SM
 constexpr int kWideMaxRows = 4096;
+constexpr uint64_t kWideWaitLimitNs = 2000000000ull;
+
+__device__ __forceinline__ void compute_warps_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(kWideComputeThreads) : "memory"); }
 
 template <typename T>
 __global__ void __launch_bounds__(kWideThreads, 1)
-scatter_add_strip_wide(const T* __restrict__ self, const int64_t* __restrict__ index, const T* __restrict__ src, T* __restrict__ out, StripArgs A, uint32_t* status) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
+scatter_add_strip_wide(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__ CUtensorMap map_src, const T* __restrict__ self, T* __restrict__ out, StripArgs A, uint32_t* status) {
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* smem_raw = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023));  // the swizzle patterns repeat every 512 bytes
   constexpr int kIdxTile = kWideTileRows * kWideCols * 8;                            // 8 KB: [row][4 chunks of 2 indices]
   constexpr int kSrcRow = kWideCols * static_cast<int>(sizeof(T));                   // 32 or 16 bytes of values per row
   constexpr int kSrcTile = kWideTileRows * kSrcRow;
   constexpr int kSrcChunks = kSrcRow / 16;                                           // 16-byte chunks per value row: 2 or 1
-  constexpr int kTile = kIdxTile + kSrcTile;
+  constexpr int kTile = kIdxTile + kSrcTile;                                         // 12 KB / 10 KB: every slot starts on a 1 KB boundary
   unsigned char* ring = smem_raw;
-  unsigned char* tags = smem_raw + kWideStages * kTile + (threadIdx.x >> 5) * kWideTagSlots;
-  float* strip = reinterpret_cast<float*>(smem_raw + kWideStages * kTile + (kWideThreads / 32) * kWideTagSlots);  // [8][rows]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  unsigned char* tags = smem_raw + kWideStages * kTile + (warp & 7) * kWideTagSlots;
+  float* strip = reinterpret_cast<float*>(smem_raw + kWideStages * kTile + 8 * kWideTagSlots);  // [8][rows]
   const int rows = static_cast<int>(A.rows);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(strip) + static_cast<size_t>(kWideMaxRows) * kWideCols * 4);  // full[S], empty[S]
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars + 2 * kWideStages);
+  const uint32_t bar_base = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kWideStages + s); };
   const int64_t nstrips = A.cols / kWideCols;
   const int ntiles = static_cast<int>((A.idx_rows + kWideTileRows - 1) / kWideTileRows);
   constexpr int kSegsPerRow = kSrcRow / 16, kPerSeg = 16 / static_cast<int>(sizeof(T));  // 16-byte segments of a destination row
 
-  // staging: this thread copies index chunk (row sr, pair sq) and the same of row sr + 64,
-  // and (threads below 128 * kSrcChunks) value chunk (row vr, chunk vq) of every tile
-  const int sr = tid >> 2, sq = tid & 3;
-  const int s_idx_off = sr * 64 + ((sq ^ ((sr >> 1) & 3)) << 4);  // + 64 * 64 for the second row: same swizzle bits
-  const int vr = tid / kSrcChunks, vq = tid % kSrcChunks;
-  const int s_src_off = kIdxTile + vr * kSrcRow + ((kSrcChunks == 2 ? (vq ^ ((vr >> 2) & 1)) : vq) << 4);
-  // compute: this lane reads row `lane` (+ 32 per step) of column `warp`
-  const int c_idx_off = lane * 64 + (((warp >> 1) ^ ((lane >> 1) & 3)) << 4) + (warp & 1) * 8;
-  const int c_src_off = kIdxTile + lane * kSrcRow + (kSrcChunks == 2 ? (((warp >> 2) ^ ((lane >> 2) & 1)) << 4) : 0) + (warp & (kPerSeg - 1)) * static_cast<int>(sizeof(T));
-  float* col = strip + warp * rows;
-  const uint64_t urows = static_cast<uint64_t>(A.rows);
+  if (tid == 0) {
+    for (int s = 0; s < kWideStages; ++s) {
+      mbar_init(full_bar(s), 1);   // the producer's expect_tx arrival; the copies complete the bytes
+      mbar_init(empty_bar(s), 8);  // one arrival per compute warp
+    }
+    *abort_flag = 0u;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
 
-  for (int64_t item = blockIdx.x; item < A.outer * nstrips; item += gridDim.x) {
-    const int64_t o = item / nstrips, j0 = (item - o * nstrips) * kWideCols;
-    const T* self_o = self + o * A.rows * A.cols + j0;
-    T* out_o = out + o * A.rows * A.cols + j0;
-    const bool active = j0 < A.idx_cols && o < A.idx_outer && ntiles > 0;
-    const int64_t* idx_g = index + o * A.idx_so + j0 + sr * A.idx_sr + sq * 2;
-    const int64_t src_pitch = A.src_sr * static_cast<int64_t>(sizeof(T));
-    const unsigned char* src_g = reinterpret_cast<const unsigned char*>(src + o * A.src_so + j0) + vr * src_pitch + vq * 16;
-    auto issue_tile = [&](int tile, int slot) {
-      if (active && tile < ntiles) {
-        unsigned char* dst = ring + slot * kTile;
-        const int64_t i0 = static_cast<int64_t>(tile) * kWideTileRows;
-        const int64_t* gi = idx_g + i0 * A.idx_sr;
-        if (i0 + kWideTileRows <= A.idx_rows) {
-          __pipeline_memcpy_async(dst + s_idx_off, gi, 16);
-          __pipeline_memcpy_async(dst + s_idx_off + 64 * 64, gi + 64 * A.idx_sr, 16);
-          if (tid < kWideTileRows * kSrcChunks) __pipeline_memcpy_async(dst + s_src_off, src_g + i0 * src_pitch, 16);
-        } else {  // the ragged last tile
-          if (i0 + sr < A.idx_rows) __pipeline_memcpy_async(dst + s_idx_off, gi, 16);
-          if (i0 + sr + 64 < A.idx_rows) __pipeline_memcpy_async(dst + s_idx_off + 64 * 64, gi + 64 * A.idx_sr, 16);
-          if (tid < kWideTileRows * kSrcChunks && i0 + vr < A.idx_rows) __pipeline_memcpy_async(dst + s_src_off, src_g + i0 * src_pitch, 16);
+  if (warp == 8) {
+    // ------------------------------------------------------------ producer: the ring, tile after tile, strip after strip
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int64_t item = blockIdx.x; item < A.outer * nstrips && ok; item += gridDim.x) {
+        const int64_t o = item / nstrips, j0 = (item - o * nstrips) * kWideCols;
+        if (!(j0 < A.idx_cols && o < A.idx_outer && ntiles > 0)) continue;
+        for (int tile = 0; tile < ntiles; ++tile) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, kWideWaitLimitNs)) { ok = false; break; }
+          const uint32_t dst = smem_u32(ring) + stage * kTile;
+          mbar_expect_tx(full_bar(stage), kTile);  // a box counts in full, rows past the end of the tensor arrive as zeros
+          tma_load_3d(dst, &map_idx, full_bar(stage), static_cast<int>(j0), tile * kWideTileRows, static_cast<int>(o));
+          tma_load_3d(dst + kIdxTile, &map_src, full_bar(stage), static_cast<int>(j0), tile * kWideTileRows, static_cast<int>(o));
+          if (++stage == kWideStages) { stage = 0; phase ^= 1u; }
         }
       }
-      __pipeline_commit();  // one group per tile slot, empty past the end, so the wait depth stays constant
-    };
-    for (int sidx = 0; sidx < kWideStages - 1; ++sidx) issue_tile(sidx, sidx);  // in flight while the strip loads
-
-    // ---- stage self[:, j0 : j0 + 8] column-major as fp32
-    for (int q0 = 0; q0 < rows * kSegsPerRow; q0 += kWideThreads * 16) {
-      uint4 seg[16];
-#pragma unroll
-      for (int u = 0; u < 16; ++u) {
-        const int id = q0 + u * kWideThreads + tid;
-        if (id < rows * kSegsPerRow) seg[u] = ld_wide(reinterpret_cast<const uint4*>(self_o + static_cast<int64_t>(id / kSegsPerRow) * A.cols + (id % kSegsPerRow) * kPerSeg));
-      }
-#pragma unroll
-      for (int u = 0; u < 16; ++u) {
-        const int id = q0 + u * kWideThreads + tid;
-        if (id < rows * kSegsPerRow) {
-          float f[kPerSeg];
-          widen<T>(seg[u], f);
-          const int r = id / kSegsPerRow, c0 = (id % kSegsPerRow) * kPerSeg;
-#pragma unroll
-          for (int c = 0; c < kPerSeg; ++c) strip[(c0 + c) * rows + r] = f[c];
-        }
+      if (!ok) {
+        *abort_flag = 1u;
+        if (status) atomicOr(status, B200_DEV_WAIT_TIMEOUT);
       }
     }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ compute warps: lane reads row `lane` (+ 32 per step) of column `warp`
+    const int c_idx_off = lane * 64 + (((warp >> 1) ^ ((lane >> 1) & 3)) << 4) + (warp & 1) * 8;
+    const int c_src_off = kIdxTile + lane * kSrcRow + (kSrcChunks == 2 ? (((warp >> 2) ^ ((lane >> 2) & 1)) << 4) : 0) + (warp & (kPerSeg - 1)) * static_cast<int>(sizeof(T));
+    float* col = strip + warp * rows;
+    const uint64_t urows = static_cast<uint64_t>(A.rows);
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int64_t item = blockIdx.x; item < A.outer * nstrips; item += gridDim.x) {
+      const int64_t o = item / nstrips, j0 = (item - o * nstrips) * kWideCols;
+      const T* self_o = self + o * A.rows * A.cols + j0;
+      T* out_o = out + o * A.rows * A.cols + j0;
+      const bool active = j0 < A.idx_cols && o < A.idx_outer && ntiles > 0;
 
-    if (active) {
-      int slot = 0, fill_slot = kWideStages - 1;
-      for (int tile = 0; tile < ntiles; ++tile) {
-        __pipeline_wait_prior(kWideStages - 2);  // this thread's copies of tile `tile` have landed
-        __syncthreads();                         // ... everyone's have; all warps are also done with tile - 1 (and with staging the strip)
-        issue_tile(tile + kWideStages - 1, fill_slot);
-        const unsigned char* tile_s = ring + slot * kTile;
-        const int valid_rows = static_cast<int>(A.idx_rows - static_cast<int64_t>(tile) * kWideTileRows);  // >= 128 except in the last tile
-        constexpr int kSteps = kWideTileRows / 32;
-        auto fetch = [&](int st, int& k, float& v) {
-          k = -1 - lane;
-          v = 0.f;
-          if (st * 32 + lane < valid_rows) {
-            const int64_t key = *reinterpret_cast<const int64_t*>(tile_s + c_idx_off + st * (32 * 64));
-            if (static_cast<uint64_t>(key) < urows) {
-              k = static_cast<int>(key);
-              v = to_f32(*reinterpret_cast<const T*>(tile_s + c_src_off + st * (32 * kSrcRow)));
-            } else {
-              flag_oob(status);
-            }
-          }
-        };
-        int k[2];
-        float v[2];
-        fetch(0, k[0], v[0]);
-        if (k[0] >= 0) tags[k[0] & (kWideTagSlots - 1)] = static_cast<unsigned char>(lane);
+      // ---- stage self[:, j0 : j0 + 8] column-major as fp32
+      for (int q0 = 0; q0 < rows * kSegsPerRow; q0 += kWideComputeThreads * 16) {
+        uint4 seg[16];
 #pragma unroll
-        for (int st = 0; st < kSteps; ++st) {
-          const int cur = st & 1, nxt = cur ^ 1;
-          if (st + 1 < kSteps) fetch(st + 1, k[nxt], v[nxt]);
-          __syncwarp();  // the tags of step st are written
-          const unsigned winner = k[cur] >= 0 ? tags[k[cur] & (kWideTagSlots - 1)] : static_cast<unsigned>(lane);
-          const bool lost = winner != static_cast<unsigned>(lane);
-          const float old = k[cur] >= 0 ? col[k[cur]] : 0.f;  // read ahead; used only by lanes that nothing clashes with
-          if (st + 1 < kSteps && k[nxt] >= 0) tags[k[nxt] & (kWideTagSlots - 1)] = static_cast<unsigned char>(lane);  // after this step's read-back, in program order
-          const unsigned losers = __ballot_sync(0xffffffffu, lost);
-          if (losers == 0u) {
-            if (k[cur] >= 0) col[k[cur]] = old + v[cur];
-          } else {
-            // All lanes that share a slot read the same tag: the one lane it names is not
-            // lost, every other one is. So the lanes in a clash are exactly the losers and
-            // the lanes they name; everybody else adds at once, and the few involved add one
-            // after the other in lane order, which is source-row order.
-            unsigned involved = losers | __reduce_or_sync(0xffffffffu, lost ? 1u << winner : 0u);
-            if (__popc(involved) <= 8) {
-              if (k[cur] >= 0 && !((involved >> lane) & 1u)) col[k[cur]] = old + v[cur];
-              while (involved) {
-                const int l = __ffs(involved) - 1;
-                if (lane == l) col[k[cur]] += v[cur];
-                involved &= involved - 1;
-                __syncwarp();
+        for (int u = 0; u < 16; ++u) {
+          const int id = q0 + u * kWideComputeThreads + tid;
+          if (id < rows * kSegsPerRow) seg[u] = ld_wide(reinterpret_cast<const uint4*>(self_o + static_cast<int64_t>(id / kSegsPerRow) * A.cols + (id % kSegsPerRow) * kPerSeg));
+        }
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+          const int id = q0 + u * kWideComputeThreads + tid;
+          if (id < rows * kSegsPerRow) {
+            float f[kPerSeg];
+            widen<T>(seg[u], f);
+            const int r = id / kSegsPerRow, c0 = (id % kSegsPerRow) * kPerSeg;
+#pragma unroll
+            for (int c = 0; c < kPerSeg; ++c) strip[(c0 + c) * rows + r] = f[c];
+          }
+        }
+      }
+      compute_warps_barrier();  // the strip is staged
+
+      if (active) {
+        for (int tile = 0; tile < ntiles && ok; ++tile) {
+          int got = 0;
+          if (lane == 0) got = mbar_wait(full_bar(stage), phase, abort_flag, kWideWaitLimitNs) ? 1 : 0;
+          got = __shfl_sync(0xffffffffu, got, 0);
+          if (!got) {
+            ok = false;
+            if (lane == 0) {
+              *abort_flag = 1u;
+              if (status) atomicOr(status, B200_DEV_WAIT_TIMEOUT);
+            }
+            break;
+          }
+          const unsigned char* tile_s = ring + stage * kTile;
+          const int valid_rows = static_cast<int>(A.idx_rows - static_cast<int64_t>(tile) * kWideTileRows);  // >= 128 except in the last tile
+          constexpr int kSteps = kWideTileRows / 32;
+          auto fetch = [&](int st, int& k, float& v) {
+            k = -1 - lane;
+            v = 0.f;
+            if (st * 32 + lane < valid_rows) {
+              const int64_t key = *reinterpret_cast<const int64_t*>(tile_s + c_idx_off + st * (32 * 64));
+              if (static_cast<uint64_t>(key) < urows) {
+                k = static_cast<int>(key);
+                v = to_f32(*reinterpret_cast<const T*>(tile_s + c_src_off + st * (32 * kSrcRow)));
+              } else {
+                flag_oob(status);
               }
+            }
+          };
+          int k[2];
+          float v[2];
+          fetch(0, k[0], v[0]);
+          if (k[0] >= 0) tags[k[0] & (kWideTagSlots - 1)] = static_cast<unsigned char>(lane);
+#pragma unroll
+          for (int st = 0; st < kSteps; ++st) {
+            const int cur = st & 1, nxt = cur ^ 1;
+            if (st + 1 < kSteps) fetch(st + 1, k[nxt], v[nxt]);
+            __syncwarp();  // the tags of step st are written
+            const unsigned winner = k[cur] >= 0 ? tags[k[cur] & (kWideTagSlots - 1)] : static_cast<unsigned>(lane);
+            const bool lost = winner != static_cast<unsigned>(lane);
+            const float old = k[cur] >= 0 ? col[k[cur]] : 0.f;  // read ahead; used only by lanes that nothing clashes with
+            if (st + 1 < kSteps && k[nxt] >= 0) tags[k[nxt] & (kWideTagSlots - 1)] = static_cast<unsigned char>(lane);  // after this step's read-back, in program order
+            const unsigned losers = __ballot_sync(0xffffffffu, lost);
+            if (losers == 0u) {
+              if (k[cur] >= 0) col[k[cur]] = old + v[cur];
             } else {
-              apply_in_rank_order(col, k[cur], v[cur], rank_among_earlier<32>(k[cur], lane));
+              // All lanes that share a slot read the same tag: the one lane it names is not
+              // lost, every other one is. So the lanes in a clash are exactly the losers and
+              // the lanes they name; everybody else adds at once, and the few involved add one
+              // after the other in lane order, which is source-row order.
+              unsigned involved = losers | __reduce_or_sync(0xffffffffu, lost ? 1u << winner : 0u);
+              if (__popc(involved) <= 8) {
+                if (k[cur] >= 0 && !((involved >> lane) & 1u)) col[k[cur]] = old + v[cur];
+                while (involved) {
+                  const int l = __ffs(involved) - 1;
+                  if (lane == l) col[k[cur]] += v[cur];
+                  involved &= involved - 1;
+                  __syncwarp();
+                }
+              } else {
+                apply_in_rank_order(col, k[cur], v[cur], rank_among_earlier<32>(k[cur], lane));
+              }
             }
           }
+          __syncwarp();                                   // every lane is done with the tile ...
+          if (lane == 0) mbar_arrive(empty_bar(stage));   // ... and this warp hands its share of the slot back
+          if (++stage == kWideStages) { stage = 0; phase ^= 1u; }
         }
-        __syncwarp();
-        if (++slot == kWideStages) slot = 0;
-        if (++fill_slot == kWideStages) fill_slot = 0;
       }
-    }
-    __pipeline_wait_prior(0);
-    __syncthreads();
-    // ---- write the strip back, rounding once
-    for (int id = tid; id < rows * kSegsPerRow; id += kWideThreads) {
-      const int r = id / kSegsPerRow, c0 = (id % kSegsPerRow) * kPerSeg;
-      float f[kPerSeg];
+      compute_warps_barrier();  // every column of the strip is final
+      // ---- write the strip back, rounding once
+      for (int id = tid; id < rows * kSegsPerRow; id += kWideComputeThreads) {
+        const int r = id / kSegsPerRow, c0 = (id % kSegsPerRow) * kPerSeg;
+        float f[kPerSeg];
 #pragma unroll
-      for (int c = 0; c < kPerSeg; ++c) f[c] = strip[(c0 + c) * rows + r];
-      __stcs(reinterpret_cast<uint4*>(out_o + static_cast<int64_t>(r) * A.cols + c0), narrow<T>(f));
+        for (int c = 0; c < kPerSeg; ++c) f[c] = strip[(c0 + c) * rows + r];
+        __stcs(reinterpret_cast<uint4*>(out_o + static_cast<int64_t>(r) * A.cols + c0), narrow<T>(f));
+      }
+      compute_warps_barrier();  // the strip is rewritten by the next item
     }
-    __syncthreads();  // the strip and the ring are rewritten by the next item
+  }
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);  // copies still under way land before the shared memory is handed on
+    __syncthreads();
   }
 }
 
@@ -1002,12 +1044,33 @@ static int launch_strip(const void* self, const void* index, const void* src, vo
 
 template <typename T>
 static int launch_strip_wide(const void* self, const void* index, const void* src, void* out, const StripArgs& A, uint32_t* status, cudaStream_t st) {
-  const size_t smem = static_cast<size_t>(kWideStages) * kWideTileRows * kWideCols * (8 + sizeof(T)) + (kWideThreads / 32) * kWideTagSlots + static_cast<size_t>(A.rows) * kWideCols * 4;
-  const cudaError_t ae = cudaFuncSetAttribute(scatter_add_strip_wide<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+  // tensor maps over the index and value tensors (this GPU's own memory, no multicast): boxes
+  // of 8 columns x 128 rows, swizzled the way the compute warps read them
+  if (!encode_fn()) return B200_EDRIVER;
+  alignas(64) CUtensorMap map_idx, map_src;
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(A.idx_cols), static_cast<cuuint64_t>(A.idx_rows), static_cast<cuuint64_t>(A.idx_outer)};
+  const cuuint32_t box[3] = {kWideCols, kWideTileRows, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  auto outer_stride = [&](int64_t so, int64_t sr, int64_t es) { return static_cast<cuuint64_t>((A.idx_outer > 1 && so > 0 ? so : sr * A.idx_rows) * es); };
+  const cuuint64_t istr[2] = {static_cast<cuuint64_t>(A.idx_sr) * 8, outer_stride(A.idx_so, A.idx_sr, 8)};
+  const int es = static_cast<int>(sizeof(T));
+  const cuuint64_t sstr[2] = {static_cast<cuuint64_t>(A.src_sr) * es, outer_stride(A.src_so, A.src_sr, es)};
+  if (istr[1] % 16 || sstr[1] % 16) return B200_EALIGN;
+  if (encode_fn()(&map_idx, CU_TENSOR_MAP_DATA_TYPE_INT64, 3, const_cast<void*>(index), dims, istr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return B200_EDRIVER;
+  const CUtensorMapDataType vt = std::is_same<T, float>::value ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : std::is_same<T, __nv_bfloat16>::value ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const CUtensorMapSwizzle vs = sizeof(T) == 4 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE;  // 16-bit rows are one 16-byte chunk
+  if (encode_fn()(&map_src, vt, 3, const_cast<void*>(src), dims, sstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, vs, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) !=
+      CUDA_SUCCESS)
+    return B200_EDRIVER;
+  // ring + tag tables + the strip at its largest + barriers + room to align the ring to 1 KB
+  const size_t smem = static_cast<size_t>(kWideStages) * kWideTileRows * kWideCols * (8 + sizeof(T)) + 8 * kWideTagSlots + static_cast<size_t>(kWideMaxRows) * kWideCols * 4 + 128 + 1024;
+  const cudaError_t ae = cudaFuncSetAttribute(scatter_add_strip_wide<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (ae != cudaSuccess) { set_last_cuda_error(ae); return B200_ELAUNCH; }
   const int64_t items = A.outer * (A.cols / kWideCols);
   const int grid = static_cast<int>(items < 2LL * kNumSMs ? items : 2LL * kNumSMs);
-  scatter_add_strip_wide<T><<<grid, kWideThreads, smem, st>>>(static_cast<const T*>(self), static_cast<const int64_t*>(index), static_cast<const T*>(src), static_cast<T*>(out), A, status);
+  scatter_add_strip_wide<T><<<grid, kWideThreads, smem, st>>>(map_idx, map_src, static_cast<const T*>(self), static_cast<T*>(out), A, status);
   return check_launch();
 }
 
