@@ -261,7 +261,8 @@ constexpr int kWideCols = 8;
 constexpr int kWideTileRows = 128;
 constexpr int kWideComputeThreads = 256;  // eight warps: one column each
 constexpr int kWideThreads = 288;         // ... and the warp that feeds the ring
-constexpr int kWideTagSlots = 4096;       // one table per warp, exact up to 4096 destinations
+constexpr int kWideTagSlots = 4096;       // one table per warp, exact up to 4096 destinations ...
+constexpr int kWideDummies = 32;          // ... plus a slot (and a strip element) per lane for rows that have nothing to add
 constexpr int kWideStages = 5;            // 12 KB tiles (fp32): 48 KB of source rows in flight per SM
 constexpr int kWideMaxRows = 4096;
 constexpr uint64_t kWideWaitLimitNs = 2000000000ull;
@@ -280,10 +281,11 @@ scatter_add_strip_wide(const __grid_constant__ CUtensorMap map_idx, const __grid
   constexpr int kTile = kIdxTile + kSrcTile;                                         // 12 KB / 10 KB: every slot starts on a 1 KB boundary
   unsigned char* ring = smem_raw;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  unsigned char* tags = smem_raw + kWideStages * kTile + (warp & 7) * kWideTagSlots;
-  float* strip = reinterpret_cast<float*>(smem_raw + kWideStages * kTile + 8 * kWideTagSlots);  // [8][rows]
+  unsigned char* tags = smem_raw + kWideStages * kTile + (warp & 7) * (kWideTagSlots + kWideDummies);
+  float* strip = reinterpret_cast<float*>(smem_raw + kWideStages * kTile + 8 * (kWideTagSlots + kWideDummies));  // [8][rows + 32]
   const int rows = static_cast<int>(A.rows);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(strip) + static_cast<size_t>(kWideMaxRows) * kWideCols * 4);  // full[S], empty[S]
+  const int cstride = rows + kWideDummies;  // a column of the strip, then one dummy element per lane
+  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(strip) + static_cast<size_t>(kWideMaxRows + kWideDummies) * kWideCols * 4);  // full[S], empty[S]
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(bars + 2 * kWideStages);
   const uint32_t bar_base = smem_u32(bars);
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
@@ -330,8 +332,9 @@ scatter_add_strip_wide(const __grid_constant__ CUtensorMap map_idx, const __grid
     // ------------------------------------------------------------ compute warps: lane reads row `lane` (+ 32 per step) of column `warp`
     const int c_idx_off = lane * 64 + (((warp >> 1) ^ ((lane >> 1) & 3)) << 4) + (warp & 1) * 8;
     const int c_src_off = kIdxTile + lane * kSrcRow + (kSrcChunks == 2 ? (((warp >> 2) ^ ((lane >> 2) & 1)) << 4) : 0) + (warp & (kPerSeg - 1)) * static_cast<int>(sizeof(T));
-    float* col = strip + warp * rows;
+    float* col = strip + warp * cstride;
     const uint64_t urows = static_cast<uint64_t>(A.rows);
+    const int dummy = rows + lane;  // where a lane with nothing to add "adds" zero: its own slot, so it never clashes
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
@@ -357,7 +360,7 @@ scatter_add_strip_wide(const __grid_constant__ CUtensorMap map_idx, const __grid
             widen<T>(seg[u], f);
             const int r = id / kSegsPerRow, c0 = (id % kSegsPerRow) * kPerSeg;
 #pragma unroll
-            for (int c = 0; c < kPerSeg; ++c) strip[(c0 + c) * rows + r] = f[c];
+            for (int c = 0; c < kPerSeg; ++c) strip[(c0 + c) * cstride + r] = f[c];
           }
         }
       }
@@ -379,35 +382,37 @@ scatter_add_strip_wide(const __grid_constant__ CUtensorMap map_idx, const __grid
           const unsigned char* tile_s = ring + stage * kTile;
           const int valid_rows = static_cast<int>(A.idx_rows - static_cast<int64_t>(tile) * kWideTileRows);  // >= 128 except in the last tile
           constexpr int kSteps = kWideTileRows / 32;
+          // Every lane always has a destination: a row past the end of the tensor, or an index
+          // out of range (reported), adds zero to the lane's own dummy element. The step below
+          // therefore has no per-lane conditions at all -- with two warps per scheduler the
+          // kernel runs at the speed of its instruction chain, and every `if (k >= 0)` cost a
+          // branch and its reconvergence bookkeeping.
           auto fetch = [&](int st, int& k, float& v) {
-            k = -1 - lane;
-            v = 0.f;
-            if (st * 32 + lane < valid_rows) {
-              const int64_t key = *reinterpret_cast<const int64_t*>(tile_s + c_idx_off + st * (32 * 64));
-              if (static_cast<uint64_t>(key) < urows) {
-                k = static_cast<int>(key);
-                v = to_f32(*reinterpret_cast<const T*>(tile_s + c_src_off + st * (32 * kSrcRow)));
-              } else {
-                flag_oob(status);
-              }
-            }
+            const int64_t key = *reinterpret_cast<const int64_t*>(tile_s + c_idx_off + st * (32 * 64));
+            const float val = to_f32(*reinterpret_cast<const T*>(tile_s + c_src_off + st * (32 * kSrcRow)));
+            const bool in_tensor = st * 32 + lane < valid_rows;
+            const bool in_range = static_cast<uint64_t>(key) < urows;
+            if (in_tensor && !in_range) flag_oob(status);
+            const bool use = in_tensor && in_range;
+            k = use ? static_cast<int>(key) : dummy;
+            v = use ? val : 0.f;
           };
           int k[2];
           float v[2];
           fetch(0, k[0], v[0]);
-          if (k[0] >= 0) tags[k[0] & (kWideTagSlots - 1)] = static_cast<unsigned char>(lane);
+          tags[k[0]] = static_cast<unsigned char>(lane);
 #pragma unroll
           for (int st = 0; st < kSteps; ++st) {
             const int cur = st & 1, nxt = cur ^ 1;
             if (st + 1 < kSteps) fetch(st + 1, k[nxt], v[nxt]);
             __syncwarp();  // the tags of step st are written
-            const unsigned winner = k[cur] >= 0 ? tags[k[cur] & (kWideTagSlots - 1)] : static_cast<unsigned>(lane);
+            const unsigned winner = tags[k[cur]];
             const bool lost = winner != static_cast<unsigned>(lane);
-            const float old = k[cur] >= 0 ? col[k[cur]] : 0.f;  // read ahead; used only by lanes that nothing clashes with
-            if (st + 1 < kSteps && k[nxt] >= 0) tags[k[nxt] & (kWideTagSlots - 1)] = static_cast<unsigned char>(lane);  // after this step's read-back, in program order
+            const float old = col[k[cur]];  // read ahead; used only by lanes that nothing clashes with
+            if (st + 1 < kSteps) tags[k[nxt]] = static_cast<unsigned char>(lane);  // after this step's read-back, in program order
             const unsigned losers = __ballot_sync(0xffffffffu, lost);
             if (losers == 0u) {
-              if (k[cur] >= 0) col[k[cur]] = old + v[cur];
+              col[k[cur]] = old + v[cur];
             } else {
               // All lanes that share a slot read the same tag: the one lane it names is not
               // lost, every other one is. So the lanes in a clash are exactly the losers and
@@ -415,7 +420,7 @@ scatter_add_strip_wide(const __grid_constant__ CUtensorMap map_idx, const __grid
               // after the other in lane order, which is source-row order.
               unsigned involved = losers | __reduce_or_sync(0xffffffffu, lost ? 1u << winner : 0u);
               if (__popc(involved) <= 8) {
-                if (k[cur] >= 0 && !((involved >> lane) & 1u)) col[k[cur]] = old + v[cur];
+                if (!((involved >> lane) & 1u)) col[k[cur]] = old + v[cur];
                 while (involved) {
                   const int l = __ffs(involved) - 1;
                   if (lane == l) col[k[cur]] += v[cur];
@@ -438,7 +443,7 @@ scatter_add_strip_wide(const __grid_constant__ CUtensorMap map_idx, const __grid
         const int r = id / kSegsPerRow, c0 = (id % kSegsPerRow) * kPerSeg;
         float f[kPerSeg];
 #pragma unroll
-        for (int c = 0; c < kPerSeg; ++c) f[c] = strip[(c0 + c) * rows + r];
+        for (int c = 0; c < kPerSeg; ++c) f[c] = strip[(c0 + c) * cstride + r];
         __stcs(reinterpret_cast<uint4*>(out_o + static_cast<int64_t>(r) * A.cols + c0), narrow<T>(f));
       }
       compute_warps_barrier();  // the strip is rewritten by the next item
@@ -1065,7 +1070,7 @@ static int launch_strip_wide(const void* self, const void* index, const void* sr
       CUDA_SUCCESS)
     return B200_EDRIVER;
   // ring + tag tables + the strip at its largest + barriers + room to align the ring to 1 KB
-  const size_t smem = static_cast<size_t>(kWideStages) * kWideTileRows * kWideCols * (8 + sizeof(T)) + 8 * kWideTagSlots + static_cast<size_t>(kWideMaxRows) * kWideCols * 4 + 128 + 1024;
+  const size_t smem = static_cast<size_t>(kWideStages) * kWideTileRows * kWideCols * (8 + sizeof(T)) + 8 * (kWideTagSlots + kWideDummies) + static_cast<size_t>(kWideMaxRows + kWideDummies) * kWideCols * 4 + 128 + 1024;
   const cudaError_t ae = cudaFuncSetAttribute(scatter_add_strip_wide<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (ae != cudaSuccess) { set_last_cuda_error(ae); return B200_ELAUNCH; }
   const int64_t items = A.outer * (A.cols / kWideCols);
