@@ -335,6 +335,7 @@ scatter_add_strip_wide(const __grid_constant__ CUtensorMap map_idx, const __grid
     float* col = strip + warp * cstride;
     const uint64_t urows = static_cast<uint64_t>(A.rows);
     const int dummy = rows + lane;  // where a lane with nothing to add "adds" zero: its own slot, so it never clashes
+    const uint32_t ring_a = smem_u32(ring), tags_a = smem_u32(tags), col_a = smem_u32(col);
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
@@ -379,40 +380,65 @@ scatter_add_strip_wide(const __grid_constant__ CUtensorMap map_idx, const __grid
             }
             break;
           }
-          const unsigned char* tile_s = ring + stage * kTile;
+          // shared-memory accesses of the step by 32-bit shared addresses (the ring, the tag table
+          // and the strip are carved out of one aligned buffer, which hides their address space
+          // from the compiler: generic accesses would cost 64-bit address arithmetic per access)
+          const uint32_t tile_a = ring_a + stage * kTile;
           const int valid_rows = static_cast<int>(A.idx_rows - static_cast<int64_t>(tile) * kWideTileRows);  // >= 128 except in the last tile
+          const bool ragged = valid_rows < kWideTileRows;
           constexpr int kSteps = kWideTileRows / 32;
+          unsigned oob = 0u;
           // Every lane always has a destination: a row past the end of the tensor, or an index
-          // out of range (reported), adds zero to the lane's own dummy element. The step below
-          // therefore has no per-lane conditions at all -- with two warps per scheduler the
-          // kernel runs at the speed of its instruction chain, and every `if (k >= 0)` cost a
-          // branch and its reconvergence bookkeeping.
+          // out of range (reported once per tile), adds zero to the lane's own dummy element.
+          // The step below therefore has no per-lane conditions at all -- with two warps per
+          // scheduler the kernel runs at the speed of its instruction chain, and every
+          // `if (k >= 0)` cost a branch and its reconvergence bookkeeping.
           auto fetch = [&](int st, int& k, float& v) {
-            const int64_t key = *reinterpret_cast<const int64_t*>(tile_s + c_idx_off + st * (32 * 64));
-            const float val = to_f32(*reinterpret_cast<const T*>(tile_s + c_src_off + st * (32 * kSrcRow)));
-            const bool in_tensor = st * 32 + lane < valid_rows;
-            const bool in_range = static_cast<uint64_t>(key) < urows;
-            if (in_tensor && !in_range) flag_oob(status);
+            uint32_t lo, hi;
+            asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(lo), "=r"(hi) : "r"(tile_a + c_idx_off + st * (32 * 64)));
+            float val;
+            if (sizeof(T) == 4) {
+              asm volatile("ld.shared.f32 %0, [%1];" : "=f"(val) : "r"(tile_a + c_src_off + st * (32 * kSrcRow)));
+            } else {
+              unsigned short raw;
+              asm volatile("ld.shared.u16 %0, [%1];" : "=h"(raw) : "r"(tile_a + c_src_off + st * (32 * kSrcRow)));
+              val = to_f32(*reinterpret_cast<const T*>(&raw));
+            }
+            const bool in_range = hi == 0u && lo < static_cast<uint32_t>(rows);
+            const bool in_tensor = !ragged || st * 32 + lane < valid_rows;
+            oob |= (in_tensor && !in_range) ? 1u : 0u;
             const bool use = in_tensor && in_range;
-            k = use ? static_cast<int>(key) : dummy;
+            k = use ? static_cast<int>(lo) : dummy;
             v = use ? val : 0.f;
           };
+          auto tag_put = [&](int k) { asm volatile("st.shared.u8 [%0], %1;" ::"r"(tags_a + k), "r"(lane) : "memory"); };
+          auto tag_get = [&](int k) {
+            uint32_t w;
+            asm volatile("ld.shared.u8 %0, [%1];" : "=r"(w) : "r"(tags_a + k) : "memory");
+            return w;
+          };
+          auto col_get = [&](int k) {
+            float f;
+            asm volatile("ld.shared.f32 %0, [%1];" : "=f"(f) : "r"(col_a + 4 * k) : "memory");
+            return f;
+          };
+          auto col_put = [&](int k, float f) { asm volatile("st.shared.f32 [%0], %1;" ::"r"(col_a + 4 * k), "f"(f) : "memory"); };
           int k[2];
           float v[2];
           fetch(0, k[0], v[0]);
-          tags[k[0]] = static_cast<unsigned char>(lane);
+          tag_put(k[0]);
 #pragma unroll
           for (int st = 0; st < kSteps; ++st) {
             const int cur = st & 1, nxt = cur ^ 1;
             if (st + 1 < kSteps) fetch(st + 1, k[nxt], v[nxt]);
             __syncwarp();  // the tags of step st are written
-            const unsigned winner = tags[k[cur]];
+            const unsigned winner = tag_get(k[cur]);
             const bool lost = winner != static_cast<unsigned>(lane);
-            const float old = col[k[cur]];  // read ahead; used only by lanes that nothing clashes with
-            if (st + 1 < kSteps) tags[k[nxt]] = static_cast<unsigned char>(lane);  // after this step's read-back, in program order
+            const float old = col_get(k[cur]);  // read ahead; used only by lanes that nothing clashes with
+            if (st + 1 < kSteps) tag_put(k[nxt]);  // after this step's read-back, in program order
             const unsigned losers = __ballot_sync(0xffffffffu, lost);
             if (losers == 0u) {
-              col[k[cur]] = old + v[cur];
+              col_put(k[cur], old + v[cur]);
             } else {
               // All lanes that share a slot read the same tag: the one lane it names is not
               // lost, every other one is. So the lanes in a clash are exactly the losers and
@@ -420,10 +446,10 @@ scatter_add_strip_wide(const __grid_constant__ CUtensorMap map_idx, const __grid
               // after the other in lane order, which is source-row order.
               unsigned involved = losers | __reduce_or_sync(0xffffffffu, lost ? 1u << winner : 0u);
               if (__popc(involved) <= 8) {
-                if (!((involved >> lane) & 1u)) col[k[cur]] = old + v[cur];
+                if (!((involved >> lane) & 1u)) col_put(k[cur], old + v[cur]);
                 while (involved) {
                   const int l = __ffs(involved) - 1;
-                  if (lane == l) col[k[cur]] += v[cur];
+                  if (lane == l) col_put(k[cur], col_get(k[cur]) + v[cur]);
                   involved &= involved - 1;
                   __syncwarp();
                 }
@@ -432,6 +458,7 @@ scatter_add_strip_wide(const __grid_constant__ CUtensorMap map_idx, const __grid
               }
             }
           }
+          if (__any_sync(0xffffffffu, oob != 0u) && lane == 0) flag_oob(status);
           __syncwarp();                                   // every lane is done with the tile ...
           if (lane == 0) mbar_arrive(empty_bar(stage));   // ... and this warp hands its share of the slot back
           if (++stage == kWideStages) { stage = 0; phase ^= 1u; }
