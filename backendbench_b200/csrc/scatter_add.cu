@@ -263,6 +263,7 @@ constexpr int kWideComputeThreads = 256;  // eight warps: one column each
 constexpr int kWideThreads = 288;         // ... and the warp that feeds the ring
 constexpr int kWideTagSlots = 4096;       // one table per warp, exact up to 4096 destinations ...
 constexpr int kWideDummies = 32;          // ... plus a slot (and a strip element) per lane for rows that have nothing to add
+constexpr int kWideSelfRows = 256;        // rows of the destination strip per ring slot on its way in (the largest TMA box)
 constexpr int kWideStages = 5;            // 12 KB tiles (fp32): 48 KB of source rows in flight per SM
 constexpr int kWideMaxRows = 4096;
 constexpr uint64_t kWideWaitLimitNs = 2000000000ull;
@@ -271,7 +272,7 @@ __device__ __forceinline__ void compute_warps_barrier() { asm volatile("bar.sync
 
 template <typename T>
 __global__ void __launch_bounds__(kWideThreads, 1)
-scatter_add_strip_wide(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__ CUtensorMap map_src, const T* __restrict__ self, T* __restrict__ out, StripArgs A, uint32_t* status) {
+scatter_add_strip_wide(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__ CUtensorMap map_src, const __grid_constant__ CUtensorMap map_self, T* __restrict__ out, StripArgs A, uint32_t* status) {
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem_raw = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023));  // the swizzle patterns repeat every 512 bytes
   constexpr int kIdxTile = kWideTileRows * kWideCols * 8;                            // 8 KB: [row][4 chunks of 2 indices]
@@ -293,6 +294,9 @@ scatter_add_strip_wide(const __grid_constant__ CUtensorMap map_idx, const __grid
   const int64_t nstrips = A.cols / kWideCols;
   const int ntiles = static_cast<int>((A.idx_rows + kWideTileRows - 1) / kWideTileRows);
   constexpr int kSegsPerRow = kSrcRow / 16, kPerSeg = 16 / static_cast<int>(sizeof(T));  // 16-byte segments of a destination row
+  constexpr int kSelfBytes = kWideSelfRows * kSrcRow;  // a slab of the destination strip fits a ring slot
+  static_assert(kSelfBytes <= kTile, "a slab of the destination strip travels in one ring slot");
+  const int nslabs = (static_cast<int>(A.rows) + kWideSelfRows - 1) / kWideSelfRows;
 
   if (tid == 0) {
     for (int s = 0; s < kWideStages; ++s) {
@@ -312,8 +316,14 @@ scatter_add_strip_wide(const __grid_constant__ CUtensorMap map_idx, const __grid
       bool ok = true;
       for (int64_t item = blockIdx.x; item < A.outer * nstrips && ok; item += gridDim.x) {
         const int64_t o = item / nstrips, j0 = (item - o * nstrips) * kWideCols;
+        for (int slab = 0; slab < nslabs && ok; ++slab) {  // self[:, j0 : j0 + 8], 256 rows per slot
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, kWideWaitLimitNs)) { ok = false; break; }
+          mbar_expect_tx(full_bar(stage), kSelfBytes);
+          tma_load_3d(smem_u32(ring) + stage * kTile, &map_self, full_bar(stage), static_cast<int>(j0), slab * kWideSelfRows, static_cast<int>(o));
+          if (++stage == kWideStages) { stage = 0; phase ^= 1u; }
+        }
         if (!(j0 < A.idx_cols && o < A.idx_outer && ntiles > 0)) continue;
-        for (int tile = 0; tile < ntiles; ++tile) {
+        for (int tile = 0; tile < ntiles && ok; ++tile) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, kWideWaitLimitNs)) { ok = false; break; }
           const uint32_t dst = smem_u32(ring) + stage * kTile;
           mbar_expect_tx(full_bar(stage), kTile);  // a box counts in full, rows past the end of the tensor arrive as zeros
@@ -333,37 +343,48 @@ scatter_add_strip_wide(const __grid_constant__ CUtensorMap map_idx, const __grid
     const int c_idx_off = lane * 64 + (((warp >> 1) ^ ((lane >> 1) & 3)) << 4) + (warp & 1) * 8;
     const int c_src_off = kIdxTile + lane * kSrcRow + (kSrcChunks == 2 ? (((warp >> 2) ^ ((lane >> 2) & 1)) << 4) : 0) + (warp & (kPerSeg - 1)) * static_cast<int>(sizeof(T));
     float* col = strip + warp * cstride;
-    const uint64_t urows = static_cast<uint64_t>(A.rows);
     const int dummy = rows + lane;  // where a lane with nothing to add "adds" zero: its own slot, so it never clashes
-    const uint32_t ring_a = smem_u32(ring), tags_a = smem_u32(tags), col_a = smem_u32(col);
+    const uint32_t ring_a = smem_u32(ring), tags_a = smem_u32(tags), col_a = smem_u32(col), strip_a = smem_u32(strip);
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
     for (int64_t item = blockIdx.x; item < A.outer * nstrips; item += gridDim.x) {
       const int64_t o = item / nstrips, j0 = (item - o * nstrips) * kWideCols;
-      const T* self_o = self + o * A.rows * A.cols + j0;
       T* out_o = out + o * A.rows * A.cols + j0;
       const bool active = j0 < A.idx_cols && o < A.idx_outer && ntiles > 0;
 
-      // ---- stage self[:, j0 : j0 + 8] column-major as fp32
-      for (int q0 = 0; q0 < rows * kSegsPerRow; q0 += kWideComputeThreads * 16) {
-        uint4 seg[16];
-#pragma unroll
-        for (int u = 0; u < 16; ++u) {
-          const int id = q0 + u * kWideComputeThreads + tid;
-          if (id < rows * kSegsPerRow) seg[u] = ld_wide(reinterpret_cast<const uint4*>(self_o + static_cast<int64_t>(id / kSegsPerRow) * A.cols + (id % kSegsPerRow) * kPerSeg));
+      // ---- self[:, j0 : j0 + 8] arrives through the ring, 256 rows per slot (the producer has
+      // the first slabs under way while the previous strip is still being written back), and
+      // is turned column-major as fp32: thread t takes row t of the slab, so that the 32 lanes
+      // of a warp store to 32 adjacent rows of one column
+      for (int slab = 0; slab < nslabs && ok; ++slab) {
+        int got = 0;
+        if (lane == 0) got = mbar_wait(full_bar(stage), phase, abort_flag, kWideWaitLimitNs) ? 1 : 0;
+        got = __shfl_sync(0xffffffffu, got, 0);
+        if (!got) {
+          ok = false;
+          if (lane == 0) {
+            *abort_flag = 1u;
+            if (status) atomicOr(status, B200_DEV_WAIT_TIMEOUT);
+          }
+          break;
         }
+        const uint32_t slab_a = ring_a + stage * kTile + tid * kSrcRow;
+        const int r = slab * kWideSelfRows + tid;
 #pragma unroll
-        for (int u = 0; u < 16; ++u) {
-          const int id = q0 + u * kWideComputeThreads + tid;
-          if (id < rows * kSegsPerRow) {
-            float f[kPerSeg];
-            widen<T>(seg[u], f);
-            const int r = id / kSegsPerRow, c0 = (id % kSegsPerRow) * kPerSeg;
+        for (int h = 0; h < kSegsPerRow; ++h) {
+          uint4 seg;
+          asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(seg.x), "=r"(seg.y), "=r"(seg.z), "=r"(seg.w) : "r"(slab_a + h * 16));
+          float f[kPerSeg];
+          widen<T>(seg, f);
+          if (r < rows) {
 #pragma unroll
-            for (int c = 0; c < kPerSeg; ++c) strip[(c0 + c) * cstride + r] = f[c];
+            for (int c = 0; c < kPerSeg; ++c) asm volatile("st.shared.f32 [%0], %1;" ::"r"(strip_a + 4u * static_cast<uint32_t>((h * kPerSeg + c) * cstride + r)), "f"(f[c]) : "memory");
           }
         }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty_bar(stage));
+        if (++stage == kWideStages) { stage = 0; phase ^= 1u; }
       }
       compute_warps_barrier();  // the strip is staged
 
@@ -1096,13 +1117,23 @@ static int launch_strip_wide(const void* self, const void* index, const void* sr
   if (encode_fn()(&map_src, vt, 3, const_cast<void*>(src), dims, sstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, vs, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) !=
       CUDA_SUCCESS)
     return B200_EDRIVER;
+  alignas(64) CUtensorMap map_self;  // the destination strip on its way in: 8 columns x 256 rows, rows as they lie
+  {
+    const cuuint64_t ddims[3] = {static_cast<cuuint64_t>(A.cols), static_cast<cuuint64_t>(A.rows), static_cast<cuuint64_t>(A.outer)};
+    const cuuint64_t dstr[2] = {static_cast<cuuint64_t>(A.cols) * es, static_cast<cuuint64_t>(A.rows) * static_cast<cuuint64_t>(A.cols) * es};
+    const cuuint32_t dbox[3] = {kWideCols, kWideSelfRows, 1};
+    if (dstr[0] % 16 || (reinterpret_cast<uintptr_t>(self) & 15)) return B200_EALIGN;
+    if (encode_fn()(&map_self, vt, 3, const_cast<void*>(self), ddims, dstr, dbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return B200_EDRIVER;
+  }
   // ring + tag tables + the strip at its largest + barriers + room to align the ring to 1 KB
   const size_t smem = static_cast<size_t>(kWideStages) * kWideTileRows * kWideCols * (8 + sizeof(T)) + 8 * (kWideTagSlots + kWideDummies) + static_cast<size_t>(kWideMaxRows + kWideDummies) * kWideCols * 4 + 128 + 1024;
   const cudaError_t ae = cudaFuncSetAttribute(scatter_add_strip_wide<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (ae != cudaSuccess) { set_last_cuda_error(ae); return B200_ELAUNCH; }
   const int64_t items = A.outer * (A.cols / kWideCols);
   const int grid = static_cast<int>(items < 2LL * kNumSMs ? items : 2LL * kNumSMs);
-  scatter_add_strip_wide<T><<<grid, kWideThreads, smem, st>>>(map_idx, map_src, static_cast<const T*>(self), static_cast<T*>(out), A, status);
+  scatter_add_strip_wide<T><<<grid, kWideThreads, smem, st>>>(map_idx, map_src, map_self, static_cast<T*>(out), A, status);
   return check_launch();
 }
 
