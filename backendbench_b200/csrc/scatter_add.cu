@@ -264,6 +264,7 @@ constexpr int kWideThreads = 288;         // ... and the warp that feeds the rin
 constexpr int kWideTagSlots = 4096;       // one table per warp, exact up to 4096 destinations ...
 constexpr int kWideDummies = 32;          // ... plus a slot (and a strip element) per lane for rows that have nothing to add
 constexpr int kWideSelfRows = 256;        // rows of the destination strip per ring slot on its way in (the largest TMA box)
+constexpr int kWideOutRows = 128;         // rows of the destination strip per tiled store on its way out
 constexpr int kWideStages = 5;            // 12 KB tiles (fp32): 48 KB of source rows in flight per SM
 constexpr int kWideMaxRows = 4096;
 constexpr uint64_t kWideWaitLimitNs = 2000000000ull;
@@ -272,7 +273,7 @@ __device__ __forceinline__ void compute_warps_barrier() { asm volatile("bar.sync
 
 template <typename T>
 __global__ void __launch_bounds__(kWideThreads, 1)
-scatter_add_strip_wide(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__ CUtensorMap map_src, const __grid_constant__ CUtensorMap map_self, T* __restrict__ out, StripArgs A, uint32_t* status) {
+scatter_add_strip_wide(const __grid_constant__ CUtensorMap map_idx, const __grid_constant__ CUtensorMap map_src, const __grid_constant__ CUtensorMap map_self, const __grid_constant__ CUtensorMap map_out, StripArgs A, uint32_t* status) {
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem_raw = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023));  // the swizzle patterns repeat every 512 bytes
   constexpr int kIdxTile = kWideTileRows * kWideCols * 8;                            // 8 KB: [row][4 chunks of 2 indices]
@@ -296,6 +297,7 @@ scatter_add_strip_wide(const __grid_constant__ CUtensorMap map_idx, const __grid
   constexpr int kSegsPerRow = kSrcRow / 16, kPerSeg = 16 / static_cast<int>(sizeof(T));  // 16-byte segments of a destination row
   constexpr int kSelfBytes = kWideSelfRows * kSrcRow;  // a slab of the destination strip fits a ring slot
   static_assert(kSelfBytes <= kTile, "a slab of the destination strip travels in one ring slot");
+  static_assert(8 * kWideOutRows * 32 <= 8 * (kWideTagSlots + kWideDummies), "the blocks on their way out are staged in the tag tables");
   const int nslabs = (static_cast<int>(A.rows) + kWideSelfRows - 1) / kWideSelfRows;
 
   if (tid == 0) {
@@ -345,12 +347,12 @@ scatter_add_strip_wide(const __grid_constant__ CUtensorMap map_idx, const __grid
     float* col = strip + warp * cstride;
     const int dummy = rows + lane;  // where a lane with nothing to add "adds" zero: its own slot, so it never clashes
     const uint32_t ring_a = smem_u32(ring), tags_a = smem_u32(tags), col_a = smem_u32(col), strip_a = smem_u32(strip);
+    const uint32_t out_stage_a = ring_a + kWideStages * kTile + warp * (kWideOutRows * 32);  // 4 KB per warp inside the tag tables
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
     for (int64_t item = blockIdx.x; item < A.outer * nstrips; item += gridDim.x) {
       const int64_t o = item / nstrips, j0 = (item - o * nstrips) * kWideCols;
-      T* out_o = out + o * A.rows * A.cols + j0;
       const bool active = j0 < A.idx_cols && o < A.idx_outer && ntiles > 0;
 
       // ---- self[:, j0 : j0 + 8] arrives through the ring, 256 rows per slot (the producer has
@@ -486,16 +488,36 @@ scatter_add_strip_wide(const __grid_constant__ CUtensorMap map_idx, const __grid
         }
       }
       compute_warps_barrier();  // every column of the strip is final
-      // ---- write the strip back, rounding once
-      for (int id = tid; id < rows * kSegsPerRow; id += kWideComputeThreads) {
-        const int r = id / kSegsPerRow, c0 = (id % kSegsPerRow) * kPerSeg;
-        float f[kPerSeg];
+      // ---- write the strip back, rounding once: every warp turns blocks of 128 rows back into
+      // rows of 8 values in its own 4 KB of the (now idle) tag tables and hands each block to
+      // the copy engine, which clips at the last row; no CTA barrier, the warp only waits for
+      // the engine to have read its previous block
+      for (int r0 = warp * kWideOutRows; r0 < rows; r0 += 8 * kWideOutRows) {
+        if (lane == 0) tma_store_wait_read();
+        __syncwarp();
 #pragma unroll
-        for (int c = 0; c < kPerSeg; ++c) f[c] = strip[(c0 + c) * cstride + r];
-        __stcs(reinterpret_cast<uint4*>(out_o + static_cast<int64_t>(r) * A.cols + c0), narrow<T>(f));
+        for (int i = 0; i < kWideOutRows / 32; ++i) {
+          const int rr = i * 32 + lane, r = r0 + rr < rows ? r0 + rr : rows - 1;  // rows past the end are clipped by the store
+          float f[kWideCols];
+#pragma unroll
+          for (int c = 0; c < kWideCols; ++c) asm volatile("ld.shared.f32 %0, [%1];" : "=f"(f[c]) : "r"(strip_a + 4u * static_cast<uint32_t>(c * cstride + r)) : "memory");
+#pragma unroll
+          for (int h = 0; h < kSegsPerRow; ++h) {
+            const uint4 seg = narrow<T>(f + h * kPerSeg);
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(out_stage_a + rr * kSrcRow + h * 16), "r"(seg.x), "r"(seg.y), "r"(seg.z), "r"(seg.w) : "memory");
+          }
+        }
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_3d(&map_out, out_stage_a, static_cast<int>(j0), r0, static_cast<int>(o));
+          tma_store_commit();
+        }
       }
+      if (lane == 0) tma_store_wait_read();  // the tag tables are free again
       compute_warps_barrier();  // the strip is rewritten by the next item
     }
+    if (lane == 0) tma_store_wait_all();
   }
   __syncthreads();
   if (*abort_flag) {
@@ -1127,13 +1149,23 @@ static int launch_strip_wide(const void* self, const void* index, const void* sr
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return B200_EDRIVER;
   }
+  alignas(64) CUtensorMap map_out;  // ... and on its way out: 8 columns x 128 rows
+  {
+    const cuuint64_t ddims[3] = {static_cast<cuuint64_t>(A.cols), static_cast<cuuint64_t>(A.rows), static_cast<cuuint64_t>(A.outer)};
+    const cuuint64_t dstr[2] = {static_cast<cuuint64_t>(A.cols) * es, static_cast<cuuint64_t>(A.rows) * static_cast<cuuint64_t>(A.cols) * es};
+    const cuuint32_t dbox[3] = {kWideCols, kWideOutRows, 1};
+    if (reinterpret_cast<uintptr_t>(out) & 15) return B200_EALIGN;
+    if (encode_fn()(&map_out, vt, 3, out, ddims, dstr, dbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) !=
+        CUDA_SUCCESS)
+      return B200_EDRIVER;
+  }
   // ring + tag tables + the strip at its largest + barriers + room to align the ring to 1 KB
   const size_t smem = static_cast<size_t>(kWideStages) * kWideTileRows * kWideCols * (8 + sizeof(T)) + 8 * (kWideTagSlots + kWideDummies) + static_cast<size_t>(kWideMaxRows + kWideDummies) * kWideCols * 4 + 128 + 1024;
   const cudaError_t ae = cudaFuncSetAttribute(scatter_add_strip_wide<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (ae != cudaSuccess) { set_last_cuda_error(ae); return B200_ELAUNCH; }
   const int64_t items = A.outer * (A.cols / kWideCols);
   const int grid = static_cast<int>(items < 2LL * kNumSMs ? items : 2LL * kNumSMs);
-  scatter_add_strip_wide<T><<<grid, kWideThreads, smem, st>>>(map_idx, map_src, map_self, static_cast<T*>(out), A, status);
+  scatter_add_strip_wide<T><<<grid, kWideThreads, smem, st>>>(map_idx, map_src, map_self, map_out, A, status);
   return check_launch();
 }
 
