@@ -264,7 +264,8 @@ constexpr int kWideThreads = 288;         // ... and the warp that feeds the rin
 constexpr int kWideTagSlots = 4096;       // one table per warp, exact up to 4096 destinations ...
 constexpr int kWideDummies = 32;          // ... plus a slot (and a strip element) per lane for rows that have nothing to add
 constexpr int kWideSelfRows = 256;        // rows of the destination strip per ring slot on its way in (the largest TMA box)
-constexpr int kWideOutRows = 128;         // rows of the destination strip per tiled store on its way out
+constexpr int kWideOutRows = 32;          // rows of the destination strip per tiled store on its way out: a warp's share of a slab
+constexpr int kWideOutBlocks = 4;         // staging blocks per warp for those stores
 constexpr int kWideStages = 5;            // 12 KB tiles (fp32): 48 KB of source rows in flight per SM
 constexpr int kWideMaxRows = 4096;
 constexpr uint64_t kWideWaitLimitNs = 2000000000ull;
@@ -297,7 +298,8 @@ scatter_add_strip_wide(const __grid_constant__ CUtensorMap map_idx, const __grid
   constexpr int kSegsPerRow = kSrcRow / 16, kPerSeg = 16 / static_cast<int>(sizeof(T));  // 16-byte segments of a destination row
   constexpr int kSelfBytes = kWideSelfRows * kSrcRow;  // a slab of the destination strip fits a ring slot
   static_assert(kSelfBytes <= kTile, "a slab of the destination strip travels in one ring slot");
-  static_assert(8 * kWideOutRows * 32 <= 8 * (kWideTagSlots + kWideDummies), "the blocks on their way out are staged in the tag tables");
+  static_assert(8 * kWideOutBlocks * kWideOutRows * 32 <= 8 * (kWideTagSlots + kWideDummies), "the blocks on their way out are staged in the tag tables");
+  static_assert(kWideSelfRows == kWideComputeThreads && kWideOutRows == 32, "thread t owns row t of every slab, on the way in and on the way out");
   const int nslabs = (static_cast<int>(A.rows) + kWideSelfRows - 1) / kWideSelfRows;
 
   if (tid == 0) {
@@ -347,7 +349,37 @@ scatter_add_strip_wide(const __grid_constant__ CUtensorMap map_idx, const __grid
     float* col = strip + warp * cstride;
     const int dummy = rows + lane;  // where a lane with nothing to add "adds" zero: its own slot, so it never clashes
     const uint32_t ring_a = smem_u32(ring), tags_a = smem_u32(tags), col_a = smem_u32(col), strip_a = smem_u32(strip);
-    const uint32_t out_stage_a = ring_a + kWideStages * kTile + warp * (kWideOutRows * 32);  // 4 KB per warp inside the tag tables
+    const uint32_t out_stage_a = ring_a + kWideStages * kTile + warp * (kWideOutBlocks * kWideOutRows * 32);  // four blocks of 32 rows per warp inside the tag tables
+    int out_parity = 0;
+    // Rows r0 .. r0 + 31 of the finished strip (this warp's share of a slab) leave for
+    // out[po, r0 .., pj0 : pj0 + 8], rounded once: back to rows of 8 values in one of the warp's
+    // four staging blocks inside the tag tables (idle between tile loops), then one tiled store,
+    // which clips at the last row. The warp only waits for the engine to have read the block it
+    // staged four stores ago.
+    auto store_rows = [&](int r0, int64_t pj0, int64_t po) {
+      if (r0 >= rows) return;
+      if (lane == 0) tma_store_wait_read_but<kWideOutBlocks - 1>();
+      __syncwarp();
+      const int r = r0 + lane < rows ? r0 + lane : rows - 1;  // rows past the end are clipped by the store
+      const uint32_t block_a = out_stage_a + out_parity * (kWideOutRows * 32);
+      float f[kWideCols];
+#pragma unroll
+      for (int c = 0; c < kWideCols; ++c) asm volatile("ld.shared.f32 %0, [%1];" : "=f"(f[c]) : "r"(strip_a + 4u * static_cast<uint32_t>(c * cstride + r)) : "memory");
+#pragma unroll
+      for (int h = 0; h < kSegsPerRow; ++h) {
+        const uint4 seg = narrow<T>(f + h * kPerSeg);
+        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(block_a + lane * kSrcRow + h * 16), "r"(seg.x), "r"(seg.y), "r"(seg.z), "r"(seg.w) : "memory");
+      }
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_3d(&map_out, block_a, static_cast<int>(pj0), r0, static_cast<int>(po));
+        tma_store_commit();
+      }
+      out_parity = (out_parity + 1) & (kWideOutBlocks - 1);
+    };
+    bool have_prev = false;
+    int64_t prev_j0 = 0, prev_o = 0;
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
@@ -355,11 +387,13 @@ scatter_add_strip_wide(const __grid_constant__ CUtensorMap map_idx, const __grid
       const int64_t o = item / nstrips, j0 = (item - o * nstrips) * kWideCols;
       const bool active = j0 < A.idx_cols && o < A.idx_outer && ntiles > 0;
 
-      // ---- self[:, j0 : j0 + 8] arrives through the ring, 256 rows per slot (the producer has
-      // the first slabs under way while the previous strip is still being written back), and
-      // is turned column-major as fp32: thread t takes row t of the slab, so that the 32 lanes
-      // of a warp store to 32 adjacent rows of one column
+      // ---- one pass over the strip, 256 rows at a time: the previous item's result leaves, and
+      // self[:, j0 : j0 + 8] of this item, which arrives through the ring (256 rows per slot),
+      // takes its place column-major as fp32. Thread t owns row t of every slab in both
+      // directions, so nothing orders the two but the thread's own program; the 32 lanes of a
+      // warp read and write 32 adjacent rows of one column.
       for (int slab = 0; slab < nslabs && ok; ++slab) {
+        if (have_prev) store_rows(slab * kWideSelfRows + warp * 32, prev_j0, prev_o);
         int got = 0;
         if (lane == 0) got = mbar_wait(full_bar(stage), phase, abort_flag, kWideWaitLimitNs) ? 1 : 0;
         got = __shfl_sync(0xffffffffu, got, 0);
@@ -388,7 +422,8 @@ scatter_add_strip_wide(const __grid_constant__ CUtensorMap map_idx, const __grid
         if (lane == 0) mbar_arrive(empty_bar(stage));
         if (++stage == kWideStages) { stage = 0; phase ^= 1u; }
       }
-      compute_warps_barrier();  // the strip is staged
+      if (lane == 0) tma_store_wait_read();  // the tag tables are free again
+      compute_warps_barrier();               // the strip is staged
 
       if (active) {
         for (int tile = 0; tile < ntiles && ok; ++tile) {
@@ -488,35 +523,12 @@ scatter_add_strip_wide(const __grid_constant__ CUtensorMap map_idx, const __grid
         }
       }
       compute_warps_barrier();  // every column of the strip is final
-      // ---- write the strip back, rounding once: every warp turns blocks of 128 rows back into
-      // rows of 8 values in its own 4 KB of the (now idle) tag tables and hands each block to
-      // the copy engine, which clips at the last row; no CTA barrier, the warp only waits for
-      // the engine to have read its previous block
-      for (int r0 = warp * kWideOutRows; r0 < rows; r0 += 8 * kWideOutRows) {
-        if (lane == 0) tma_store_wait_read();
-        __syncwarp();
-#pragma unroll
-        for (int i = 0; i < kWideOutRows / 32; ++i) {
-          const int rr = i * 32 + lane, r = r0 + rr < rows ? r0 + rr : rows - 1;  // rows past the end are clipped by the store
-          float f[kWideCols];
-#pragma unroll
-          for (int c = 0; c < kWideCols; ++c) asm volatile("ld.shared.f32 %0, [%1];" : "=f"(f[c]) : "r"(strip_a + 4u * static_cast<uint32_t>(c * cstride + r)) : "memory");
-#pragma unroll
-          for (int h = 0; h < kSegsPerRow; ++h) {
-            const uint4 seg = narrow<T>(f + h * kPerSeg);
-            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(out_stage_a + rr * kSrcRow + h * 16), "r"(seg.x), "r"(seg.y), "r"(seg.z), "r"(seg.w) : "memory");
-          }
-        }
-        fence_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          tma_store_3d(&map_out, out_stage_a, static_cast<int>(j0), r0, static_cast<int>(o));
-          tma_store_commit();
-        }
-      }
-      if (lane == 0) tma_store_wait_read();  // the tag tables are free again
-      compute_warps_barrier();  // the strip is rewritten by the next item
+      have_prev = true;
+      prev_j0 = j0;
+      prev_o = o;
     }
+    if (have_prev)  // the last strip of this CTA
+      for (int slab = 0; slab < nslabs; ++slab) store_rows(slab * kWideSelfRows + warp * 32, prev_j0, prev_o);
     if (lane == 0) tma_store_wait_all();
   }
   __syncthreads();
@@ -1149,7 +1161,7 @@ static int launch_strip_wide(const void* self, const void* index, const void* sr
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return B200_EDRIVER;
   }
-  alignas(64) CUtensorMap map_out;  // ... and on its way out: 8 columns x 128 rows
+  alignas(64) CUtensorMap map_out;  // ... and on its way out: 8 columns x 32 rows
   {
     const cuuint64_t ddims[3] = {static_cast<cuuint64_t>(A.cols), static_cast<cuuint64_t>(A.rows), static_cast<cuuint64_t>(A.outer)};
     const cuuint64_t dstr[2] = {static_cast<cuuint64_t>(A.cols) * es, static_cast<cuuint64_t>(A.rows) * static_cast<cuuint64_t>(A.cols) * es};
@@ -1164,7 +1176,7 @@ static int launch_strip_wide(const void* self, const void* index, const void* sr
   const cudaError_t ae = cudaFuncSetAttribute(scatter_add_strip_wide<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (ae != cudaSuccess) { set_last_cuda_error(ae); return B200_ELAUNCH; }
   const int64_t items = A.outer * (A.cols / kWideCols);
-  const int grid = static_cast<int>(items < 2LL * kNumSMs ? items : 2LL * kNumSMs);
+  const int grid = static_cast<int>(items < kNumSMs ? items : kNumSMs);  // one CTA per SM: a strip leaves while the next one comes in
   scatter_add_strip_wide<T><<<grid, kWideThreads, smem, st>>>(map_idx, map_src, map_self, map_out, A, status);
   return check_launch();
 }
