@@ -11,6 +11,10 @@ int gemm_tc_dispatch(const void* A, const void* B, const void* bias, void* C, in
                      int64_t sBb, int64_t sBk, int64_t sBn, int64_t sbm, int64_t sbn, double alpha, double beta, int dtype, uint32_t* status, cudaStream_t st,
                      uint64_t wait_probe_limit_ns = 0, bool allow_pair = true);
 
+int64_t gemm_tc_splitk_scratch_bytes(int64_t batch, int64_t M, int64_t N, int64_t K);
+int gemm_tc_splitk_dispatch(const void* A, const void* B, const void* bias, void* C, int64_t M, int64_t N, int64_t K, int64_t sAm, int64_t sAk, int64_t sBk, int64_t sBn, int64_t sbm,
+                            int64_t sbn, double alpha, double beta, int dtype, void* scratch, int64_t scratch_bytes, uint32_t* status, cudaStream_t st);
+
 int64_t gemm_f32_split_scratch_bytes(int64_t batch, int64_t M, int64_t N, int64_t K);
 bool gemm_f32_split_eligible(int64_t batch, int64_t M, int64_t N, int64_t K);
 int gemm_f32_split_dispatch(const void* A, const void* B, const void* bias, void* C, int64_t batch, int64_t M, int64_t N, int64_t K, int64_t sAb, int64_t sAm, int64_t sAk, int64_t sBb,
@@ -73,4 +77,20 @@ extern "C" int b200_gemm_f32(const void* A, const void* B, const void* bias, voi
   if (K == 0 || !gemm_f32_split_eligible(batch, M, N, K)) return b200_gemm(A, B, bias, C, batch, M, N, K, sAb, sAm, sAk, sBb, sBk, sBn, sbm, sbn, alpha, beta, B200_F32, status, stream);
   if (!A || !B || !C) return B200_EINVAL;
   return gemm_f32_split_dispatch(A, B, bias, C, batch, M, N, K, sAb, sAm, sAk, sBb, sBk, sBn, sbm, sbn, alpha, beta, scratch, scratch_bytes, status, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int64_t b200_gemm_splitk_scratch_bytes(const void* A, const void* B, const void* C, int64_t batch, int64_t M, int64_t N, int64_t K, int64_t sAb, int64_t sAm, int64_t sAk,
+                                                  int64_t sBb, int64_t sBk, int64_t sBn, int dtype) {
+  if (batch != 1 || M < 1 || N < 1 || K < 1) return 0;
+  if (!gemm_tc_eligible(batch, M, N, K, sAb, sAm, sAk, sBb, sBk, sBn, dtype, A, B, C)) return 0;
+  return gemm_tc_splitk_scratch_bytes(batch, M, N, K);
+}
+
+extern "C" int b200_gemm_splitk(const void* A, const void* B, const void* bias, void* C, int64_t batch, int64_t M, int64_t N, int64_t K, int64_t sAb, int64_t sAm, int64_t sAk,
+                                int64_t sBb, int64_t sBk, int64_t sBn, int64_t sbm, int64_t sbn, double alpha, double beta, int dtype, void* scratch, int64_t scratch_bytes,
+                                uint32_t* status, void* stream) {
+  // anything the split does not serve (see b200_gemm_splitk_scratch_bytes) is an ordinary product
+  if (b200_gemm_splitk_scratch_bytes(A, B, C, batch, M, N, K, sAb, sAm, sAk, sBb, sBk, sBn, dtype) == 0)
+    return b200_gemm(A, B, bias, C, batch, M, N, K, sAb, sAm, sAk, sBb, sBk, sBn, sbm, sbn, alpha, beta, dtype, status, stream);
+  return gemm_tc_splitk_dispatch(A, B, bias, C, M, N, K, sAm, sAk, sBk, sBn, sbm, sbn, alpha, beta, dtype, scratch, scratch_bytes, status, static_cast<cudaStream_t>(stream));
 }

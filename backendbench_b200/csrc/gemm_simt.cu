@@ -8,6 +8,9 @@
 // no atomics: the result does not depend on scheduling).
 #include <cooperative_groups.h>
 
+#include <cstdlib>
+#include <type_traits>
+
 #include "b200_common.cuh"
 
 namespace b200 {
@@ -24,19 +27,51 @@ struct GemmArgs {
   int64_t kchunk;        // K elements per CTA of the cluster, a multiple of kTK
 };
 
+// Copies of 4 or 16 bytes global -> shared that complete in the background. `bytes` of the
+// source are read (0 .. size), the rest of the destination is filled with zeros.
+__device__ __forceinline__ void cp_async4_zfill(void* smem_dst, const void* gsrc, bool valid) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))), "l"(gsrc), "r"(valid ? 4 : 0) : "memory");
+}
+__device__ __forceinline__ void cp_async16_zfill(void* smem_dst, const void* gsrc, int bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))), "l"(gsrc), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// K slices in flight per CTA for fp32 operands (16-bit operands go through registers, one
+// slice ahead: they are converted on the way into shared memory)
+template <typename T, int kTM, int kTN> struct SimtStages { static constexpr int value = 1; };
+template <int kTM, int kTN> struct SimtStages<float, kTM, kTN> { static constexpr int value = (kTM + kTN > 192) ? 2 : 4; };
+
 // TM x TN outputs per CTA (256 threads, (TM/16) x (TN/16) per thread), 16-deep K slices.
-// The next slice is fetched from global memory into registers while the current one is
-// multiplied out of shared memory, so one barrier pair per slice is the only serialisation.
+// fp32 operands: the slices arrive through a ring of `cp.async` stages (4 for the small
+// tiles, 2 for 128 x 128), 16 bytes per copy where the operand is contiguous along the
+// tile's row of shared memory and aligned, 4 bytes otherwise, zero-filled past the edges; one
+// barrier per slice. A CTA that walked K one global-memory round trip per slice took 1.5 us a
+// slice (21 x 1024 x 256 in 64 batches: 98 us). 16-bit operands: the next slice is fetched
+// into registers while the current one is multiplied out of shared memory.
 // Tile shapes: 128x128 for large problems, 64x64 / 128x32 / 32x128 when M or N is small.
 // KSPLIT: launched as clusters of g.ksplit CTAs along z; CTA s of a cluster contracts the K
 // range [s * kchunk, (s + 1) * kchunk) of the same output tile, leaves its partial tile in
 // shared memory, and after a cluster barrier every CTA finishes a share of the tile's
 // elements, adding the partials of ranks 0 .. ksplit-1 in that order.
-template <typename T, int kTM, int kTN, bool KSPLIT>
+// AROWS (fp32, A with unit K stride, rows and base on the 16-byte grid): a stage keeps A as
+// [m][k] -- 16-byte copies along K, four k of a row per 16-byte read in the product -- instead
+// of [k][m]; the common row-major A then costs kTM / 64 copies per thread and slice, not kTM / 16.
+template <typename T, int kTM, int kTN, bool KSPLIT, bool AROWS = false>
 __global__ void __launch_bounds__(256) gemm_simt(const T* __restrict__ A, const T* __restrict__ B, const T* __restrict__ bias, T* __restrict__ C, GemmArgs g) {
-  __shared__ __align__(16) float As[kTK][kTM + 4];
-  __shared__ __align__(16) float Bs[kTK][kTN + 4];
-  __shared__ __align__(16) float part[KSPLIT ? kTM * kTN : 4];
+  constexpr bool kAsync = SimtStages<T, kTM, kTN>::value > 1;
+  static_assert(!AROWS || kAsync, "the [m][k] stage layout belongs to the cp.async path");
+  constexpr int kAPitch = AROWS ? kTK + 4 : kTM + 4;  // floats per row of the A part of a stage
+  constexpr int kAFloats = AROWS ? kTM * kAPitch : kTK * kAPitch;
+  constexpr int kStageFloats = kAFloats + kTK * (kTN + 4);
+  constexpr int kS = (SimtStages<T, kTM, kTN>::value == 4 && 4 * kStageFloats * 4 > 48 * 1024) ? 3 : SimtStages<T, kTM, kTN>::value;  // static shared memory ends at 48 KB
+  constexpr int kPartFloats = KSPLIT ? kTM * kTN : 4;
+  // the partial tile of a K split reuses the stage ring once the contraction is done
+  __shared__ __align__(16) float smem[(kS * kStageFloats > kPartFloats) ? kS * kStageFloats : kPartFloats];
+  auto As = [&](int st) { return reinterpret_cast<float(*)[kAPitch]>(smem + st * kStageFloats); };
+  auto Bs = [&](int st) { return reinterpret_cast<float(*)[kTN + 4]>(smem + st * kStageFloats + kAFloats); };
+  float* part = smem;
   if (g.gate && *g.gate == 0u) return;  // the same word for every CTA: whole clusters leave together
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
   const int64_t m0 = static_cast<int64_t>(blockIdx.y) * kTM, n0 = static_cast<int64_t>(blockIdx.x) * kTN;
@@ -51,54 +86,193 @@ __global__ void __launch_bounds__(256) gemm_simt(const T* __restrict__ A, const 
   constexpr int RM = kTM / 16, RN = kTN / 16;        // outputs per thread
   constexpr int QA = kTM * kTK / 256, QB = kTN * kTK / 256;  // slice elements per thread
   float acc[RM][RN] = {};
-  float pa[QA], pb[QB];
-  auto fetch = [&](int64_t k0) {
+  // Columns of C a thread owns: groups of four adjacent ones, 64 apart (one 16-byte read of a
+  // B row per group; the 16 threads of a row of the CTA read 256 contiguous bytes), or every
+  // 16th column for the 32-wide tile. Eight adjacent columns per thread, read one by one, put
+  // the 16 threads on four banks (34 shared-memory wavefronts per k instead of 6:
+  // 21 x 1024 x 256 in 64 batches took 98 us for that reason alone).
+  auto col = [&](int j) { return (RN % 4 == 0) ? (j / 4) * 64 + tx * 4 + (j % 4) : tx + 16 * j; };
+  auto load_b = [&](const float(*bs)[kTN + 4], int kk, float* bb) {
+    if constexpr (RN % 4 == 0) {
 #pragma unroll
-    for (int q = 0; q < QA; ++q) {
-      const int e = tid + q * 256;
-      // consecutive threads walk the contiguous direction of the operand
-      const int kk = a_kfast ? (e & 15) : (e / kTM), mm = a_kfast ? (e >> 4) : (e % kTM);
-      const int64_t m = m0 + mm, k = k0 + kk;
-      pa[q] = (m < g.M && k < k_hi) ? to_f32(Ab[m * g.sAm + k * g.sAk]) : 0.f;
-    }
+      for (int j = 0; j < RN; j += 4) *reinterpret_cast<float4*>(bb + j) = *reinterpret_cast<const float4*>(&bs[kk][(j / 4) * 64 + tx * 4]);
+    } else {
 #pragma unroll
-    for (int q = 0; q < QB; ++q) {
-      const int e = tid + q * 256;
-      const int kk = b_nfast ? (e / kTN) : (e & 15), nn = b_nfast ? (e % kTN) : (e >> 4);
-      const int64_t n = n0 + nn, k = k0 + kk;
-      pb[q] = (n < g.N && k < k_hi) ? to_f32(Bb[k * g.sBk + n * g.sBn]) : 0.f;
+      for (int j = 0; j < RN; ++j) bb[j] = bs[kk][tx + 16 * j];
     }
   };
-  auto stash = [&]() {
+  auto multiply = [&](int st) {
+    const float(*as)[kAPitch] = As(st);
+    const float(*bs)[kTN + 4] = Bs(st);
+    if constexpr (AROWS) {
 #pragma unroll
-    for (int q = 0; q < QA; ++q) {
-      const int e = tid + q * 256;
-      As[a_kfast ? (e & 15) : (e / kTM)][a_kfast ? (e >> 4) : (e % kTM)] = pa[q];
-    }
+      for (int k4 = 0; k4 < kTK; k4 += 4) {
+        float a[RM][4];
 #pragma unroll
-    for (int q = 0; q < QB; ++q) {
-      const int e = tid + q * 256;
-      Bs[b_nfast ? (e / kTN) : (e & 15)][b_nfast ? (e % kTN) : (e >> 4)] = pb[q];
+        for (int i = 0; i < RM; ++i) *reinterpret_cast<float4*>(a[i]) = *reinterpret_cast<const float4*>(&as[ty * RM + i][k4]);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          float bb[RN];
+          load_b(bs, k4 + u, bb);
+#pragma unroll
+          for (int i = 0; i < RM; ++i)
+#pragma unroll
+            for (int j = 0; j < RN; ++j) acc[i][j] = fmaf(a[i][u], bb[j], acc[i][j]);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int kk = 0; kk < kTK; ++kk) {
+        float a[RM], bb[RN];
+        if constexpr (RM % 4 == 0) {
+#pragma unroll
+          for (int i = 0; i < RM; i += 4) *reinterpret_cast<float4*>(a + i) = *reinterpret_cast<const float4*>(&as[kk][ty * RM + i]);
+        } else {
+          *reinterpret_cast<float2*>(a) = *reinterpret_cast<const float2*>(&as[kk][ty * RM]);
+        }
+        load_b(bs, kk, bb);
+#pragma unroll
+        for (int i = 0; i < RM; ++i)
+#pragma unroll
+          for (int j = 0; j < RN; ++j) acc[i][j] = fmaf(a[i], bb[j], acc[i][j]);
+      }
     }
   };
-  fetch(k_lo);
-  for (int64_t k0 = k_lo; k0 < k_hi; k0 += kTK) {
-    stash();
-    __syncthreads();
-    if (k0 + kTK < k_hi) fetch(k0 + kTK);
+  static_assert(RM == 2 || RM % 4 == 0, "rows per thread: 2, 4 or 8");
+  if constexpr (kAsync) {
+    // Every copy a thread issues has the same place in the tile for all slices: its source
+    // pointer (advanced by one slice per issue), its destination offset inside a stage, its
+    // first k inside the slice and whether its row / column exists are worked out once.
+    // Rows of shared memory that are contiguous in global memory and on the 16-byte grid
+    // there travel 16 bytes per copy (A along K with AROWS, A along M or B along N otherwise).
+    struct Copy { const float* src; uint32_t dst; int kq; int bytes; };  // bytes: what exists of the copy's row (0 = zeros only, -1 = no such copy)
+    const bool a_vec = !AROWS && g.sAm == 1 && g.sAk % 4 == 0 && g.sAb % 4 == 0 && (reinterpret_cast<uintptr_t>(A) & 15u) == 0;
+    const bool b_vec = g.sBn == 1 && g.sBk % 4 == 0 && g.sBb % 4 == 0 && (reinterpret_cast<uintptr_t>(B) & 15u) == 0;
+    constexpr int NA = AROWS ? (kTM * 4 + 255) / 256 : QA, NB = QB;
+    Copy ca[NA], cb[NB];
+    const uint32_t smem_a = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+    const int na = AROWS ? NA : (a_vec ? (QA + 3) / 4 : QA), nb = b_vec ? (QB + 3) / 4 : QB;
 #pragma unroll
-    for (int kk = 0; kk < kTK; ++kk) {
-      float a[RM], bb[RN];
-#pragma unroll
-      for (int i = 0; i < RM; ++i) a[i] = As[kk][ty * RM + i];
-#pragma unroll
-      for (int j = 0; j < RN; ++j) bb[j] = Bs[kk][tx * RN + j];
-#pragma unroll
-      for (int i = 0; i < RM; ++i)
-#pragma unroll
-        for (int j = 0; j < RN; ++j) acc[i][j] = fmaf(a[i], bb[j], acc[i][j]);
+    for (int q = 0; q < NA; ++q) {
+      const int e = tid + q * 256;
+      int kk, mm, span;  // span: elements along the copy's contiguous direction
+      if (AROWS) { mm = e >> 2; kk = (e & 3) * 4; span = 1; }
+      else if (a_vec) { kk = e / (kTM / 4); mm = (e % (kTM / 4)) * 4; span = 4; }
+      else { kk = a_kfast ? (e & 15) : (e / kTM); mm = a_kfast ? (e >> 4) : (e % kTM); span = 1; }
+      const bool in_tile = AROWS ? e < kTM * 4 : (a_vec ? e < kTM * kTK / 4 : true);
+      const int64_t m = m0 + mm, left = g.M - m;
+      ca[q].kq = kk;
+      ca[q].bytes = !in_tile ? -1 : left > 0 ? (AROWS ? 16 : (left >= span ? span * 4 : static_cast<int>(left) * 4)) : 0;
+      ca[q].src = ca[q].bytes > 0 ? Ab + m * g.sAm + (k_lo + kk) * g.sAk : Ab;
+      ca[q].dst = smem_a + 4u * static_cast<uint32_t>(AROWS ? mm * kAPitch + kk : kk * kAPitch + mm);
     }
-    __syncthreads();
+#pragma unroll
+    for (int q = 0; q < NB; ++q) {
+      const int e = tid + q * 256;
+      int kk, nn, span;
+      if (b_vec) { kk = e / (kTN / 4); nn = (e % (kTN / 4)) * 4; span = 4; }
+      else { kk = b_nfast ? (e / kTN) : (e & 15); nn = b_nfast ? (e % kTN) : (e >> 4); span = 1; }
+      const bool in_tile = b_vec ? e < kTN * kTK / 4 : true;
+      const int64_t n = n0 + nn, left = g.N - n;
+      cb[q].kq = kk;
+      cb[q].bytes = !in_tile ? -1 : left > 0 ? (left >= span ? span * 4 : static_cast<int>(left) * 4) : 0;
+      cb[q].src = cb[q].bytes > 0 ? Bb + (k_lo + kk) * g.sBk + n * g.sBn : Bb;
+      cb[q].dst = smem_a + 4u * static_cast<uint32_t>(kAFloats + kk * (kTN + 4) + nn);
+    }
+    const int64_t a_step = kTK * g.sAk, b_step = kTK * g.sBk;
+    auto cp16 = [](uint32_t dst, const void* src, int bytes) { asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory"); };
+    auto cp4 = [](uint32_t dst, const void* src, int bytes) { asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory"); };
+    auto issue = [&](int64_t k0, int st) {
+      if (k0 < k_hi) {
+        const int rem = static_cast<int>(k_hi - k0 < kTK ? k_hi - k0 : kTK);  // k of this slice that exist
+        const uint32_t stage = static_cast<uint32_t>(st) * (kStageFloats * 4u);
+#pragma unroll
+        for (int q = 0; q < NA; ++q) {
+          if (q < na && ca[q].bytes >= 0) {
+            const int r = rem - ca[q].kq;
+            if (AROWS) cp16(ca[q].dst + stage, ca[q].src, ca[q].bytes ? (r >= 4 ? 16 : (r > 0 ? r * 4 : 0)) : 0);
+            else if (a_vec) cp16(ca[q].dst + stage, ca[q].src, r > 0 ? ca[q].bytes : 0);
+            else cp4(ca[q].dst + stage, ca[q].src, r > 0 ? ca[q].bytes : 0);
+            if (ca[q].bytes > 0) ca[q].src += a_step;
+          }
+        }
+#pragma unroll
+        for (int q = 0; q < NB; ++q) {
+          if (q < nb && cb[q].bytes >= 0) {
+            const int r = rem - cb[q].kq;
+            if (b_vec) cp16(cb[q].dst + stage, cb[q].src, r > 0 ? cb[q].bytes : 0);
+            else cp4(cb[q].dst + stage, cb[q].src, r > 0 ? cb[q].bytes : 0);
+            if (cb[q].bytes > 0) cb[q].src += b_step;
+          }
+        }
+      }
+    cp_async_commit();  // an empty group past the end keeps the group count in step
+    };
+#pragma unroll
+    for (int s = 0; s < kS - 1; ++s) issue(k_lo + s * kTK, s);
+    int st = 0;
+    for (int64_t k0 = k_lo; k0 < k_hi; k0 += kTK) {
+      cp_async_wait<kS - 2>();  // this thread's copies of the current slice have landed ...
+      __syncthreads();          // ... and everybody's; the stage refilled below was multiplied out before this barrier
+      issue(k0 + (kS - 1) * kTK, st == 0 ? kS - 1 : st - 1);
+      multiply(st);
+      st = st + 1 == kS ? 0 : st + 1;
+    }
+    cp_async_wait<0>();
+    __syncthreads();  // the ring is free (a K split reuses it for the partial tile)
+  } else {
+    // kD slices are on their way in registers at any time (four for the small tiles): a
+    // contraction of a few slices -- most 16-bit products that come here are small -- costs
+    // one global-memory round trip, not one per slice.
+    constexpr int kD = (QA + QB <= 8) ? 4 : (QA + QB <= 12 ? 3 : 2);
+    T pa[kD][QA], pb[kD][QB];
+    auto fetch = [&](int64_t k0, T* ra, T* rb) {
+#pragma unroll
+      for (int q = 0; q < QA; ++q) {
+        const int e = tid + q * 256;
+        // consecutive threads walk the contiguous direction of the operand
+        const int kk = a_kfast ? (e & 15) : (e / kTM), mm = a_kfast ? (e >> 4) : (e % kTM);
+        const int64_t m = m0 + mm, k = k0 + kk;
+        ra[q] = (m < g.M && k < k_hi) ? Ab[m * g.sAm + k * g.sAk] : from_f32<T>(0.f);
+      }
+#pragma unroll
+      for (int q = 0; q < QB; ++q) {
+        const int e = tid + q * 256;
+        const int kk = b_nfast ? (e / kTN) : (e & 15), nn = b_nfast ? (e % kTN) : (e >> 4);
+        const int64_t n = n0 + nn, k = k0 + kk;
+        rb[q] = (n < g.N && k < k_hi) ? Bb[k * g.sBk + n * g.sBn] : from_f32<T>(0.f);
+      }
+    };
+    auto stash = [&](const T* ra, const T* rb) {
+      float(*as)[kTM + 4] = As(0);
+      float(*bs)[kTN + 4] = Bs(0);
+#pragma unroll
+      for (int q = 0; q < QA; ++q) {
+        const int e = tid + q * 256;
+        as[a_kfast ? (e & 15) : (e / kTM)][a_kfast ? (e >> 4) : (e % kTM)] = to_f32(ra[q]);
+      }
+#pragma unroll
+      for (int q = 0; q < QB; ++q) {
+        const int e = tid + q * 256;
+        bs[b_nfast ? (e / kTN) : (e & 15)][b_nfast ? (e % kTN) : (e >> 4)] = to_f32(rb[q]);
+      }
+    };
+#pragma unroll
+    for (int d = 0; d < kD; ++d)
+      if (k_lo + d * kTK < k_hi) fetch(k_lo + d * kTK, pa[d], pb[d]);
+    for (int64_t k0 = k_lo; k0 < k_hi; k0 += kD * kTK) {
+#pragma unroll
+      for (int d = 0; d < kD; ++d) {
+        const int64_t kd = k0 + d * kTK;
+        if (kd < k_hi) {  // uniform over the CTA
+          stash(pa[d], pb[d]);
+          __syncthreads();
+          if (kd + kD * kTK < k_hi) fetch(kd + kD * kTK, pa[d], pb[d]);
+          multiply(0);
+          __syncthreads();
+        }
+      }
+    }
   }
   T* Cb = C + b * g.M * g.N;
   if (KSPLIT) {
@@ -106,7 +280,7 @@ __global__ void __launch_bounds__(256) gemm_simt(const T* __restrict__ A, const 
 #pragma unroll
     for (int i = 0; i < RM; ++i)
 #pragma unroll
-      for (int j = 0; j < RN; ++j) part[(ty * RM + i) * kTN + tx * RN + j] = acc[i][j];
+      for (int j = 0; j < RN; ++j) part[(ty * RM + i) * kTN + col(j)] = acc[i][j];
     cluster.sync();
     for (int e = rank * 256 + tid; e < kTM * kTN; e += nsplit * 256) {
       float sum = 0.f;
@@ -127,7 +301,7 @@ __global__ void __launch_bounds__(256) gemm_simt(const T* __restrict__ A, const 
       if (m >= g.M) continue;
 #pragma unroll
       for (int j = 0; j < RN; ++j) {
-        const int64_t n = n0 + tx * RN + j;
+        const int64_t n = n0 + col(j);
         if (n >= g.N) continue;
         float r = g.alpha * acc[i][j];
         // beta == 0 drops the bias term entirely (a NaN bias must not leak through)
@@ -145,16 +319,22 @@ __global__ void __launch_bounds__(256) gemm_simt(const T* __restrict__ A, const 
 // in 64 batches: 102 us unsplit, 115-140 us split). Each CTA keeps at least four K slices
 // and the cluster stays within the portable size of 8.
 static int pick_ksplit(int64_t tiles, int64_t K) {
-  if (tiles >= kNumSMs / 2 || K < 8 * kTK) return 1;
+  static const int64_t limit = []() { const char* e = getenv("B200_SIMT_SPLIT_BELOW"); return e ? atoll(e) : static_cast<int64_t>(kNumSMs / 2); }();
+  static const int64_t want = []() { const char* e = getenv("B200_SIMT_SPLIT_FILL"); return e ? atoll(e) : 4LL; }();
+  if (tiles >= limit || K < 8 * kTK) return 1;
   int64_t s = K / (4 * kTK);
-  const int64_t fill = (4 * kNumSMs + tiles - 1) / tiles;
+  const int64_t fill = (want * kNumSMs + tiles - 1) / tiles;
   if (s > fill) s = fill;
   if (s > 8) s = 8;
   return s < 2 ? 1 : static_cast<int>(s);
 }
 
-template <typename T, int kTM, int kTN, bool KSPLIT = false>
+template <typename T, int kTM, int kTN, bool KSPLIT = false, bool AROWS = false>
 static int launch_simt_tile(const void* A, const void* B, const void* bias, void* C, int64_t batch, GemmArgs g, cudaStream_t st) {
+  if constexpr (std::is_same<T, float>::value && !AROWS) {
+    // row-major fp32 A on the 16-byte grid: the variant that copies it 16 bytes at a time along K
+    if (g.sAk == 1 && g.sAm % 4 == 0 && g.sAb % 4 == 0 && aligned16(A)) return launch_simt_tile<T, kTM, kTN, KSPLIT, true>(A, B, bias, C, batch, g, st);
+  }
   const int64_t gx = (g.N + kTN - 1) / kTN, gy = (g.M + kTM - 1) / kTM;
   if (gx > 0x7fffffffLL || gy > 65535) return B200_EINVAL;
   const int64_t per_launch = 65535 / g.ksplit;  // batches per launch: grid z holds batch x ksplit
@@ -177,10 +357,10 @@ static int launch_simt_tile(const void* A, const void* B, const void* bias, void
       attr[0].val.clusterDim.z = static_cast<unsigned>(g.ksplit);
       cfg.attrs = attr;
       cfg.numAttrs = 1;
-      const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_simt<T, kTM, kTN, KSPLIT>, a, b, bs, c, g);
+      const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_simt<T, kTM, kTN, KSPLIT, AROWS>, a, b, bs, c, g);
       if (e != cudaSuccess) { set_last_cuda_error(e); return B200_ELAUNCH; }
     } else {
-      gemm_simt<T, kTM, kTN, KSPLIT><<<grid, 256, 0, st>>>(a, b, bs, c, g);
+      gemm_simt<T, kTM, kTN, KSPLIT, AROWS><<<grid, 256, 0, st>>>(a, b, bs, c, g);
     }
   }
   return check_launch();

@@ -690,6 +690,105 @@ int gemm_tc_dispatch(const void* A, const void* B, const void* bias, void* C, in
   return check_launch();
 }
 
+// ------------------------------------------------------------------ long contraction, few output tiles
+// A 16-bit product whose C is a handful of tiles leaves most SMs idle while one CTA per tile
+// walks all of K (5 x 4096 x 512: two CTAs, 64 K slabs each, 26 us). Here the contraction is
+// cut into S equal ranges that the kernel above sees as S batch entries -- A as [S][M][K/S],
+// B as [S][K/S][N], both only a different tensor map over the same memory -- and writes as
+// fp32 partial products [S][M][N] into caller scratch; a second kernel adds the S partials of
+// every element in the order 0 .. S-1, applies alpha, beta and the bias and rounds once. No
+// atomics: the result does not depend on scheduling.
+struct SplitKPlan {
+  int splits;      // 1 = not worth it / not possible
+  int64_t kchunk;  // K / splits
+};
+static SplitKPlan plan_splitk(int64_t batch, int64_t M, int64_t N, int64_t K) {
+  SplitKPlan r{1, K};
+  if (batch != 1) return r;
+  const int bn = N <= 128 ? 128 : 256;
+  const int64_t tiles = ((M + kBM - 1) / kBM) * ((N + bn - 1) / bn), slabs = (K + kBK - 1) / kBK;
+  // (more tiles than a quarter of the SMs: 5722 x 4096 x 256, 45 tiles, ran 30 us in two ranges against 26 us whole)
+  if (tiles > kNumSMs / 4 || slabs < 16) return r;
+  int64_t s = kNumSMs / tiles;
+  if (s > slabs / 4) s = slabs / 4;  // every range keeps at least four K slabs
+  if (s > 32) s = 32;
+  for (; s >= 2; --s)
+    if (K % (8 * s) == 0) break;     // ranges start on the 16-byte grid of a K-major operand
+  if (s < 2) return r;
+  r.splits = static_cast<int>(s);
+  r.kchunk = K / s;
+  return r;
+}
+
+int64_t gemm_tc_splitk_scratch_bytes(int64_t batch, int64_t M, int64_t N, int64_t K) {
+  const SplitKPlan pl = plan_splitk(batch, M, N, K);
+  return pl.splits < 2 ? 0 : static_cast<int64_t>(pl.splits) * M * N * 4 + 256;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) splitk_reduce(const float* __restrict__ part, int splits, int64_t M, int64_t N, const T* __restrict__ bias, int64_t sbm, int64_t sbn, float alpha, float beta,
+                                                     T* __restrict__ C) {
+  const int64_t total = M * N;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    float sum = 0.f;
+    for (int s = 0; s < splits; ++s) sum += part[s * total + i];
+    float r = alpha * sum;
+    if (bias && beta != 0.f) {
+      const int64_t m = i / N, n = i - m * N;
+      r = fmaf(beta, to_f32(bias[m * sbm + n * sbn]), r);
+    }
+    C[i] = from_f32<T>(r);
+  }
+}
+
+int gemm_tc_splitk_dispatch(const void* A, const void* B, const void* bias, void* C, int64_t M, int64_t N, int64_t K, int64_t sAm, int64_t sAk, int64_t sBk, int64_t sBn, int64_t sbm,
+                            int64_t sbn, double alpha, double beta, int dtype, void* scratch, int64_t scratch_bytes, uint32_t* status, cudaStream_t st) {
+  const SplitKPlan pl = plan_splitk(1, M, N, K);
+  if (pl.splits < 2) return B200_EINVAL;
+  if (!scratch || scratch_bytes < gemm_tc_splitk_scratch_bytes(1, M, N, K)) return B200_ESCRATCH;
+  float* part = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(scratch) + 255) & ~static_cast<uintptr_t>(255));
+  const int64_t S = pl.splits, Kc = pl.kchunk;
+  const int64_t sAb = Kc * sAk, sBb = Kc * sBk;  // range s of the contraction starts s * Kc further along K
+  const OperandLayout la = operand_layout(M, Kc, sAm, sAk, sAb, S, A);
+  const OperandLayout lb = operand_layout(N, Kc, sBn, sBk, sBb, S, B);
+  if (!la.ok || !lb.ok || !encode_fn()) return B200_EALIGN;
+  const int bn = N <= 128 ? 128 : 256;
+  alignas(64) CUtensorMap map_a, map_b;
+  if (!encode_operand(&map_a, A, dtype, la.mn_major, M, Kc, sAm, sAk, sAb, S, kBM)) return B200_EDRIVER;
+  if (!encode_operand(&map_b, B, dtype, lb.mn_major, N, Kc, sBn, sBk, sBb, S, bn)) return B200_EDRIVER;
+  GemmTcParams p;
+  p.tma_store = 0;
+  p.M = M; p.N = N; p.K = Kc; p.batch = S;
+  p.sbm = 0; p.sbn = 0;
+  p.alpha = 1.f;
+  p.beta = 0.f;
+  p.a_mn_major = la.mn_major ? 1 : 0;
+  p.b_mn_major = lb.mn_major ? 1 : 0;
+  p.is_bf16 = dtype == B200_BF16 ? 1 : 0;
+  p.has_bias = 0;
+  p.col_fastest = 1;
+  p.split_slabs = 0;
+  p.skip_if_set = nullptr;
+  p.wait_limit_ns = kWaitLimitNs;
+  p.withhold_first_slab = 0;
+  p.group_m = group_rows_for(Kc) / kBM;
+  const int64_t tiles = S * ((M + kBM - 1) / kBM) * ((N + bn - 1) / bn);
+  const int grid = static_cast<int>(tiles < kNumSMs ? tiles : kNumSMs);
+  auto launch = [&](auto kernel) -> int { return launch_tc(kernel, false, grid, st, map_a, map_b, map_a, static_cast<const float*>(nullptr), part, p, status); };
+  int rc;
+  if (dtype == B200_BF16) rc = bn == 128 ? launch(gemm_tcgen05_kernel<__nv_bfloat16, 128, float>) : launch(gemm_tcgen05_kernel<__nv_bfloat16, 256, float>);
+  else rc = bn == 128 ? launch(gemm_tcgen05_kernel<__half, 128, float>) : launch(gemm_tcgen05_kernel<__half, 256, float>);
+  if (rc) return rc;
+  int64_t blocks = (M * N + 255) / 256;
+  if (blocks > kNumSMs * 8) blocks = kNumSMs * 8;
+  const float al = static_cast<float>(alpha), be = static_cast<float>(beta);
+  if (dtype == B200_BF16)
+    splitk_reduce<__nv_bfloat16><<<static_cast<int>(blocks), 256, 0, st>>>(part, static_cast<int>(S), M, N, static_cast<const __nv_bfloat16*>(bias), sbm, sbn, al, be, static_cast<__nv_bfloat16*>(C));
+  else
+    splitk_reduce<__half><<<static_cast<int>(blocks), 256, 0, st>>>(part, static_cast<int>(S), M, N, static_cast<const __half*>(bias), sbm, sbn, al, be, static_cast<__half*>(C));
+  return check_launch(2);
+}
+
 // ------------------------------------------------------------------ fp32 operands on the tensor cores
 // An fp32 value is the sum of three bf16 values to within 2^-25 of itself (x1 = bf16(x),
 // x2 = bf16(x - x1), x3 = bf16(x - x1 - x2); the subtractions are exact). A product of fp32

@@ -291,6 +291,23 @@ int b200_gemm_f32(const void* A, const void* B, const void* bias, void* C, int64
                   double alpha, double beta, void* scratch, int64_t scratch_bytes,
                   uint32_t* status, void* stream);
 
+/* A 16-bit product with a long contraction and a C of a few tiles (batch 1, at most a quarter
+ * of the SMs' worth of 128 x 256 tiles, K >= 1024, K divisible by 8 x the number of ranges):
+ * the contraction is cut into up to 32 ranges that run as separate CTAs of the tensor-core
+ * kernel and leave fp32 partial products in caller scratch; a second kernel adds them in a
+ * fixed order, applies alpha / beta / bias and rounds once (deterministic, no atomics).
+ * b200_gemm_splitk_scratch_bytes returns the scratch the call needs, 0 when the product does
+ * not qualify; b200_gemm_splitk then behaves exactly like b200_gemm. (No counterpart in the
+ * reference, which leaves the choice to cuBLAS: eval.py:100-102.) */
+int64_t b200_gemm_splitk_scratch_bytes(const void* A, const void* B, const void* C, int64_t batch,
+                                       int64_t M, int64_t N, int64_t K, int64_t sAb, int64_t sAm,
+                                       int64_t sAk, int64_t sBb, int64_t sBk, int64_t sBn, int dtype);
+int b200_gemm_splitk(const void* A, const void* B, const void* bias, void* C, int64_t batch,
+                     int64_t M, int64_t N, int64_t K, int64_t sAb, int64_t sAm, int64_t sAk,
+                     int64_t sBb, int64_t sBk, int64_t sBn, int64_t sbias_m, int64_t sbias_n,
+                     double alpha, double beta, int dtype, void* scratch, int64_t scratch_bytes,
+                     uint32_t* status, void* stream);
+
 /* ------------------------------------------------------------- evaluation path */
 
 /* One pass replacing BackendBench/eval.py:68-90 (`allclose`: torch.testing.assert_close

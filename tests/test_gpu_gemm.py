@@ -306,3 +306,29 @@ def test_cta_pair_epilogue_and_batches(dtype):
         yt = _rand((B, N, K), dtype, g, 1.0).transpose(1, 2)
         _check(ops.bmm_default(x, yt), x.double() @ yt.double(), dtype)
     ops.check_device_status()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_long_contraction_with_few_tiles_is_split_along_k(dtype):
+    """A handful of output tiles and K >= 1024: the contraction runs as up to 32 ranges side by
+    side and the fp32 partial products are added in a fixed order. Same answer as the unsplit
+    product to rounding, bit-identical from run to run, every operand layout, bias and scales
+    applied once, and shapes the split declines (K not divisible) fall through."""
+    g = torch.Generator(device=DEV).manual_seed(15)
+    dt = _abi.BF16 if dtype == torch.bfloat16 else _abi.F16
+    for M, N, K, split in [(5, 512, 4096, True), (45, 2048, 4096, True), (12, 512, 2048, True), (44, 32, 4096, True), (130, 264, 1096, False), (1, 7, 4104, True), (300, 200, 8200, True)]:
+        a, b = _rand((M, K), dtype, g, K**-0.5), _rand((K, N), dtype, g, 1.0)
+        c = torch.empty(M, N, dtype=dtype, device=DEV)
+        need = _abi.lib().b200_gemm_splitk_scratch_bytes(a.data_ptr(), b.data_ptr(), c.data_ptr(), 1, M, N, K, 0, K, 1, 0, N, 1, dt)
+        if N % 8 == 0:  # B [K, N] with rows off the 16-byte grid never reaches the tensor cores
+            assert (need > 0) == split, (M, N, K, need)
+        exact = a.double() @ b.double()
+        got = ops.mm_default(a, b)
+        _check(got, exact, dtype)
+        assert torch.equal(got, ops.mm_default(a, b))
+        bias = _rand((N,), dtype, g, 1.0)
+        _check(ops.addmm_default(bias, a, b, beta=0.5, alpha=2), 2 * exact + 0.5 * bias.double(), dtype)
+        at = _rand((K, (M + 7) // 8 * 8), dtype, g, K**-0.5).t()[:M]  # M-major A
+        bt = _rand(((N + 7) // 8 * 8, K), dtype, g, 1.0).t()[:, :N]   # K-major B
+        _check(ops.mm_default(at, bt), at.double() @ bt.double(), dtype)
+    ops.check_device_status()
