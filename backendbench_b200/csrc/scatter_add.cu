@@ -591,6 +591,49 @@ __global__ void __launch_bounds__(256) scatter_add_rows(const T* __restrict__ se
   }
 }
 
+// Few rows, long ones (17 x 2051: nine warps of the kernel above would walk 2051 sources
+// each, one global-memory round trip per 64): the destinations of a row are cut into
+// `slices` ranges and a warp owns one range of one row. It reads ALL sources of the row (32
+// per step, the next step's loads in flight while this one is applied; the other warps of the
+// row read the same lines out of L1 / L2) and applies those that fall into its range, in
+// source order. The order of the additions into a destination is untouched.
+template <typename T>
+__global__ void __launch_bounds__(256) scatter_add_rows_sliced(const T* __restrict__ self, const int64_t* __restrict__ index, const T* __restrict__ src, T* __restrict__ out, RowArgs A,
+                                                               int slices, int slice_rows, uint32_t* status) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  unsigned char* tags = smem_raw + warp * kTagSlots;
+  float* mine = reinterpret_cast<float*>(smem_raw + nwarps * kTagSlots) + static_cast<int64_t>(warp) * slice_rows;
+  const int64_t items = A.outer * slices;
+  for (int64_t item = static_cast<int64_t>(blockIdx.x) * nwarps + warp; item < items; item += static_cast<int64_t>(gridDim.x) * nwarps) {
+    const int64_t o = item / slices;
+    const int d = static_cast<int>(item - o * slices);
+    const int64_t lo = static_cast<int64_t>(d) * slice_rows;
+    const int n = static_cast<int>(A.rows - lo < slice_rows ? A.rows - lo : slice_rows);  // > 0 by the choice of slices
+    for (int r = lane; r < n; r += 32) mine[r] = to_f32(self[o * A.rows + lo + r]);
+    __syncwarp();
+    if (o < A.idx_outer) {
+      const int64_t* irow = index + o * A.idx_so;
+      const T* srow = src + o * A.src_so;
+      int64_t key = lane < A.idx_len ? irow[lane] : -1;
+      T val = lane < A.idx_len ? srow[lane] : from_f32<T>(0.f);
+      for (int64_t j0 = 0; j0 < A.idx_len; j0 += 32) {
+        const int64_t jn = j0 + 32 + lane;
+        const int64_t key_n = jn < A.idx_len ? irow[jn] : -1;
+        const T val_n = jn < A.idx_len ? srow[jn] : from_f32<T>(0.f);
+        const bool real = j0 + lane < A.idx_len;
+        if (real && d == 0 && (key < 0 || key >= A.rows)) flag_oob(status);
+        const bool take = real && key >= lo && key < lo + n;
+        ordered_step<32>(mine, tags, take ? static_cast<int>(key - lo) : -1 - lane, take ? to_f32(val) : 0.f, 0, lane, lane);
+        key = key_n;
+        val = val_n;
+      }
+    }
+    for (int r = lane; r < n; r += 32) out[o * A.rows + lo + r] = from_f32<T>(mine[r]);
+    __syncwarp();
+  }
+}
+
 // ------------------------------------------------------------------ generic line kernel
 struct ScatterArgs {
   int ndim, dim;
@@ -1183,6 +1226,32 @@ static int launch_strip_wide(const void* self, const void* index, const void* sr
 
 template <typename T>
 static int launch_rows(const void* self, const void* index, const void* src, void* out, RowArgs A, uint32_t* status, cudaStream_t st) {
+  // few long rows: several warps per row, each with a range of the row's destinations
+  if (A.outer < 2LL * kNumSMs && A.idx_len >= 256 && A.rows >= 128) {
+    int64_t slices = (4LL * kNumSMs + A.outer - 1) / A.outer;
+    if (slices > A.rows / 64) slices = A.rows / 64;
+    if (slices > 32) slices = 32;
+    if (slices >= 2) {
+      const int64_t slice_rows = (A.rows + slices - 1) / slices;
+      slices = (A.rows + slice_rows - 1) / slice_rows;  // no empty range at the end
+      int warps = 8;
+      while (warps > 1 && static_cast<int64_t>(warps) * (slice_rows * 4 + kTagSlots) > 96 * 1024) warps >>= 1;
+      const size_t smem = static_cast<size_t>(warps) * (slice_rows * 4 + kTagSlots);
+      if (smem <= static_cast<size_t>(kSmemBudget)) {
+        const cudaError_t ae = cudaFuncSetAttribute(scatter_add_rows_sliced<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+        if (ae != cudaSuccess) { set_last_cuda_error(ae); return B200_ELAUNCH; }
+        const int64_t items = A.outer * slices;
+        // one item per warp where the machine has room: spread the items over the SMs first
+        int per_cta = static_cast<int>((items + kNumSMs - 1) / kNumSMs);
+        if (per_cta > warps) per_cta = warps;
+        if (per_cta < 1) per_cta = 1;
+        const int64_t blocks = (items + per_cta - 1) / per_cta;
+        scatter_add_rows_sliced<T><<<static_cast<int>(blocks), per_cta * 32, static_cast<size_t>(per_cta) * (slice_rows * 4 + kTagSlots), st>>>(
+            static_cast<const T*>(self), static_cast<const int64_t*>(index), static_cast<const T*>(src), static_cast<T*>(out), A, static_cast<int>(slices), static_cast<int>(slice_rows), status);
+        return check_launch();
+      }
+    }
+  }
   // two destination rows per warp; shrink the CTA before windowing the destination
   int warps = 8;
   while (warps > 1 && static_cast<int64_t>(warps) * (2 * A.rows * 4 + kTagSlots) > 96 * 1024) warps >>= 1;

@@ -352,6 +352,42 @@ def test_scatter_add_grouped_by_destination_path_bit_exact(backend, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_scatter_add_few_long_rows_bit_exact(backend, dtype):
+    """Scatter along the last dim with a handful of long rows: several warps share a row, each
+    with a range of its destinations, every one reading all of the row's sources in order."""
+    impl = backend[torch.ops.aten.scatter_add.default]
+    g = torch.Generator().manual_seed(41)
+
+    def rn(*shape):
+        return torch.randn(*shape, generator=g).to(dtype)
+
+    def ri(high, *shape):
+        return torch.randint(0, high, shape, generator=g)
+
+    cases = [
+        (rn(34, 2051), 1, ri(2051, 17, 2051), rn(17, 2051)),
+        (rn(3, 5000), 1, ri(5000, 3, 4000), rn(3, 4000)),
+        (rn(1, 300), 1, ri(300, 1, 1000), rn(1, 1000)),          # ~3 contributions per destination
+        (rn(5, 129), 1, ri(2, 5, 700), rn(5, 700)),              # two hot destinations: every step is ranked
+        (rn(2, 3, 1000), 2, ri(1000, 2, 3, 999), rn(2, 3, 1001)[:, :, :999]),
+        (rn(40, 6000), 1, ri(6000, 40, 257), rn(40, 257)),
+    ]
+    for x, dim, idx, src in cases:
+        got = impl(x.to(DEV), dim, idx.to(DEV), src.to(DEV))
+        assert bits_equal(oracle.scatter_add(x, dim, idx, src), got), (tuple(x.shape), dim, tuple(idx.shape))
+    ops.check_device_status()
+    x, idx, src = rn(6, 700), ri(700, 6, 900), rn(6, 900)
+    idx[2, 5] = 700
+    idx[5, 899] = -1
+    got = impl(x.to(DEV), 1, idx.to(DEV), src.to(DEV))
+    with pytest.raises(IndexError):
+        ops.check_device_status()
+    src[2, 5] = 0
+    src[5, 899] = 0
+    assert bits_equal(oracle.scatter_add(x, 1, idx.clamp(0, 699), src), got)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
 def test_many_short_rows_and_long_non_last_dims(backend, dtype):
     """Millions-of-tiny-rows geometries take the thread-per-row kernels; a long reduction over
     a non-last dim with few columns takes the transposed route / split reductions."""
