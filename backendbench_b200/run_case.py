@@ -2,6 +2,7 @@
 device time -- the small, self-contained command used for profiler captures.
 
     python -m backendbench_b200.run_case --case softmax_bf16_8192x4096 [--scale 4] [--reps 3] [--warmup 2]
+    python -m backendbench_b200.run_case --label "mm.default[f32][16384, 1024, 19]"   # a case of the 512-case sweep
     python -m backendbench_b200.run_case --list
 
 `--scale F` divides the leading extent by F (same operator, same row length) so that a
@@ -24,6 +25,7 @@ from .opregistry import get_operator
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--case")
+    ap.add_argument("--label", help="a case of the 512-case sweep, by its label")
     ap.add_argument("--scale", type=int, default=1)
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=2)
@@ -32,10 +34,18 @@ def main():
     ap.add_argument("--compare", action="store_true", help="time the fused compare kernel on (aten result, backend result) of the case instead of the operator")
     ap.add_argument("--list", action="store_true")
     args = ap.parse_args()
-    if args.list or not args.case:
+    if args.label:
+        from .cases import sweep_cases
+
+        found = [c for c in sweep_cases(512, 0) if c.label() == args.label]
+        if not found:
+            raise SystemExit(f"no sweep case labelled {args.label!r}")
+        case = found[0]
+    elif args.list or not args.case:
         print("\n".join(c.name for c in named_cases() + neighbour_cases()))
         return
-    case = named_case(args.case)
+    else:
+        case = named_case(args.case)
     if args.scale > 1:
         case = scaled_down(case, args.scale)
     op = get_operator(case.op)
