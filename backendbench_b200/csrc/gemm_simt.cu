@@ -315,12 +315,18 @@ __global__ void __launch_bounds__(256) gemm_simt(const T* __restrict__ A, const 
 // Few output tiles and a long contraction: how many CTAs share a tile (1 = no split). One
 // CTA walks K at a slice per global-memory round trip, so with under half the SMs busy the
 // time falls with every CTA added (measured: 2 x 2048 x 256 fp32, 192 us unsplit, 41 us
-// at 8); from about one tile per SM on, splitting only adds the exchange (21 x 1024 x 256
-// in 64 batches: 102 us unsplit, 115-140 us split). Each CTA keeps at least four K slices
-// and the cluster stays within the portable size of 8.
-static int pick_ksplit(int64_t tiles, int64_t K) {
-  static const int64_t limit = []() { const char* e = getenv("B200_SIMT_SPLIT_BELOW"); return e ? atoll(e) : static_cast<int64_t>(kNumSMs / 2); }();
-  static const int64_t want = []() { const char* e = getenv("B200_SIMT_SPLIT_FILL"); return e ? atoll(e) : 4LL; }();
+// at 8). Between half a tile and one tile per SM two CTAs per tile still pay for the tiles of
+// 64 rows or more (16384 x 1024 x 19: 60 -> 50 us, 16384 x 2060 x 32: 117 -> 87 us,
+// 3991 x 4120 x 96: 185 -> 147 us) but not for the 32-row tile, whose CTAs stream a wide B
+// and gain nothing from a shorter K (21 x 1024 x 256 in 64 batches: 52 us unsplit, 66-71 us
+// split); from one tile per SM on, splitting only adds the exchange. Each CTA keeps at least
+// four K slices and the cluster stays within the portable size of 8.
+// B200_SIMT_SPLIT_BELOW / B200_SIMT_SPLIT_FILL override the two thresholds (for comparisons).
+static int pick_ksplit(int64_t tiles, int64_t K, int tile_rows) {
+  static const int64_t env_limit = []() { const char* e = getenv("B200_SIMT_SPLIT_BELOW"); return e ? atoll(e) : 0LL; }();
+  static const int64_t env_want = []() { const char* e = getenv("B200_SIMT_SPLIT_FILL"); return e ? atoll(e) : 0LL; }();
+  const int64_t limit = env_limit > 0 ? env_limit : (tile_rows >= 64 ? kNumSMs : kNumSMs / 2);
+  const int64_t want = env_want > 0 ? env_want : (tiles >= kNumSMs / 2 ? 2 : 4);  // CTAs per SM aimed at
   if (tiles >= limit || K < 8 * kTK) return 1;
   int64_t s = K / (4 * kTK);
   const int64_t fill = (want * kNumSMs + tiles - 1) / tiles;
@@ -369,7 +375,7 @@ static int launch_simt_tile(const void* A, const void* B, const void* bias, void
 template <typename T, int kTM, int kTN>
 static int launch_simt_small(const void* A, const void* B, const void* bias, void* C, int64_t batch, GemmArgs g, cudaStream_t st) {
   const int64_t tiles = batch * ((g.M + kTM - 1) / kTM) * ((g.N + kTN - 1) / kTN);
-  g.ksplit = pick_ksplit(tiles, g.K);
+  g.ksplit = pick_ksplit(tiles, g.K, kTM);
   if (g.ksplit == 1) return launch_simt_tile<T, kTM, kTN, false>(A, B, bias, C, batch, g, st);
   const int64_t per = (g.K + g.ksplit - 1) / g.ksplit;
   g.kchunk = (per + kTK - 1) / kTK * kTK;
