@@ -184,6 +184,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   // pair: rank of this CTA in its 2-CTA cluster (0 = the CTA that issues the MMAs), and the
   // shared::cluster addresses of the even CTA's barriers that both CTAs signal
   const uint32_t cta_rank = kPair ? cluster_ctarank() : 0u;
+  if (threadIdx.x == 64) {
+    // the copy engine's descriptors are on their way while the barriers and the tensor memory are set up
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_b)) : "memory");
+    if (p.tma_store) asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_c)) : "memory");
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(full_bar(s), 1);   // pair: only the even CTA's is used (its producer arms it for both CTAs' bytes)
@@ -485,7 +491,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       }
       if (++acc == kAccs) { acc = 0; acc_phase ^= 1u; }
     }
-    if (lane == 0) tma_store_wait_all();  // tile stores must have left shared memory before the CTA exits
+    if (lane == 0) tma_store_wait_read();  // the tile stores have read their shared memory: the CTA may exit (the writes complete on their own)
     if (!ok && lane == 0) {
       *abort_flag = 1;
       if (status) atomicOr(status, B200_DEV_WAIT_TIMEOUT);
@@ -708,7 +714,7 @@ static SplitKPlan plan_splitk(int64_t batch, int64_t M, int64_t N, int64_t K) {
   const int bn = N <= 128 ? 128 : 256;
   const int64_t tiles = ((M + kBM - 1) / kBM) * ((N + bn - 1) / bn), slabs = (K + kBK - 1) / kBK;
   // (more tiles than a quarter of the SMs: 5722 x 4096 x 256, 45 tiles, ran 30 us in two ranges against 26 us whole)
-  if (tiles > kNumSMs / 4 || slabs < 16) return r;
+  if (tiles > kNumSMs / 4 || slabs < 24) return r;  // (16 slabs: 104 x 1024 x 1024 took 12 us either way)
   int64_t s = kNumSMs / tiles;
   if (s > slabs / 4) s = slabs / 4;  // every range keeps at least four K slabs
   if (s > 32) s = 32;

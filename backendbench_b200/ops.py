@@ -661,7 +661,7 @@ def scatter_add_default(self: torch.Tensor, dim: int, index: torch.Tensor, src: 
 
 # --------------------------------------------------------------------- contraction
 F32_SPLIT_MIN_MACS = 1 << 26  # batch*M*N*K from which an fp32 product takes the split tensor-core path
-SPLITK_MIN_K = 1024  # a 16-bit product is offered to the K-split only from this depth ...
+SPLITK_MIN_K = 1536  # a 16-bit product is offered to the K-split only from this depth ...
 SPLITK_MAX_OUTPUTS = 37 * 128 * 256  # ... and up to this many outputs (the library has the last word)
 
 def _tma_ready(t: torch.Tensor, s_b: int, s_mn: int, s_k: int, batch: int) -> bool:

@@ -292,7 +292,7 @@ int b200_gemm_f32(const void* A, const void* B, const void* bias, void* C, int64
                   uint32_t* status, void* stream);
 
 /* A 16-bit product with a long contraction and a C of a few tiles (batch 1, at most a quarter
- * of the SMs' worth of 128 x 256 tiles, K >= 1024, K divisible by 8 x the number of ranges):
+ * of the SMs' worth of 128 x 256 tiles, K >= 1536, K divisible by 8 x the number of ranges):
  * the contraction is cut into up to 32 ranges that run as separate CTAs of the tensor-core
  * kernel and leave fp32 partial products in caller scratch; a second kernel adds them in a
  * fixed order, applies alpha / beta / bias and rounds once (deterministic, no atomics).
