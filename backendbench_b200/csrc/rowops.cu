@@ -868,6 +868,14 @@ __global__ void __launch_bounds__(256) reduce_cols(const T* __restrict__ x, void
       s2 += to_f32(p[(k + 2) * inner]);
       s3 += to_f32(p[(k + 3) * inner]);
     }
+  } else {
+    for (; k + 7 < k1; k += 8) {  // eight rows requested before the first comparison
+      T f[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) f[u] = p[(k + u) * inner];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) arg_take(a, to_f32(f[u]), k + u);
+    }
   }
   for (; k < k1; ++k) {
     const float fv = to_f32(p[k * inner]);
@@ -959,16 +967,34 @@ template <bool ARG>
 __global__ void __launch_bounds__(256) reduce_finalize(const float* __restrict__ part_v, const int64_t* __restrict__ part_i, void* __restrict__ out, int64_t n, int splits, int dto) {
   const int64_t o = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (o >= n) return;
+  // eight partials are requested before the first one is combined: a thread that waited for
+  // each in turn spent a round trip to L2 per partial (1059 x 3072 argmax over dim 0: 12 us)
   if (ARG) {
     ArgPair a{0.f, -1};
-    for (int s = 0; s < splits; ++s) {
-      const int64_t i = part_i[s * n + o];
-      if (i >= 0) arg_take(a, part_v[s * n + o], i);
+    for (int s0 = 0; s0 < splits; s0 += 8) {
+      int64_t i[8];
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const bool in = s0 + u < splits;
+        i[u] = in ? part_i[(s0 + u) * n + o] : -1;
+        v[u] = in ? part_v[(s0 + u) * n + o] : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (i[u] >= 0) arg_take(a, v[u], i[u]);
     }
     static_cast<int64_t*>(out)[o] = a.i;
   } else {
     float s = 0.f;
-    for (int k = 0; k < splits; ++k) s += part_v[k * n + o];
+    for (int k0 = 0; k0 < splits; k0 += 8) {
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = k0 + u < splits ? part_v[(k0 + u) * n + o] : 0.f;
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (k0 + u < splits) s += v[u];  // the same order of additions as one by one
+    }
     store_from_f32(out, o, dto, s);
   }
 }
