@@ -158,6 +158,41 @@ __global__ void __launch_bounds__(256) gather_dim0_vec(const U* __restrict__ sel
   }
 }
 
+// 2-D, along the LAST dim (out[i][j] = self[i][index[i][j]]), contiguous index and unit element
+// stride in self: each thread produces the 16 bytes of adjacent outputs of one row -- 16-byte
+// index loads, look-ups that stay inside the row (its lines are in L1 / L2 after the first
+// touch), one 16-byte store, one 32-bit division per thread instead of a coordinate
+// decomposition per element.
+template <typename U>
+__global__ void __launch_bounds__(256) gather_lastdim_vec(const U* __restrict__ self, const int64_t* __restrict__ index, U* __restrict__ out, int64_t rows, int64_t cols, int64_t self_pitch,
+                                                          int64_t self_cols, uint32_t* status) {
+  constexpr int VE = 16 / static_cast<int>(sizeof(U));
+  const int64_t gpr = cols / VE, ngroup = rows * gpr;
+  for (int64_t q = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; q < ngroup; q += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t i = ngroup <= 0x7fffffffLL ? static_cast<int64_t>(static_cast<uint32_t>(q) / static_cast<uint32_t>(gpr)) : q / gpr;
+    const int64_t p = q * VE;  // = i * cols + first column of the group
+    int64_t k[VE];
+#pragma unroll
+    for (int h = 0; h < VE / 2; ++h) {
+      const longlong2 t = __ldcs(reinterpret_cast<const longlong2*>(index + p) + h);
+      k[2 * h] = t.x;
+      k[2 * h + 1] = t.y;
+    }
+    const U* row = self + i * self_pitch;
+    __align__(16) U v[VE];
+#pragma unroll
+    for (int e = 0; e < VE; ++e) {
+      if (k[e] < 0 || k[e] >= self_cols) {
+        flag_oob(status);
+        v[e] = zero_of<U>();
+      } else {
+        v[e] = row[k[e]];
+      }
+    }
+    __stcs(reinterpret_cast<uint4*>(out + p), *reinterpret_cast<const uint4*>(v));
+  }
+}
+
 // The same gather when a strip of `self` -- all its rows, kStripW columns -- fits in shared
 // memory: a CTA copies the strip in once (32-byte segments, each source sector read once)
 // and then streams index rows past it, looking every element up in shared memory. Index
@@ -476,6 +511,14 @@ extern "C" int b200_gather(const void* self, const void* index, void* out, int n
         gather_dim0_vec<uint16_t><<<grid, 256, 0, st>>>(static_cast<const uint16_t*>(self), static_cast<const int64_t*>(index), static_cast<uint16_t*>(out), index_shape[0], index_shape[1], self_strides[0], self_dim_size, wcols, status);
       return check_launch();
     }
+  }
+  if (ndim == 2 && dim == 1 && (elem_size == 4 || elem_size == 2) && idx_contig && self_strides[1] == 1 && index_shape[1] % ve == 0 && aligned16(index) && aligned16(out)) {
+    const int g2 = capped_grid(A.n / ve, 256, 32);
+    if (elem_size == 4)
+      gather_lastdim_vec<uint32_t><<<g2, 256, 0, st>>>(static_cast<const uint32_t*>(self), static_cast<const int64_t*>(index), static_cast<uint32_t*>(out), index_shape[0], index_shape[1], self_strides[0], self_dim_size, status);
+    else
+      gather_lastdim_vec<uint16_t><<<g2, 256, 0, st>>>(static_cast<const uint16_t*>(self), static_cast<const int64_t*>(index), static_cast<uint16_t*>(out), index_shape[0], index_shape[1], self_strides[0], self_dim_size, status);
+    return check_launch();
   }
   const int g = capped_grid(A.n, 256, 32);
   const int64_t* pi = static_cast<const int64_t*>(index);

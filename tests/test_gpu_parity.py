@@ -265,6 +265,32 @@ def test_gather_rows_of_self_held_in_shared_memory(backend):
     assert bits_equal(want, got)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_gather_along_the_last_dim(backend, dtype):
+    """2-D gather along the last dim: 16 bytes of adjacent outputs per thread; fewer index rows
+    than source rows, a pitched source, an index width that is not a multiple of the vector
+    (falls to the element kernel), an out-of-range index."""
+    impl = backend[torch.ops.aten.gather.default]
+    g = torch.Generator(device="cpu").manual_seed(17)
+    for self_rows, self_cols, rows, cols in [(300, 1024, 200, 1024), (64, 5000, 64, 256), (17, 33, 17, 4096), (500, 100, 500, 1003)]:
+        wide = torch.randn(self_rows, self_cols + 8, generator=g).to(dtype).to(DEV)
+        for x in (wide[:, :self_cols].contiguous(), wide[:, 3 : self_cols + 3]):
+            idx = torch.randint(0, self_cols, (rows, cols), generator=g).to(DEV)
+            assert bits_equal(torch.gather(x, 1, idx), impl(x, 1, idx))
+            ops.check_device_status()
+    x = torch.randn(40, 96, device=DEV).to(dtype)
+    idx = torch.randint(0, 96, (40, 64), device=DEV)
+    idx[3, 7] = 96
+    idx[39, 63] = -5
+    got = impl(x, 1, idx)
+    with pytest.raises(IndexError):
+        ops.check_device_status()
+    want = torch.gather(x, 1, idx.clamp(0, 95))
+    want[3, 7] = 0
+    want[39, 63] = 0
+    assert bits_equal(want, got)
+
+
 def test_full_size_scatter_add_bit_exact_vs_aten_cpu_order(backend):
     c, op, impl, args, kwargs = _full("scatter_add_f32_4096x4096", backend)
     x, dim, idx, src = args
