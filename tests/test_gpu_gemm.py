@@ -332,3 +332,25 @@ def test_long_contraction_with_few_tiles_is_split_along_k(dtype):
         bt = _rand(((N + 7) // 8 * 8, K), dtype, g, 1.0).t()[:, :N]   # K-major B
         _check(ops.mm_default(at, bt), at.double() @ bt.double(), dtype)
     ops.check_device_status()
+
+
+def test_fp32_products_with_a_narrow_result():
+    """C of at most 16 columns under a long row-major fp32 A: a warp per row of A (16-byte
+    pieces of the row per lane, B in shared memory, the lanes' partial sums folded by a halving
+    exchange). Ragged K, every N up to 16, batches, bias and scales, rows that do not fill the
+    last CTA; against an fp64 product."""
+    g = torch.Generator(device=DEV).manual_seed(23)
+    for B, M, K, N in [(1, 2000, 280, 8), (1, 1500, 128, 16), (1, 5001, 1000, 3), (3, 700, 260, 9), (1, 16384, 256, 8), (2, 1999, 2052, 16), (1, 1300, 132, 1)]:
+        a = torch.randn(B, M, K, generator=g, device=DEV) * K**-0.5
+        b = torch.randn(B, K, N, generator=g, device=DEV)
+        exact = a.double() @ b.double()
+        got = ops.bmm_default(a, b)
+        assert got.shape == (B, M, N) and got.dtype == torch.float32
+        ok, ea, er = compare(exact.float(), got, 1e-4, 1e-4)
+        assert ok, (B, M, K, N, ea, er)
+        assert torch.equal(got, ops.bmm_default(a, b))  # fixed order of additions
+        bias = torch.randn(M, N, generator=g, device=DEV)
+        got = ops.addmm_default(bias, a[0], b[0], beta=0.5, alpha=2)
+        ok, ea, er = compare((2 * exact[0] + 0.5 * bias.double()).float(), got, 1e-4, 1e-4)
+        assert ok, (M, K, N, ea, er)
+    ops.check_device_status()
