@@ -523,6 +523,88 @@ layernorm_resident(const T* __restrict__ x, const TW* __restrict__ w, const TW* 
   }
 }
 
+// The same for many 16-bit rows with weight and bias: persistent CTAs. A thread owns the same
+// columns of every row its CTA sees, so it widens its share of weight and bias ONCE (the
+// per-row kernel above fetched and unpacked 16 KB of them for every 8 KB row: two of its
+// eighteen instructions per element, and more L2-to-SM traffic than the rows themselves), and
+// the next row's vectors are requested before this row's two reductions.
+template <typename T, typename TW, int VPT>
+__global__ void __launch_bounds__(256, 4)
+layernorm_persistent(const T* __restrict__ x, const TW* __restrict__ w, const TW* __restrict__ b, T* __restrict__ y, void* __restrict__ mean, void* __restrict__ rstd, int64_t rows, int cols,
+                     float inv_cols, float eps, int dt_stat) {
+  constexpr int VE = Vec<T>::N;
+  __shared__ float red[64];
+  const int t = threadIdx.x, tpr = blockDim.x;
+  const int nvec = cols / VE;
+  float wv[VPT][VE], bv[VPT][VE];
+#pragma unroll
+  for (int u = 0; u < VPT; ++u) {
+    const int j = t + u * tpr;
+    if (j < nvec) {
+      load_weights<VE, TW>(w, j * VE, wv[u]);
+      load_weights<VE, TW>(b, j * VE, bv[u]);
+    }
+  }
+  uint4 nxt[VPT];
+  int64_t row = blockIdx.x;
+  if (row < rows) {
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+      const int j = t + u * tpr;
+      if (j < nvec) nxt[u] = ld_stream(x + row * cols + j * VE);
+    }
+  }
+  for (; row < rows; row += gridDim.x) {
+    // the row stays packed (16 bytes per vector) and is widened again in each of the three
+    // passes: held as fp32 it costs a CTA per SM (three instead of four) and ran 7 % slower
+    uint4 raw[VPT];
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) raw[u] = nxt[u];
+    const int64_t nrow = row + gridDim.x;
+    if (nrow < rows) {
+#pragma unroll
+      for (int u = 0; u < VPT; ++u) {
+        const int j = t + u * tpr;
+        if (j < nvec) nxt[u] = ld_stream(x + nrow * cols + j * VE);
+      }
+    }
+    float s = 0.f;
+#pragma unroll
+    for (int u = 0; u < VPT; ++u)
+      if (t + u * tpr < nvec) vec_accumulate<T>(s, raw[u]);
+    s = block_reduce_once(s, SumF{}, 0.f, red, 0);
+    float mu = s * inv_cols;
+    if (!isfinite(mu)) mu = CUDART_NAN_F;  // as the per-row kernel: NaN statistics for a row holding NaN or inf
+    float q = 0.f;
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+      if (t + u * tpr < nvec) {
+        float d[VE];
+        vec_minus<T>(raw[u], mu, d);
+#pragma unroll
+        for (int e = 0; e < VE; ++e) q = fmaf(d[e], d[e], q);
+      }
+    }
+    q = block_reduce_once(q, SumF{}, 0.f, red, 1);
+    const float rs = rsqrtf(fmaf(q, inv_cols, eps));
+    if (t == 0) {
+      store_from_f32(mean, row, dt_stat, mu);
+      store_from_f32(rstd, row, dt_stat, rs);
+    }
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+      const int j = t + u * tpr;
+      if (j < nvec) {
+        float d[VE], o[VE];
+        vec_minus<T>(raw[u], mu, d);
+#pragma unroll
+        for (int e = 0; e < VE; ++e) o[e] = fmaf(d[e] * rs, wv[u][e], bv[u][e]);
+        st_stream(y + row * cols + j * VE, narrow<T>(o));
+      }
+    }
+  }
+}
+
 // ------------------------------------------------------------------ layer norm backward
 // aten.native_layer_norm_backward: with xhat = (x - mean) * rstd and gy = dy * w per row,
 //   dx = rstd * (gy - mean_j(gy) - xhat * mean_j(gy * xhat))
@@ -1403,6 +1485,11 @@ static int layernorm_launch(const T* px, const TW* pw, const TW* pb, T* py, void
   const float inv_cols = 1.f / static_cast<float>(cols);
   if (c.warp) {
     B200_DISPATCH_VPT(c.vpt, MAXV, (layernorm_resident<T, TW, VPT, true, HOLD, AFFINE><<<grid_for(rows, 4), 128, 0, st>>>(px, pw, pb, py, mean, rstd, rows, static_cast<int>(cols), inv_cols, eps, dt_stat)))
+  } else if (AFFINE && !HOLD && c.vpt <= 2 && c.threads <= 256 && rows >= 8LL * kNumSMs) {
+    // many 16-bit rows: persistent CTAs that keep weight and bias in registers (four CTAs per SM)
+    const unsigned grid = static_cast<unsigned>(4 * kNumSMs);
+    if (c.vpt == 1) layernorm_persistent<T, TW, 1><<<grid, c.threads, 0, st>>>(px, pw, pb, py, mean, rstd, rows, static_cast<int>(cols), inv_cols, eps, dt_stat);
+    else layernorm_persistent<T, TW, 2><<<grid, c.threads, 0, st>>>(px, pw, pb, py, mean, rstd, rows, static_cast<int>(cols), inv_cols, eps, dt_stat);
   } else {
     B200_DISPATCH_VPT(c.vpt, MAXV, (layernorm_resident<T, TW, VPT, false, HOLD, AFFINE><<<static_cast<unsigned>(rows), c.threads, 0, st>>>(px, pw, pb, py, mean, rstd, rows, static_cast<int>(cols), inv_cols, eps, dt_stat)))
   }
