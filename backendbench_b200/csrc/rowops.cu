@@ -831,6 +831,22 @@ __device__ __forceinline__ void arg_take_ascending(ArgPair& a, float v, int64_t 
     if (a.i < 0 || a.v == a.v) { a.v = v; a.i = i; }
   }
 }
+// A whole vector of consecutive elements at once: when none of them exceeds the best so far
+// and none is NaN, nothing changes and no index is computed. The largest element is found
+// with fmaxf, which skips NaN, so the sum of the vector stands guard for it (a sum that is
+// NaN without a NaN element, +inf with -inf, only sends the vector the long way).
+template <int VE>
+__device__ __forceinline__ void arg_take_vector(ArgPair& a, const float* fw, int64_t i0) {
+  float m = fw[0], s = fw[0];
+#pragma unroll
+  for (int e = 1; e < VE; ++e) {
+    m = fmaxf(m, fw[e]);
+    s += fw[e];
+  }
+  if (m <= a.v && s == s && a.i >= 0) return;
+#pragma unroll
+  for (int e = 0; e < VE; ++e) arg_take_ascending(a, fw[e], i0 + e);
+}
 __device__ __forceinline__ ArgPair arg_warp_reduce(ArgPair a) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
@@ -873,8 +889,7 @@ __global__ void __launch_bounds__(256) reduce_rows(const T* __restrict__ x, void
         if (ARG) {
           float fw[VE];
           widen<T>(v[u].raw, fw);
-#pragma unroll
-          for (int e = 0; e < VE; ++e) arg_take_ascending(a, fw[e], (j + u * tpr) * VE + e);
+          arg_take_vector<VE>(a, fw, (j + u * tpr) * VE);
         } else {
           vec_accumulate<T>(s, v[u].raw);  // 16-bit elements are widened inside the add
         }
@@ -885,8 +900,7 @@ __global__ void __launch_bounds__(256) reduce_rows(const T* __restrict__ x, void
       if (ARG) {
         float fw[VE];
         widen<T>(raw, fw);
-#pragma unroll
-        for (int e = 0; e < VE; ++e) arg_take_ascending(a, fw[e], j * VE + e);
+        arg_take_vector<VE>(a, fw, j * VE);
       } else {
         vec_accumulate<T>(s, raw);
       }

@@ -266,6 +266,30 @@ def test_gather_rows_of_self_held_in_shared_memory(backend):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_argmax_rows_where_whole_vectors_are_skipped(backend, dtype):
+    """The row kernel screens 16-byte vectors (largest element and a NaN guard) before it looks
+    at elements: ties must still go to the first index, NaN to the first NaN, and vectors
+    holding both infinities (whose guard sum is NaN) must take the exact path."""
+    impl = backend[torch.ops.aten.argmax.default]
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(64, 4096, generator=g).to(dtype)
+    x[0] = 1.5                                   # all equal: index 0
+    x[1] = float("-inf")                         # all -inf: index 0
+    x[2, 100] = float("inf"); x[2, 101] = float("-inf"); x[2, 3000] = float("inf")   # first +inf wins
+    x[3, 7] = 9.0; x[3, 2049] = float("nan"); x[3, 4000] = float("nan")              # first NaN wins over a larger value before it
+    x[4, 4095] = 50.0                            # the very last element
+    x[5, :2048] = 2.0; x[5, 2048:] = 2.0; x[5, 1234] = 2.0                            # a plateau
+    x[6] = torch.arange(4096, 0, -1).to(dtype)   # descending: nothing after index 0 is ever taken
+    x[7] = torch.arange(4096).to(dtype)          # ascending: every vector replaces the best
+    want = torch.argmax(x, dim=-1)
+    got = impl(x.to(DEV), -1)
+    assert torch.equal(want, got.cpu())
+    long_rows = torch.randn(3, 70000, generator=g).to(dtype)  # split rows
+    long_rows[1, 69999] = float("nan")
+    assert torch.equal(torch.argmax(long_rows, dim=-1), impl(long_rows.to(DEV), -1).cpu())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
 def test_gather_along_the_last_dim(backend, dtype):
     """2-D gather along the last dim: 16 bytes of adjacent outputs per thread; fewer index rows
     than source rows, a pitched source, an index width that is not a multiple of the vector
