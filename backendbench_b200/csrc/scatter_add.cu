@@ -1365,6 +1365,13 @@ extern "C" int b200_scatter_add(const void* self, const void* index, const void*
   const int es = dtype_size(dtype);
   const ScatterPlan P = plan_scatter(self, index, src, out, ndim, self_shape, index_shape, index_strides, src_strides, dim, dtype);
 
+  if (P.path == kPathNone) {  // nothing to add: the result is a copy of self (no scratch, whatever the dtype)
+    if (out != self) {
+      const cudaError_t ce = cudaMemcpyAsync(out, self, static_cast<size_t>(n_self) * es, cudaMemcpyDeviceToDevice, st);
+      if (ce != cudaSuccess) { set_last_cuda_error(ce); return B200_ELAUNCH; }
+    }
+    return B200_OK;
+  }
   if (P.path == kPathStrip) {
     switch (dtype) {
       case B200_F32: return launch_strip<float>(self, index, src, out, P.strip, status, st);

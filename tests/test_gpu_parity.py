@@ -402,6 +402,21 @@ def test_scatter_add_grouped_by_destination_path_bit_exact(backend, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_scatter_add_with_an_empty_index_copies_self(backend, dtype):
+    """No contributions at all (an index with a zero extent): the result is self, for every
+    dtype and geometry, and no scratch is asked for."""
+    impl = backend[torch.ops.aten.scatter_add.default]
+    g = torch.Generator().manual_seed(5)
+    for shape, dim, ishape in [((605, 128), 0, (0, 128)), ((184566, 16), 1, (0, 16)), ((61, 32), 0, (0, 32)), ((7, 9, 11), 1, (7, 0, 11)), ((4096, 1024), 0, (0, 1024))]:
+        x = torch.randn(*shape, generator=g).to(dtype).to(DEV)
+        idx = torch.zeros(ishape, dtype=torch.int64, device=DEV)
+        src = torch.zeros(ishape, dtype=dtype, device=DEV)
+        got = impl(x, dim, idx, src)
+        assert got.data_ptr() != x.data_ptr() and bits_equal(x, got), (shape, dim, ishape)
+    ops.check_device_status()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
 def test_scatter_add_few_long_rows_bit_exact(backend, dtype):
     """Scatter along the last dim with a handful of long rows: several warps share a row, each
     with a range of its destinations, every one reading all of the row's sources in order."""
