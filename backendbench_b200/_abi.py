@@ -75,6 +75,8 @@ SIGNATURES = {
     "b200_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p] + [c_int64] * 12 + [c_double, c_double, c_int, c_void_p, c_void_p]),
     "b200_gemm_uses_tensor_cores": (c_int, [c_int64] * 10 + [c_int, c_void_p, c_void_p, c_void_p]),
     "b200_gemm_wait_probe": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int64, c_void_p, c_void_p]),
+    "b200_gemm_prefers_small": (c_int, [c_void_p, c_void_p] + [c_int64] * 10 + [c_int]),
+    "b200_gemm_small_path": (c_int, [c_int]),
     "b200_gemm_splitk_scratch_bytes": (c_int64, [c_void_p, c_void_p, c_void_p] + [c_int64] * 10 + [c_int]),
     "b200_gemm_splitk": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p] + [c_int64] * 12 + [c_double, c_double, c_int, c_void_p, c_int64, c_void_p, c_void_p]),
     "b200_gemm_f32_scratch_bytes": (c_int64, [c_int64, c_int64, c_int64, c_int64]),

@@ -1,5 +1,7 @@
 // mm / addmm / bmm entry point: picks the tcgen05 tensor-core kernel when the operands
 // qualify (bf16/f16, TMA-compatible layout) and the CUDA-core kernel otherwise.
+#include <atomic>
+
 #include "b200_common.cuh"
 
 namespace b200 {
@@ -11,6 +13,10 @@ int gemm_tc_dispatch(const void* A, const void* B, const void* bias, void* C, in
                      int64_t sBb, int64_t sBk, int64_t sBn, int64_t sbm, int64_t sbn, double alpha, double beta, int dtype, uint32_t* status, cudaStream_t st,
                      uint64_t wait_probe_limit_ns = 0, bool allow_pair = true);
 
+bool gemm_mma_small_preferred(const void* A, const void* B, int64_t batch, int64_t M, int64_t N, int64_t K, int64_t sAb, int64_t sAm, int64_t sAk, int64_t sBb, int64_t sBk, int64_t sBn,
+                              int dtype);
+int gemm_mma_small_dispatch(const void* A, const void* B, const void* bias, void* C, int64_t batch, int64_t M, int64_t N, int64_t K, int64_t sAb, int64_t sAm, int64_t sAk, int64_t sBb,
+                            int64_t sBk, int64_t sBn, int64_t sbm, int64_t sbn, double alpha, double beta, int dtype, cudaStream_t st);
 int64_t gemm_tc_splitk_scratch_bytes(int64_t batch, int64_t M, int64_t N, int64_t K);
 int gemm_tc_splitk_dispatch(const void* A, const void* B, const void* bias, void* C, int64_t M, int64_t N, int64_t K, int64_t sAm, int64_t sAk, int64_t sBk, int64_t sBn, int64_t sbm,
                             int64_t sbn, double alpha, double beta, int dtype, void* scratch, int64_t scratch_bytes, uint32_t* status, cudaStream_t st);
@@ -19,6 +25,11 @@ int64_t gemm_f32_split_scratch_bytes(int64_t batch, int64_t M, int64_t N, int64_
 bool gemm_f32_split_eligible(int64_t batch, int64_t M, int64_t N, int64_t K);
 int gemm_f32_split_dispatch(const void* A, const void* B, const void* bias, void* C, int64_t batch, int64_t M, int64_t N, int64_t K, int64_t sAb, int64_t sAm, int64_t sAk, int64_t sBb,
                             int64_t sBk, int64_t sBn, int64_t sbm, int64_t sbn, double alpha, double beta, void* scratch, int64_t scratch_bytes, uint32_t* status, cudaStream_t st);
+
+// 1: small 16-bit products take the mma.sync kernel (the default); 0: they go where they went
+// without it (tcgen05 or CUDA cores) -- how the two are compared and the larger kernels tested
+// on small shapes.
+static std::atomic<int> g_small_path{1};
 
 __global__ void fill_bias_only(void* C, const void* bias, int64_t batch, int64_t M, int64_t N, int64_t sbm, int64_t sbn, float beta, int dt) {
   const int64_t total = batch * M * N;
@@ -51,6 +62,8 @@ extern "C" int b200_gemm(const void* A, const void* B, const void* bias, void* C
     return check_launch();
   }
   if (!A || !B) return B200_EINVAL;
+  if (g_small_path.load(std::memory_order_relaxed) && gemm_mma_small_preferred(A, B, batch, M, N, K, sAb, sAm, sAk, sBb, sBk, sBn, dtype))
+    return gemm_mma_small_dispatch(A, B, bias, C, batch, M, N, K, sAb, sAm, sAk, sBb, sBk, sBn, sbm, sbn, alpha, beta, dtype, st);
   if (gemm_tc_eligible(batch, M, N, K, sAb, sAm, sAk, sBb, sBk, sBn, dtype, A, B, C))
     return gemm_tc_dispatch(A, B, bias, C, batch, M, N, K, sAb, sAm, sAk, sBb, sBk, sBn, sbm, sbn, alpha, beta, dtype, status, st);
   return gemm_simt_dispatch(A, B, bias, C, batch, M, N, K, sAb, sAm, sAk, sBb, sBk, sBn, sbm, sbn, alpha, beta, dtype, st);
@@ -93,4 +106,11 @@ extern "C" int b200_gemm_splitk(const void* A, const void* B, const void* bias, 
   if (b200_gemm_splitk_scratch_bytes(A, B, C, batch, M, N, K, sAb, sAm, sAk, sBb, sBk, sBn, dtype) == 0)
     return b200_gemm(A, B, bias, C, batch, M, N, K, sAb, sAm, sAk, sBb, sBk, sBn, sbm, sbn, alpha, beta, dtype, status, stream);
   return gemm_tc_splitk_dispatch(A, B, bias, C, M, N, K, sAm, sAk, sBk, sBn, sbm, sbn, alpha, beta, dtype, scratch, scratch_bytes, status, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int b200_gemm_small_path(int enable) { return g_small_path.exchange(enable ? 1 : 0); }
+
+extern "C" int b200_gemm_prefers_small(const void* A, const void* B, int64_t batch, int64_t M, int64_t N, int64_t K, int64_t sAb, int64_t sAm, int64_t sAk, int64_t sBb, int64_t sBk,
+                                       int64_t sBn, int dtype) {
+  return (g_small_path.load(std::memory_order_relaxed) && gemm_mma_small_preferred(A, B, batch, M, N, K, sAb, sAm, sAk, sBb, sBk, sBn, dtype)) ? 1 : 0;
 }

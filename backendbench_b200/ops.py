@@ -694,7 +694,8 @@ def _gemm(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor], batch:
     # the tensor cores to pay for the extra copy; otherwise the CUDA-core kernel takes them
     # (a long contraction with a small output is re-pitched too: the CUDA-core kernel would
     # walk all of K in one or two CTAs)
-    if a.dtype != torch.float32 and (M * N * K * batch >= (1 << 24) or K >= 1024) and K >= 16:
+    # (small products whose operands are on the 16-byte grid go to the mma.sync kernel as they are)
+    if a.dtype != torch.float32 and (M * N * K * batch >= (1 << 24) or K >= 1024) and K >= 16 and not lib().b200_gemm_prefers_small(a.data_ptr(), b.data_ptr(), batch, M, N, K, sa[0], sa[1], sa[2], sb[0], sb[1], sb[2], _dt(a.dtype)):
         if not _tma_ready(a, sa[0], sa[1], sa[2], batch):
             if sa[1] != 1 or sa[2] == 1:  # keep A K-major unless it is M-major
                 a, (pb, pr) = _repitch(a, batch, M, K, sa[0], sa[1], sa[2])

@@ -291,6 +291,18 @@ int b200_gemm_f32(const void* A, const void* B, const void* bias, void* C, int64
                   double alpha, double beta, void* scratch, int64_t scratch_bytes,
                   uint32_t* status, void* stream);
 
+/* Small 16-bit products (at most 148 tiles of 64 x 64, K <= 256, at most 2^26 multiply-adds,
+ * both operands with one unit stride and base / other strides on the 16-byte grid) are served
+ * by a four-warp mma.sync kernel with cp.async staging instead of the tcgen05 kernel, whose
+ * set-up alone takes about 5 us. b200_gemm_prefers_small tells a caller whether b200_gemm
+ * will go that way.
+ * b200_gemm_small_path(0) switches the path off process-wide (1 on again) and returns the
+ * previous setting -- for comparisons and for testing the larger kernels on small shapes. */
+int b200_gemm_prefers_small(const void* A, const void* B, int64_t batch, int64_t M, int64_t N,
+                            int64_t K, int64_t sAb, int64_t sAm, int64_t sAk, int64_t sBb, int64_t sBk,
+                            int64_t sBn, int dtype);
+int b200_gemm_small_path(int enable);
+
 /* A 16-bit product with a long contraction and a C of a few tiles (batch 1, at most a quarter
  * of the SMs' worth of 128 x 256 tiles, K >= 1536, K divisible by 8 x the number of ranges):
  * the contraction is cut into up to 32 ranges that run as separate CTAs of the tensor-core

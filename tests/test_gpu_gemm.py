@@ -13,6 +13,17 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
+@pytest.fixture(params=[1, 0], ids=["small-path-on", "small-path-off"])
+def small_path(request):
+    """Small 16-bit products normally take the mma.sync kernel; with the path switched off the
+    same shapes exercise the tcgen05 / CUDA-core kernels (ragged tiles, every layout)."""
+    prev = _abi.lib().b200_gemm_small_path(request.param)
+    try:
+        yield request.param
+    finally:
+        _abi.lib().b200_gemm_small_path(prev)
+
+
 def _uses_tc(a, b, batch, M, N, K, sa, sb):
     return bool(_abi.lib().b200_gemm_uses_tensor_cores(batch, M, N, K, sa[0], sa[1], sa[2], sb[0], sb[1], sb[2], _abi.BF16 if a.dtype == torch.bfloat16 else _abi.F16, a.data_ptr(), b.data_ptr(), a.data_ptr()))
 
@@ -32,7 +43,7 @@ SHAPES = [(128, 256, 64), (128, 256, 256), (256, 512, 128), (130, 264, 72), (33,
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("a_t,b_t", [(False, False), (False, True), (True, False), (True, True)])
-def test_mm_all_layouts(dtype, a_t, b_t):
+def test_mm_all_layouts(dtype, a_t, b_t, small_path):
     g = torch.Generator(device=DEV).manual_seed(5)
     for M, N, K in SHAPES:
         Mp, Kp, Np = (M + 7) // 8 * 8, (K + 7) // 8 * 8, (N + 7) // 8 * 8
@@ -46,7 +57,7 @@ def test_mm_all_layouts(dtype, a_t, b_t):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-def test_addmm_epilogue_variants(dtype):
+def test_addmm_epilogue_variants(dtype, small_path):
     g = torch.Generator(device=DEV).manual_seed(6)
     M, N, K = 300, 520, 192
     a, b = _rand((M, K), dtype, g, K**-0.5), _rand((K, N), dtype, g, 1.0)
@@ -61,7 +72,7 @@ def test_addmm_epilogue_variants(dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-def test_bmm_batches_and_strided_views(dtype):
+def test_bmm_batches_and_strided_views(dtype, small_path):
     g = torch.Generator(device=DEV).manual_seed(7)
     for B, M, K, N in [(3, 128, 64, 256), (5, 200, 72, 136), (32, 256, 128, 320), (2, 64, 1024, 64)]:
         a, b = _rand((B, M, K), dtype, g, K**-0.5), _rand((B, K, N), dtype, g, 1.0)
@@ -353,4 +364,43 @@ def test_fp32_products_with_a_narrow_result():
         got = ops.addmm_default(bias, a[0], b[0], beta=0.5, alpha=2)
         ok, ea, er = compare((2 * exact[0] + 0.5 * bias.double()).float(), got, 1e-4, 1e-4)
         assert ok, (M, K, N, ea, er)
+    ops.check_device_status()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_small_products_on_the_mma_kernel(dtype):
+    """Few 64 x 64 tiles and a short contraction: the four-warp mma.sync kernel when both
+    operands are on the 16-byte grid (all four layout pairs, ragged M / N / K, batches, bias and
+    scales); offset bases, odd pitches and operands with no unit stride go to the other kernels."""
+    g = torch.Generator(device=DEV).manual_seed(29)
+    dt = _abi.BF16 if dtype == torch.bfloat16 else _abi.F16
+
+    def prefers(a, b, B, M, N, K):
+        sa = (a.stride(0) if B > 1 else 0, a.stride(-2), a.stride(-1))
+        sb = (b.stride(0) if B > 1 else 0, b.stride(-2), b.stride(-1))
+        return _abi.lib().b200_gemm_prefers_small(a.data_ptr(), b.data_ptr(), B, M, N, K, sa[0], sa[1], sa[2], sb[0], sb[1], sb[2], dt)
+
+    for B, M, N, K in [(1, 41, 64, 256), (64, 2, 64, 64), (1, 367, 264, 40), (1, 227, 72, 256), (1, 36, 24, 32), (32, 15, 8, 256), (2, 4, 72, 64), (1, 1, 8, 200), (3, 136, 72, 104), (1, 64, 64, 8),
+                       (1, 5, 8, 248), (8, 6, 16, 40), (1, 17, 9 * 8, 136), (2, 49, 40, 72)]:
+        for a_t in (False, True):
+            for b_t in (False, True):
+                Mp = (M + 7) // 8 * 8
+                a = _rand((B, K, Mp), dtype, g, K**-0.5).transpose(1, 2)[:, :M] if a_t else _rand((B, M, K), dtype, g, K**-0.5)
+                b = _rand((B, N, K), dtype, g, 1.0).transpose(1, 2) if b_t else _rand((B, K, N), dtype, g, 1.0)
+                assert prefers(a, b, B, M, N, K) == 1, (B, M, N, K, a.stride(), b.stride())
+                got = ops.bmm_default(a, b)
+                assert got.shape == (B, M, N) and got.dtype == dtype and got.is_contiguous()
+                _check(got, a.double() @ b.double(), dtype)
+        a2, b2 = _rand((M, K), dtype, g, K**-0.5), _rand((K, N), dtype, g, 1.0)
+        for bias_shape in [(N,), (M, N), (M, 1), ()]:
+            bias = _rand(bias_shape, dtype, g, 1.0)
+            _check(ops.addmm_default(bias, a2, b2, beta=0.5, alpha=2), 2 * (a2.double() @ b2.double()) + 0.5 * bias.double(), dtype)
+        nan_bias = torch.full((N,), float("nan"), dtype=dtype, device=DEV)
+        _check(ops.addmm_default(nan_bias, a2, b2, beta=0), a2.double() @ b2.double(), dtype)
+        # off the grid: an offset base, an odd pitch, no unit stride -- other kernels, same answer
+        shifted = _rand((M, K + 8), dtype, g, K**-0.5)[:, 3 : K + 3]
+        every_other = _rand((M, 2 * K), dtype, g, K**-0.5)[:, ::2]
+        for a3 in (shifted, every_other):
+            assert prefers(a3, b2, 1, M, N, K) == 0
+            _check(ops.mm_default(a3, b2), a3.double() @ b2.double(), dtype)
     ops.check_device_status()
